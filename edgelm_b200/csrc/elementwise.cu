@@ -1,0 +1,152 @@
+// Embedding gather, RMSNorm (with optional row gather) and RoPE + cache append.
+//
+// The residual stream is float32 in both precisions; `T` below is the storage type of
+// weights, of normalised activations and of the cache (float or bfloat16).
+#include "common.cuh"
+
+namespace edgelm {
+
+// ---------------------------------------------------------------- embedding: x[t,:] = E[id_t,:]
+template <typename TW>
+__global__ void embed_gather_kernel(const int32_t* __restrict__ ids, const TW* __restrict__ table,
+                                    float* __restrict__ x, int dim, int vocab, int* __restrict__ err) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  if (id < 0 || id >= vocab) {  // the host checks ids that it has seen; ids sampled on the device are checked here
+    if (threadIdx.x == 0) atomicOr(err, ERR_TOKEN_RANGE);
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) x[(size_t)t * dim + i] = 0.f;
+    return;
+  }
+  const TW* row = table + (size_t)id * dim;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) x[(size_t)t * dim + i] = to_f32(row[i]);
+}
+
+// ---------------------------------------------------------------- RMSNorm
+// y[r,:] = x[src(r),:] * (1 / sqrt(mean(x^2) + eps)) * w, statistics in float32.
+// `rows_idx` (may be null) picks the source row of each output row: the gather of the
+// wanted positions before the final norm.
+template <typename TOut>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, TOut* __restrict__ y,
+                               const int32_t* __restrict__ rows_idx, int dim, float eps) {
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  const float* xr = x + (size_t)(rows_idx ? rows_idx[r] : r) * dim;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    const float v = xr[i];
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) y[(size_t)r * dim + i] = from_f32<TOut>(xr[i] * inv * w[i]);
+}
+
+// ---------------------------------------------------------------- RoPE + cache append
+// qkv: [tokens, (nh + 2 nkv) * hd], the fused projection's output.  For every token: rotate
+// the nh query heads in place, rotate the nkv key heads and write them, with the raw value
+// heads, into the cache page that holds the token's position.  Rotation in float32 with the
+// half-split pairing (i, i + hd/2); cos/sin come from a table [max_pos, hd/2] that the host
+// computed in float64.
+template <typename T>
+__global__ void rope_kv_append_kernel(T* __restrict__ qkv, const int32_t* __restrict__ tok_pos,
+                                      const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ seq_slot,
+                                      const int32_t* __restrict__ page_table, int table_stride, int n_pages,
+                                      const float* __restrict__ cos_t, const float* __restrict__ sin_t, int max_pos,
+                                      T* __restrict__ kcache, T* __restrict__ vcache, int nh, int nkv, int hd,
+                                      int* __restrict__ err) {
+  const int t = blockIdx.x;
+  const int pos = tok_pos[t];
+  const int half = hd >> 1;
+  if (pos < 0 || pos >= max_pos) {
+    if (threadIdx.x == 0) atomicOr(err, ERR_POSITION_RANGE);
+    return;
+  }
+  const int slot = seq_slot[tok_seq[t]];
+  const int page = page_table[(size_t)slot * table_stride + pos / PAGE];
+  if (page < 0 || page >= n_pages) {
+    if (threadIdx.x == 0) atomicOr(err, ERR_PAGE_RANGE);
+    return;
+  }
+  const int in_page = pos % PAGE;
+  const float* c = cos_t + (size_t)pos * half;
+  const float* s = sin_t + (size_t)pos * half;
+  T* row = qkv + (size_t)t * (nh + 2 * nkv) * hd;
+  // queries, in place
+  for (int i = threadIdx.x; i < nh * half; i += blockDim.x) {
+    const int h = i / half, j = i - h * half;
+    T* p = row + h * hd;
+    const float a = to_f32(p[j]), b = to_f32(p[j + half]);
+    p[j] = from_f32<T>(a * c[j] - b * s[j]);
+    p[j + half] = from_f32<T>(b * c[j] + a * s[j]);
+  }
+  // keys (rotated) and values (raw) into the page
+  const T* krow = row + (size_t)nh * hd;
+  const T* vrow = krow + (size_t)nkv * hd;
+  for (int i = threadIdx.x; i < nkv * half; i += blockDim.x) {
+    const int h = i / half, j = i - h * half;
+    const float a = to_f32(krow[h * hd + j]), b = to_f32(krow[h * hd + j + half]);
+    T* dst = kcache + (((size_t)page * nkv + h) * PAGE + in_page) * hd;
+    dst[j] = from_f32<T>(a * c[j] - b * s[j]);
+    dst[j + half] = from_f32<T>(b * c[j] + a * s[j]);
+  }
+  for (int i = threadIdx.x; i < nkv * hd; i += blockDim.x) {
+    const int h = i / hd, j = i - h * hd;
+    vcache[(((size_t)page * nkv + h) * PAGE + in_page) * hd + j] = vrow[i];
+  }
+}
+
+}  // namespace edgelm
+
+using namespace edgelm;
+
+extern "C" int edgelm_embed_gather(const int32_t* ids, const void* table, int table_dtype, float* x, int n_tokens,
+                                   int dim, int vocab, int* err, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  EL_REFUSE(n_tokens > 0 && dim > 0 && vocab > 0, "embed_gather: bad sizes tokens=%d dim=%d vocab=%d", n_tokens, dim, vocab);
+  const int threads = dim >= 256 ? 256 : 128;
+  if (table_dtype == DT_F32)
+    embed_gather_kernel<float><<<n_tokens, threads, 0, stream>>>(ids, (const float*)table, x, dim, vocab, err);
+  else if (table_dtype == DT_BF16)
+    embed_gather_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, x, dim, vocab, err);
+  else
+    EL_REFUSE(false, "embed_gather: unknown dtype code %d", table_dtype);
+  EL_LAUNCH_CHECK("embed_gather");
+  return 0;
+}
+
+extern "C" int edgelm_rmsnorm(const float* x, const float* w, void* y, int out_dtype, const int32_t* rows_idx,
+                              int rows, int dim, float eps, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  EL_REFUSE(rows > 0 && dim > 0, "rmsnorm: bad sizes rows=%d dim=%d", rows, dim);
+  const int threads = dim >= 1024 ? 256 : 128;
+  if (out_dtype == DT_F32)
+    rmsnorm_kernel<float><<<rows, threads, 0, stream>>>(x, w, (float*)y, rows_idx, dim, eps);
+  else if (out_dtype == DT_BF16)
+    rmsnorm_kernel<__nv_bfloat16><<<rows, threads, 0, stream>>>(x, w, (__nv_bfloat16*)y, rows_idx, dim, eps);
+  else
+    EL_REFUSE(false, "rmsnorm: unknown dtype code %d", out_dtype);
+  EL_LAUNCH_CHECK("rmsnorm");
+  return 0;
+}
+
+extern "C" int edgelm_rope_kv_append(void* qkv, int dtype, const int32_t* tok_pos, const int32_t* tok_seq,
+                                     const int32_t* seq_slot, const int32_t* page_table, int table_stride, int n_pages,
+                                     const float* cos_t, const float* sin_t, int max_pos, void* kcache, void* vcache,
+                                     int n_tokens, int nh, int nkv, int hd, int* err, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  EL_REFUSE(hd > 0 && hd % 2 == 0, "rope_kv_append: head size %d is not even", hd);
+  EL_REFUSE(nh > 0 && nkv > 0 && n_tokens > 0, "rope_kv_append: bad sizes");
+  const int threads = 128;
+  if (dtype == DT_F32)
+    rope_kv_append_kernel<float><<<n_tokens, threads, 0, stream>>>((float*)qkv, tok_pos, tok_seq, seq_slot, page_table,
+                                                                    table_stride, n_pages, cos_t, sin_t, max_pos,
+                                                                    (float*)kcache, (float*)vcache, nh, nkv, hd, err);
+  else if (dtype == DT_BF16)
+    rope_kv_append_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+        (__nv_bfloat16*)qkv, tok_pos, tok_seq, seq_slot, page_table, table_stride, n_pages, cos_t, sin_t, max_pos,
+        (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, nh, nkv, hd, err);
+  else
+    EL_REFUSE(false, "rope_kv_append: unknown dtype code %d", dtype);
+  EL_LAUNCH_CHECK("rope_kv_append");
+  return 0;
+}

@@ -1,0 +1,188 @@
+"""Python face of the kernel library: torch tensors in, kernel launches on the current stream.
+
+Each function checks dtypes, shapes and contiguity, passes raw device pointers through
+ctypes, and raises `KernelError` with the library's message when a size is refused or a
+launch fails.  Nothing here computes on the host or falls back to another implementation:
+without the library, or without a device of compute capability 10.x, importing the ops
+raises.
+"""
+import ctypes
+import threading
+
+import torch
+
+from . import build as _build
+
+F32, BF16 = 0, 1
+EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2
+PAGE = 64  # tokens per cache page, as in common.cuh
+
+ERR_BITS = {1: "a token id outside the vocabulary", 2: "a position beyond the position table",
+            4: "a page id outside the cache", 8: "a device-side wait ran out"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_lib = None
+_lock = threading.Lock()
+
+
+def lib():
+    """The loaded kernel library (built at the first call if needed)."""
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                path = _build.library_path()
+                try:
+                    loaded = ctypes.CDLL(path)
+                except OSError as e:  # pragma: no cover
+                    raise KernelError(f"edgelm_b200: cannot load the kernel library {path}: {e}") from e
+                loaded.edgelm_last_error.restype = ctypes.c_char_p
+                _lib = loaded
+    return _lib
+
+
+def require_device():
+    """Fail loudly unless a Blackwell-class CUDA device is current; there is no other path."""
+    if not torch.cuda.is_available():
+        raise KernelError("edgelm_b200 runs on a CUDA device (sm_100a) only; torch sees none")
+    arch = lib().edgelm_device_arch()
+    if arch // 10 != 10:
+        raise KernelError(f"edgelm_b200's kernels are built for sm_100a; the current device reports sm_{arch}")
+
+
+def _check(rc):
+    if rc != 0:
+        raise KernelError(lib().edgelm_last_error().decode())
+
+
+def _dt(t):
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"unsupported dtype {t.dtype}")
+
+
+def _p(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need(cond, msg):
+    if not cond:
+        raise KernelError(msg)
+
+
+def _i32(t, name):
+    _need(t.dtype == torch.int32 and t.is_cuda and t.is_contiguous(), f"{name} must be a contiguous int32 CUDA tensor")
+
+
+def embed_gather(ids, table, x, err):
+    """x[t, :] = table[ids[t], :] as float32; ids outside the table set bit 1 of `err`."""
+    _i32(ids, "ids")
+    _need(table.dim() == 2 and table.is_contiguous() and x.dtype == torch.float32 and x.is_contiguous(), "embed_gather: layout")
+    _need(x.shape == (ids.numel(), table.shape[1]), "embed_gather: x has the wrong shape")
+    _check(lib().edgelm_embed_gather(_p(ids), _p(table), _dt(table), _p(x), ids.numel(), table.shape[1], table.shape[0],
+                                     _p(err), _stream()))
+
+
+def rmsnorm(x, w, eps, out, rows_idx=None):
+    """out[r] = x[rows_idx[r] or r] * rsqrt(mean(x^2) + eps) * w; x and w float32, out float32 or bfloat16."""
+    _need(x.dtype == torch.float32 and w.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous(), "rmsnorm: layout")
+    rows = out.shape[0]
+    dim = x.shape[1]
+    _need(out.shape[1] == dim and w.numel() == dim, "rmsnorm: widths differ")
+    if rows_idx is not None:
+        _i32(rows_idx, "rows_idx")
+        _need(rows_idx.numel() == rows, "rmsnorm: one source row per output row")
+    else:
+        _need(x.shape[0] == rows, "rmsnorm: row counts differ")
+    _check(lib().edgelm_rmsnorm(_p(x), _p(w), _p(out), _dt(out), _p(rows_idx), rows, dim, ctypes.c_float(eps), _stream()))
+
+
+def gemm_simt(a, w, out, epilogue=EPI_STORE, w2=None, residual=None, force_kernel=0):
+    """out = a @ w.T (+ epilogue) with float32 accumulation on the CUDA cores."""
+    _need(a.dim() == 2 and w.dim() == 2 and out.dim() == 2, "gemm: 2-D operands")
+    M, K = a.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and out.shape == (M, N), f"gemm: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    _need(a.stride(1) == 1 and out.stride(1) == 1 and w.is_contiguous(), "gemm: rows must be contiguous")
+    _need(a.dtype == w.dtype and (w2 is None or (w2.dtype == w.dtype and w2.shape == w.shape and w2.is_contiguous())), "gemm: weight dtypes")
+    if residual is not None:
+        _need(residual.dtype == torch.float32 and residual.shape == out.shape and residual.stride() == out.stride(), "gemm: residual layout")
+    _check(lib().edgelm_gemm_simt(_p(a), a.stride(0), _p(w), _p(w2), _p(out), out.stride(0), _p(residual), M, N, K,
+                                  _dt(a), _dt(out), epilogue, force_kernel, _stream()))
+
+
+def rope_kv_append(qkv, tok_pos, tok_seq, seq_slot, page_table, cos, sin, kcache, vcache, nh, nkv, hd, err):
+    """Rotate q and k of the fused projection output in float32; write k and v into their pages."""
+    T = qkv.shape[0]
+    _need(qkv.is_contiguous() and qkv.shape[1] == (nh + 2 * nkv) * hd, "rope_kv_append: qkv layout")
+    _need(kcache.dtype == qkv.dtype and vcache.dtype == qkv.dtype and kcache.is_contiguous() and vcache.is_contiguous(), "rope_kv_append: cache dtype")
+    _need(kcache.shape[1:] == (nkv, PAGE, hd) and vcache.shape == kcache.shape, "rope_kv_append: cache shape")
+    _need(cos.dtype == torch.float32 and cos.shape[1] == hd // 2 and cos.is_contiguous() and sin.shape == cos.shape and sin.is_contiguous(), "rope_kv_append: table layout")
+    for t, n in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (seq_slot, "seq_slot"), (page_table, "page_table")):
+        _i32(t, n)
+    _need(tok_pos.numel() >= T and tok_seq.numel() >= T, "rope_kv_append: one position per token")
+    _check(lib().edgelm_rope_kv_append(_p(qkv), _dt(qkv), _p(tok_pos), _p(tok_seq), _p(seq_slot), _p(page_table),
+                                       page_table.stride(0), kcache.shape[0], _p(cos), _p(sin), cos.shape[0], _p(kcache),
+                                       _p(vcache), T, nh, nkv, hd, _p(err), _stream()))
+
+
+def attn_prefill(qkv, out, kcache, vcache, page_table, seq_slot, tile_seq, tile_tok0, tile_ntok, tile_pos0, n_tiles,
+                 max_tile_tokens, nh, nkv, hd, scale):
+    """Causal attention of new tokens (any number per sequence) over the paged cache."""
+    _need(qkv.dtype == out.dtype == kcache.dtype and qkv.stride(1) == 1 and out.stride(1) == 1, "attn_prefill: layout")
+    for t, n in ((page_table, "page_table"), (seq_slot, "seq_slot"), (tile_seq, "tile_seq"), (tile_tok0, "tile_tok0"),
+                 (tile_ntok, "tile_ntok"), (tile_pos0, "tile_pos0")):
+        _i32(t, n)
+    _check(lib().edgelm_attn_prefill(_p(qkv), qkv.stride(0), _p(out), out.stride(0), _p(kcache), _p(vcache), _dt(qkv),
+                                     _p(page_table), page_table.stride(0), _p(seq_slot), _p(tile_seq), _p(tile_tok0),
+                                     _p(tile_ntok), _p(tile_pos0), n_tiles, max_tile_tokens, nh, nkv, hd,
+                                     ctypes.c_float(scale), _stream()))
+
+
+def attn_decode(qkv, out, kcache, vcache, page_table, seq_slot, seq_pos, n_seqs, nh, nkv, hd, scale, n_splits=1,
+                part_o=None, part_ml=None):
+    """Attention of one new token per sequence over the paged cache, pages dealt to `n_splits` blocks."""
+    _need(qkv.dtype == out.dtype == kcache.dtype and qkv.stride(1) == 1 and out.stride(1) == 1, "attn_decode: layout")
+    for t, n in ((page_table, "page_table"), (seq_slot, "seq_slot"), (seq_pos, "seq_pos")):
+        _i32(t, n)
+    if n_splits > 1:
+        _need(part_o is not None and part_o.dtype == torch.float32 and part_o.numel() >= n_seqs * nh * n_splits * hd, "attn_decode: part_o too small")
+        _need(part_ml is not None and part_ml.dtype == torch.float32 and part_ml.numel() >= n_seqs * nh * n_splits * 2, "attn_decode: part_ml too small")
+    _check(lib().edgelm_attn_decode(_p(qkv), qkv.stride(0), _p(out), out.stride(0), _p(kcache), _p(vcache), _dt(qkv),
+                                    _p(page_table), page_table.stride(0), _p(seq_slot), _p(seq_pos), n_seqs, nh, nkv, hd,
+                                    ctypes.c_float(scale), n_splits, _p(part_o), _p(part_ml), _stream()))
+
+
+def argmax_rows(logits, out):
+    """out[r] = index of the first maximum of logits[r]."""
+    _need(logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1, "argmax_rows: float32 rows")
+    _i32(out, "out")
+    _check(lib().edgelm_argmax_rows(_p(logits), logits.stride(0), logits.shape[0], logits.shape[1], _p(out), _stream()))
+
+
+def sample_topk(logits, temperature, top_k, rng_state, out):
+    """Temperature + top-k draw per row; rng_state (int64, one xorshift64 state per row) advances by one draw."""
+    _need(logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1, "sample_topk: float32 rows")
+    _need(rng_state.dtype == torch.int64 and rng_state.is_contiguous() and rng_state.numel() >= logits.shape[0], "sample_topk: rng_state")
+    _i32(out, "out")
+    _check(lib().edgelm_sample_topk(_p(logits), logits.stride(0), logits.shape[0], logits.shape[1],
+                                    ctypes.c_float(temperature), int(top_k), _p(rng_state), _p(out), _stream()))
+
+
+def read_error_word(err):
+    """Host-side reading of the device error word; raises when a kernel reported bad input."""
+    v = int(err.item())
+    if v:
+        what = [m for b, m in ERR_BITS.items() if v & b]
+        err.zero_()
+        raise KernelError("a kernel reported: " + "; ".join(what))

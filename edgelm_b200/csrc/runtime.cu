@@ -1,0 +1,30 @@
+// Error reporting and small queries of the kernel library.
+#include <cstdarg>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace edgelm {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+}  // namespace edgelm
+
+// Message of the last refused or failed call of this thread.
+extern "C" const char* edgelm_last_error() { return edgelm::g_error; }
+
+// Compute capability of the current device as major * 10 + minor, or a negative code.
+extern "C" int edgelm_device_arch() {
+  int dev = 0, major = 0, minor = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return -1;
+  if (cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev) != cudaSuccess) return -1;
+  return major * 10 + minor;
+}

@@ -1,0 +1,355 @@
+"""Each CUDA kernel alone against a plain float64/float32 restatement of its formula, at sizes
+that the tiny models do not use (odd widths, head sizes 16..256, ragged tails)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as plain
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def ops():
+    from edgelm_b200.csrc import ops as o
+    o.require_device()
+    return o
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def tol(dtype):
+    return 2e-5 if dtype == torch.float32 else 1.6e-2
+
+
+def rel_err(a, b):
+    a = a.double().cpu()
+    b = b.double().cpu()
+    return float((a - b).abs().max() / max(1.0, float(b.abs().max())))
+
+
+def rnd(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).to(dev())
+
+
+# ----------------------------------------------------------------------------- embedding
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("vocab,dim", [(397, 96), (1000, 576), (50, 20)])
+def test_embed_gather(dtype, vocab, dim):
+    o = ops()
+    table = rnd((vocab, dim), dtype, 1)
+    ids = torch.tensor([0, vocab - 1, 3, 3, vocab // 2], dtype=torch.int32, device=dev())
+    x = torch.empty(ids.numel(), dim, dtype=torch.float32, device=dev())
+    err = torch.zeros(1, dtype=torch.int32, device=dev())
+    o.embed_gather(ids, table, x, err)
+    assert torch.equal(x, table[ids.long()].float())
+    assert int(err.item()) == 0
+    bad = torch.tensor([1, vocab, -1], dtype=torch.int32, device=dev())
+    o.embed_gather(bad, table, x[:3], err)
+    assert int(err.item()) & 1
+    with pytest.raises(o.KernelError):
+        o.read_error_word(err)
+    assert int(err.item()) == 0
+
+
+# ----------------------------------------------------------------------------- RMSNorm
+@pytest.mark.parametrize("out_dtype", DTYPES)
+@pytest.mark.parametrize("rows,dim,eps", [(5, 96, 1e-6), (33, 576, 1e-5), (1, 2048, 1e-5), (7, 250, 1e-3)])
+def test_rmsnorm(out_dtype, rows, dim, eps):
+    o = ops()
+    x = rnd((rows, dim), torch.float32, 2, 3.0)
+    w = 1 + rnd((dim,), torch.float32, 3, 0.1)
+    out = torch.empty(rows, dim, dtype=out_dtype, device=dev())
+    o.rmsnorm(x, w, eps, out)
+    want = torch.from_numpy(plain.rmsnorm(x.cpu().numpy(), w.cpu().numpy(), eps))
+    assert rel_err(out, want) < (2e-6 if out_dtype == torch.float32 else 8e-3)
+    idx = torch.tensor([rows - 1, 0, rows // 2], dtype=torch.int32, device=dev())
+    out2 = torch.empty(3, dim, dtype=out_dtype, device=dev())
+    o.rmsnorm(x, w, eps, out2, rows_idx=idx)
+    assert torch.equal(out2, out[idx.long()])
+
+
+# ----------------------------------------------------------------------------- GEMM (CUDA cores)
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 48, 64), (3, 37, 96), (17, 130, 160), (5, 397, 200), (70, 200, 96),
+                                     (129, 65, 33), (16, 256, 576), (9, 31, 7)])
+@pytest.mark.parametrize("force", [1, 2])
+def test_gemm_simt_store_and_residual(dtype, M, N, K, force):
+    o = ops()
+    a = rnd((M, K), dtype, 4)
+    w = rnd((N, K), dtype, 5, 0.2)
+    want = a.double().cpu() @ w.double().cpu().T
+    out = torch.empty(M, N, dtype=dtype, device=dev())
+    o.gemm_simt(a, w, out, force_kernel=force)
+    assert rel_err(out, want) < tol(dtype)
+    if dtype == torch.bfloat16:  # logits: bfloat16 operands, float32 result
+        out32 = torch.empty(M, N, dtype=torch.float32, device=dev())
+        o.gemm_simt(a, w, out32, force_kernel=force)
+        assert rel_err(out32, want) < 2e-5
+    res = rnd((M, N), torch.float32, 6)
+    res0 = res.clone()
+    o.gemm_simt(a, w, res, epilogue=o.EPI_RESIDUAL, residual=res, force_kernel=force)  # in place on the residual stream
+    assert rel_err(res, res0.double().cpu() + want) < 2e-5
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(2, 200, 96), (40, 130, 64), (1, 1536, 576), (67, 77, 50)])
+def test_gemm_simt_swiglu(dtype, M, N, K):
+    o = ops()
+    a = rnd((M, K), dtype, 7)
+    wg = rnd((N, K), dtype, 8, 0.3)
+    wu = rnd((N, K), dtype, 9, 0.3)
+    g = a.double().cpu() @ wg.double().cpu().T
+    u = a.double().cpu() @ wu.double().cpu().T
+    want = g / (1 + torch.exp(-g)) * u
+    for force in (1, 2):
+        out = torch.empty(M, N, dtype=dtype, device=dev())
+        o.gemm_simt(a, wg, out, epilogue=o.EPI_SWIGLU, w2=wu, force_kernel=force)
+        assert rel_err(out, want) < tol(dtype)
+
+
+def test_gemm_row_independent_of_batch():
+    """A row's result is the same bits whether it is computed alone or among others."""
+    o = ops()
+    a = rnd((40, 96), torch.float32, 10)
+    w = rnd((50, 96), torch.float32, 11)
+    full = torch.empty(40, 50, device=dev())
+    o.gemm_simt(a, w, full, force_kernel=2)
+    part = torch.empty(3, 50, device=dev())
+    o.gemm_simt(a[5:8], w, part, force_kernel=2)
+    assert torch.equal(part, full[5:8])
+    o.gemm_simt(a[5:8], w, part, force_kernel=1)
+    full1 = torch.empty(40, 50, device=dev())
+    o.gemm_simt(a, w, full1, force_kernel=1)
+    assert torch.equal(part, full1[5:8])
+
+
+# ----------------------------------------------------------------------------- paged cache helpers
+class PagedCase:
+    """Sequences with keys/values in a paged cache whose pages are dealt in a scrambled order."""
+
+    def __init__(self, o, dtype, lengths, nkv, hd, seed, extra_pages=3):
+        self.o, self.dtype, self.lengths, self.nkv, self.hd = o, dtype, lengths, nkv, hd
+        P = o.PAGE
+        need = [(n + P - 1) // P for n in lengths]
+        n_pages = sum(need) + extra_pages
+        g = torch.Generator().manual_seed(seed)
+        perm = torch.randperm(n_pages, generator=g).tolist()
+        self.max_pages = max(need) + 1
+        self.n_slots = len(lengths) + 2
+        slots = torch.randperm(self.n_slots, generator=g).tolist()[:len(lengths)]
+        table = torch.full((self.n_slots, self.max_pages), -1, dtype=torch.int32)
+        self.k = [torch.randn(n, nkv, hd, generator=g) for n in lengths]
+        self.v = [torch.randn(n, nkv, hd, generator=g) for n in lengths]
+        # unused rows hold huge values: reading them would show
+        kc = torch.full((n_pages, nkv, P, hd), 1e4)
+        vc = torch.full((n_pages, nkv, P, hd), float("nan"))
+        it = iter(perm)
+        for s, n in enumerate(lengths):
+            for pg in range(need[s]):
+                page = next(it)
+                table[slots[s], pg] = page
+                lo, hi = pg * P, min(n, (pg + 1) * P)
+                kc[page, :, :hi - lo] = self.k[s][lo:hi].transpose(0, 1)
+                vc[page, :, :hi - lo] = self.v[s][lo:hi].transpose(0, 1)
+        self.k = [t.to(dtype).float() for t in self.k]
+        self.v = [t.to(dtype).float() for t in self.v]
+        self.kcache = kc.to(dtype).to(dev())
+        self.vcache = vc.to(dtype).to(dev())
+        self.table = table.to(dev())
+        self.seq_slot = torch.tensor(slots, dtype=torch.int32, device=dev())
+
+
+def attention_rows(q, k, v, pos0, nh, nkv, hd):
+    """Plain causal attention of new rows at positions pos0.. over keys 0..pos0+t (float64)."""
+    T = q.shape[0]
+    q = q.double().reshape(T, nh, hd)
+    k = k.double()
+    v = v.double()
+    g = nh // nkv
+    out = torch.zeros(T, nh, hd, dtype=torch.float64)
+    for t in range(T):
+        n = pos0 + t + 1
+        for h in range(nh):
+            s = (k[:n, h // g] @ q[t, h]) / math.sqrt(hd)
+            p = torch.softmax(s, dim=0)
+            out[t, h] = p @ v[:n, h // g]
+    return out.reshape(T, nh * hd)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (3, 1, 32), (9, 3, 64), (2, 2, 48), (8, 1, 128), (40, 1, 16), (2, 1, 256), (5, 5, 80)])
+def test_attn_prefill(dtype, nh, nkv, hd):
+    o = ops()
+    # (cached length before the step, new tokens): whole prompts, continued prompts, single tokens
+    seqs = [(0, 5), (0, 70), (64, 1), (100, 29), (63, 2), (0, 1)]
+    lengths = [a + b for a, b in seqs]
+    case = PagedCase(o, dtype, lengths, nkv, hd, seed=nh * 100 + hd)
+    g = nh // nkv
+    T = sum(b for _, b in seqs)
+    width = (nh + 2 * nkv) * hd
+    qkv = rnd((T, width), dtype, 20)
+    tq = max(1, 32 // g)
+    tile_seq, tile_tok0, tile_ntok, tile_pos0 = [], [], [], []
+    t0 = 0
+    for s, (p0, n) in enumerate(seqs):
+        for a in range(0, n, tq):
+            tile_seq.append(s)
+            tile_tok0.append(t0 + a)
+            tile_ntok.append(min(tq, n - a))
+            tile_pos0.append(p0 + a)
+        t0 += n
+    mk = lambda x: torch.tensor(x, dtype=torch.int32, device=dev())
+    out = torch.zeros(T, nh * hd, dtype=dtype, device=dev())
+    o.attn_prefill(qkv, out, case.kcache, case.vcache, case.table, case.seq_slot, mk(tile_seq), mk(tile_tok0),
+                   mk(tile_ntok), mk(tile_pos0), len(tile_seq), tq, nh, nkv, hd, 1.0 / math.sqrt(hd))
+    t0 = 0
+    for s, (p0, n) in enumerate(seqs):
+        want = attention_rows(qkv[t0:t0 + n, :nh * hd].float().cpu(), case.k[s], case.v[s], p0, nh, nkv, hd)
+        assert rel_err(out[t0:t0 + n], want) < (1e-5 if dtype == torch.float32 else 1e-2), (s, p0, n)
+        t0 += n
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (3, 1, 32), (9, 3, 64), (32, 32, 64), (6, 1, 96), (2, 1, 256)])
+@pytest.mark.parametrize("n_splits", [1, 3, 16])
+def test_attn_decode(dtype, nh, nkv, hd, n_splits):
+    o = ops()
+    lengths = [1, 64, 65, 700, 128, 37]
+    case = PagedCase(o, dtype, lengths, nkv, hd, seed=nh + hd + n_splits)
+    B = len(lengths)
+    qkv = rnd((B, (nh + 2 * nkv) * hd), dtype, 21)
+    seq_pos = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=dev())
+    out = torch.zeros(B, nh * hd, dtype=dtype, device=dev())
+    part_o = torch.full((B * nh * n_splits * hd,), float("nan"), device=dev())
+    part_ml = torch.full((B * nh * n_splits * 2,), float("nan"), device=dev())
+    o.attn_decode(qkv, out, case.kcache, case.vcache, case.table, case.seq_slot, seq_pos, B, nh, nkv, hd,
+                  1.0 / math.sqrt(hd), n_splits, part_o, part_ml)
+    for s, n in enumerate(lengths):
+        want = attention_rows(qkv[s:s + 1, :nh * hd].float().cpu(), case.k[s], case.v[s], n - 1, nh, nkv, hd)
+        assert rel_err(out[s:s + 1], want) < (1e-5 if dtype == torch.float32 else 1e-2), (s, n)
+
+
+def test_attention_far_key_stands_out():
+    """One early key among hundreds is made to dominate: the output must be its value."""
+    o = ops()
+    nh, nkv, hd, n = 2, 1, 32, 900
+    case = PagedCase(o, torch.float32, [n], nkv, hd, seed=5)
+    q = torch.zeros(1, (nh + 2 * nkv) * hd)
+    q[0, :hd] = 8.0 * case.k[0][3, 0]          # head 0 looks at key 3
+    q[0, hd:2 * hd] = 8.0 * case.k[0][n - 1, 0]  # head 1 looks at the newest key
+    qkv = q.to(dev())
+    seq_pos = torch.tensor([n - 1], dtype=torch.int32, device=dev())
+    for splits in (1, 4):
+        out = torch.zeros(1, nh * hd, device=dev())
+        po = torch.zeros(nh * splits * hd, device=dev())
+        pm = torch.zeros(nh * splits * 2, device=dev())
+        o.attn_decode(qkv, out, case.kcache, case.vcache, case.table, case.seq_slot, seq_pos, 1, nh, nkv, hd,
+                      1.0 / math.sqrt(hd), splits, po, pm)
+        want = attention_rows(q[:, :nh * hd], case.k[0], case.v[0], n - 1, nh, nkv, hd)
+        assert rel_err(out, want) < 1e-5
+        assert rel_err(out[0, :hd], case.v[0][3, 0]) < 1e-2
+        assert rel_err(out[0, hd:], case.v[0][n - 1, 0]) < 1e-2
+
+
+def test_attention_refuses_sizes():
+    o = ops()
+    t = torch.zeros(1, 4 * 24, device=dev())
+    i = torch.zeros(1, 1, dtype=torch.int32, device=dev())
+    c = torch.zeros(1, 1, 64, 24, device=dev())
+    with pytest.raises(o.KernelError, match="head size"):
+        o.attn_decode(t, t[:, :48], c, c, i, i[0], i[0], 1, 2, 1, 24, 1.0)
+    with pytest.raises(o.KernelError, match="multiple"):
+        o.attn_decode(t, t[:, :48], c, c, i, i[0], i[0], 1, 3, 2, 16, 1.0)
+
+
+# ----------------------------------------------------------------------------- RoPE + cache append
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,theta", [(4, 2, 16, 1e4), (3, 1, 32, 1e5), (9, 3, 64, 1e5), (2, 2, 48, 500.0)])
+def test_rope_kv_append(dtype, nh, nkv, hd, theta):
+    o = ops()
+    max_pos = 300
+    cos, sin = plain.rope_angles(np.arange(max_pos), hd, theta)
+    cos_t, sin_t = torch.from_numpy(cos).to(dev()), torch.from_numpy(sin).to(dev())
+    seqs = [(0, 5), (62, 4), (130, 1)]  # (first position, new tokens); the second crosses a page edge
+    T = sum(n for _, n in seqs)
+    n_pages, n_slots, max_pages = 9, 4, 5
+    table = torch.full((n_slots, max_pages), -1, dtype=torch.int32)
+    slots = [2, 0, 3]
+    table[2, 0] = 7
+    table[0, 0], table[0, 1] = 1, 4
+    table[3, 2] = 0
+    tok_pos, tok_seq = [], []
+    for s, (p0, n) in enumerate(seqs):
+        tok_pos += list(range(p0, p0 + n))
+        tok_seq += [s] * n
+    mk = lambda x: torch.tensor(x, dtype=torch.int32, device=dev())
+    qkv = rnd((T, (nh + 2 * nkv) * hd), dtype, 30)
+    orig = qkv.clone().float().cpu().numpy()
+    kc = torch.zeros(n_pages, nkv, o.PAGE, hd, dtype=dtype, device=dev())
+    vc = torch.zeros_like(kc)
+    err = torch.zeros(1, dtype=torch.int32, device=dev())
+    o.rope_kv_append(qkv, mk(tok_pos), mk(tok_seq), mk(slots), table.to(dev()), cos_t, sin_t, kc, vc, nh, nkv, hd, err)
+    assert int(err.item()) == 0
+    q_want = plain.rope(orig[:, :nh * hd], tok_pos, nh, hd, theta)
+    k_want = plain.rope(orig[:, nh * hd:(nh + nkv) * hd], tok_pos, nkv, hd, theta)
+    v_want = orig[:, (nh + nkv) * hd:]
+    t = 2e-6 if dtype == torch.float32 else 8e-3
+    assert rel_err(qkv[:, :nh * hd], torch.from_numpy(q_want)) < t
+    written = 0
+    for i, (p, s) in enumerate(zip(tok_pos, tok_seq)):
+        page = int(table[slots[s], p // o.PAGE])
+        krow = kc[page, :, p % o.PAGE].reshape(-1)
+        vrow = vc[page, :, p % o.PAGE].reshape(-1)
+        assert rel_err(krow, torch.from_numpy(k_want[i])) < t
+        assert torch.equal(vrow.float().cpu(), torch.from_numpy(v_want[i]))
+        written += 1
+    assert int((kc.float().abs().sum(dim=(1, 3)) > 0).sum()) == written  # nothing else was touched
+    bad = mk([max_pos])
+    o.rope_kv_append(qkv[:1], bad, mk([0]), mk(slots), table.to(dev()), cos_t, sin_t, kc, vc, nh, nkv, hd, err)
+    assert int(err.item()) & 2
+    err.zero_()
+
+
+# ----------------------------------------------------------------------------- sampling
+@pytest.mark.parametrize("vocab", [256, 397, 49152, 1000])
+def test_argmax_first_maximum(vocab):
+    o = ops()
+    x = rnd((6, vocab), torch.float32, 40)
+    x[1, 17] = x[1, vocab - 5] = 50.0
+    x[2, :] = 1.0
+    x[3, vocab - 1] = 60.0
+    out = torch.zeros(6, dtype=torch.int32, device=dev())
+    o.argmax_rows(x, out)
+    want = [plain.argmax(r) for r in x.cpu().numpy()]
+    assert out.tolist() == want
+    assert out[1] == 17 and out[2] == 0 and out[3] == vocab - 1
+
+
+@pytest.mark.parametrize("vocab,temp,k,seed", [(397, 0.8, 20, 7), (256, 1.0, 40, 42), (100, 0.5, 0, 3), (64, 1.3, 1000, 9),
+                                                 (49152, 0.9, 40, 1), (5000, 2.0, -1, 12), (1000, 0.3, 2, 5)])
+def test_sample_topk_matches_plain(vocab, temp, k, seed):
+    o = ops()
+    import golden_models as gm
+    rows = 6
+    steps = 8
+    state = [(s * 0x9E3779B97F4A7C15 + 1) & plain.MASK64 for s in range(seed, seed + rows)]
+    st = torch.tensor([s - (1 << 64) if s >= (1 << 63) else s for s in state], dtype=torch.int64, device=dev())
+    samplers = [plain.Sampler(temp, k, s) for s in range(seed, seed + rows)]
+    out = torch.zeros(rows, dtype=torch.int32, device=dev())
+    for step in range(steps):
+        if step % 2 == 0:
+            x = torch.from_numpy(gm.sampler_logits(rows, vocab, step))  # coarse grid: many exact ties
+        else:
+            x = torch.randn(rows, vocab, generator=torch.Generator().manual_seed(step)) * 3
+        xd = x.to(dev())
+        o.sample_topk(xd, temp, k, st, out)
+        want = [s.sample(r) for s, r in zip(samplers, x.numpy())]
+        assert out.tolist() == want, (step,)
+    assert [v & plain.MASK64 for v in st.tolist()] == [s.state for s in samplers]
