@@ -170,13 +170,18 @@ def argmax_rows(logits, out):
     _check(lib().edgelm_argmax_rows(_p(logits), logits.stride(0), logits.shape[0], logits.shape[1], _p(out), _stream()))
 
 
-def sample_topk(logits, temperature, top_k, rng_state, out):
-    """Temperature + top-k draw per row; rng_state (int64, one xorshift64 state per row) advances by one draw."""
+def sample_topk(logits, temperature, top_k, rng_state, out, state_index=None):
+    """Temperature + top-k draw per row; rng_state (int64 xorshift64 states) advances by one draw.
+    Row r uses state state_index[r] when given (a sequence's slot), else state r."""
     _need(logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1, "sample_topk: float32 rows")
-    _need(rng_state.dtype == torch.int64 and rng_state.is_contiguous() and rng_state.numel() >= logits.shape[0], "sample_topk: rng_state")
+    _need(rng_state.dtype == torch.int64 and rng_state.is_contiguous(), "sample_topk: rng_state")
+    if state_index is None:
+        _need(rng_state.numel() >= logits.shape[0], "sample_topk: one state per row")
+    else:
+        _i32(state_index, "state_index")
     _i32(out, "out")
     _check(lib().edgelm_sample_topk(_p(logits), logits.stride(0), logits.shape[0], logits.shape[1],
-                                    ctypes.c_float(temperature), int(top_k), _p(rng_state), _p(out), _stream()))
+                                    ctypes.c_float(temperature), int(top_k), _p(rng_state), _p(state_index), _p(out), _stream()))
 
 
 def read_error_word(err):

@@ -107,7 +107,8 @@ __device__ __forceinline__ unsigned long long fixed_p(float logit, float lmax, f
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_topk_kernel(const float* __restrict__ logits, int ld, int vocab, float temperature, int top_k,
-                   unsigned long long* __restrict__ rng_state, int32_t* __restrict__ out) {
+                   unsigned long long* __restrict__ rng_state, const int32_t* __restrict__ state_index,
+                   int32_t* __restrict__ out) {
   __shared__ SampleShared sh;
   const float* row = logits + (size_t)blockIdx.x * ld;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -174,11 +175,12 @@ sample_topk_kernel(const float* __restrict__ logits, int ld, int vocab, float te
       if (level == 0) {
         unsigned long long total = 0;
         for (int d = 0; d < 256; ++d) total += sh.hist[d];
-        unsigned long long s = rng_state[blockIdx.x];
+        const int si = state_index ? state_index[blockIdx.x] : (int)blockIdx.x;
+        unsigned long long s = rng_state[si];
         s ^= s << 13;
         s ^= s >> 7;
         s ^= s << 17;
-        rng_state[blockIdx.x] = s;
+        rng_state[si] = s;
         const double u = (double)(s >> 11) * (1.0 / 9007199254740992.0);
         unsigned long long t = (unsigned long long)ceil(u * (double)total);
         if (t < 1) t = 1;
@@ -206,13 +208,11 @@ sample_topk_kernel(const float* __restrict__ logits, int ld, int vocab, float te
   int idx = nth_equal_index(row, vocab, dprefix, n, sh);
   if (idx >= vocab || (dprefix == kth && idx >= tie_end)) {
     // rounding put the target past the last kept token of this value: take the last kept one
-    unsigned int cnt = 0;
     int last = -1;
     if (threadIdx.x == 0) {
       for (int i = 0; i < vocab; ++i)
         if (order_key(row[i]) == dprefix && (dprefix != kth || i < tie_end)) {
           last = i;
-          ++cnt;
         }
       sh.found_idx = (unsigned int)(last < 0 ? 0 : last);
     }
@@ -234,14 +234,16 @@ extern "C" int edgelm_argmax_rows(const float* logits, int ld, int rows, int voc
   return 0;
 }
 
-// rng_state: one 64-bit xorshift state per row, advanced by one draw.
+// rng_state: 64-bit xorshift states, advanced by one draw; row r uses state state_index[r]
+// (the sequence's slot), or state r when state_index is null.
 extern "C" int edgelm_sample_topk(const float* logits, int ld, int rows, int vocab, float temperature, int top_k,
-                                  unsigned long long* rng_state, int32_t* out, cudaStream_t stream) {
+                                  unsigned long long* rng_state, const int32_t* state_index, int32_t* out,
+                                  cudaStream_t stream) {
   if (rows == 0) return 0;
   EL_REFUSE(rows > 0 && vocab > 0 && ld >= vocab, "sample_topk: bad sizes rows=%d vocab=%d ld=%d", rows, vocab, ld);
   EL_REFUSE(temperature > 0.f, "sample_topk: temperature %g is not positive (greedy goes through argmax_rows)", temperature);
   EL_REFUSE(vocab <= (1 << 24), "sample_topk: vocabulary %d too large for the fixed-point sums", vocab);
-  sample_topk_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, vocab, temperature, top_k, rng_state, out);
+  sample_topk_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, vocab, temperature, top_k, rng_state, state_index, out);
   EL_LAUNCH_CHECK("sample_topk");
   return 0;
 }

@@ -1,0 +1,152 @@
+"""A step's batch: which sequences bring which tokens, and everything the kernels need to know
+about it, packed into one host buffer that goes to the device in one copy.
+
+Tokens of all sequences are packed along one axis.  Per token: its id, its absolute position
+and its sequence's index in the batch.  Per sequence: the position of its last new token, and
+its row of each cache group's page table.  For steps with more than one token per sequence
+there are also attention tiles (runs of at most `tile_tokens` consecutive tokens of one
+sequence).  Nothing here is padded: a kernel sees exactly the tokens the step brings.
+"""
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from .profiler import NULL_PROFILER
+
+
+@dataclass
+class Tiles:
+    seq: torch.Tensor
+    tok0: torch.Tensor
+    ntok: torch.Tensor
+    pos0: torch.Tensor
+    count: int
+
+
+def make_tiles(seq_ntok, seq_pos0, tile_tokens):
+    """Host lists (seq, first packed token, token count, first position) of the attention tiles."""
+    seq, tok0, ntok, pos0 = [], [], [], []
+    t0 = 0
+    for s, (n, p0) in enumerate(zip(seq_ntok, seq_pos0)):
+        for a in range(0, n, tile_tokens):
+            seq.append(s)
+            tok0.append(t0 + a)
+            ntok.append(min(tile_tokens, n - a))
+            pos0.append(p0 + a)
+        t0 += n
+    return seq, tok0, ntok, pos0
+
+
+class StepContext:
+    """What parts see of a step.  Built by the engine; parts read, never write."""
+
+    def __init__(self, ws, err, device, n_sms, profiler=None):
+        self.ws, self.err, self.device, self.n_sms = ws, err, device, n_sms
+        self.prof = profiler or NULL_PROFILER
+        self.n_tokens = self.n_seqs = 0
+        self.all_single = False
+        self.token_ids = self.tok_pos = self.tok_seq = self.seq_index = self.seq_pos = self.want_rows = None
+        self.seq_slots = None          # real slot of each sequence (int32 device tensor): state groups, sampler streams
+        self._tables = {}              # cache group id -> device page-table rows [n_seqs, stride]
+        self._tiles = {}
+        self._seq_ntok = self._seq_pos0 = None
+        self._fixed_splits = None
+
+    def page_table(self, group):
+        """Device page-table rows [n_seqs, pages] of a key/value cache group, one row per sequence of the batch."""
+        return self._tables[group.id]
+
+    @property
+    def seq_lengths(self):
+        """Host list: how many tokens each sequence brings in this step (packed in this order)."""
+        return list(self._seq_ntok)
+
+    @property
+    def seq_first_positions(self):
+        """Host list: the absolute position of each sequence's first token of this step."""
+        return list(self._seq_pos0)
+
+    def decode_splits(self, n_kv_heads):
+        """Blocks per (sequence, kv head) of the decode attention: enough to fill the device."""
+        if self._fixed_splits is not None:
+            return self._fixed_splits
+        blocks = max(1, self.n_seqs * n_kv_heads)
+        return int(min(64, max(1, (2 * self.n_sms + blocks - 1) // blocks)))
+
+    def tiles(self, tile_tokens):
+        if tile_tokens not in self._tiles:
+            seq, tok0, ntok, pos0 = make_tiles(self._seq_ntok, self._seq_pos0, tile_tokens)
+            n = len(seq)
+            host = torch.tensor(seq + tok0 + ntok + pos0, dtype=torch.int32).pin_memory()
+            d = host.to(self.device, non_blocking=True)
+            self._tiles[tile_tokens] = Tiles(d[:n], d[n:2 * n], d[2 * n:3 * n], d[3 * n:], n)
+        return self._tiles[tile_tokens]
+
+
+class BatchBuffers:
+    """Pinned host staging and its device twin for the per-step metadata, sized once for the
+    largest step; `fill` lays a step out and issues the single host-to-device copy."""
+
+    def __init__(self, max_tokens, max_seqs, kv_groups, max_want, device):
+        self.device = device
+        self.max_tokens, self.max_seqs, self.max_want = max_tokens, max_seqs, max_want
+        self.groups = list(kv_groups)
+        self.stride = {g.id: g.table.shape[1] for g in self.groups}
+        n = 3 * max_tokens + 4 * max_seqs + max_want + sum(max_seqs * s for s in self.stride.values())
+        self.host = torch.zeros(n, dtype=torch.int32).pin_memory()
+        self.host_np = self.host.numpy()
+        self.dev = torch.zeros(n, dtype=torch.int32, device=device)
+        self.seq_index_full = torch.arange(max_seqs, dtype=torch.int32, device=device)
+        self.last_bytes = 0
+        self._copied = torch.cuda.Event()
+
+    def fill(self, ctx, token_ids, seq_slots, seq_ntok, seq_pos0, want_rows, cache):
+        """Lay out the step and copy it; sets every tensor of `ctx` (views of the device buffer)."""
+        T, B, R = len(token_ids), len(seq_slots), len(want_rows)
+        if T > self.max_tokens or B > self.max_seqs or R > self.max_want:
+            raise ValueError(f"a step of {T} tokens, {B} sequences and {R} wanted rows exceeds the buffers "
+                             f"({self.max_tokens}, {self.max_seqs}, {self.max_want})")
+        self._copied.synchronize()  # the previous step's copy has read the staging buffer
+        h = self.host_np
+        ntok = np.asarray(seq_ntok, dtype=np.int64)
+        pos0 = np.asarray(seq_pos0, dtype=np.int64)
+        o = 0
+        views = {}
+
+        def put(name, arr, n):
+            nonlocal o
+            h[o:o + n] = arr
+            views[name] = (o, n)
+            o += n
+
+        put("token_ids", np.asarray(token_ids, dtype=np.int32), T)
+        seq_of_tok = np.repeat(np.arange(B, dtype=np.int32), ntok)
+        starts = np.concatenate([[0], np.cumsum(ntok)[:-1]])
+        put("tok_pos", (np.arange(T, dtype=np.int64) - np.repeat(starts, ntok) + np.repeat(pos0, ntok)).astype(np.int32), T)
+        put("tok_seq", seq_of_tok, T)
+        put("seq_pos", (pos0 + ntok - 1).astype(np.int32), B)
+        put("want_rows", np.asarray(want_rows, dtype=np.int32), R)
+        slots = np.asarray(seq_slots, dtype=np.int64)
+        put("seq_slots", slots.astype(np.int32), B)
+        for g in self.groups:
+            s = self.stride[g.id]
+            put(("table", g.id), g.table[slots].reshape(-1), B * s)
+        self.dev[:o].copy_(self.host[:o], non_blocking=True)
+        self._copied.record()
+        self.last_bytes = o * 4
+
+        def view(name):
+            a, n = views[name]
+            return self.dev[a:a + n]
+
+        ctx.n_tokens, ctx.n_seqs = T, B
+        ctx.all_single = bool(T == B and T > 0)
+        ctx.token_ids, ctx.tok_pos, ctx.tok_seq = view("token_ids"), view("tok_pos"), view("tok_seq")
+        ctx.seq_pos, ctx.want_rows = view("seq_pos"), view("want_rows")
+        ctx.seq_index = self.seq_index_full[:B]
+        ctx._tables = {g.id: view(("table", g.id)).view(B, self.stride[g.id]) for g in self.groups}
+        ctx._tiles = {}
+        ctx._seq_ntok, ctx._seq_pos0 = [int(x) for x in ntok], [int(x) for x in pos0]
+        ctx.seq_slots = view("seq_slots")
+        return ctx

@@ -1,0 +1,261 @@
+"""The engine: a model, its cache, and the one step function.
+
+`step(entries)` is the only way tokens reach the model.  Each entry names a live sequence,
+brings its next tokens (a whole prompt, a piece of one, or one decoded token) and says at which
+of these tokens logits are wanted.  The step runs exactly the tokens it is given, as one packed
+batch, on top of what earlier steps left in the cache, and returns float32 logits [wanted,
+vocab] in the order of the entries and of their wanted places.  Sequences of any lengths share
+a step; nothing is padded.  A step larger than `max_step_tokens` is cut into consecutive
+smaller ones, which gives the same logits, since every token attends through the cache.
+
+Decoding one token per sequence can be replayed from a CUDA graph (`decode_sampled`): the
+graph holds the forward pass and the sampler; per step the host copies the batch's metadata
+in (one copy) and the sampled tokens out (one copy).
+"""
+from dataclasses import dataclass
+from typing import List, Sequence
+
+import torch
+
+from ..cache import SequenceCache
+from ..config import read_config
+from ..csrc import ops
+from ..sampling.device import DeviceSampler
+from ..weights import load_checked
+from .arena import Workspace
+from .batch import BatchBuffers, StepContext
+from .model import DecoderModel
+from .profiler import Profiler
+
+DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+          "f32": torch.float32}
+
+
+class EngineError(RuntimeError):
+    pass
+
+
+@dataclass
+class StepEntry:
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+def load_model(model_dir, dtype="bfloat16", device="cuda:0"):
+    """Model folder (config.json + *.safetensors) -> DecoderModel on the device.  The model
+    class comes from config.json through the architecture registry."""
+    ops.require_device()
+    torch_dtype = DTYPES[dtype] if isinstance(dtype, str) else dtype
+    config = read_config(model_dir)
+    model = DecoderModel(config.plan(), torch_dtype)
+    tensors = load_checked(model_dir, model.expected_weights(), model.ignorable_weights())
+    model.load(tensors, device)
+    model.config = config
+    return model
+
+
+class Engine:
+    def __init__(self, model: DecoderModel, max_tokens, max_step_tokens=8192, max_seqs=None, profile=False,
+                 use_graphs=True):
+        ops.require_device()
+        if model.device is None:
+            raise EngineError("the model has no weights yet (load them first)")
+        self.model, self.device = model, model.device
+        self.plan = model.plan
+        self.cache = SequenceCache(model.cache_needs(), max_tokens, self.plan.max_positions, dtype=model.dtype,
+                                   device=self.device, max_seqs=max_seqs)
+        self.max_step_tokens = int(min(max_step_tokens, max(64, self.cache.n_pages * 64)))
+        self.max_step_seqs = min(self.cache.n_slots, self.max_step_tokens)
+        props = torch.cuda.get_device_properties(self.device)
+        self.n_sms = props.multi_processor_count
+        ws_bytes = model.workspace_bytes(self.max_step_tokens, self.max_step_seqs, self.max_step_tokens)
+        self.ws = Workspace(ws_bytes, self.device)
+        self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.buffers = BatchBuffers(self.max_step_tokens, self.max_step_seqs, self.cache.kv_groups, self.max_step_tokens,
+                                    self.device)
+        self.profiler = Profiler() if profile else None
+        self.ctx = StepContext(self.ws, self.err, self.device, self.n_sms, self.profiler)
+        self.sampler = DeviceSampler(self.cache.n_slots, self.device)
+        self.use_graphs = bool(use_graphs) and not profile
+        self._graphs = {}
+        self.steps_run = 0
+        self.h2d_bytes_last = 0
+        self.kernel_launches_last = 0
+
+    @classmethod
+    def from_dir(cls, model_dir, dtype="bfloat16", max_tokens=4096, device="cuda:0", **kw):
+        return cls(load_model(model_dir, dtype, device), max_tokens, **kw)
+
+    # ------------------------------------------------------------------ sequences
+    def open(self, n=1):
+        """Slots for `n` new sequences."""
+        return [self.cache.open() for _ in range(n)]
+
+    def close(self, slots):
+        """The sequences are finished: what they hold is given back."""
+        for s in slots:
+            self.cache.close(s)
+
+    def length(self, slot):
+        return int(self.cache.length[slot])
+
+    @property
+    def capacity_tokens(self):
+        return self.cache.n_pages * 64
+
+    @property
+    def max_positions(self):
+        return self.plan.max_positions
+
+    def seed(self, slots, params, first_request_index=0):
+        """Start the sampler streams of new sequences (request i of a call draws from seed + i)."""
+        self.sampler.seed(slots, params, first_request_index)
+
+    # ------------------------------------------------------------------ the step
+    def _validate(self, entries):
+        seen = set()
+        vocab = self.plan.vocab_size
+        for e in entries:
+            if e.slot in seen:
+                raise EngineError(f"slot {e.slot} appears twice in one step")
+            seen.add(e.slot)
+            n = len(e.tokens)
+            if n == 0:
+                raise EngineError(f"slot {e.slot} brings no token")
+            for t in e.tokens:
+                if not 0 <= int(t) < vocab:
+                    raise EngineError(f"token id {t} is outside the vocabulary of {vocab}")
+            for w in e.want:
+                if not 0 <= int(w) < n:
+                    raise EngineError(f"slot {e.slot} wants logits at place {w} of {n} tokens")
+
+    def step(self, entries: List[StepEntry]):
+        """Run the entries' tokens; return float32 logits [total wanted, vocab] on the device."""
+        entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        self._validate(entries)
+        for e in entries:  # room for every token before anything runs
+            self.cache.reserve(e.slot, len(e.tokens))
+        n_want = sum(len(e.want) for e in entries)
+        logits = torch.empty((n_want, self.plan.vocab_size), dtype=torch.float32, device=self.device)
+        # cut into micro-steps of at most max_step_tokens tokens and max_step_seqs sequences
+        micro, cur, cur_tokens = [], [], 0
+        for e in entries:
+            start = 0
+            n = len(e.tokens)
+            while start < n:
+                room = self.max_step_tokens - cur_tokens
+                if room == 0 or len(cur) == self.max_step_seqs:
+                    micro.append(cur)
+                    cur, cur_tokens = [], 0
+                    room = self.max_step_tokens
+                take = min(room, n - start)
+                cur.append((e, start, take))
+                cur_tokens += take
+                start += take
+        if cur:
+            micro.append(cur)
+        # global row of every wanted place, in the order of the entries and of their `want` lists
+        base, row_of = 0, {}
+        for e in entries:
+            for j, w in enumerate(e.want):
+                row_of.setdefault((id(e), int(w)), []).append(base + j)
+            base += len(e.want)
+        order = []
+        row0 = 0
+        for pieces in micro:
+            row0 += self._run_pieces(pieces, logits, row0, row_of, order)
+        if order != list(range(n_want)):  # a cut sequence with unsorted wants: put the rows where they belong
+            dest = torch.tensor(order, dtype=torch.int64, device=self.device)
+            logits = torch.empty_like(logits).index_copy_(0, dest, logits)
+        return logits
+
+    def _run_pieces(self, pieces, logits, row0, row_of, order):
+        token_ids, slots, ntok, pos0, want_rows = [], [], [], [], []
+        t0 = 0
+        for e, start, take in pieces:
+            token_ids.extend(int(t) for t in e.tokens[start:start + take])
+            slots.append(e.slot)
+            ntok.append(take)
+            pos0.append(int(self.cache.length[e.slot]))
+            for w in e.want:
+                if start <= int(w) < start + take:
+                    want_rows.append(t0 + int(w) - start)
+                    order.append(row_of[(id(e), int(w))].pop(0))
+            t0 += take
+        ctx = self.buffers.fill(self.ctx, token_ids, slots, ntok, pos0, want_rows, self.cache)
+        self.h2d_bytes_last = self.buffers.last_bytes
+        out = logits[row0:row0 + len(want_rows)]
+        if self.profiler is not None:
+            self.profiler.begin_step("decode" if ctx.all_single else "prefill", ctx.n_tokens, ctx.n_seqs, min(pos0))
+        self.model.forward(ctx, self.cache, out)
+        if self.profiler is not None:
+            self.profiler.end_step()
+        for s, n in zip(slots, ntok):
+            self.cache.advance(s, n)
+        self.steps_run += 1
+        return len(want_rows)
+
+    def check_device_errors(self):
+        """Raise if a kernel flagged bad input since the last check (synchronises)."""
+        ops.read_error_word(self.err)
+
+    # ------------------------------------------------------------------ sampled steps (generation)
+    def prefill_sampled(self, slots, prompts, params):
+        """Prompts of sequences that start together, in one step; returns a sampled token per sequence."""
+        entries = [StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)]
+        logits = self.step(entries)
+        tokens = torch.empty(len(slots), dtype=torch.int32, device=self.device)
+        self.sampler.sample(logits, params, self.ctx.seq_slots if len(slots) == self.ctx.n_seqs else
+                            torch.tensor(slots, dtype=torch.int32, device=self.device), tokens)
+        return tokens.tolist()
+
+    def decode_sampled(self, slots, last_tokens, params):
+        """One token per sequence, sampled on the device; from a CUDA graph when enabled."""
+        B = len(slots)
+        if not self.use_graphs or B > self.max_step_seqs:
+            logits = self.step([StepEntry(s, [t], [0]) for s, t in zip(slots, last_tokens)])
+            tokens = torch.empty(B, dtype=torch.int32, device=self.device)
+            self.sampler.sample(logits, params, self.ctx.seq_slots, tokens)
+            return tokens.tolist()
+        vocab = self.plan.vocab_size
+        for s, t in zip(slots, last_tokens):
+            if not 0 <= int(t) < vocab:
+                raise EngineError(f"token id {t} is outside the vocabulary of {vocab}")
+            self.cache.reserve(s, 1)
+        pos0 = [int(self.cache.length[s]) for s in slots]
+        ctx = self.buffers.fill(self.ctx, list(last_tokens), slots, [1] * B, pos0, list(range(B)), self.cache)
+        self.h2d_bytes_last = self.buffers.last_bytes
+        key = (B, params.key())
+        g = self._graphs.get(key)
+        if g is None:
+            g = self._capture_decode(ctx, B, params)
+            self._graphs[key] = g
+        g["graph"].replay()
+        for s in slots:
+            self.cache.advance(s, 1)
+        self.steps_run += 1
+        g["host"].copy_(g["tokens"], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return g["host"].tolist()
+
+    def _capture_decode(self, ctx, B, params):
+        """Capture forward + sampling for a batch of B single tokens.  The views of `ctx` have
+        the same addresses for every step of B sequences, so the graph reads each step's fresh
+        metadata; the number of attention splits is frozen with the graph."""
+        logits = torch.empty((B, self.plan.vocab_size), dtype=torch.float32, device=self.device)
+        tokens = torch.empty(B, dtype=torch.int32, device=self.device)
+        host = torch.empty(B, dtype=torch.int32).pin_memory()
+        ops.lib()  # library loaded and kernels' attributes set before capture
+        # one eager run first: it sets kernel attributes (shared-memory sizes) outside of the capture.
+        # It writes the same cache rows and advances no state but the sampler's, which is restored.
+        saved = self.sampler.state.clone()
+        self.model.forward(ctx, self.cache, logits)
+        self.sampler.sample(logits, params, ctx.seq_slots, tokens)
+        torch.cuda.synchronize()
+        self.sampler.state.copy_(saved)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.model.forward(ctx, self.cache, logits)
+            self.sampler.sample(logits, params, ctx.seq_slots, tokens)
+        return {"graph": graph, "logits": logits, "tokens": tokens, "host": host}

@@ -1,0 +1,81 @@
+"""Grouped-query causal attention over the paged cache.
+
+q, k, v = h Wq^T, h Wk^T, h Wv^T (no bias; one matrix product over the three weights stacked);
+rotary positions on q and k; k and v appended to the cache; for query head h and key head
+h // (heads / kv_heads): softmax((q . K_j) / sqrt(head_dim)) over j <= the token's position,
+times V; then x += a Wo^T (adarsh-sgh/edgelm src/kernels_ref.cpp:100-141, tools/elm.py:126-139).
+"""
+import math
+
+import torch
+
+from ..csrc import ops
+from . import linear
+from .base import KVNeed, Part, as_matrix, nbytes
+from .registry import register_mixer
+
+
+@register_mixer("attention")
+class Attention(Part):
+    def __init__(self, spec, env):
+        self.hidden = spec["hidden_size"]
+        self.nh, self.nkv, self.hd = spec["num_heads"], spec["num_kv_heads"], spec["head_dim"]
+        self.names = dict(spec["names"])
+        self.dtype = env.dtype
+        self.positions = env.build_shared("positions", spec["positions"])
+        self.scale = 1.0 / math.sqrt(self.hd)
+        self.group = self.nh // self.nkv
+        self.tile_tokens = max(1, 32 // self.group)  # tokens whose heads fill one block of the prefill kernel
+        self.w_qkv = self.w_o = None
+
+    def weight_shapes(self, prefix):
+        n = self.names
+        return {prefix + n["q"]: (self.nh * self.hd, self.hidden), prefix + n["k"]: (self.nkv * self.hd, self.hidden),
+                prefix + n["v"]: (self.nkv * self.hd, self.hidden), prefix + n["o"]: (self.hidden, self.nh * self.hd)}
+
+    def load(self, tensors, prefix, device):
+        n = self.names
+        # the three projections share their input: stacked once here, they are one matrix product per step
+        self.w_qkv = torch.cat([as_matrix(tensors[prefix + n[k]], self.dtype, device) for k in ("q", "k", "v")], dim=0).contiguous()
+        self.w_o = as_matrix(tensors[prefix + n["o"]], self.dtype, device)
+        self.positions.load(tensors, prefix, device)
+
+    def cache_need(self):
+        return KVNeed(self.nkv, self.hd)
+
+    def _splits(self, ctx):
+        return ctx.decode_splits(self.nkv)
+
+    def workspace_bytes(self, n_tokens, n_seqs):
+        qkv = nbytes((n_tokens, (self.nh + 2 * self.nkv) * self.hd), self.dtype)
+        out = nbytes((n_tokens, self.nh * self.hd), self.dtype)
+        part = nbytes((n_seqs * self.nh * 64 * (self.hd + 2),), torch.float32)  # split partials, at most 64 splits
+        return qkv + out + 2 * part
+
+    def forward(self, ctx, h, x, cache):
+        T = h.shape[0]
+        ws = ctx.ws
+        with ws.frame():
+            qkv = ws.alloc((T, (self.nh + 2 * self.nkv) * self.hd), self.dtype)
+            with ctx.prof("qkv_proj"):
+                linear.matmul(h, self.w_qkv, qkv)
+            with ctx.prof("rope_kv_append"):
+                self.positions.encode_and_append(ctx, qkv, cache, self.nh, self.nkv)
+            a = ws.alloc((T, self.nh * self.hd), self.dtype)
+            table = ctx.page_table(cache.group)
+            if ctx.all_single:
+                splits = self._splits(ctx)
+                part_o = part_ml = None
+                if splits > 1:
+                    part_o = ws.alloc((ctx.n_seqs * self.nh * splits * self.hd,), torch.float32)
+                    part_ml = ws.alloc((ctx.n_seqs * self.nh * splits * 2,), torch.float32)
+                with ctx.prof("attn_decode"):
+                    ops.attn_decode(qkv, a, cache.k, cache.v, table, ctx.seq_index, ctx.seq_pos, ctx.n_seqs, self.nh, self.nkv,
+                                    self.hd, self.scale, splits, part_o, part_ml)
+            else:
+                tiles = ctx.tiles(self.tile_tokens)
+                with ctx.prof("attn_prefill"):
+                    ops.attn_prefill(qkv, a, cache.k, cache.v, table, ctx.seq_index, tiles.seq, tiles.tok0, tiles.ntok,
+                                     tiles.pos0, tiles.count, self.tile_tokens, self.nh, self.nkv, self.hd, self.scale)
+            with ctx.prof("o_proj_residual"):
+                linear.matmul(a, self.w_o, x, epilogue=linear.EPI_RESIDUAL, residual=x)

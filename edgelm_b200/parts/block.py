@@ -1,0 +1,44 @@
+"""Arrangement of one layer's parts.  "prenorm": x += mixer(norm1(x)); x += ffn(norm2(x))
+(adarsh-sgh/edgelm tools/elm.py:122-153)."""
+from .base import Part, nbytes
+from .registry import register_block
+
+
+@register_block("prenorm")
+class PreNormBlock(Part):
+    def __init__(self, layer_spec, env):
+        self.prefix = layer_spec.prefix
+        self.dtype = env.dtype
+        self.mixer_norm = env.build("norm", layer_spec.mixer_norm)
+        self.mixer = env.build("mixer", layer_spec.mixer)
+        self.ffn_norm = env.build("norm", layer_spec.ffn_norm)
+        self.ffn = env.build("ffn", layer_spec.ffn)
+        self.parts = (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
+        self.hidden = layer_spec.mixer_norm["dim"]
+
+    def weight_shapes(self, prefix=None):
+        out = {}
+        for p in self.parts:
+            out.update(p.weight_shapes(self.prefix))
+        return out
+
+    def load(self, tensors, prefix, device):
+        for p in self.parts:
+            p.load(tensors, self.prefix, device)
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def workspace_bytes(self, n_tokens, n_seqs):
+        return nbytes((n_tokens, self.hidden), self.dtype) + max(self.mixer.workspace_bytes(n_tokens, n_seqs),
+                                                                  self.ffn.workspace_bytes(n_tokens, n_seqs))
+
+    def forward(self, ctx, x, cache):
+        with ctx.ws.frame():
+            h = ctx.ws.alloc((x.shape[0], self.hidden), self.dtype)
+            with ctx.prof("mixer_norm"):
+                self.mixer_norm.forward(ctx, x, h)
+            self.mixer.forward(ctx, h, x, cache)
+            with ctx.prof("ffn_norm"):
+                self.ffn_norm.forward(ctx, x, h)
+            self.ffn.forward(ctx, h, x)

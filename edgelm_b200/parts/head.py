@@ -1,0 +1,27 @@
+"""Output head: logits = norm(x[wanted rows]) H^T in float32, H the embedding table when tied
+(adarsh-sgh/edgelm tools/elm.py:154-160).  The final norm is applied by the model before this
+part; here is the matrix product alone."""
+from . import linear
+from .base import Part, as_matrix
+from .registry import register_head
+
+
+@register_head("lm_head")
+class LMHead(Part):
+    def __init__(self, spec, env):
+        self.vocab_size, self.dim, self.name, self.tied_to = spec["vocab_size"], spec["dim"], spec["name"], spec["tied_to"]
+        self.dtype = env.dtype
+        self.weight = None
+
+    def weight_shapes(self, prefix=""):
+        return {} if self.tied_to else {self.name: (self.vocab_size, self.dim)}
+
+    def ignorable(self):
+        """Names that a file may hold without their being used: a tied model's stored copy of the head."""
+        return (self.name,) if self.tied_to else ()
+
+    def load(self, tensors, prefix, device, tied_table=None):
+        self.weight = tied_table if self.tied_to else as_matrix(tensors[self.name], self.dtype, device)
+
+    def forward(self, ctx, xn, logits):
+        linear.matmul(xn, self.weight, logits)

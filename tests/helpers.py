@@ -1,0 +1,120 @@
+"""Shared by the GPU tests: the two tiny configurations, model folders with random weights in a
+temporary place, the plain implementation's logits, and drivers that cut one token stream
+through the engine in different ways."""
+import numpy as np
+import torch
+
+import plain_llama as plain
+
+# Two tiny configurations that differ in every size and option: layers, width, head counts and
+# grouping (4/2 grouped vs 3/1 multi-query), head size, feed-forward width (200 is no multiple
+# of 16), vocabulary (397 is odd), theta, eps, tied vs separate head, positions, weight scale.
+TINY_A = dict(model_type="llama", architectures=["LlamaForCausalLM"], vocab_size=256, hidden_size=64,
+              intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+              max_position_embeddings=128, rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=True,
+              bos_token_id=0, eos_token_id=0)
+TINY_B = dict(model_type="llama", architectures=["LlamaForCausalLM"], vocab_size=397, hidden_size=96,
+              intermediate_size=200, num_hidden_layers=3, num_attention_heads=3, num_key_value_heads=1, head_dim=32,
+              max_position_embeddings=256, rope_theta=100000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
+              bos_token_id=1, eos_token_id=2)
+TINY = {"tiny_a": (TINY_A, 0, 0.09), "tiny_b": (TINY_B, 2, 0.07)}  # config, seed, sigma (large enough for logits of order 1)
+
+TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+
+
+def rel_err(a, b):
+    """adarsh-sgh/edgelm's metric (tests/common.hpp:69-76): max |a-b| / max(1, max |b|)."""
+    a = np.asarray(a, dtype=np.float64)
+    b = np.asarray(b, dtype=np.float64)
+    assert a.shape == b.shape, (a.shape, b.shape)
+    return float(np.abs(a - b).max() / max(1.0, np.abs(b).max()))
+
+
+def make_model_dir(tmp, name, file_dtype="bfloat16"):
+    from edgelm_b200 import write_model_dir
+    from edgelm_b200.config import config_class_for
+    cfg_dict, seed, sigma = TINY[name]
+    cfg = config_class_for(cfg_dict).from_dict(cfg_dict)
+    return write_model_dir(str(tmp / f"{name}_{file_dtype}"), cfg, seed, sigma=sigma, dtype=file_dtype)
+
+
+def tokens_for(name, n, salt):
+    vocab = TINY[name][0]["vocab_size"]
+    rng = np.random.default_rng(1000 + salt)
+    return [int(t) for t in rng.integers(0, vocab, size=n)]
+
+
+class Oracle:
+    """The plain implementation on a model folder, logits cached per token tuple."""
+
+    def __init__(self, model_dir):
+        self.cfg, self.W = plain.read_model(model_dir)
+        self._memo = {}
+
+    def logits(self, tokens):
+        key = tuple(tokens)
+        if key not in self._memo:
+            self._memo[key] = plain.forward(self.cfg, self.W, list(tokens))
+        return self._memo[key]
+
+
+def run_whole(engine, tokens):
+    """One request alone and whole: one step, logits at every position."""
+    from edgelm_b200.engine.engine import StepEntry
+    slot = engine.open(1)[0]
+    out = engine.step([StepEntry(slot, tokens, list(range(len(tokens))))]).cpu().numpy()
+    engine.close([slot])
+    return out
+
+
+def run_tail_one_by_one(engine, tokens, tail=32):
+    """The first len - tail tokens in one step, then the last `tail` tokens one by one."""
+    from edgelm_b200.engine.engine import StepEntry
+    slot = engine.open(1)[0]
+    head = max(0, len(tokens) - tail)
+    parts = []
+    if head:
+        parts.append(engine.step([StepEntry(slot, tokens[:head], list(range(head)))]).cpu().numpy())
+    for t in tokens[head:]:
+        parts.append(engine.step([StepEntry(slot, [t], [0])]).cpu().numpy())
+    engine.close([slot])
+    return np.concatenate(parts, axis=0)
+
+
+def run_batches(engine, requests, batch_size, decode_tail):
+    """Batches of unequal lengths, one after another.  In each batch all requests start together:
+    step 0 brings each request's first len - decode_tail tokens (at least 1), then every step
+    brings one token per request still running; shorter requests end earlier and give back what
+    they hold.  Returns per request its logits at every position."""
+    from edgelm_b200.engine.engine import StepEntry
+    out = [None] * len(requests)
+    for b0 in range(0, len(requests), batch_size):
+        idxs = list(range(b0, min(len(requests), b0 + batch_size)))
+        slots = dict(zip(idxs, engine.open(len(idxs))))
+        fed = {}
+        entries = []
+        for i in idxs:
+            n0 = max(1, len(requests[i]) - decode_tail)
+            entries.append(StepEntry(slots[i], requests[i][:n0], list(range(n0))))
+            fed[i] = n0
+        lg = engine.step(entries).cpu().numpy()
+        rows = {i: [] for i in idxs}
+        r = 0
+        for i in idxs:
+            rows[i].append(lg[r:r + fed[i]])
+            r += fed[i]
+        live = list(idxs)
+        while live:
+            for i in [i for i in live if fed[i] == len(requests[i])]:
+                engine.close([slots.pop(i)])
+                live.remove(i)
+            if not live:
+                break
+            lg = engine.step([StepEntry(slots[i], [requests[i][fed[i]]], [0]) for i in live]).cpu().numpy()
+            for r, i in enumerate(live):
+                rows[i].append(lg[r:r + 1])
+                fed[i] += 1
+        for i in idxs:
+            out[i] = np.concatenate(rows[i], axis=0)
+        engine.cache.check()
+    return out
