@@ -54,9 +54,18 @@ def require_device():
         raise KernelError(f"edgelm_b200's kernels are built for sm_100a; the current device reports sm_{arch}")
 
 
-def _check(rc):
+LAUNCHES = 0  # kernels launched through this module since import (a graph replay counts what it captured)
+
+
+def count_launches(n):
+    global LAUNCHES
+    LAUNCHES += n
+
+
+def _check(rc, launches=1):
     if rc != 0:
         raise KernelError(lib().edgelm_last_error().decode())
+    count_launches(launches)
 
 
 def _dt(t):
@@ -160,7 +169,8 @@ def attn_decode(qkv, out, kcache, vcache, page_table, seq_slot, seq_pos, n_seqs,
         _need(part_ml is not None and part_ml.dtype == torch.float32 and part_ml.numel() >= n_seqs * nh * n_splits * 2, "attn_decode: part_ml too small")
     _check(lib().edgelm_attn_decode(_p(qkv), qkv.stride(0), _p(out), out.stride(0), _p(kcache), _p(vcache), _dt(qkv),
                                     _p(page_table), page_table.stride(0), _p(seq_slot), _p(seq_pos), n_seqs, nh, nkv, hd,
-                                    ctypes.c_float(scale), n_splits, _p(part_o), _p(part_ml), _stream()))
+                                    ctypes.c_float(scale), n_splits, _p(part_o), _p(part_ml), _stream()),
+           launches=2 if n_splits > 1 else 1)
 
 
 def argmax_rows(logits, out):

@@ -211,13 +211,23 @@ class Engine:
         return tokens.tolist()
 
     def decode_sampled(self, slots, last_tokens, params):
-        """One token per sequence, sampled on the device; from a CUDA graph when enabled."""
+        """One token per sequence, sampled on the device; from a CUDA graph when enabled.
+        Host token ids in, host token ids out."""
         B = len(slots)
         if not self.use_graphs or B > self.max_step_seqs:
             logits = self.step([StepEntry(s, [t], [0]) for s, t in zip(slots, last_tokens)])
             tokens = torch.empty(B, dtype=torch.int32, device=self.device)
             self.sampler.sample(logits, params, self.ctx.seq_slots, tokens)
             return tokens.tolist()
+        g = self.decode_launch(slots, last_tokens, params)
+        g["host"].copy_(g["tokens"], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return g["host"].tolist()
+
+    def decode_launch(self, slots, last_tokens, params):
+        """Issue one decode step (metadata copy + graph replay) without waiting for it; the
+        sampled tokens land in the returned record's device tensor `tokens`."""
+        B = len(slots)
         vocab = self.plan.vocab_size
         for s, t in zip(slots, last_tokens):
             if not 0 <= int(t) < vocab:
@@ -232,12 +242,11 @@ class Engine:
             g = self._capture_decode(ctx, B, params)
             self._graphs[key] = g
         g["graph"].replay()
+        ops.count_launches(g["launches"])
         for s in slots:
             self.cache.advance(s, 1)
         self.steps_run += 1
-        g["host"].copy_(g["tokens"], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        return g["host"].tolist()
+        return g
 
     def _capture_decode(self, ctx, B, params):
         """Capture forward + sampling for a batch of B single tokens.  The views of `ctx` have
@@ -255,7 +264,10 @@ class Engine:
         torch.cuda.synchronize()
         self.sampler.state.copy_(saved)
         graph = torch.cuda.CUDAGraph()
+        before = ops.LAUNCHES
         with torch.cuda.graph(graph):
             self.model.forward(ctx, self.cache, logits)
             self.sampler.sample(logits, params, ctx.seq_slots, tokens)
-        return {"graph": graph, "logits": logits, "tokens": tokens, "host": host}
+        launches = ops.LAUNCHES - before
+        ops.count_launches(-launches)  # captured, not run
+        return {"graph": graph, "logits": logits, "tokens": tokens, "host": host, "launches": launches}
