@@ -1,0 +1,391 @@
+// out = a . W^T in bfloat16 on the fifth-generation tensor cores (tcgen05), float32 accumulation
+// in tensor memory, operands staged by TMA, with the same fused epilogues as the CUDA-core kernel.
+//
+//   a [M, K] bfloat16 (row pitch lda), W [N, K] bfloat16 row-major (out, in): both K-major, which is
+//   what tcgen05.mma takes for A and B without a transpose.
+//
+// One CTA computes a 128 x BN tile.  Six warps, three roles:
+//   warp 0    one lane issues TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle) of a 128 x 64
+//             tile of `a` and a BN x 64 tile of W (two for SwiGLU) into a ring of STAGES stages,
+//             each guarded by a full/empty mbarrier pair;
+//   warp 1    allocates BN (or 2 BN) columns of tensor memory; one lane issues four tcgen05.mma
+//             (M 128, N BN, K 16) per stage and commits the stage's release, then the tile's end;
+//   warps 2-5 wait for the accumulator, read it with tcgen05.ld (each warp its 32 lanes = rows),
+//             apply the epilogue and store.
+// M, N and K tails need no special code: TMA fills what lies outside a tensor with zeros, and the
+// epilogue stores only rows < M and columns < N.  K must be a multiple of 8 (16-byte row pitch).
+//
+// Every wait on an mbarrier is bounded (about a second of SM clock): when it runs out the kernel
+// sets ERR_WAIT_TIMEOUT in the error word, raises a block-wide abort flag that ends the other
+// roles' waits, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace edgelm {
+
+enum : int { TC_EPI_STORE = 0, TC_EPI_RESIDUAL = 1, TC_EPI_SWIGLU = 2 };
+
+constexpr int TC_BM = 128;   // rows of `a` per tile = lanes of tensor memory
+constexpr int TC_BK = 64;    // 64 bfloat16 = one 128-byte swizzle row
+constexpr int TC_STAGES = 3;
+constexpr int TC_THREADS = 192;
+constexpr long long TC_WAIT_CYCLES = 2000000000LL;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  False: it ran out, or another role of the block gave up; the caller leaves its loop.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err) {
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+    if (mbar_try(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > TC_WAIT_CYCLES) {
+      *abort_flag = 1;
+      atomicOr(err, ERR_WAIT_TIMEOUT);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y)
+               : "memory");
+}
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes,
+// groups of 8 rows 1024 bytes apart (stride byte offset), descriptor version 1.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+  uint64_t d = (uint64_t)((saddr >> 4) & 0x3FFF);
+  d |= (uint64_t)1 << 16;                 // leading byte offset: not used by swizzled K-major layouts
+  d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset
+  d |= (uint64_t)1 << 46;                 // version
+  d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor of kind::f16: D float32, A and B bfloat16, both K-major, M x N.
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ float silu_tc(float z) { return z / (1.0f + expf(-z)); }
+
+template <typename TOut> struct OutVec;
+template <> struct OutVec<float> {
+  static __device__ __forceinline__ void store8(float* p, const float* v) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  }
+};
+template <> struct OutVec<__nv_bfloat16> {
+  static __device__ __forceinline__ void store8(__nv_bfloat16* p, const float* v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    __nv_bfloat162 c = __floats2bfloat162_rn(v[4], v[5]), d = __floats2bfloat162_rn(v[6], v[7]);
+    uint4 u;
+    u.x = *reinterpret_cast<uint32_t*>(&a);
+    u.y = *reinterpret_cast<uint32_t*>(&b);
+    u.z = *reinterpret_cast<uint32_t*>(&c);
+    u.w = *reinterpret_cast<uint32_t*>(&d);
+    *reinterpret_cast<uint4*>(p) = u;
+  }
+};
+
+template <int BN, int EPI, typename TOut>
+__global__ void __launch_bounds__(TC_THREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_b2, TOut* out, int ldo, const float* residual,
+               int M, int N, int K, int vec_ok, int* err) {
+  constexpr int NB = EPI == TC_EPI_SWIGLU ? 2 : 1;
+  constexpr int A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
+  constexpr int STAGE_BYTES = A_BYTES + NB * B_BYTES;
+  constexpr uint32_t TMEM_COLS = NB * BN < 32 ? 32 : NB * BN;  // 64, 128 or 256: powers of two
+  static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "tensor memory columns: a power of two");
+  static_assert(STAGE_BYTES % 1024 == 0, "stages keep the 1024-byte alignment of swizzled tiles");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TC_STAGES * STAGE_BYTES);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + TC_STAGES;
+  uint64_t* tmem_full_bar = bars + 2 * TC_STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * TC_STAGES + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN;
+  const int n_k = (K + TC_BK - 1) / TC_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < TC_STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    mbar_init(smem_u32(tmem_full_bar), 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int i = 0; i < n_k; ++i) {
+        const int s = i % TC_STAGES;
+        if (!mbar_wait(smem_u32(&empty_bar[s]), ((i / TC_STAGES) & 1) ^ 1, abort_flag, err)) break;
+        const uint32_t bar = smem_u32(&full_bar[s]);
+        mbar_expect_tx(bar, STAGE_BYTES);
+        const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+        tma_load_2d(sa, &map_a, bar, i * TC_BK, m0);
+        tma_load_2d(sa + A_BYTES, &map_b, bar, i * TC_BK, n0);
+        if (NB == 2) tma_load_2d(sa + A_BYTES + B_BYTES, &map_b2, bar, i * TC_BK, n0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(TC_BM, BN);
+      bool ok = true;
+      for (int i = 0; i < n_k && ok; ++i) {
+        const int s = i % TC_STAGES;
+        ok = mbar_wait(smem_u32(&full_bar[s]), (i / TC_STAGES) & 1, abort_flag, err);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+        const uint64_t da = umma_desc(sa), db = umma_desc(sa + A_BYTES), db2 = umma_desc(sa + A_BYTES + B_BYTES);
+#pragma unroll
+        for (int k = 0; k < TC_BK / 16; ++k) {  // 16 bfloat16 = 32 bytes = 2 descriptor address units per step
+          const uint32_t acc = (i | k) != 0;
+          umma_f16(tmem_base, da + 2 * k, db + 2 * k, idesc, acc);
+          if (NB == 2) umma_f16(tmem_base + BN, da + 2 * k, db2 + 2 * k, idesc, acc);
+        }
+        umma_commit(smem_u32(&empty_bar[s]));  // arrives when these MMAs have read the stage
+      }
+      if (ok) umma_commit(smem_u32(tmem_full_bar));
+    }
+  } else {
+    const int q = warp & 3;  // a warp reads the 32 lanes of tensor memory that its index modulo 4 selects
+    const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(tmem_full_bar), 0, abort_flag, err));  // one decision per warp
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {
+      const int row = m0 + q * 32 + lane;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (n0 + c0 >= N) break;  // uniform over the block
+        uint32_t r[32], r2[32];
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+        tmem_ld32(taddr, r);
+        if (NB == 2) tmem_ld32(taddr + BN, r2);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (row < M) {
+          const size_t base = (size_t)row * ldo + n0 + c0;
+          const bool full = vec_ok && (n0 + c0 + 32 <= N);
+#pragma unroll
+          for (int j0 = 0; j0 < 32; j0 += 8) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float acc = __uint_as_float(r[j0 + j]);
+              if (EPI == TC_EPI_SWIGLU) v[j] = silu_tc(acc) * __uint_as_float(r2[j0 + j]);
+              else v[j] = acc;
+            }
+            if (full) {
+              if (EPI == TC_EPI_RESIDUAL) {
+                const float4 a = *reinterpret_cast<const float4*>(residual + base + j0);
+                const float4 b = *reinterpret_cast<const float4*>(residual + base + j0 + 4);
+                v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
+                v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+              }
+              OutVec<TOut>::store8(out + base + j0, v);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                if (n0 + c0 + j0 + j < N) {
+                  float x = v[j];
+                  if (EPI == TC_EPI_RESIDUAL) x += residual[base + j0 + j];
+                  out[base + j0 + j] = from_f32<TOut>(x);
+                }
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  int rows, cols, ld, box_rows;
+  bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr);
+    for (int v : {k.rows, k.cols, k.ld, k.box_rows}) h = h * 1000003u ^ (size_t)v;
+    return h;
+  }
+};
+
+// Tensor map of a row-major bfloat16 matrix [rows, cols] with row pitch ld, boxes of box_rows x 64,
+// 128-byte swizzle, zero fill outside.  Cached: activations live at fixed workspace addresses.
+static int tensor_map(const void* ptr, int rows, int cols, int ld, int box_rows, CUtensorMap* out) {
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  static std::mutex mu;
+  const MapKey key{ptr, rows, cols, ld, box_rows};
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return 0;
+  }
+  EncodeTiledFn enc = encode_fn();
+  EL_REFUSE(enc != nullptr, "gemm_tc: the driver does not provide cuTensorMapEncodeTiled");
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  const CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  EL_REFUSE(r == CUDA_SUCCESS, "gemm_tc: cuTensorMapEncodeTiled failed with code %d for a [%d, %d] matrix of pitch %d", (int)r, rows, cols, ld);
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, m);
+  *out = m;
+  return 0;
+}
+
+template <int BN, int EPI, typename TOut>
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, void* out, int ldo,
+                     const float* residual, int M, int N, int K, int vec_ok, int* err, cudaStream_t stream) {
+  constexpr int NB = EPI == TC_EPI_SWIGLU ? 2 : 1;
+  constexpr int smem = TC_STAGES * (TC_BM * TC_BK * 2 + NB * BN * TC_BK * 2) + 1024 + 256;
+  auto kern = gemm_tc_kernel<BN, EPI, TOut>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) {
+      set_error("gemm_tc: %d bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+      return -2;
+    }
+    configured = true;
+  }
+  dim3 grid((N + BN - 1) / BN, (M + TC_BM - 1) / TC_BM);
+  kern<<<grid, TC_THREADS, smem, stream>>>(ma, mb, mb2, (TOut*)out, ldo, residual, M, N, K, vec_ok, err);
+  return 0;
+}
+
+}  // namespace edgelm
+
+using namespace edgelm;
+
+// 1 if the tensor-core kernel takes these operands (alignment and pitch rules of TMA), else 0.
+extern "C" int edgelm_gemm_tc_takes(const void* a, int lda, const void* w, const void* w2, int K) {
+  const bool ok = K > 0 && K % 8 == 0 && lda % 8 == 0 && (uintptr_t)a % 16 == 0 && (uintptr_t)w % 16 == 0 &&
+                  (w2 == nullptr || (uintptr_t)w2 % 16 == 0);
+  return ok ? 1 : 0;
+}
+
+extern "C" int edgelm_gemm_tc(const void* a, int lda, const void* w, const void* w2, void* out, int ldo,
+                              const float* residual, int M, int N, int K, int out_dtype, int epilogue, int* err,
+                              cudaStream_t stream) {
+  if (M == 0) return 0;
+  EL_REFUSE(M > 0 && N > 0 && K > 0 && lda >= K && ldo >= N, "gemm_tc: bad sizes M=%d N=%d K=%d lda=%d ldo=%d", M, N, K, lda, ldo);
+  EL_REFUSE(edgelm_gemm_tc_takes(a, lda, w, w2, K), "gemm_tc: K=%d and lda=%d must be multiples of 8 and the operands 16-byte aligned", K, lda);
+  EL_REFUSE(epilogue != TC_EPI_SWIGLU || w2 != nullptr, "gemm_tc: SwiGLU needs the second weight");
+  EL_REFUSE(epilogue != TC_EPI_RESIDUAL || (residual != nullptr && out_dtype == DT_F32), "gemm_tc: residual epilogue needs a float32 residual and output");
+  EL_REFUSE(err != nullptr, "gemm_tc: needs the error word");
+  EL_REFUSE((M + TC_BM - 1) / TC_BM <= 65535, "gemm_tc: too many rows (%d)", M);
+  const int bn = epilogue == TC_EPI_SWIGLU ? 64 : 128;
+  CUtensorMap ma, mb, mb2;
+  if (tensor_map(a, M, K, lda, TC_BM, &ma)) return -1;
+  if (tensor_map(w, N, K, K, bn, &mb)) return -1;
+  mb2 = mb;
+  if (w2 && tensor_map(w2, N, K, K, bn, &mb2)) return -1;
+  const size_t esz = out_dtype == DT_F32 ? 4 : 2;
+  const int vec_ok = ((uintptr_t)out % 16 == 0) && ((size_t)ldo * esz % 16 == 0) &&
+                     (residual == nullptr || (uintptr_t)residual % 16 == 0);
+  int rc = 0;
+  if (epilogue == TC_EPI_STORE && out_dtype == DT_BF16)
+    rc = launch_tc<128, TC_EPI_STORE, __nv_bfloat16>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream);
+  else if (epilogue == TC_EPI_STORE && out_dtype == DT_F32)
+    rc = launch_tc<128, TC_EPI_STORE, float>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream);
+  else if (epilogue == TC_EPI_RESIDUAL)
+    rc = launch_tc<128, TC_EPI_RESIDUAL, float>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream);
+  else if (epilogue == TC_EPI_SWIGLU && out_dtype == DT_BF16)
+    rc = launch_tc<64, TC_EPI_SWIGLU, __nv_bfloat16>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream);
+  else
+    EL_REFUSE(false, "gemm_tc: unsupported epilogue %d with output dtype %d", epilogue, out_dtype);
+  if (rc) return rc;
+  EL_LAUNCH_CHECK("gemm_tc");
+  return 0;
+}

@@ -130,6 +130,28 @@ def gemm_simt(a, w, out, epilogue=EPI_STORE, w2=None, residual=None, force_kerne
                                   _dt(a), _dt(out), epilogue, force_kernel, _stream()))
 
 
+def gemm_tc_takes(a, w, out, w2=None):
+    """Whether the tensor-core kernel takes these operands: bfloat16, K a multiple of 8, 16-byte aligned rows."""
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or a.stride(1) != 1 or not w.is_contiguous():
+        return False
+    return bool(lib().edgelm_gemm_tc_takes(_p(a), a.stride(0), _p(w), _p(w2), a.shape[1]))
+
+
+def gemm_tc(a, w, out, err, epilogue=EPI_STORE, w2=None, residual=None):
+    """out = a @ w.T (+ epilogue) on the tcgen05 tensor cores: bfloat16 operands, float32 accumulation."""
+    _need(a.dim() == 2 and w.dim() == 2 and out.dim() == 2, "gemm_tc: 2-D operands")
+    M, K = a.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and out.shape == (M, N), f"gemm_tc: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    _need(a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "gemm_tc: bfloat16 operands")
+    _need(a.stride(1) == 1 and out.stride(1) == 1 and w.is_contiguous(), "gemm_tc: rows must be contiguous")
+    _need(w2 is None or (w2.dtype == w.dtype and w2.shape == w.shape and w2.is_contiguous()), "gemm_tc: second weight")
+    if residual is not None:
+        _need(residual.dtype == torch.float32 and residual.shape == out.shape and residual.stride() == out.stride(), "gemm_tc: residual layout")
+    _check(lib().edgelm_gemm_tc(_p(a), a.stride(0), _p(w), _p(w2), _p(out), out.stride(0), _p(residual), M, N, K, _dt(out),
+                                epilogue, _p(err), _stream()))
+
+
 def rope_kv_append(qkv, tok_pos, tok_seq, seq_slot, page_table, cos, sin, kcache, vcache, nh, nkv, hd, err):
     """Rotate q and k of the fused projection output in float32; write k and v into their pages."""
     T = qkv.shape[0]

@@ -58,7 +58,7 @@ class Attention(Part):
         with ws.frame():
             qkv = ws.alloc((T, (self.nh + 2 * self.nkv) * self.hd), self.dtype)
             with ctx.prof("qkv_proj"):
-                linear.matmul(h, self.w_qkv, qkv)
+                linear.matmul(ctx, h, self.w_qkv, qkv)
             with ctx.prof("rope_kv_append"):
                 self.positions.encode_and_append(ctx, qkv, cache, self.nh, self.nkv)
             a = ws.alloc((T, self.nh * self.hd), self.dtype)
@@ -78,4 +78,4 @@ class Attention(Part):
                     ops.attn_prefill(qkv, a, cache.k, cache.v, table, ctx.seq_index, tiles.seq, tiles.tok0, tiles.ntok,
                                      tiles.pos0, tiles.count, self.tile_tokens, self.nh, self.nkv, self.hd, self.scale)
             with ctx.prof("o_proj_residual"):
-                linear.matmul(a, self.w_o, x, epilogue=linear.EPI_RESIDUAL, residual=x)
+                linear.matmul(ctx, a, self.w_o, x, epilogue=linear.EPI_RESIDUAL, residual=x)

@@ -24,4 +24,4 @@ class LMHead(Part):
         self.weight = tied_table if self.tied_to else as_matrix(tensors[self.name], self.dtype, device)
 
     def forward(self, ctx, xn, logits):
-        linear.matmul(xn, self.weight, logits)
+        linear.matmul(ctx, xn, self.weight, logits)

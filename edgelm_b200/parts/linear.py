@@ -14,9 +14,9 @@ EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU = ops.EPI_STORE, ops.EPI_RESIDUAL, ops.EPI_S
 TENSOR_CORE_MIN_ROWS = 17  # fewer rows: one pass over the weights on the CUDA cores is bandwidth-bound already
 
 
-def matmul(a, w, out, epilogue=EPI_STORE, w2=None, residual=None):
-    if (a.dtype == torch.bfloat16 and a.shape[0] >= TENSOR_CORE_MIN_ROWS and hasattr(ops, "gemm_tc")
-            and ops.gemm_tc_takes(a, w, out)):
-        ops.gemm_tc(a, w, out, epilogue=epilogue, w2=w2, residual=residual)
+def matmul(ctx, a, w, out, epilogue=EPI_STORE, w2=None, residual=None):
+    """`ctx` gives the device error word that the tensor-core kernel's bounded waits report to."""
+    if a.dtype == torch.bfloat16 and a.shape[0] >= TENSOR_CORE_MIN_ROWS and ops.gemm_tc_takes(a, w, out, w2):
+        ops.gemm_tc(a, w, out, ctx.err, epilogue=epilogue, w2=w2, residual=residual)
     else:
         ops.gemm_simt(a, w, out, epilogue=epilogue, w2=w2, residual=residual)

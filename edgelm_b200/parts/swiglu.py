@@ -33,6 +33,6 @@ class SwiGLU(Part):
         with ctx.ws.frame():
             mid = ctx.ws.alloc((h.shape[0], self.inter), self.dtype)
             with ctx.prof("gate_up_swiglu"):
-                linear.matmul(h, self.w_gate, mid, epilogue=linear.EPI_SWIGLU, w2=self.w_up)
+                linear.matmul(ctx, h, self.w_gate, mid, epilogue=linear.EPI_SWIGLU, w2=self.w_up)
             with ctx.prof("down_proj_residual"):
-                linear.matmul(mid, self.w_down, x, epilogue=linear.EPI_RESIDUAL, residual=x)
+                linear.matmul(ctx, mid, self.w_down, x, epilogue=linear.EPI_RESIDUAL, residual=x)

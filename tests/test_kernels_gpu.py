@@ -353,3 +353,64 @@ def test_sample_topk_matches_plain(vocab, temp, k, seed):
         want = [s.sample(r) for s, r in zip(samplers, x.numpy())]
         assert out.tolist() == want, (step,)
     assert [v & plain.MASK64 for v in st.tolist()] == [s.state for s in samplers]
+
+
+# ----------------------------------------------------------------------------- GEMM (tcgen05 tensor cores)
+TC_SHAPES = [(128, 128, 64), (17, 64, 72), (129, 192, 576), (300, 100, 200), (256, 960, 576), (2048, 576, 1536),
+             (64, 397, 96), (130, 49, 8), (1000, 130, 136)]
+
+
+@pytest.mark.parametrize("M,N,K", TC_SHAPES)
+def test_gemm_tc_store_and_residual(M, N, K):
+    o = ops()
+    a = rnd((M, K), torch.bfloat16, 50)
+    w = rnd((N, K), torch.bfloat16, 51, 0.2)
+    err = torch.zeros(1, dtype=torch.int32, device=dev())
+    assert o.gemm_tc_takes(a, w, None)
+    want = a.double().cpu() @ w.double().cpu().T
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev())
+    o.gemm_tc(a, w, out, err)
+    assert int(err.item()) == 0
+    assert rel_err(out, want) < 1.6e-2
+    out32 = torch.full((M, N), float("nan"), dtype=torch.float32, device=dev())
+    o.gemm_tc(a, w, out32, err)
+    assert rel_err(out32, want) < 2e-5
+    res = rnd((M, N), torch.float32, 52)
+    res0 = res.clone()
+    o.gemm_tc(a, w, res, err, epilogue=o.EPI_RESIDUAL, residual=res)
+    assert rel_err(res, res0.double().cpu() + want) < 2e-5
+    assert int(err.item()) == 0
+    # the same numbers as the CUDA-core kernel up to the order of float32 sums
+    simt = torch.empty(M, N, dtype=torch.float32, device=dev())
+    o.gemm_simt(a, w, simt)
+    assert rel_err(out32, simt) < 2e-5
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 64, 64), (200, 200, 96), (2048, 1536, 576), (33, 130, 40)])
+def test_gemm_tc_swiglu(M, N, K):
+    o = ops()
+    a = rnd((M, K), torch.bfloat16, 53)
+    wg = rnd((N, K), torch.bfloat16, 54, 0.3)
+    wu = rnd((N, K), torch.bfloat16, 55, 0.3)
+    err = torch.zeros(1, dtype=torch.int32, device=dev())
+    g = a.double().cpu() @ wg.double().cpu().T
+    u = a.double().cpu() @ wu.double().cpu().T
+    want = g / (1 + torch.exp(-g)) * u
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev())
+    o.gemm_tc(a, wg, out, err, epilogue=o.EPI_SWIGLU, w2=wu)
+    assert int(err.item()) == 0
+    assert rel_err(out, want) < 1.6e-2
+
+
+def test_gemm_tc_strided_rows_and_refusals():
+    o = ops()
+    big = rnd((70, 3 * 64), torch.bfloat16, 56)
+    a = big[:, 64:128]  # row pitch 192, a view as the attention output's columns would be
+    w = rnd((40, 64), torch.bfloat16, 57)
+    err = torch.zeros(1, dtype=torch.int32, device=dev())
+    out = torch.zeros(70, 40, dtype=torch.float32, device=dev())
+    o.gemm_tc(a, w, out, err)
+    assert rel_err(out, a.double().cpu() @ w.double().cpu().T) < 2e-5
+    assert not o.gemm_tc_takes(rnd((4, 12), torch.bfloat16, 1), rnd((4, 12), torch.bfloat16, 2), None)  # K = 12: pitch of 24 bytes
+    with pytest.raises(o.KernelError, match="multiples of 8"):
+        o.gemm_tc(rnd((4, 12), torch.bfloat16, 1), rnd((4, 12), torch.bfloat16, 2), torch.zeros(4, 4, device=dev()), err)
