@@ -18,6 +18,8 @@
 //                 split, in a scratch buffer that attn_decode_combine folds in a fixed order.
 #include <math_constants.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace edgelm {
@@ -447,5 +449,68 @@ extern "C" int edgelm_attn_decode(const void* q, int ldq, void* out, int ldo, co
   EL_ATT_DISPATCH(launch_decode, q, ldq, out, ldo, kcache, vcache, page_table, table_stride, seq_slot, seq_pos, n_seqs, nh,
                   nkv, hd, scale, n_splits, part_o, part_ml, stream);
   EL_LAUNCH_CHECK("attn_decode");
+  return 0;
+}
+
+// ------------------------------------------------------------------------- no-allocation variant
+// See no_alloc.h for who this is for and for its rules.  The split partials live in this
+// file-scope device array instead of caller-provided buffers.  In host code the array's name is
+// only a handle; its device address comes from cudaGetSymbolAddress, looked up once per device
+// with that device current.
+#include "no_alloc.h"
+
+static __device__ __align__(256) float g_noalloc_scratch[EDGELM_NOALLOC_SCRATCH_FLOATS];
+
+namespace edgelm {
+constexpr int NOALLOC_MAX_DEVICES = 64;
+static float* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};
+static std::mutex g_noalloc_mu;
+
+// Device address of the scratch array on the current device (first call per device: set-up).
+static int noalloc_scratch(float** ptr) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) {
+    set_error("attn_decode_noalloc: cannot tell the current device (%s)", e == cudaSuccess ? "index out of range" : cudaGetErrorString(e));
+    return -2;
+  }
+  std::lock_guard<std::mutex> lock(g_noalloc_mu);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      set_error("attn_decode_noalloc: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+      return -2;
+    }
+    g_noalloc_ptr[dev] = static_cast<float*>(p);
+  }
+  *ptr = g_noalloc_ptr[dev];
+  return 0;
+}
+}  // namespace edgelm
+
+extern "C" int edgelm_attn_decode_noalloc(const void* q, int ldq, void* out, int ldo, const void* kcache,
+                                          const void* vcache, int dtype, const int32_t* page_table, int table_stride,
+                                          const int32_t* seq_slot, const int32_t* seq_pos, int n_seqs, int nh, int nkv,
+                                          int hd, float scale, int n_splits, cudaStream_t stream) {
+  if (n_seqs == 0) return 0;
+  if (check_heads("attn_decode_noalloc", nh, nkv, hd)) return -1;
+  EL_REFUSE(n_seqs > 0 && n_splits >= 1 && n_splits <= 65535 && nkv <= 65535, "attn_decode_noalloc: bad counts (%d sequences, %d splits)", n_seqs, n_splits);
+  float* part_o = nullptr;
+  float* part_ml = nullptr;
+  if (n_splits > 1) {
+    const long long cells = (long long)n_seqs * nh * n_splits;
+    const long long need = cells * (hd + 2);
+    EL_REFUSE(need <= (long long)EDGELM_NOALLOC_SCRATCH_FLOATS,
+              "attn_decode_noalloc: %d sequences x %d heads x %d splits x (%d + 2) = %lld floats of scratch; the built-in array holds %d",
+              n_seqs, nh, n_splits, hd, need, (int)EDGELM_NOALLOC_SCRATCH_FLOATS);
+    float* base = nullptr;
+    if (noalloc_scratch(&base)) return -2;
+    part_o = base;                 // [cells][hd]
+    part_ml = base + cells * hd;   // [cells][2]
+  }
+  EL_ATT_DISPATCH(launch_decode, q, ldq, out, ldo, kcache, vcache, page_table, table_stride, seq_slot, seq_pos, n_seqs, nh,
+                  nkv, hd, scale, n_splits, part_o, part_ml, stream);
+  EL_LAUNCH_CHECK("attn_decode_noalloc");
   return 0;
 }
