@@ -160,7 +160,7 @@ attn_prefill_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int l
   }
 }
 
-// ------------------------------------------------------------------------- decode
+// (KVec: 16-byte vector loads of a key row)
 template <typename T> struct KVec;
 template <> struct KVec<float> {
   static constexpr int N = 4;
@@ -182,25 +182,89 @@ template <> struct KVec<__nv_bfloat16> {
   }
 };
 
+// ------------------------------------------------------------------------- decode
+// One new token per sequence.  grid (sequence, kv head, split), 4 warps per block.  The pages of
+// the sequence that fall to this split are cut into tiles of `tk` keys (a tile of K and of V is
+// at most 8 KB); tiles are dealt to the block's warps.  For each tile a warp
+//   1. has one lane issue two bulk async copies (cp.async.bulk, completion on the warp's
+//      mbarrier) that bring the K rows and the V rows, contiguous in the page, into the warp's
+//      own shared memory, and waits for them (bounded);
+//   2. scores: a lane owns one or two keys and walks its key's 16-byte chunks in an order
+//      rotated by the key index, so that the lanes of a quarter-warp read different banks;
+//   3. softmax bookkeeping in float32 (running max, sum), probabilities to shared memory;
+//   4. values: a lane owns pairs of dims and walks the keys.
+// Other warps and blocks of the SM compute while a warp waits for its copy.  Partial results
+// meet in shared memory (warps, folded in the order 0..3) and, with more than one split, in the
+// scratch that attn_decode_combine_kernel folds in the order of the splits.
+constexpr int DEC_WARPS = 4;
+constexpr int DEC_TILE_BYTES = 8192;
+constexpr long long DEC_WAIT_CYCLES = 2000000000LL;
+
+__device__ __forceinline__ uint32_t dec_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ bool dec_mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+
+template <typename T> struct Pair;  // two neighbouring dims of a value row
+template <> struct Pair<float> {
+  static __device__ __forceinline__ float2 load(const float* p) { return *reinterpret_cast<const float2*>(p); }
+  static __device__ __forceinline__ void store(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+};
+template <> struct Pair<__nv_bfloat16> {
+  static __device__ __forceinline__ float2 load(const __nv_bfloat16* p) {
+    const uint32_t u = *reinterpret_cast<const uint32_t*>(p);
+    return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+  }
+};
+
 // Partial results of one split: part_o [seq][head][split][hd], part_ml [seq][head][split][2].
-template <typename T, int NC>
-__global__ void __launch_bounds__(ATT_WARPS * 32)
+template <typename T, int NP>  // NP = ceil(hd / 64): pairs of value dims a lane owns
+__global__ void __launch_bounds__(DEC_WARPS * 32)
 attn_decode_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ldo, const T* __restrict__ kcache,
                    const T* __restrict__ vcache, const int32_t* __restrict__ page_table, int table_stride,
                    const int32_t* __restrict__ seq_slot, const int32_t* __restrict__ seq_pos, int nh, int nkv, int hd,
-                   float scale, int n_splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
-  extern __shared__ float smem[];
-  float* Qs = smem;                        // [RW][hd]   the row chunk's queries
-  float* Ws = Qs + RW * hd;                // [ATT_WARPS][RW][hd + 2]   per-warp partials
+                   float scale, int n_splits, int tk, float* __restrict__ part_o, float* __restrict__ part_ml, int* err) {
+  constexpr int VEC = KVec<T>::N;
+  extern __shared__ __align__(128) uint8_t dec_smem[];
+  const int ws = hd + 2;
+  float* Qs = reinterpret_cast<float*>(dec_smem);                 // [RW][hd]
+  float* Ps = Qs + RW * hd;                                       // [DEC_WARPS][RW][64]
+  float* Wp = Ps + DEC_WARPS * RW * 64;                           // [DEC_WARPS][RW][hd + 2]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(Wp + DEC_WARPS * RW * ws);  // [DEC_WARPS]  (offset is a multiple of 8 bytes)
+  const size_t head_bytes = ((size_t)(RW * hd + DEC_WARPS * RW * 64 + DEC_WARPS * RW * ws) * 4 + DEC_WARPS * 8 + 127) / 128 * 128;
+  const int tile_elems = tk * hd;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  T* Kt = reinterpret_cast<T*>(dec_smem + head_bytes) + (size_t)warp * 2 * tile_elems;  // this warp's K tile, then its V tile
+  T* Vt = Kt + tile_elems;
+
   const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
   const int g = nh / nkv;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nkeys = seq_pos[seq] + 1;      // the new token's own key is the last one
   const int32_t* pages = page_table + (size_t)seq_slot[seq] * table_stride;
-  const int n_tiles = (nkeys + PAGE - 1) / PAGE;
-  const int per_split = (n_tiles + n_splits - 1) / n_splits;
-  const int t_begin = split * per_split, t_end = min(n_tiles, t_begin + per_split);
-  const int ws = hd + 2;
+  const int n_pages = (nkeys + PAGE - 1) / PAGE;
+  const int per_split = (n_pages + n_splits - 1) / n_splits;
+  const int p_begin = split * per_split, p_end = min(n_pages, p_begin + per_split);
+  const int tiles_per_page = PAGE / tk;
+  const int n_tiles = max(0, p_end - p_begin) * tiles_per_page;
+  const int cpr = hd / VEC;                // 16-byte chunks per key row
+  const uint32_t bar = dec_smem_u32(&bars[warp]);
+  if (lane == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(1));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  uint32_t phase = 0;
+  bool failed = false;
 
   for (int h0 = 0; h0 < g; h0 += RW) {     // chunks of RW query heads of this kv head
     const int rows = min(RW, g - h0);
@@ -210,71 +274,130 @@ attn_decode_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ld
       Qs[i] = to_f32(q[(size_t)seq * ldq + (kvh * g + h0 + r) * hd + d]);
     }
     __syncthreads();
-    float m[RW], l[RW], acc[RW][NC];
+    float m[RW], l[RW], acc[RW][NP][2];
 #pragma unroll
     for (int r = 0; r < RW; ++r) {
       m[r] = -CUDART_INF_F;
       l[r] = 0.f;
 #pragma unroll
-      for (int c = 0; c < NC; ++c) acc[r][c] = 0.f;
+      for (int c = 0; c < NP; ++c) acc[r][c][0] = acc[r][c][1] = 0.f;
     }
-    for (int kt = t_begin + warp; kt < t_end; kt += ATT_WARPS) {
-      const int page = pages[kt];
-      const T* kp = kcache + ((size_t)page * nkv + kvh) * PAGE * hd;
-      const T* vp = vcache + ((size_t)page * nkv + kvh) * PAGE * hd;
-      const int valid = min(PAGE, nkeys - kt * PAGE);
-      float s0[RW] = {}, s1[RW] = {};
-      const bool ok0 = lane < valid, ok1 = lane + 32 < valid;
-      for (int d = 0; d < hd; d += KVec<T>::N) {
-        float a[KVec<T>::N] = {}, b[KVec<T>::N] = {};
-        if (ok0) KVec<T>::load(kp + (size_t)lane * hd + d, a);
-        if (ok1) KVec<T>::load(kp + (size_t)(lane + 32) * hd + d, b);
-#pragma unroll
-        for (int v = 0; v < KVec<T>::N; ++v)
-#pragma unroll
-          for (int r = 0; r < RW; ++r) {
-            const float qv = Qs[r * hd + d + v];
-            s0[r] = fmaf(qv, a[v], s0[r]);
-            s1[r] = fmaf(qv, b[v], s1[r]);
-          }
+    for (int t = warp; t < n_tiles && !failed; t += DEC_WARPS) {
+      const int pg = p_begin + t / tiles_per_page, sub = t - (t / tiles_per_page) * tiles_per_page;
+      const int key0 = pg * PAGE + sub * tk;
+      if (key0 >= nkeys) break;            // later tiles of the last page hold no key (tiles ascend)
+      const int valid = min(tk, nkeys - key0);
+      const size_t src = (((size_t)pages[pg] * nkv + kvh) * PAGE + (size_t)sub * tk) * hd;
+      if (lane == 0) {
+        const uint32_t bytes = (uint32_t)(tile_elems * sizeof(T));
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // earlier reads of the buffers are done
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(2 * bytes) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(dec_smem_u32(Kt)), "l"(kcache + src), "r"(bytes), "r"(bar) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(dec_smem_u32(Vt)), "l"(vcache + src), "r"(bytes), "r"(bar) : "memory");
       }
-      float p0[RW], p1[RW];
+      {  // bounded wait for the two copies
+        const long long t0 = clock64();
+        bool done = dec_mbar_try(bar, phase);
+        while (!done) {
+          done = dec_mbar_try(bar, phase);
+          if (!done && clock64() - t0 > DEC_WAIT_CYCLES) break;
+        }
+        failed = !__all_sync(0xffffffffu, done);
+        if (failed) break;
+        phase ^= 1;
+      }
+      // scores
+      float s[2][RW];
+#pragma unroll
+      for (int kk2 = 0; kk2 < 2; ++kk2) {
+        const int kk = lane + 32 * kk2;
+#pragma unroll
+        for (int r = 0; r < RW; ++r) s[kk2][r] = 0.f;
+        if (kk < valid) {
+          const T* krow = Kt + (size_t)kk * hd;
+          for (int c = 0; c < cpr; ++c) {
+            int cc = c + kk;
+            cc -= (cc / cpr) * cpr;          // rotated chunk order: neighbouring keys start at different banks
+            float kf[VEC];
+            KVec<T>::load(krow + cc * VEC, kf);
+#pragma unroll
+            for (int r = 0; r < RW; ++r) {
+              if (r < rows) {
+                const float* qr = Qs + r * hd + cc * VEC;
+#pragma unroll
+                for (int v = 0; v < VEC; v += 4) {
+                  const float4 qv = *reinterpret_cast<const float4*>(qr + v);
+                  s[kk2][r] = fmaf(qv.x, kf[v], s[kk2][r]);
+                  s[kk2][r] = fmaf(qv.y, kf[v + 1], s[kk2][r]);
+                  s[kk2][r] = fmaf(qv.z, kf[v + 2], s[kk2][r]);
+                  s[kk2][r] = fmaf(qv.w, kf[v + 3], s[kk2][r]);
+                }
+              }
+            }
+          }
+        }
+      }
+      float* pw = Ps + warp * RW * 64;
 #pragma unroll
       for (int r = 0; r < RW; ++r) {
-        const float a = ok0 ? s0[r] * scale : -CUDART_INF_F;
-        const float b = ok1 ? s1[r] * scale : -CUDART_INF_F;
-        const float mx = fmaxf(m[r], warp_max(fmaxf(a, b)));  // finite: valid >= 1
-        const float corr = expf(m[r] - mx);
-        p0[r] = expf(a - mx);
-        p1[r] = expf(b - mx);
-        l[r] = l[r] * corr + warp_sum(p0[r] + p1[r]);
-        m[r] = mx;
+        if (r < rows) {
+          const float a = lane < valid ? s[0][r] * scale : -CUDART_INF_F;
+          const float b = lane + 32 < valid ? s[1][r] * scale : -CUDART_INF_F;
+          const float mx = fmaxf(m[r], warp_max(fmaxf(a, b)));  // finite: valid >= 1
+          const float corr = expf(m[r] - mx);
+          const float p0 = expf(a - mx), p1 = expf(b - mx);
+          l[r] = l[r] * corr + warp_sum(p0 + p1);
+          m[r] = mx;
+          pw[r * 64 + lane] = p0;
+          pw[r * 64 + lane + 32] = p1;
 #pragma unroll
-        for (int c = 0; c < NC; ++c) acc[r][c] *= corr;
+          for (int c = 0; c < NP; ++c) {
+            acc[r][c][0] *= corr;
+            acc[r][c][1] *= corr;
+          }
+        }
       }
+      __syncwarp();
+      // values
       for (int j = 0; j < valid; ++j) {
-        float v[NC];
+        float2 v[NP];
 #pragma unroll
-        for (int c = 0; c < NC; ++c) {
-          const int d = lane + 32 * c;
-          v[c] = d < hd ? to_f32(vp[(size_t)j * hd + d]) : 0.f;
+        for (int c = 0; c < NP; ++c) {
+          const int d = 2 * lane + 64 * c;
+          v[c] = d < hd ? Pair<T>::load(Vt + (size_t)j * hd + d) : make_float2(0.f, 0.f);
         }
 #pragma unroll
         for (int r = 0; r < RW; ++r) {
-          const float p = __shfl_sync(0xffffffffu, j < 32 ? p0[r] : p1[r], j & 31);
+          if (r < rows) {
+            const float p = pw[r * 64 + j];
 #pragma unroll
-          for (int c = 0; c < NC; ++c) acc[r][c] = fmaf(p, v[c], acc[r][c]);
+            for (int c = 0; c < NP; ++c) {
+              acc[r][c][0] = fmaf(p, v[c].x, acc[r][c][0]);
+              acc[r][c][1] = fmaf(p, v[c].y, acc[r][c][1]);
+            }
+          }
         }
       }
+      __syncwarp();
+    }
+    if (failed) {  // a copy did not arrive: report, and make the rows unmistakably wrong
+      if (lane == 0 && err) atomicOr(err, ERR_WAIT_TIMEOUT);
+#pragma unroll
+      for (int r = 0; r < RW; ++r) m[r] = l[r] = CUDART_NAN_F;
     }
     // warps -> shared memory
 #pragma unroll
     for (int r = 0; r < RW; ++r) {
-      float* w = Ws + (warp * RW + r) * ws;
+      float* w = Wp + (warp * RW + r) * ws;
 #pragma unroll
-      for (int c = 0; c < NC; ++c) {
-        const int d = lane + 32 * c;
-        if (d < hd) w[d] = acc[r][c];
+      for (int c = 0; c < NP; ++c) {
+        const int d = 2 * lane + 64 * c;
+        if (d < hd) {
+          w[d] = acc[r][c][0];
+          w[d + 1] = acc[r][c][1];
+        }
       }
       if (lane == 0) {
         w[hd] = m[r];
@@ -282,41 +405,54 @@ attn_decode_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ld
       }
     }
     __syncthreads();
-    // fold the warps in the order 0..7; warp r folds row r
+    // fold the warps in the order 0..3; warp r folds row r
     if (warp < rows) {
       const int r = warp;
       float M = -CUDART_INF_F;
-      for (int w = 0; w < ATT_WARPS; ++w) M = fmaxf(M, Ws[(w * RW + r) * ws + hd]);
-      float L = 0.f, o[NC];
+      for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, Wp[(w * RW + r) * ws + hd]);
+      if (M != M) M = CUDART_NAN_F;
+      float L = 0.f, o[NP][2];
 #pragma unroll
-      for (int c = 0; c < NC; ++c) o[c] = 0.f;
-      if (M != -CUDART_INF_F) {
-        for (int w = 0; w < ATT_WARPS; ++w) {
-          const float* p = Ws + (w * RW + r) * ws;
+      for (int c = 0; c < NP; ++c) o[c][0] = o[c][1] = 0.f;
+      bool bad = false;
+      for (int w = 0; w < DEC_WARPS; ++w) bad = bad || (Wp[(w * RW + r) * ws + hd] != Wp[(w * RW + r) * ws + hd]);
+      if (M != -CUDART_INF_F && !bad) {
+        for (int w = 0; w < DEC_WARPS; ++w) {
+          const float* p = Wp + (w * RW + r) * ws;
           if (p[hd] == -CUDART_INF_F) continue;
           const float f = expf(p[hd] - M);
           L = fmaf(p[hd + 1], f, L);
 #pragma unroll
-          for (int c = 0; c < NC; ++c) {
-            const int d = lane + 32 * c;
-            if (d < hd) o[c] = fmaf(p[d], f, o[c]);
+          for (int c = 0; c < NP; ++c) {
+            const int d = 2 * lane + 64 * c;
+            if (d < hd) {
+              o[c][0] = fmaf(p[d], f, o[c][0]);
+              o[c][1] = fmaf(p[d + 1], f, o[c][1]);
+            }
           }
         }
+      }
+      if (bad) {
+        M = 0.f;
+        L = CUDART_NAN_F;
       }
       const int head = kvh * g + h0 + r;
       if (n_splits == 1) {
         const float inv = 1.0f / L;
 #pragma unroll
-        for (int c = 0; c < NC; ++c) {
-          const int d = lane + 32 * c;
-          if (d < hd) out[(size_t)seq * ldo + head * hd + d] = from_f32<T>(o[c] * inv);
+        for (int c = 0; c < NP; ++c) {
+          const int d = 2 * lane + 64 * c;
+          if (d < hd) Pair<T>::store(out + (size_t)seq * ldo + head * hd + d, o[c][0] * inv, o[c][1] * inv);
         }
       } else {
         const size_t pi = ((size_t)seq * nh + head) * n_splits + split;
 #pragma unroll
-        for (int c = 0; c < NC; ++c) {
-          const int d = lane + 32 * c;
-          if (d < hd) part_o[pi * hd + d] = o[c];
+        for (int c = 0; c < NP; ++c) {
+          const int d = 2 * lane + 64 * c;
+          if (d < hd) {
+            part_o[pi * hd + d] = o[c][0];
+            part_o[pi * hd + d + 1] = o[c][1];
+          }
         }
         if (lane == 0) {
           part_ml[pi * 2] = M;
@@ -367,22 +503,35 @@ int launch_prefill(const void* q, int ldq, void* out, int ldo, const void* kc, c
   return 0;
 }
 
+// Device error word that decode attention reports a copy that never arrived to (may stay null:
+// the affected rows are then NaN, which no caller can overlook).
+static int* g_attn_err = nullptr;
+
+// Keys per tile: the largest power of two up to 64 whose K rows fit DEC_TILE_BYTES.
+static int decode_tile_keys(int hd, size_t elem) {
+  int tk = PAGE;
+  while (tk > 1 && (size_t)tk * hd * elem > (size_t)DEC_TILE_BYTES) tk >>= 1;
+  return tk;
+}
+
 template <typename T, int NC>
 int launch_decode(const void* q, int ldq, void* out, int ldo, const void* kc, const void* vc, const int32_t* page_table,
                   int table_stride, const int32_t* seq_slot, const int32_t* seq_pos, int n_seqs, int nh, int nkv, int hd,
                   float scale, int n_splits, float* part_o, float* part_ml, cudaStream_t stream) {
-  const size_t smem = sizeof(float) * ((size_t)RW * hd + (size_t)ATT_WARPS * RW * (hd + 2));
-  auto kern = attn_decode_kernel<T, NC>;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) {
-      set_error("attn_decode: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
-      return -2;
-    }
+  constexpr int NP = NC <= 2 ? 1 : NC / 2;  // pairs of dims per lane: ceil(hd / 64)
+  const int tk = decode_tile_keys(hd, sizeof(T));
+  const size_t head = ((size_t)(RW * hd + DEC_WARPS * RW * 64 + DEC_WARPS * RW * (hd + 2)) * 4 + DEC_WARPS * 8 + 127) / 128 * 128;
+  const size_t smem = head + (size_t)DEC_WARPS * 2 * tk * hd * sizeof(T);
+  auto kern = attn_decode_kernel<T, NP>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) {
+    set_error("attn_decode: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+    return -2;
   }
   dim3 grid(n_seqs, nkv, n_splits);
-  kern<<<grid, ATT_WARPS * 32, smem, stream>>>((const T*)q, ldq, (T*)out, ldo, (const T*)kc, (const T*)vc, page_table,
-                                              table_stride, seq_slot, seq_pos, nh, nkv, hd, scale, n_splits, part_o, part_ml);
+  kern<<<grid, DEC_WARPS * 32, smem, stream>>>((const T*)q, ldq, (T*)out, ldo, (const T*)kc, (const T*)vc, page_table,
+                                              table_stride, seq_slot, seq_pos, nh, nkv, hd, scale, n_splits, tk, part_o,
+                                              part_ml, g_attn_err);
   if (n_splits > 1) {
     dim3 cgrid(n_seqs, nh);
     attn_decode_combine_kernel<T><<<cgrid, 64, 0, stream>>>(part_o, part_ml, (T*)out, ldo, nh, hd, n_splits);
@@ -434,6 +583,12 @@ extern "C" int edgelm_attn_prefill(const void* q, int ldq, void* out, int ldo, c
   EL_ATT_DISPATCH(launch_prefill, q, ldq, out, ldo, kcache, vcache, page_table, table_stride, seq_slot, tile_seq, tile_tok0,
                   tile_ntok, tile_pos0, n_tiles, max_tile_tokens, nh, nkv, hd, scale, stream);
   EL_LAUNCH_CHECK("attn_prefill");
+  return 0;
+}
+
+// The device error word (one int32) that decode attention ORs ERR_WAIT_TIMEOUT into; null: none.
+extern "C" int edgelm_attn_set_error_word(int* err) {
+  g_attn_err = err;
   return 0;
 }
 

@@ -1,0 +1,262 @@
+// Few-rows bfloat16 matrix products for decoding on the tensor cores:
+// out[M, N] = act[M, K] . W[N, K]^T for M <= 16, float32 accumulation.
+//
+// With a handful of rows the work is reading W once; what the CUDA-core kernel (gemv.cu) adds on
+// top, eight multiply-adds and eight shared-memory reads per weight and row, is what limits it
+// from 4 rows up.  Here the weights are the 16-row operand of mma.sync.m16n8k16 and the batch is
+// its 8 columns, so the arithmetic disappears behind the loads:
+//   * a block owns 16 output columns (16 rows of W); its 4 warps take the 32-wide K blocks in turn
+//     and their partial 16 x 8 tiles are added in shared memory at the end (fixed order 0..3);
+//   * a lane loads 16 bytes (8 consecutive k) of two weight rows per K block straight from global
+//     memory and uses them as the A fragments of two MMAs; the K index inside a block is permuted
+//     (the same permutation on both operands leaves the sum unchanged) so that those 16 bytes are
+//     exactly the lane's fragment: no shuffles, no staging of W;
+//   * the activations of all rows sit in shared memory (pitch chosen so that the fragment reads
+//     hit distinct banks), optionally produced here as RMSNorm(x) from the float32 residual
+//     stream, rounded to bfloat16 as the stand-alone norm kernel rounds;
+//   * epilogues: store (bfloat16 or float32), += residual (float32), SwiGLU of two weights.
+// K must be a multiple of 8 with 16-byte aligned rows; M <= 16.
+#include "common.cuh"
+
+namespace edgelm {
+
+enum : int { GM_STORE = 0, GM_RESIDUAL = 1, GM_SWIGLU = 2 };
+constexpr int GM_WARPS = 4;
+constexpr int GM_COLS = 16;  // output columns per block
+
+__device__ __forceinline__ void mma_bf16_16x8x16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                                 uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ float gm_silu(float z) { return z / (1.0f + expf(-z)); }
+
+// NT: 8-row tiles of the batch (1: M <= 8, 2: M <= 16).  NORM: activations = RMSNorm(x).
+template <int EPI, typename TOut, int NT, bool NORM>
+__global__ void __launch_bounds__(GM_WARPS * 32)
+gemv_mma_kernel(const __nv_bfloat16* __restrict__ act, int lda, const float* __restrict__ x,
+                const float* __restrict__ norm_w, float eps, const __nv_bfloat16* __restrict__ W,
+                const __nv_bfloat16* __restrict__ W2, TOut* out, int ldo, const float* residual, int M, int N, int K,
+                int pitch /* bfloat16 elements per activation row in shared memory */) {
+  constexpr int NW = EPI == GM_SWIGLU ? 2 : 1;
+  constexpr int ROWS = 8 * NT;
+  extern __shared__ __align__(16) uint8_t gm_smem[];
+  __nv_bfloat16* As = reinterpret_cast<__nv_bfloat16*>(gm_smem);                       // [ROWS][pitch]
+  float* red = reinterpret_cast<float*>(gm_smem + (size_t)ROWS * pitch * 2);           // [GM_WARPS][NW][NT][32][4]
+  float* inv = red + GM_WARPS * NW * NT * 128;                                         // [ROWS]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int gid = lane >> 2, tig = lane & 3;
+  const int n0 = blockIdx.x * GM_COLS;
+  const int ra = min(n0 + gid, N - 1), rb = min(n0 + gid + 8, N - 1);  // the two weight rows of this lane (clamped)
+  const int n_kb = (K + 31) / 32;
+
+  // this warp's first K block of weights: on its way while the activations are staged
+  uint4 pa[NW], pb[NW];
+  {
+    const int k = warp * 32 + tig * 8;
+    const bool ok = warp < n_kb && k < K;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) {
+      const __nv_bfloat16* Wp = w == 0 ? W : W2;
+      pa[w] = ok ? *reinterpret_cast<const uint4*>(Wp + (size_t)ra * K + k) : make_uint4(0, 0, 0, 0);
+      pb[w] = ok ? *reinterpret_cast<const uint4*>(Wp + (size_t)rb * K + k) : make_uint4(0, 0, 0, 0);
+    }
+  }
+
+  // ---- activations into shared memory (rows >= M are zero)
+  if (NORM) {
+    for (int r = warp; r < ROWS; r += GM_WARPS) {
+      float ss = 0.f;
+      if (r < M) {
+        const float* xr = x + (size_t)r * K;
+        for (int k = lane * 4; k < K; k += 128) {
+          const float4 v = *reinterpret_cast<const float4*>(xr + k);
+          ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        }
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) inv[r] = 1.0f / sqrtf(ss / (float)K + eps);
+    }
+    __syncthreads();
+  }
+  const int kvec = K / 8;
+  for (int i = threadIdx.x; i < ROWS * kvec; i += blockDim.x) {
+    const int r = i / kvec, k = (i - r * kvec) * 8;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < M) {
+      if (NORM) {
+        const float s = inv[r];
+        const float4 x0 = *reinterpret_cast<const float4*>(x + (size_t)r * K + k);
+        const float4 x1 = *reinterpret_cast<const float4*>(x + (size_t)r * K + k + 4);
+        const float4 w0 = *reinterpret_cast<const float4*>(norm_w + k);
+        const float4 w1 = *reinterpret_cast<const float4*>(norm_w + k + 4);
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(x0.x * s * w0.x, x0.y * s * w0.y);
+        __nv_bfloat162 h1 = __floats2bfloat162_rn(x0.z * s * w0.z, x0.w * s * w0.w);
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(x1.x * s * w1.x, x1.y * s * w1.y);
+        __nv_bfloat162 h3 = __floats2bfloat162_rn(x1.z * s * w1.z, x1.w * s * w1.w);
+        v.x = *reinterpret_cast<uint32_t*>(&h0);
+        v.y = *reinterpret_cast<uint32_t*>(&h1);
+        v.z = *reinterpret_cast<uint32_t*>(&h2);
+        v.w = *reinterpret_cast<uint32_t*>(&h3);
+      } else {
+        v = *reinterpret_cast<const uint4*>(act + (size_t)r * lda + k);
+      }
+    }
+    *reinterpret_cast<uint4*>(As + (size_t)r * pitch + k) = v;
+  }
+  __syncthreads();
+
+  float acc[NW][NT][4];
+#pragma unroll
+  for (int w = 0; w < NW; ++w)
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[w][t][j] = 0.f;
+
+  constexpr int UN = 4;  // K blocks whose weight loads are in flight together
+  for (int kb0 = warp; kb0 < n_kb; kb0 += GM_WARPS * UN) {
+    uint4 wa[UN][NW], wb[UN][NW];
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const int kb = kb0 + u * GM_WARPS;
+      const int k = kb * 32 + tig * 8;
+      const bool ok = kb < n_kb && k < K;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) {
+        if (u == 0 && kb0 == warp) {
+          wa[u][w] = pa[w];
+          wb[u][w] = pb[w];
+        } else {
+          const __nv_bfloat16* Wp = w == 0 ? W : W2;
+          wa[u][w] = ok ? *reinterpret_cast<const uint4*>(Wp + (size_t)ra * K + k) : make_uint4(0, 0, 0, 0);
+          wb[u][w] = ok ? *reinterpret_cast<const uint4*>(Wp + (size_t)rb * K + k) : make_uint4(0, 0, 0, 0);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const int kb = kb0 + u * GM_WARPS;
+      const int k = kb * 32 + tig * 8;
+      const bool ok = kb < n_kb && k < K;
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        const uint4 av = ok ? *reinterpret_cast<const uint4*>(As + (size_t)(t * 8 + gid) * pitch + k) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+          mma_bf16_16x8x16(acc[w][t], wa[u][w].x, wb[u][w].x, wa[u][w].y, wb[u][w].y, av.x, av.y);
+          mma_bf16_16x8x16(acc[w][t], wa[u][w].z, wb[u][w].z, wa[u][w].w, wb[u][w].w, av.z, av.w);
+        }
+      }
+    }
+  }
+
+  // ---- add the warps' partial tiles (order 0..3), then the epilogue by warp 0
+  float* mine = red + (size_t)warp * NW * NT * 128;
+#pragma unroll
+  for (int w = 0; w < NW; ++w)
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+      *reinterpret_cast<float4*>(mine + ((w * NT + t) * 32 + lane) * 4) = make_float4(acc[w][t][0], acc[w][t][1], acc[w][t][2], acc[w][t][3]);
+  __syncthreads();
+  if (warp != 0) return;
+#pragma unroll
+  for (int t = 0; t < NT; ++t) {
+    float s[NW][4];
+#pragma unroll
+    for (int w = 0; w < NW; ++w) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s[w][j] = 0.f;
+      for (int ww = 0; ww < GM_WARPS; ++ww) {
+        const float4 p = *reinterpret_cast<const float4*>(red + (((size_t)ww * NW + w) * NT + t) * 128 + lane * 4);
+        s[w][0] += p.x; s[w][1] += p.y; s[w][2] += p.z; s[w][3] += p.w;
+      }
+    }
+    // fragment layout: s[.][0], s[.][1]: column n0 + gid, batch rows 2 tig, 2 tig + 1; s[.][2], s[.][3]: column n0 + gid + 8
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + gid + (j >> 1) * 8;
+      const int m = t * 8 + tig * 2 + (j & 1);
+      if (n < N && m < M) {
+        const size_t idx = (size_t)m * ldo + n;
+        if (EPI == GM_STORE) out[idx] = from_f32<TOut>(s[0][j]);
+        if (EPI == GM_RESIDUAL) out[idx] = from_f32<TOut>(residual[idx] + s[0][j]);
+        if (EPI == GM_SWIGLU) out[idx] = from_f32<TOut>(gm_silu(s[0][j]) * s[NW - 1][j]);
+      }
+    }
+  }
+}
+
+// Activation row pitch in shared memory: K rounded up so that pitch * 2 bytes = 64 (mod 128); then
+// the fragment reads of a quarter-warp (two rows, four 16-byte chunks each) hit distinct banks.
+static int act_pitch(int K) {
+  int p = (K + 7) / 8 * 8;
+  while ((p * 2) % 128 != 64) p += 8;
+  return p;
+}
+
+template <int EPI, typename TOut, int NT, bool NORM>
+static int launch_gemv_mma(const void* act, int lda, const float* x, const float* norm_w, float eps, const void* W,
+                           const void* W2, void* out, int ldo, const float* residual, int M, int N, int K,
+                           cudaStream_t stream) {
+  constexpr int NW = EPI == GM_SWIGLU ? 2 : 1;
+  const int pitch = act_pitch(K);
+  const size_t smem = (size_t)8 * NT * pitch * 2 + (size_t)GM_WARPS * NW * NT * 128 * 4 + 8 * NT * 4;
+  auto kern = gemv_mma_kernel<EPI, TOut, NT, NORM>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) {
+      set_error("gemv_mma: %zu bytes of shared memory refused (K = %d): %s", smem, K, cudaGetErrorString(e));
+      return -2;
+    }
+  }
+  kern<<<(N + GM_COLS - 1) / GM_COLS, GM_WARPS * 32, smem, stream>>>((const __nv_bfloat16*)act, lda, x, norm_w, eps,
+                                                                    (const __nv_bfloat16*)W, (const __nv_bfloat16*)W2,
+                                                                    (TOut*)out, ldo, residual, M, N, K, pitch);
+  return 0;
+}
+
+}  // namespace edgelm
+
+using namespace edgelm;
+
+// 1 if the kernel takes these operands, else 0: bfloat16, M <= 16, K a multiple of 8 (and small enough
+// for all rows to sit in shared memory), 16-byte aligned rows.
+extern "C" int edgelm_gemv_mma_takes(const void* act, int lda, const void* w, const void* w2, int M, int K, int normed) {
+  bool ok = M >= 1 && M <= 16 && K > 0 && K % 8 == 0 && K <= 6144 && (uintptr_t)w % 16 == 0 &&
+            (w2 == nullptr || (uintptr_t)w2 % 16 == 0) && (uintptr_t)act % 16 == 0;
+  if (!normed) ok = ok && lda % 8 == 0;
+  return ok ? 1 : 0;
+}
+
+extern "C" int edgelm_gemv_mma(const void* act, int lda, const float* norm_w, float eps, const void* w, const void* w2,
+                               void* out, int ldo, const float* residual, int M, int N, int K, int out_dtype, int epilogue,
+                               cudaStream_t stream) {
+  if (M == 0) return 0;
+  const bool normed = norm_w != nullptr;
+  EL_REFUSE(N > 0 && ldo >= N && (normed || lda >= K), "gemv_mma: bad sizes M=%d N=%d K=%d lda=%d ldo=%d", M, N, K, lda, ldo);
+  EL_REFUSE(edgelm_gemv_mma_takes(act, lda, w, w2, M, K, normed ? 1 : 0), "gemv_mma: takes M <= 16, K a multiple of 8 up to 6144, 16-byte aligned rows (M=%d K=%d)", M, K);
+  EL_REFUSE(epilogue != GM_SWIGLU || w2 != nullptr, "gemv_mma: SwiGLU needs the second weight");
+  EL_REFUSE(epilogue != GM_RESIDUAL || (residual != nullptr && out_dtype == DT_F32), "gemv_mma: residual epilogue needs a float32 residual and output");
+  const float* x = normed ? (const float*)act : nullptr;
+  int rc = 0;
+#define EL_GM(EPI, TOUT)                                                                                                 \
+  do {                                                                                                                   \
+    if (M <= 8) rc = normed ? launch_gemv_mma<EPI, TOUT, 1, true>(nullptr, 0, x, norm_w, eps, w, w2, out, ldo, residual, M, N, K, stream)  \
+                            : launch_gemv_mma<EPI, TOUT, 1, false>(act, lda, nullptr, nullptr, 0.f, w, w2, out, ldo, residual, M, N, K, stream); \
+    else rc = normed ? launch_gemv_mma<EPI, TOUT, 2, true>(nullptr, 0, x, norm_w, eps, w, w2, out, ldo, residual, M, N, K, stream)         \
+                     : launch_gemv_mma<EPI, TOUT, 2, false>(act, lda, nullptr, nullptr, 0.f, w, w2, out, ldo, residual, M, N, K, stream);  \
+  } while (0)
+  if (epilogue == GM_STORE && out_dtype == DT_BF16) EL_GM(GM_STORE, __nv_bfloat16);
+  else if (epilogue == GM_STORE && out_dtype == DT_F32) EL_GM(GM_STORE, float);
+  else if (epilogue == GM_RESIDUAL) EL_GM(GM_RESIDUAL, float);
+  else if (epilogue == GM_SWIGLU && out_dtype == DT_BF16) EL_GM(GM_SWIGLU, __nv_bfloat16);
+  else EL_REFUSE(false, "gemv_mma: unsupported epilogue %d with output dtype %d", epilogue, out_dtype);
+#undef EL_GM
+  if (rc) return rc;
+  EL_LAUNCH_CHECK("gemv_mma");
+  return 0;
+}

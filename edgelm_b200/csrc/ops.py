@@ -130,6 +130,66 @@ def gemm_simt(a, w, out, epilogue=EPI_STORE, w2=None, residual=None, force_kerne
                                   _dt(a), _dt(out), epilogue, force_kernel, _stream()))
 
 
+def gemv_takes(a, w, w2=None, normed=False):
+    """Whether the vector few-rows kernel takes these operands (K a multiple of a 16-byte vector, aligned rows).
+    With `normed`, `a` is the float32 residual stream and the weights give the compute dtype."""
+    if not w.is_contiguous() or a.stride(1) != 1:
+        return False
+    if normed and (a.dtype != torch.float32 or not a.is_contiguous()):
+        return False
+    if not normed and a.dtype != w.dtype:
+        return False
+    return bool(lib().edgelm_gemv_takes(_p(a), a.stride(0), _p(w), _p(w2), a.shape[1], _dt(w), 1 if normed else 0))
+
+
+def gemv(a, w, out, epilogue=EPI_STORE, w2=None, residual=None, norm_weight=None, eps=0.0, n_sms=0):
+    """out = act @ w.T (+ epilogue) for a few rows.  act = a, or RMSNorm(a) * norm_weight rounded to
+    w's dtype when norm_weight is given (a is then the float32 residual stream)."""
+    M, K = a.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and out.shape == (M, N), f"gemv: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    _need(out.stride(1) == 1 and w.is_contiguous(), "gemv: rows must be contiguous")
+    _need(w2 is None or (w2.dtype == w.dtype and w2.shape == w.shape and w2.is_contiguous()), "gemv: second weight")
+    if norm_weight is not None:
+        _need(a.dtype == torch.float32 and a.is_contiguous() and norm_weight.dtype == torch.float32 and norm_weight.numel() == K, "gemv: norm operands")
+    else:
+        _need(a.dtype == w.dtype and a.stride(1) == 1, "gemv: activation dtype")
+    if residual is not None:
+        _need(residual.dtype == torch.float32 and residual.shape == out.shape and residual.stride() == out.stride(), "gemv: residual layout")
+    _check(lib().edgelm_gemv(_p(a), a.stride(0), _p(norm_weight), ctypes.c_float(eps), _p(w), _p(w2), _p(out), out.stride(0),
+                             _p(residual), M, N, K, _dt(w), _dt(out), epilogue, int(n_sms), _stream()))
+
+
+def gemv_mma_takes(a, w, w2=None, normed=False):
+    """Whether the tensor-core few-rows kernel takes these operands: bfloat16 weights, at most 16 rows,
+    K a multiple of 8 up to 6144, aligned rows.  With `normed`, `a` is the float32 residual stream."""
+    if w.dtype != torch.bfloat16 or not w.is_contiguous() or a.stride(1) != 1:
+        return False
+    if normed and (a.dtype != torch.float32 or not a.is_contiguous()):
+        return False
+    if not normed and a.dtype != torch.bfloat16:
+        return False
+    return bool(lib().edgelm_gemv_mma_takes(_p(a), a.stride(0), _p(w), _p(w2), a.shape[0], a.shape[1], 1 if normed else 0))
+
+
+def gemv_mma(a, w, out, epilogue=EPI_STORE, w2=None, residual=None, norm_weight=None, eps=0.0):
+    """out = act @ w.T (+ epilogue) for at most 16 rows on mma.sync tensor cores; act = a, or
+    RMSNorm(a) * norm_weight rounded to bfloat16 when norm_weight is given."""
+    M, K = a.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and out.shape == (M, N), f"gemv_mma: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    _need(out.stride(1) == 1 and w.is_contiguous() and w.dtype == torch.bfloat16, "gemv_mma: weight layout")
+    _need(w2 is None or (w2.dtype == w.dtype and w2.shape == w.shape and w2.is_contiguous()), "gemv_mma: second weight")
+    if norm_weight is not None:
+        _need(a.dtype == torch.float32 and a.is_contiguous() and norm_weight.dtype == torch.float32 and norm_weight.numel() == K, "gemv_mma: norm operands")
+    else:
+        _need(a.dtype == torch.bfloat16 and a.stride(1) == 1, "gemv_mma: activation dtype")
+    if residual is not None:
+        _need(residual.dtype == torch.float32 and residual.shape == out.shape and residual.stride() == out.stride(), "gemv_mma: residual layout")
+    _check(lib().edgelm_gemv_mma(_p(a), a.stride(0), _p(norm_weight), ctypes.c_float(eps), _p(w), _p(w2), _p(out), out.stride(0),
+                                 _p(residual), M, N, K, _dt(out), epilogue, _stream()))
+
+
 def gemm_tc_takes(a, w, out, w2=None):
     """Whether the tensor-core kernel takes these operands: bfloat16, K a multiple of 8, 16-byte aligned rows."""
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or a.stride(1) != 1 or not w.is_contiguous():
@@ -193,6 +253,11 @@ def attn_decode(qkv, out, kcache, vcache, page_table, seq_slot, seq_pos, n_seqs,
                                     _p(page_table), page_table.stride(0), _p(seq_slot), _p(seq_pos), n_seqs, nh, nkv, hd,
                                     ctypes.c_float(scale), n_splits, _p(part_o), _p(part_ml), _stream()),
            launches=2 if n_splits > 1 else 1)
+
+
+def attn_set_error_word(err):
+    """The device int32 that decode attention reports a copy that never arrived to (bit 8)."""
+    _check(lib().edgelm_attn_set_error_word(_p(err)), launches=0)
 
 
 def argmax_rows(logits, out):

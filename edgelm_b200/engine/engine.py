@@ -72,6 +72,7 @@ class Engine:
         ws_bytes = model.workspace_bytes(self.max_step_tokens, self.max_step_seqs, self.max_step_tokens)
         self.ws = Workspace(ws_bytes, self.device)
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        ops.attn_set_error_word(self.err)
         self.buffers = BatchBuffers(self.max_step_tokens, self.max_step_seqs, self.cache.kv_groups, self.max_step_tokens,
                                     self.device)
         self.profiler = Profiler() if profile else None

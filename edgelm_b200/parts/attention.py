@@ -17,6 +17,8 @@ from .registry import register_mixer
 
 @register_mixer("attention")
 class Attention(Part):
+    takes_normed_input = True
+
     def __init__(self, spec, env):
         self.hidden = spec["hidden_size"]
         self.nh, self.nkv, self.hd = spec["num_heads"], spec["num_kv_heads"], spec["head_dim"]
@@ -43,39 +45,38 @@ class Attention(Part):
     def cache_need(self):
         return KVNeed(self.nkv, self.hd)
 
-    def _splits(self, ctx):
-        return ctx.decode_splits(self.nkv)
-
     def workspace_bytes(self, n_tokens, n_seqs):
         qkv = nbytes((n_tokens, (self.nh + 2 * self.nkv) * self.hd), self.dtype)
         out = nbytes((n_tokens, self.nh * self.hd), self.dtype)
-        part = nbytes((n_seqs * self.nh * 64 * (self.hd + 2),), torch.float32)  # split partials, at most 64 splits
-        return qkv + out + 2 * part
+        h = nbytes((n_tokens, self.hidden), self.dtype)  # the normalised input, when it is written out
+        # split partials of decoding: sequences x heads x splits cells, and splits <= 2 SMs / (sequences x kv heads) + 1
+        cells = self.group * (2 * 256 + n_seqs * self.nkv)
+        part = nbytes((cells * self.hd,), torch.float32) + nbytes((cells * 2,), torch.float32)
+        return qkv + out + h + part
 
     def forward(self, ctx, h, x, cache):
         T = h.shape[0]
         ws = ctx.ws
-        with ws.frame():
-            qkv = ws.alloc((T, (self.nh + 2 * self.nkv) * self.hd), self.dtype)
-            with ctx.prof("qkv_proj"):
-                linear.matmul(ctx, h, self.w_qkv, qkv)
-            with ctx.prof("rope_kv_append"):
-                self.positions.encode_and_append(ctx, qkv, cache, self.nh, self.nkv)
-            a = ws.alloc((T, self.nh * self.hd), self.dtype)
-            table = ctx.page_table(cache.group)
-            if ctx.all_single:
-                splits = self._splits(ctx)
-                part_o = part_ml = None
-                if splits > 1:
-                    part_o = ws.alloc((ctx.n_seqs * self.nh * splits * self.hd,), torch.float32)
-                    part_ml = ws.alloc((ctx.n_seqs * self.nh * splits * 2,), torch.float32)
-                with ctx.prof("attn_decode"):
-                    ops.attn_decode(qkv, a, cache.k, cache.v, table, ctx.seq_index, ctx.seq_pos, ctx.n_seqs, self.nh, self.nkv,
-                                    self.hd, self.scale, splits, part_o, part_ml)
-            else:
-                tiles = ctx.tiles(self.tile_tokens)
-                with ctx.prof("attn_prefill"):
-                    ops.attn_prefill(qkv, a, cache.k, cache.v, table, ctx.seq_index, tiles.seq, tiles.tok0, tiles.ntok,
-                                     tiles.pos0, tiles.count, self.tile_tokens, self.nh, self.nkv, self.hd, self.scale)
-            with ctx.prof("o_proj_residual"):
-                linear.matmul(ctx, a, self.w_o, x, epilogue=linear.EPI_RESIDUAL, residual=x)
+        qkv = ws.alloc((T, (self.nh + 2 * self.nkv) * self.hd), self.dtype)
+        with ctx.prof("qkv_proj"):
+            linear.matmul(ctx, h, self.w_qkv, qkv)
+        with ctx.prof("rope_kv_append"):
+            self.positions.encode_and_append(ctx, qkv, cache, self.nh, self.nkv)
+        a = ws.alloc((T, self.nh * self.hd), self.dtype)
+        table = ctx.page_table(cache.group)
+        if ctx.all_single:
+            splits = ctx.decode_splits(self.nkv)
+            part_o = part_ml = None
+            if splits > 1:
+                part_o = ws.alloc((ctx.n_seqs * self.nh * splits * self.hd,), torch.float32)
+                part_ml = ws.alloc((ctx.n_seqs * self.nh * splits * 2,), torch.float32)
+            with ctx.prof("attn_decode"):
+                ops.attn_decode(qkv, a, cache.k, cache.v, table, ctx.seq_index, ctx.seq_pos, ctx.n_seqs, self.nh, self.nkv,
+                                self.hd, self.scale, splits, part_o, part_ml)
+        else:
+            tiles = ctx.tiles(self.tile_tokens)
+            with ctx.prof("attn_prefill"):
+                ops.attn_prefill(qkv, a, cache.k, cache.v, table, ctx.seq_index, tiles.seq, tiles.tok0, tiles.ntok,
+                                 tiles.pos0, tiles.count, self.tile_tokens, self.nh, self.nkv, self.hd, self.scale)
+        with ctx.prof("o_proj_residual"):
+            linear.matmul(ctx, a, self.w_o, x, epilogue=linear.EPI_RESIDUAL, residual=x)

@@ -1,5 +1,6 @@
 """Arrangement of one layer's parts.  "prenorm": x += mixer(norm1(x)); x += ffn(norm2(x))
 (adarsh-sgh/edgelm tools/elm.py:122-153)."""
+from . import linear
 from .base import Part, nbytes
 from .registry import register_block
 
@@ -33,12 +34,18 @@ class PreNormBlock(Part):
         return nbytes((n_tokens, self.hidden), self.dtype) + max(self.mixer.workspace_bytes(n_tokens, n_seqs),
                                                                   self.ffn.workspace_bytes(n_tokens, n_seqs))
 
+    def _normed(self, ctx, x, norm, part):
+        """The part's input: lazily normalised if both the norm and the part can work that way
+        (the part's first matrix product then computes the norm itself when the step is small)."""
+        if getattr(part, "takes_normed_input", False) and getattr(norm, "fusable", False):
+            return linear.NormedInput(ctx, x, norm, self.dtype)
+        h = ctx.ws.alloc((x.shape[0], self.hidden), self.dtype)
+        with ctx.prof("norm"):
+            norm.forward(ctx, x, h)
+        return h
+
     def forward(self, ctx, x, cache):
         with ctx.ws.frame():
-            h = ctx.ws.alloc((x.shape[0], self.hidden), self.dtype)
-            with ctx.prof("mixer_norm"):
-                self.mixer_norm.forward(ctx, x, h)
-            self.mixer.forward(ctx, h, x, cache)
-            with ctx.prof("ffn_norm"):
-                self.ffn_norm.forward(ctx, x, h)
-            self.ffn.forward(ctx, h, x)
+            self.mixer.forward(ctx, self._normed(ctx, x, self.mixer_norm, self.mixer), x, cache)
+        with ctx.ws.frame():
+            self.ffn.forward(ctx, self._normed(ctx, x, self.ffn_norm, self.ffn), x)

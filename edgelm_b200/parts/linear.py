@@ -1,9 +1,12 @@
 """out = a . W^T with an epilogue, on the kernel that fits the sizes.
 
-bfloat16 with enough rows goes to the tcgen05 tensor-core kernel (operands by TMA, accumulator
-in tensor memory); everything else, and the whole float32 path, to the CUDA-core kernels.
-Both take any M, N; the tensor-core kernel needs K to be a multiple of 8 (a TMA row pitch of
-16 bytes) and falls back, not fails, when it is not.
+  rows <= 16        the few-rows kernels: weights streamed once, activations in shared memory, the
+                    preceding RMSNorm computed in the prologue (`NormedInput`).  bfloat16 runs
+                    on mma.sync tensor cores (gemv_mma.cu), float32 on the CUDA cores (gemv.cu);
+  bfloat16, more    the tcgen05 tensor-core kernel (gemm_tc.cu): operands by TMA, accumulator in
+                    tensor memory;
+  anything else     the CUDA-core kernels of gemm_simt.cu: the whole float32 path for many rows,
+                    and every size the other two do not take (K not a multiple of 8, unaligned rows).
 """
 import torch
 
@@ -11,12 +14,56 @@ from ..csrc import ops
 
 EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU = ops.EPI_STORE, ops.EPI_RESIDUAL, ops.EPI_SWIGLU
 
-TENSOR_CORE_MIN_ROWS = 17  # fewer rows: one pass over the weights on the CUDA cores is bandwidth-bound already
+FEW_ROWS = 16  # up to here one pass over the weights with all rows in shared memory is bandwidth-bound already
+MMA_MIN_ROWS = 3        # below, narrow outputs run faster on the CUDA-core kernel (more blocks, no tile padding)
+MMA_WIDE_COLUMNS = 8192  # from here on (the vocabulary) the tensor-core kernel wins at any row count
+
+
+def _few_rows_on_mma(rows, n_cols):
+    return rows >= MMA_MIN_ROWS or n_cols >= MMA_WIDE_COLUMNS
+
+
+class NormedInput:
+    """A normalised input that may never be written out: `x` (the float32 residual stream) and the
+    RMSNorm to apply.  A matrix product of few rows computes the norm in its own prologue; any
+    other consumer calls `tensor()`, which runs the norm kernel once into the step's workspace."""
+
+    def __init__(self, ctx, x, norm, dtype):
+        self.ctx, self.x, self.norm, self.dtype = ctx, x, norm, dtype
+        self._t = None
+        self.shape = x.shape
+
+    def tensor(self):
+        if self._t is None:
+            self._t = self.ctx.ws.alloc(tuple(self.x.shape), self.dtype)
+            with self.ctx.prof("norm"):
+                self.norm.forward(self.ctx, self.x, self._t)
+        return self._t
+
+
+def as_tensor(a):
+    return a.tensor() if isinstance(a, NormedInput) else a
 
 
 def matmul(ctx, a, w, out, epilogue=EPI_STORE, w2=None, residual=None):
-    """`ctx` gives the device error word that the tensor-core kernel's bounded waits report to."""
-    if a.dtype == torch.bfloat16 and a.shape[0] >= TENSOR_CORE_MIN_ROWS and ops.gemm_tc_takes(a, w, out, w2):
+    """`a`: a tensor in the compute dtype or a NormedInput.  `ctx` gives the device error word that
+    the tensor-core kernel's bounded waits report to."""
+    rows = a.shape[0]
+    if isinstance(a, NormedInput):
+        if rows <= FEW_ROWS and a._t is None:
+            if _few_rows_on_mma(rows, w.shape[0]) and ops.gemv_mma_takes(a.x, w, w2, normed=True):
+                ops.gemv_mma(a.x, w, out, epilogue=epilogue, w2=w2, residual=residual, norm_weight=a.norm.weight, eps=a.norm.eps)
+                return
+            if ops.gemv_takes(a.x, w, w2, normed=True):
+                ops.gemv(a.x, w, out, epilogue=epilogue, w2=w2, residual=residual, norm_weight=a.norm.weight, eps=a.norm.eps,
+                         n_sms=ctx.n_sms)
+                return
+        a = a.tensor()
+    if rows <= FEW_ROWS and _few_rows_on_mma(rows, w.shape[0]) and ops.gemv_mma_takes(a, w, w2):
+        ops.gemv_mma(a, w, out, epilogue=epilogue, w2=w2, residual=residual)
+    elif rows <= FEW_ROWS and ops.gemv_takes(a, w, w2):
+        ops.gemv(a, w, out, epilogue=epilogue, w2=w2, residual=residual, n_sms=ctx.n_sms)
+    elif a.dtype == torch.bfloat16 and rows > FEW_ROWS and ops.gemm_tc_takes(a, w, out, w2):
         ops.gemm_tc(a, w, out, ctx.err, epilogue=epilogue, w2=w2, residual=residual)
     else:
         ops.gemm_simt(a, w, out, epilogue=epilogue, w2=w2, residual=residual)

@@ -7,6 +7,8 @@ from .registry import register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Part):
+    fusable = True  # a few-rows matrix product can compute this norm in its prologue (weight, eps)
+
     def __init__(self, spec, env):
         self.dim, self.eps, self.name = spec["dim"], float(spec["eps"]), spec["name"]
         self.weight = None

@@ -9,6 +9,8 @@ from .registry import register_ffn
 
 @register_ffn("swiglu")
 class SwiGLU(Part):
+    takes_normed_input = True
+
     def __init__(self, spec, env):
         self.hidden, self.inter = spec["hidden_size"], spec["intermediate_size"]
         self.names = dict(spec["names"])
@@ -27,12 +29,11 @@ class SwiGLU(Part):
         self.w_down = as_matrix(tensors[prefix + n["down"]], self.dtype, device)
 
     def workspace_bytes(self, n_tokens, n_seqs):
-        return nbytes((n_tokens, self.inter), self.dtype)
+        return nbytes((n_tokens, self.inter), self.dtype) + nbytes((n_tokens, self.hidden), self.dtype)
 
     def forward(self, ctx, h, x):
-        with ctx.ws.frame():
-            mid = ctx.ws.alloc((h.shape[0], self.inter), self.dtype)
-            with ctx.prof("gate_up_swiglu"):
-                linear.matmul(ctx, h, self.w_gate, mid, epilogue=linear.EPI_SWIGLU, w2=self.w_up)
-            with ctx.prof("down_proj_residual"):
-                linear.matmul(ctx, mid, self.w_down, x, epilogue=linear.EPI_RESIDUAL, residual=x)
+        mid = ctx.ws.alloc((h.shape[0], self.inter), self.dtype)
+        with ctx.prof("gate_up_swiglu"):
+            linear.matmul(ctx, h, self.w_gate, mid, epilogue=linear.EPI_SWIGLU, w2=self.w_up)
+        with ctx.prof("down_proj_residual"):
+            linear.matmul(ctx, mid, self.w_down, x, epilogue=linear.EPI_RESIDUAL, residual=x)

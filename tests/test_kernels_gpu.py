@@ -414,3 +414,120 @@ def test_gemm_tc_strided_rows_and_refusals():
     assert not o.gemm_tc_takes(rnd((4, 12), torch.bfloat16, 1), rnd((4, 12), torch.bfloat16, 2), None)  # K = 12: pitch of 24 bytes
     with pytest.raises(o.KernelError, match="multiples of 8"):
         o.gemm_tc(rnd((4, 12), torch.bfloat16, 1), rnd((4, 12), torch.bfloat16, 2), torch.zeros(4, 4, device=dev()), err)
+
+
+# ----------------------------------------------------------------------------- few-rows kernel (decode)
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 576, 576), (8, 960, 576), (3, 37, 96), (9, 130, 160), (16, 49152, 64), (5, 397, 200),
+                                     (8, 100, 8192), (2, 3000, 2048)])
+def test_gemv_epilogues(dtype, M, N, K):
+    o = ops()
+    a = rnd((M, K), dtype, 60)
+    w = rnd((N, K), dtype, 61, 0.2)
+    w2 = rnd((N, K), dtype, 62, 0.2)
+    assert o.gemv_takes(a, w, w2)
+    want = a.double().cpu() @ w.double().cpu().T
+    out = torch.full((M, N), float("nan"), dtype=dtype, device=dev())
+    o.gemv(a, w, out)
+    assert rel_err(out, want) < tol(dtype)
+    out32 = torch.full((M, N), float("nan"), dtype=torch.float32, device=dev())
+    o.gemv(a, w, out32)
+    assert rel_err(out32, want) < 2e-5
+    ref = torch.empty(M, N, dtype=torch.float32, device=dev())
+    o.gemm_simt(a, w, ref, force_kernel=1)
+    assert torch.equal(out32, ref)  # the same order of sums as the scalar kernel: the same bits
+    res = rnd((M, N), torch.float32, 63)
+    res0 = res.clone()
+    o.gemv(a, w, res, epilogue=o.EPI_RESIDUAL, residual=res)
+    assert rel_err(res, res0.double().cpu() + want) < 2e-5
+    u = a.double().cpu() @ w2.double().cpu().T
+    sw = torch.full((M, N), float("nan"), dtype=dtype, device=dev())
+    o.gemv(a, w, sw, epilogue=o.EPI_SWIGLU, w2=w2)
+    assert rel_err(sw, want / (1 + torch.exp(-want)) * u) < tol(dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K,eps", [(8, 960, 576, 1e-5), (1, 200, 96, 1e-6), (12, 64, 2048, 1e-5), (3, 50, 8200, 1e-3)])
+def test_gemv_with_norm_prologue(dtype, M, N, K, eps):
+    o = ops()
+    x = rnd((M, K), torch.float32, 64, 2.0)
+    nw = 1 + rnd((K,), torch.float32, 65, 0.1)
+    w = rnd((N, K), dtype, 66, 0.2)
+    assert o.gemv_takes(x, w, None, normed=True)
+    h = torch.empty(M, K, dtype=dtype, device=dev())
+    o.rmsnorm(x, nw, eps, h)
+    want = torch.empty(M, N, dtype=torch.float32, device=dev())
+    o.gemv(h, w, want)
+    got = torch.full((M, N), float("nan"), dtype=torch.float32, device=dev())
+    o.gemv(x, w, got, norm_weight=nw, eps=eps)
+    assert rel_err(got, want) < (2e-6 if dtype == torch.float32 else 4e-3)  # the norm's sum runs in another order
+    plain_h = torch.from_numpy(plain.rmsnorm(x.cpu().numpy(), nw.cpu().numpy(), eps)).double()
+    assert rel_err(got, plain_h @ w.double().cpu().T) < tol(dtype)
+
+
+def test_gemv_refuses_unaligned():
+    o = ops()
+    assert not o.gemv_takes(rnd((2, 12), torch.bfloat16, 1), rnd((4, 12), torch.bfloat16, 2))
+    assert not o.gemv_takes(rnd((2, 6), torch.float32, 1), rnd((4, 6), torch.float32, 2))
+    with pytest.raises(o.KernelError, match="16-byte"):
+        o.gemv(rnd((2, 12), torch.bfloat16, 1), rnd((4, 12), torch.bfloat16, 2), torch.zeros(2, 4, device=dev()))
+
+
+# ----------------------------------------------------------------------------- few-rows kernel on mma.sync (bfloat16 decode)
+@pytest.mark.parametrize("M,N,K", [(1, 576, 576), (8, 960, 576), (3, 37, 96), (9, 130, 160), (16, 4000, 64), (5, 397, 200),
+                                     (8, 100, 6144), (2, 3000, 2048), (7, 16, 8), (13, 31, 40)])
+def test_gemv_mma_epilogues(M, N, K):
+    o = ops()
+    a = rnd((M, K), torch.bfloat16, 70)
+    w = rnd((N, K), torch.bfloat16, 71, 0.2)
+    w2 = rnd((N, K), torch.bfloat16, 72, 0.2)
+    assert o.gemv_mma_takes(a, w, w2)
+    want = a.double().cpu() @ w.double().cpu().T
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev())
+    o.gemv_mma(a, w, out)
+    assert rel_err(out, want) < 1.6e-2
+    out32 = torch.full((M, N), float("nan"), dtype=torch.float32, device=dev())
+    o.gemv_mma(a, w, out32)
+    assert rel_err(out32, want) < 2e-5
+    res = rnd((M, N), torch.float32, 73)
+    res0 = res.clone()
+    o.gemv_mma(a, w, res, epilogue=o.EPI_RESIDUAL, residual=res)
+    assert rel_err(res, res0.double().cpu() + want) < 2e-5
+    u = a.double().cpu() @ w2.double().cpu().T
+    sw = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev())
+    o.gemv_mma(a, w, sw, epilogue=o.EPI_SWIGLU, w2=w2)
+    assert rel_err(sw, want / (1 + torch.exp(-want)) * u) < 1.6e-2
+
+
+@pytest.mark.parametrize("M,N,K,eps", [(8, 960, 576, 1e-5), (1, 200, 96, 1e-6), (12, 64, 2048, 1e-5), (3, 50, 4104, 1e-3)])
+def test_gemv_mma_with_norm_prologue(M, N, K, eps):
+    o = ops()
+    x = rnd((M, K), torch.float32, 74, 2.0)
+    nw = 1 + rnd((K,), torch.float32, 75, 0.1)
+    w = rnd((N, K), torch.bfloat16, 76, 0.2)
+    assert o.gemv_mma_takes(x, w, None, normed=True)
+    h = torch.empty(M, K, dtype=torch.bfloat16, device=dev())
+    o.rmsnorm(x, nw, eps, h)
+    want = torch.empty(M, N, dtype=torch.float32, device=dev())
+    o.gemv_mma(h, w, want)
+    got = torch.full((M, N), float("nan"), dtype=torch.float32, device=dev())
+    o.gemv_mma(x, w, got, norm_weight=nw, eps=eps)
+    assert rel_err(got, want) < 4e-3  # the norm's sum runs in another order: a last-bit difference before rounding
+    plain_h = torch.from_numpy(plain.rmsnorm(x.cpu().numpy(), nw.cpu().numpy(), eps)).double()
+    assert rel_err(got, plain_h @ w.double().cpu().T) < 1.6e-2
+
+
+def test_gemv_mma_row_independent_of_batch_and_refusals():
+    o = ops()
+    a = rnd((16, 96), torch.bfloat16, 77)
+    w = rnd((50, 96), torch.bfloat16, 78)
+    full = torch.empty(16, 50, device=dev())
+    o.gemv_mma(a, w, full)
+    one = torch.empty(1, 50, device=dev())
+    o.gemv_mma(a[11:12], w, one)
+    assert torch.equal(one, full[11:12])
+    assert not o.gemv_mma_takes(rnd((17, 96), torch.bfloat16, 1), w)
+    assert not o.gemv_mma_takes(rnd((2, 12), torch.bfloat16, 1), rnd((4, 12), torch.bfloat16, 2))
+    assert not o.gemv_mma_takes(rnd((2, 96), torch.float32, 1), rnd((4, 96), torch.float32, 2))
+    with pytest.raises(o.KernelError, match="M <= 16"):
+        o.gemv_mma(rnd((17, 96), torch.bfloat16, 1), w, torch.zeros(17, 50, device=dev()))
