@@ -1,0 +1,264 @@
+"""Each part of a layer alone against the plain implementation, and the framework's openness:
+a toy mixer with a state of its own, a toy architecture, a schedule that runs a layer twice;
+all defined here, none of them touching the package's files."""
+import json
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+import plain_llama as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+class Ctx:
+    """The least a part needs from a step: an engine's context filled for given sequences."""
+
+    def __init__(self, engine, seqs):
+        from edgelm_b200.engine.engine import StepEntry
+        self.engine = engine
+        self.slots = engine.open(len(seqs))
+        self.entries = [StepEntry(s, t, list(range(len(t)))) for s, t in zip(self.slots, seqs)]
+
+
+def build_part(role, spec, dtype, tensors, prefix=""):
+    from edgelm_b200.parts.registry import BuildEnv
+    part = BuildEnv(dtype=dtype).build(role, spec)
+    part.load(tensors, prefix, DEV)
+    return part
+
+
+def null_ctx(n_tokens=0):
+    from edgelm_b200.engine.arena import Workspace
+    from edgelm_b200.engine.batch import StepContext
+    ws = Workspace(1 << 24, torch.device(DEV))
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    return StepContext(ws, err, torch.device(DEV), 148)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_embedding_head_swiglu_alone(dtype):
+    from edgelm_b200.config.base import PartSpec
+    g = torch.Generator().manual_seed(5)
+    D, I, V, T = 88, 136, 301, 37
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    ctx = null_ctx()
+    # norm
+    w = (1 + 0.1 * torch.randn(D, generator=g))
+    x = torch.randn(T, D, generator=g) * 2
+    norm = build_part("norm", PartSpec("rmsnorm", {"dim": D, "eps": 1e-4, "name": "n.weight"}), dtype, {"p.n.weight": w}, "p.")
+    out = torch.empty(T, D, dtype=dtype, device=DEV)
+    norm.forward(ctx, x.to(DEV), out)
+    assert H.rel_err(out.float().cpu().numpy(), plain.rmsnorm(x.numpy(), w.numpy(), 1e-4)) < tol
+    # embedding
+    table = torch.randn(V, D, generator=g).to(dtype)
+    emb = build_part("embedding", PartSpec("embedding", {"vocab_size": V, "dim": D, "name": "e"}), dtype, {"e": table})
+    ctx.token_ids = torch.tensor([0, V - 1, 7], dtype=torch.int32, device=DEV)
+    xe = torch.empty(3, D, device=DEV)
+    emb.forward(ctx, xe)
+    assert np.array_equal(xe.cpu().numpy(), plain.embed(table.float().numpy(), [0, V - 1, 7]))
+    # head, untied and tied
+    hw = (torch.randn(V, D, generator=g) * 0.1).to(dtype)
+    head = build_part("head", PartSpec("lm_head", {"vocab_size": V, "dim": D, "tied_to": None, "name": "h"}), dtype, {"h": hw})
+    xn = torch.randn(T, D, generator=g).to(dtype)
+    logits = torch.empty(T, V, device=DEV)
+    head.forward(ctx, xn.to(DEV), logits)
+    assert H.rel_err(logits.cpu().numpy(), xn.float().numpy() @ hw.float().numpy().T) < 2e-5
+    # feed-forward, many rows (tile / tensor-core kernels) and few (decode kernels)
+    wg, wu, wd = [(torch.randn(*s, generator=g) * 0.1).to(dtype) for s in ((I, D), (I, D), (D, I))]
+    ffn = build_part("ffn", PartSpec("swiglu", {"hidden_size": D, "intermediate_size": I,
+                                                 "names": {"gate": "g", "up": "u", "down": "d"}}), dtype,
+                     {"p.g": wg, "p.u": wu, "p.d": wd}, "p.")
+    for rows in (T, 3):
+        h = torch.randn(rows, D, generator=g).to(dtype)
+        xr = torch.randn(rows, D, generator=g)
+        xd = xr.clone().to(DEV)
+        ctx.ws.reset()
+        ffn.forward(ctx, h.to(DEV), xd)
+        want = xr.numpy() + plain.swiglu_mlp(h.float().numpy(), wg.float().numpy(), wu.float().numpy(), wd.float().numpy())
+        assert H.rel_err(xd.cpu().numpy(), want) < tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rope_table_and_attention_alone(dtype, tmp_path):
+    """The attention mixer through a one-layer model whose feed-forward weights are zero: what comes
+    out of the layer is x + attention(x), prompt in one step and token by token."""
+    from edgelm_b200.engine.engine import Engine, StepEntry, load_model
+    from edgelm_b200.weights import read_dir, write_file
+    cfg = dict(H.TINY_B, num_hidden_layers=1, num_attention_heads=6, num_key_value_heads=2, head_dim=16, hidden_size=48,
+               intermediate_size=24, vocab_size=61, rope_theta=500.0)
+    from edgelm_b200 import write_model_dir
+    from edgelm_b200.config import config_class_for
+    d = write_model_dir(str(tmp_path / "m"), config_class_for(cfg).from_dict(cfg), seed=4, sigma=0.2, dtype="float32")
+    t = dict(read_dir(d))
+    t["model.layers.0.mlp.down_proj.weight"] = torch.zeros_like(t["model.layers.0.mlp.down_proj.weight"])
+    write_file(str(tmp_path / "m" / "model.safetensors"), {k: v.clone() for k, v in t.items()})
+    model = load_model(d, "float32" if dtype == torch.float32 else "bfloat16")
+    rope = model.layers[0].mixer.positions
+    c, s = plain.rope_angles(np.arange(cfg["max_position_embeddings"]), 16, 500.0)
+    assert np.array_equal(rope.cos.cpu().numpy(), c) and np.array_equal(rope.sin.cpu().numpy(), s)  # float64 angles, then float32
+    eng = Engine(model, max_tokens=256)
+    pcfg, W = plain.read_model(d)
+    toks = [int(v) for v in np.random.default_rng(3).integers(0, 61, size=90)]
+    want = plain.forward(pcfg, W, toks)
+    tol = 2e-5 if dtype == torch.float32 else 3e-2
+    assert H.rel_err(H.run_whole(eng, toks), want) < tol
+    assert H.rel_err(H.run_tail_one_by_one(eng, toks, 40), want) < tol
+
+
+# ----------------------------------------------------------------------------- a toy mixer with a state of its own
+def _register_toy():
+    """A mixer that keeps one vector per sequence: s <- decay * s + h_t; output s W^T.  Torch ops
+    on the device, token by token: a toy to show the interfaces, not a kernel."""
+    from edgelm_b200.config import register_architecture
+    from edgelm_b200.config.base import LayerSpec, ModelPlan, PartSpec, ScheduleEntry
+    from edgelm_b200.parts import Part, StateNeed, register_mixer
+    from edgelm_b200.parts.registry import MIXERS
+
+    if "toy_decay_state" in MIXERS:
+        return
+
+    @register_mixer("toy_decay_state")
+    class ToyStateMixer(Part):
+        def __init__(self, spec, env):
+            self.dim, self.decay, self.name = spec["dim"], float(spec["decay"]), spec["name"]
+            self.w = None
+
+        def weight_shapes(self, prefix):
+            return {prefix + self.name: (self.dim, self.dim)}
+
+        def load(self, tensors, prefix, device):
+            self.w = tensors[prefix + self.name].to(device=device, dtype=torch.float32)
+
+        def cache_need(self):
+            return StateNeed((self.dim,))
+
+        def forward(self, ctx, h, x, cache):
+            state = cache.state                      # [slots, dim] float32, zero when a sequence starts
+            slots = ctx.seq_slots.long()
+            t0 = 0
+            for i, n in enumerate(ctx.seq_lengths):
+                s = state[slots[i]]
+                for t in range(t0, t0 + n):
+                    s = self.decay * s + h[t].float()
+                    x[t] += s @ self.w.T
+                state[slots[i]] = s
+                t0 += n
+
+    @register_architecture("ToyStateForCausalLM", model_type="toy_state")
+    class ToyConfig:
+        def __init__(self, d):
+            self.d = d
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d)
+
+        def plan(self):
+            d = self.d
+            D, V = d["width"], d["vocab_size"]
+            norm = lambda name: PartSpec("rmsnorm", {"dim": D, "eps": d["eps"], "name": name})
+            toy = PartSpec("toy_decay_state", {"dim": D, "decay": d["decay"], "name": "mix.weight"})
+            att = PartSpec("attention", {"hidden_size": D, "num_heads": 2, "num_kv_heads": 1, "head_dim": 16,
+                                         "positions": PartSpec("rope", {"head_dim": 16, "theta": 1000.0, "max_positions": 128}),
+                                         "names": {"q": "q.weight", "k": "k.weight", "v": "v.weight", "o": "o.weight"}})
+            ffn = PartSpec("swiglu", {"hidden_size": D, "intermediate_size": d["inner"],
+                                      "names": {"gate": "g.weight", "up": "u.weight", "down": "d.weight"}})
+            layers = (LayerSpec("l0.", "prenorm", toy, norm("n1.weight"), ffn, norm("n2.weight")),
+                      LayerSpec("l1.", "prenorm", att, norm("n1.weight"), ffn, norm("n2.weight")))
+            # the state layer runs twice (each run has a state of its own), with the attention layer between
+            schedule = (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0))
+            return ModelPlan(hidden_size=D, vocab_size=V, max_positions=128,
+                             embedding=PartSpec("embedding", {"vocab_size": V, "dim": D, "name": "emb.weight"}),
+                             layers=layers, schedule=schedule, final_norm=norm("final.weight"),
+                             head=PartSpec("lm_head", {"vocab_size": V, "dim": D, "tied_to": "emb.weight", "name": "head.weight"}))
+
+
+def _toy_plain(W, d, tokens):
+    """The toy model in plain NumPy: whole sequence, no cache."""
+    D = d["width"]
+
+    def toy_layer(x):
+        h = plain.rmsnorm(x, W["l0.n1.weight"], d["eps"])
+        s = np.zeros(D, dtype=np.float32)
+        out = x.copy()
+        for t in range(len(x)):
+            s = np.float32(d["decay"]) * s + h[t]
+            out[t] += s @ W["l0.mix.weight"].T
+        h2 = plain.rmsnorm(out, W["l0.n2.weight"], d["eps"])
+        return out + plain.swiglu_mlp(h2, W["l0.g.weight"], W["l0.u.weight"], W["l0.d.weight"])
+
+    def att_layer(x):
+        h = plain.rmsnorm(x, W["l1.n1.weight"], d["eps"])
+        pos = np.arange(len(x))
+        q = plain.rope(h @ W["l1.q.weight"].T, pos, 2, 16, 1000.0)
+        k = plain.rope(h @ W["l1.k.weight"].T, pos, 1, 16, 1000.0)
+        a = plain.attention(q, k, h @ W["l1.v.weight"].T, 2, 1, 16)
+        x = x + a @ W["l1.o.weight"].T
+        h2 = plain.rmsnorm(x, W["l1.n2.weight"], d["eps"])
+        return x + plain.swiglu_mlp(h2, W["l1.g.weight"], W["l1.u.weight"], W["l1.d.weight"])
+
+    x = plain.embed(W["emb.weight"], tokens)
+    x = toy_layer(att_layer(toy_layer(x)))
+    return plain.rmsnorm(x, W["final.weight"], d["eps"]) @ W["emb.weight"].T
+
+
+def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
+    _register_toy()
+    from edgelm_b200.config import read_config, registered_architectures
+    from edgelm_b200.engine.engine import Engine, load_model
+    from edgelm_b200.engine.model import expected_weights
+    from edgelm_b200.weights import random_tensors, write_file
+    assert "ToyStateForCausalLM" in registered_architectures()
+    d = {"architectures": ["ToyStateForCausalLM"], "vocab_size": 53, "width": 40, "inner": 56, "eps": 1e-5, "decay": 0.8}
+    folder = tmp_path / "toy"
+    folder.mkdir()
+    (folder / "config.json").write_text(json.dumps(d))
+    cfg = read_config(str(folder))
+    exp = expected_weights(cfg.plan())
+    assert exp["l0.mix.weight"] == (40, 40) and "head.weight" not in exp
+    write_file(str(folder / "model.safetensors"), random_tensors(exp, seed=9, sigma=0.15, dtype=torch.float32))
+    model = load_model(str(folder), "float32")
+    eng = Engine(model, max_tokens=512)
+    assert len(eng.cache.state_groups) == 1 and eng.cache.state_groups[0].n_entries == 2  # two runs, two states
+    assert len(eng.cache.kv_groups) == 1 and eng.cache.kv_groups[0].n_entries == 1
+    W = {k: v.float().numpy() for k, v in __import__("edgelm_b200.weights", fromlist=["read_dir"]).read_dir(str(folder)).items()}
+    reqs = [[int(v) for v in np.random.default_rng(i).integers(0, 53, size=n)] for i, n in enumerate([20, 7, 70, 33])]
+    for r in reqs:
+        want = _toy_plain(W, d, r)
+        assert H.rel_err(H.run_whole(eng, r), want) < 5e-5
+        assert H.rel_err(H.run_tail_one_by_one(eng, r, 10), want) < 5e-5
+    # unequal batches on reused slots: a slot's state starts from zero again
+    got = H.run_batches(eng, reqs, batch_size=2, decode_tail=5)
+    for r, g in zip(reqs, got):
+        assert H.rel_err(g, _toy_plain(W, d, r)) < 5e-5
+    eng.cache.check()
+
+
+def test_cli_commands(tmp_path, capsys):
+    from edgelm_b200.cli import main
+    d = H.make_model_dir(tmp_path, "tiny_a")
+    o = H.Oracle(d)
+    assert main(["info", "-m", d, "--ops", "--dtype", "f32"]) == 0
+    out = capsys.readouterr().out
+    assert "kv cache" in out and "attention" in out and "swiglu" in out
+    toks = H.tokens_for("tiny_a", 12, 400)
+    path = str(tmp_path / "lg.f32")
+    assert main(["logits", "-m", d, "--dtype", "f32", "--tokens", ",".join(map(str, toks)), "--prefill", "5", "--out", path]) == 0
+    lg = np.fromfile(path, dtype="<f4").reshape(12, -1)
+    assert H.rel_err(lg, o.logits(toks)) < 2e-5
+    capsys.readouterr()
+    trace = str(tmp_path / "t.json")
+    assert main(["run", "-m", d, "--dtype", "f32", "-p", "5,17,3;9", "-n", "6", "--ignore-eos", "--profile", trace, "--stats"]) == 0
+    out = capsys.readouterr().out
+    want = [plain.generate(o.cfg, o.W, p, 6, stop_ids=[], ignore_eos=True) for p in ([5, 17, 3], [9])]
+    assert "5,17,3 => " + ",".join(map(str, want[0])) in out and "9 => " + ",".join(map(str, want[1])) in out
+    assert "decode" in out and json.load(open(trace))["traceEvents"]
+    assert main(["bench", "--preset", "tiny-b", "--prompt-len", "20", "--gen", "4", "--reps", "1", "--batch-sizes", "1,3", "--json"]) == 0
+    rows = [json.loads(l) for l in capsys.readouterr().out.strip().splitlines()]
+    assert [r["batch"] for r in rows] == [1, 3] and all(r["decode_tok_s"] > 0 for r in rows)
+    assert main(["run", "-m", str(tmp_path / "nowhere")]) == 1
