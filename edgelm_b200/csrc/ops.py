@@ -240,6 +240,26 @@ def attn_prefill(qkv, out, kcache, vcache, page_table, seq_slot, tile_seq, tile_
                                      ctypes.c_float(scale), _stream()))
 
 
+MMA_PREFILL_TILE = 64  # new tokens per tile of the tensor-core prefill kernel (PM_ROWS in attention_mma.cu)
+
+
+def attn_prefill_mma_takes(dtype, hd):
+    """Whether the tensor-core prefill attention takes this dtype and head size (bfloat16; 32, 64, 96, 128)."""
+    return dtype == torch.bfloat16 and bool(lib().edgelm_attn_prefill_mma_takes(int(hd)))
+
+
+def attn_prefill_mma(qkv, out, kcache, vcache, page_table, seq_slot, tile_seq, tile_tok0, tile_ntok, tile_pos0, n_tiles,
+                     nh, nkv, hd, scale):
+    """Causal attention of new tokens over the paged cache on mma.sync tensor cores; tiles of at most 64 tokens."""
+    _need(qkv.dtype == out.dtype == kcache.dtype == torch.bfloat16 and qkv.stride(1) == 1 and out.stride(1) == 1, "attn_prefill_mma: layout")
+    for t, n in ((page_table, "page_table"), (seq_slot, "seq_slot"), (tile_seq, "tile_seq"), (tile_tok0, "tile_tok0"),
+                 (tile_ntok, "tile_ntok"), (tile_pos0, "tile_pos0")):
+        _i32(t, n)
+    _check(lib().edgelm_attn_prefill_mma(_p(qkv), qkv.stride(0), _p(out), out.stride(0), _p(kcache), _p(vcache),
+                                         _p(page_table), page_table.stride(0), _p(seq_slot), _p(tile_seq), _p(tile_tok0),
+                                         _p(tile_ntok), _p(tile_pos0), n_tiles, nh, nkv, hd, ctypes.c_float(scale), _stream()))
+
+
 def attn_decode(qkv, out, kcache, vcache, page_table, seq_slot, seq_pos, n_seqs, nh, nkv, hd, scale, n_splits=1,
                 part_o=None, part_ml=None):
     """Attention of one new token per sequence over the paged cache, pages dealt to `n_splits` blocks."""

@@ -75,6 +75,9 @@ class StepContext:
         return int(min(64, max(1, (2 * self.n_sms + blocks - 1) // blocks)))
 
     def tiles(self, tile_tokens):
+        """Attention tiles of at most `tile_tokens` consecutive tokens of one sequence.  Sizes that
+        the model's parts announced (`tile_sizes`) lie in the step's metadata already; any other
+        size is built and copied now (which a replayed CUDA graph could not do)."""
         if tile_tokens not in self._tiles:
             seq, tok0, ntok, pos0 = make_tiles(self._seq_ntok, self._seq_pos0, tile_tokens)
             n = len(seq)
@@ -88,12 +91,14 @@ class BatchBuffers:
     """Pinned host staging and its device twin for the per-step metadata, sized once for the
     largest step; `fill` lays a step out and issues the single host-to-device copy."""
 
-    def __init__(self, max_tokens, max_seqs, kv_groups, max_want, device):
+    def __init__(self, max_tokens, max_seqs, kv_groups, max_want, device, tile_sizes=()):
         self.device = device
         self.max_tokens, self.max_seqs, self.max_want = max_tokens, max_seqs, max_want
         self.groups = list(kv_groups)
         self.stride = {g.id: g.table.shape[1] for g in self.groups}
+        self.tile_sizes = sorted(set(int(t) for t in tile_sizes))
         n = 3 * max_tokens + 4 * max_seqs + max_want + sum(max_seqs * s for s in self.stride.values())
+        n += sum(4 * (max_tokens // t + max_seqs) for t in self.tile_sizes)
         self.host = torch.zeros(n, dtype=torch.int32).pin_memory()
         self.host_np = self.host.numpy()
         self.dev = torch.zeros(n, dtype=torch.int32, device=device)
@@ -132,6 +137,13 @@ class BatchBuffers:
         for g in self.groups:
             s = self.stride[g.id]
             put(("table", g.id), g.table[slots].reshape(-1), B * s)
+        tile_counts = {}
+        if T != B:  # steps of one token per sequence use no tiles
+            for ts in self.tile_sizes:
+                cols = make_tiles([int(v) for v in ntok], [int(v) for v in pos0], ts)
+                tile_counts[ts] = len(cols[0])
+                for j, col in enumerate(cols):
+                    put(("tiles", ts, j), np.asarray(col, dtype=np.int32), len(col))
         self.dev[:o].copy_(self.host[:o], non_blocking=True)
         self._copied.record()
         self.last_bytes = o * 4
@@ -146,7 +158,8 @@ class BatchBuffers:
         ctx.seq_pos, ctx.want_rows = view("seq_pos"), view("want_rows")
         ctx.seq_index = self.seq_index_full[:B]
         ctx._tables = {g.id: view(("table", g.id)).view(B, self.stride[g.id]) for g in self.groups}
-        ctx._tiles = {}
+        ctx._tiles = {ts: Tiles(view(("tiles", ts, 0)), view(("tiles", ts, 1)), view(("tiles", ts, 2)), view(("tiles", ts, 3)), n)
+                      for ts, n in tile_counts.items()}
         ctx._seq_ntok, ctx._seq_pos0 = [int(x) for x in ntok], [int(x) for x in pos0]
         ctx.seq_slots = view("seq_slots")
         return ctx

@@ -74,12 +74,14 @@ class Engine:
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
         ops.attn_set_error_word(self.err)
         self.buffers = BatchBuffers(self.max_step_tokens, self.max_step_seqs, self.cache.kv_groups, self.max_step_tokens,
-                                    self.device)
+                                    self.device, tile_sizes=model.tile_sizes())
         self.profiler = Profiler() if profile else None
         self.ctx = StepContext(self.ws, self.err, self.device, self.n_sms, self.profiler)
         self.sampler = DeviceSampler(self.cache.n_slots, self.device)
-        self.use_graphs = bool(use_graphs) and not profile
+        self.use_graphs = bool(use_graphs) and not profile and model.graph_safe
         self._graphs = {}
+        self._step_graphs = {}     # shape of a step (tokens per sequence, wanted rows) -> captured forward
+        self._step_seen = {}
         self.steps_run = 0
         self.h2d_bytes_last = 0
         self.kernel_launches_last = 0
@@ -189,13 +191,55 @@ class Engine:
         out = logits[row0:row0 + len(want_rows)]
         if self.profiler is not None:
             self.profiler.begin_step("decode" if ctx.all_single else "prefill", ctx.n_tokens, ctx.n_seqs, min(pos0))
-        self.model.forward(ctx, self.cache, out)
+        if not self._replay_step(ctx, tuple(ntok), len(want_rows), out):
+            self.model.forward(ctx, self.cache, out)
         if self.profiler is not None:
             self.profiler.end_step()
         for s, n in zip(slots, ntok):
             self.cache.advance(s, n)
         self.steps_run += 1
         return len(want_rows)
+
+    # A step's launches depend on its shape only (tokens per sequence, number of wanted rows): ids,
+    # positions, page tables, tiles and wanted rows are data in the fixed metadata buffer.  So a
+    # shape that comes back is replayed from a CUDA graph, which removes the host's launch work
+    # (a prompt step is otherwise bound by it).  Captured at a shape's second appearance; the
+    # graph writes logits into a buffer of its own, copied out after the replay.
+    STEP_GRAPH_MIN_TOKENS = 32
+    STEP_GRAPH_MAX_LOGIT_BYTES = 64 << 20
+    STEP_GRAPH_LIMIT = 12
+
+    def _replay_step(self, ctx, shape, n_want, out):
+        if not self.use_graphs or ctx.n_tokens < self.STEP_GRAPH_MIN_TOKENS or ctx.all_single:
+            return False
+        if n_want * self.plan.vocab_size * 4 > self.STEP_GRAPH_MAX_LOGIT_BYTES:
+            return False
+        if any(t not in ctx._tiles for t in self.model.tile_sizes()):
+            return False
+        key = (shape, n_want)
+        g = self._step_graphs.get(key)
+        if g is None:
+            self._step_seen[key] = self._step_seen.get(key, 0) + 1
+            if self._step_seen[key] < 2:
+                return False
+            if len(self._step_graphs) >= self.STEP_GRAPH_LIMIT:
+                self._step_graphs.pop(next(iter(self._step_graphs)))
+            buf = torch.empty((n_want, self.plan.vocab_size), dtype=torch.float32, device=self.device)
+            self.model.forward(ctx, self.cache, buf)   # once eagerly: kernel attributes are set outside the capture
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            before = ops.LAUNCHES
+            with torch.cuda.graph(graph):
+                self.model.forward(ctx, self.cache, buf)
+            launches = ops.LAUNCHES - before
+            ops.count_launches(-launches)
+            g = {"graph": graph, "logits": buf, "launches": launches}
+            self._step_graphs[key] = g
+        g["graph"].replay()
+        ops.count_launches(g["launches"])
+        if n_want:
+            out.copy_(g["logits"])
+        return True
 
     def check_device_errors(self):
         """Raise if a kernel flagged bad input since the last check (synchronises)."""

@@ -67,6 +67,15 @@ class DecoderModel:
         """One need (or None) per schedule entry, in schedule order."""
         return [None if e.reads_cache_of is not None else self.layers[e.layer].cache_need() for e in self.schedule]
 
+    @property
+    def graph_safe(self):
+        """Whether every part allows its steps to be replayed from a CUDA graph."""
+        return all(p.graph_safe for p in [self.embedding, self.final_norm, self.head] + self.layers)
+
+    def tile_sizes(self):
+        """Every attention tile size a layer will ask the step for."""
+        return sorted({t for l in self.layers for t in l.tile_sizes()})
+
     def workspace_bytes(self, n_tokens, n_seqs, n_want):
         d = self.plan.hidden_size
         x = nbytes((n_tokens, d), torch.float32)

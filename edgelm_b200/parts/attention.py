@@ -17,6 +17,7 @@ from .registry import register_mixer
 
 @register_mixer("attention")
 class Attention(Part):
+    graph_safe = True
     takes_normed_input = True
 
     def __init__(self, spec, env):
@@ -29,6 +30,7 @@ class Attention(Part):
         self.group = self.nh // self.nkv
         self.tile_tokens = max(1, 32 // self.group)  # tokens whose heads fill one block of the prefill kernel
         self.w_qkv = self.w_o = None
+        self._mma = None  # whether the tensor-core prefill kernel takes this head size (asked once a device is there)
 
     def weight_shapes(self, prefix):
         n = self.names
@@ -44,6 +46,14 @@ class Attention(Part):
 
     def cache_need(self):
         return KVNeed(self.nkv, self.hd)
+
+    def tile_sizes(self):
+        return (ops.MMA_PREFILL_TILE,) if self._mma_prefill() else (self.tile_tokens,)
+
+    def _mma_prefill(self):
+        if self._mma is None:
+            self._mma = ops.attn_prefill_mma_takes(self.dtype, self.hd)
+        return self._mma
 
     def workspace_bytes(self, n_tokens, n_seqs):
         qkv = nbytes((n_tokens, (self.nh + 2 * self.nkv) * self.hd), self.dtype)
@@ -73,6 +83,11 @@ class Attention(Part):
             with ctx.prof("attn_decode"):
                 ops.attn_decode(qkv, a, cache.k, cache.v, table, ctx.seq_index, ctx.seq_pos, ctx.n_seqs, self.nh, self.nkv,
                                 self.hd, self.scale, splits, part_o, part_ml)
+        elif self._mma_prefill():
+            tiles = ctx.tiles(ops.MMA_PREFILL_TILE)
+            with ctx.prof("attn_prefill"):
+                ops.attn_prefill_mma(qkv, a, cache.k, cache.v, table, ctx.seq_index, tiles.seq, tiles.tok0, tiles.ntok,
+                                     tiles.pos0, tiles.count, self.nh, self.nkv, self.hd, self.scale)
         else:
             tiles = ctx.tiles(self.tile_tokens)
             with ctx.prof("attn_prefill"):

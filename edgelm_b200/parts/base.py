@@ -44,6 +44,9 @@ class StateNeed:
 
 class Part:
     kind = "?"
+    # True if `forward` only launches work on the current stream from fixed-address buffers (no host
+    # reads of device data, no allocation): then steps through it may be replayed from a CUDA graph.
+    graph_safe = False
 
     def weight_shapes(self, prefix):
         return {}
@@ -56,6 +59,11 @@ class Part:
 
     def cache_need(self):
         return None
+
+    def tile_sizes(self):
+        """Sizes of attention tiles (`ctx.tiles(n)`) this part will ask for: the engine lays them out
+        with the step's metadata, which is what lets a whole step be replayed from a CUDA graph."""
+        return ()
 
 
 def as_matrix(t, dtype, device):

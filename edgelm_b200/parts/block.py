@@ -30,6 +30,13 @@ class PreNormBlock(Part):
     def cache_need(self):
         return self.mixer.cache_need()
 
+    def tile_sizes(self):
+        return tuple(self.mixer.tile_sizes())
+
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for p in self.parts)
+
     def workspace_bytes(self, n_tokens, n_seqs):
         return nbytes((n_tokens, self.hidden), self.dtype) + max(self.mixer.workspace_bytes(n_tokens, n_seqs),
                                                                   self.ffn.workspace_bytes(n_tokens, n_seqs))

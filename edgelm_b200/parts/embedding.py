@@ -6,6 +6,7 @@ from .registry import register_embedding
 
 @register_embedding("embedding")
 class Embedding(Part):
+    graph_safe = True
     def __init__(self, spec, env):
         self.vocab_size, self.dim, self.name = spec["vocab_size"], spec["dim"], spec["name"]
         self.dtype = env.dtype

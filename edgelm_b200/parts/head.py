@@ -8,6 +8,7 @@ from .registry import register_head
 
 @register_head("lm_head")
 class LMHead(Part):
+    graph_safe = True
     def __init__(self, spec, env):
         self.vocab_size, self.dim, self.name, self.tied_to = spec["vocab_size"], spec["dim"], spec["name"], spec["tied_to"]
         self.dtype = env.dtype

@@ -7,6 +7,7 @@ from .registry import register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Part):
+    graph_safe = True
     fusable = True  # a few-rows matrix product can compute this norm in its prologue (weight, eps)
 
     def __init__(self, spec, env):

@@ -15,6 +15,7 @@ from .registry import register_positions
 
 @register_positions("rope")
 class RotaryPositions(Part):
+    graph_safe = True
     def __init__(self, spec, env):
         self.head_dim, self.theta, self.max_positions = spec["head_dim"], float(spec["theta"]), spec["max_positions"]
         self.cos = self.sin = None

@@ -9,6 +9,7 @@ from .registry import register_ffn
 
 @register_ffn("swiglu")
 class SwiGLU(Part):
+    graph_safe = True
     takes_normed_input = True
 
     def __init__(self, spec, env):

@@ -531,3 +531,58 @@ def test_gemv_mma_row_independent_of_batch_and_refusals():
     assert not o.gemv_mma_takes(rnd((2, 96), torch.float32, 1), rnd((4, 96), torch.float32, 2))
     with pytest.raises(o.KernelError, match="M <= 16"):
         o.gemv_mma(rnd((17, 96), torch.bfloat16, 1), w, torch.zeros(17, 50, device=dev()))
+
+
+# ----------------------------------------------------------------------------- prefill attention on mma.sync (bfloat16)
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 32), (9, 3, 64), (3, 1, 96), (4, 4, 128), (8, 1, 64)])
+def test_attn_prefill_mma(nh, nkv, hd):
+    o = ops()
+    assert o.attn_prefill_mma_takes(torch.bfloat16, hd) and not o.attn_prefill_mma_takes(torch.bfloat16, 48)
+    assert not o.attn_prefill_mma_takes(torch.float32, hd)
+    seqs = [(0, 5), (0, 70), (64, 1), (100, 129), (63, 2), (0, 64), (30, 200)]  # (cached before, new tokens)
+    lengths = [a + b for a, b in seqs]
+    case = PagedCase(o, torch.bfloat16, lengths, nkv, hd, seed=nh * 10 + hd)
+    T = sum(b for _, b in seqs)
+    qkv = rnd((T, (nh + 2 * nkv) * hd), torch.bfloat16, 80)
+    tq = o.MMA_PREFILL_TILE
+    tile_seq, tile_tok0, tile_ntok, tile_pos0 = [], [], [], []
+    t0 = 0
+    for s, (p0, n) in enumerate(seqs):
+        for a in range(0, n, tq):
+            tile_seq.append(s)
+            tile_tok0.append(t0 + a)
+            tile_ntok.append(min(tq, n - a))
+            tile_pos0.append(p0 + a)
+        t0 += n
+    mk = lambda x: torch.tensor(x, dtype=torch.int32, device=dev())
+    out = torch.full((T, nh * hd), float("nan"), dtype=torch.bfloat16, device=dev())
+    o.attn_prefill_mma(qkv, out, case.kcache, case.vcache, case.table, case.seq_slot, mk(tile_seq), mk(tile_tok0),
+                       mk(tile_ntok), mk(tile_pos0), len(tile_seq), nh, nkv, hd, 1.0 / math.sqrt(hd))
+    t0 = 0
+    for s, (p0, n) in enumerate(seqs):
+        want = attention_rows(qkv[t0:t0 + n, :nh * hd].float().cpu(), case.k[s], case.v[s], p0, nh, nkv, hd)
+        assert rel_err(out[t0:t0 + n], want) < 1.2e-2, (s, p0, n)
+        t0 += n
+
+
+def test_attn_prefill_mma_far_key_and_diagonal():
+    """Scaled queries make one early key, or the token's own key, dominate: a wrong mask or page shows."""
+    o = ops()
+    nh, nkv, hd, p0, n = 2, 1, 64, 130, 150
+    case = PagedCase(o, torch.bfloat16, [p0 + n], nkv, hd, seed=8)
+    q = torch.zeros(n, (nh + 2 * nkv) * hd)
+    for t in range(n):
+        q[t, :hd] = 12.0 * case.k[0][3, 0]                 # head 0: key 3, far back
+        q[t, hd:2 * hd] = 12.0 * case.k[0][p0 + t, 0]      # head 1: its own position, the last it may see
+    qkv = q.to(torch.bfloat16).to(dev())
+    tq = o.MMA_PREFILL_TILE
+    tiles = [(0, a, min(tq, n - a), p0 + a) for a in range(0, n, tq)]
+    mk = lambda x: torch.tensor(x, dtype=torch.int32, device=dev())
+    out = torch.zeros(n, nh * hd, dtype=torch.bfloat16, device=dev())
+    o.attn_prefill_mma(qkv, out, case.kcache, case.vcache, case.table, case.seq_slot, mk([t[0] for t in tiles]),
+                       mk([t[1] for t in tiles]), mk([t[2] for t in tiles]), mk([t[3] for t in tiles]), len(tiles), nh, nkv,
+                       hd, 1.0 / math.sqrt(hd))
+    want = attention_rows(qkv[:, :nh * hd].float().cpu(), case.k[0], case.v[0], p0, nh, nkv, hd)
+    assert rel_err(out, want) < 1.2e-2
+    assert rel_err(out[:, :hd], case.v[0][3, 0].expand(n, hd)) < 5e-2
+    assert rel_err(out[:, hd:], case.v[0][p0:p0 + n, 0]) < 5e-2
