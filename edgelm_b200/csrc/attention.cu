@@ -200,6 +200,16 @@ constexpr int DEC_WARPS = 4;
 constexpr int DEC_TILE_BYTES = 8192;
 constexpr long long DEC_WAIT_CYCLES = 2000000000LL;
 
+// Bytes of the decode kernel's shared memory before the per-warp tiles: queries (padded rows), probabilities,
+// per-warp partials, the new token's key and value (as floats' worth of room), the warps' mbarriers.
+// Floats per staged query row: the head, 4 floats of padding after every 32, rounded to whole 16-byte pieces.
+__host__ __device__ inline int decode_query_pitch(int hd) { return (hd + hd / 8 + 3) / 4 * 4; }
+
+__host__ __device__ inline size_t decode_head_bytes(int hd) {
+  const size_t floats = (size_t)RW * decode_query_pitch(hd) + (size_t)DEC_WARPS * RW * 64 + (size_t)DEC_WARPS * RW * (hd + 2) + 2 * (size_t)hd;
+  return (floats * 4 + DEC_WARPS * 8 + 127) / 128 * 128;
+}
+
 __device__ __forceinline__ uint32_t dec_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ bool dec_mbar_try(uint32_t bar, uint32_t parity) {
@@ -230,18 +240,24 @@ template <> struct Pair<__nv_bfloat16> {
 // Partial results of one split: part_o [seq][head][split][hd], part_ml [seq][head][split][2].
 template <typename T, int NP>  // NP = ceil(hd / 64): pairs of value dims a lane owns
 __global__ void __launch_bounds__(DEC_WARPS * 32)
-attn_decode_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ldo, const T* __restrict__ kcache,
-                   const T* __restrict__ vcache, const int32_t* __restrict__ page_table, int table_stride,
-                   const int32_t* __restrict__ seq_slot, const int32_t* __restrict__ seq_pos, int nh, int nkv, int hd,
-                   float scale, int n_splits, int tk, float* __restrict__ part_o, float* __restrict__ part_ml, int* err) {
+attn_decode_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ldo, T* kcache, T* vcache,
+                   const int32_t* __restrict__ page_table, int table_stride, const int32_t* __restrict__ seq_slot,
+                   const int32_t* __restrict__ seq_pos, int nh, int nkv, int hd, float scale, int n_splits, int tk,
+                   float* __restrict__ part_o, float* __restrict__ part_ml, int* err,
+                   const float* __restrict__ cos_t, const float* __restrict__ sin_t, int max_pos) {
+  // cos_t given: q, k, v are the raw projections of the new token; this kernel rotates q and k at
+  // the token's position (float32, half-split pairing, rounded to T as the stand-alone kernel
+  // stores them) and the block that owns the token's page appends k and v to the cache.
   constexpr int VEC = KVec<T>::N;
   extern __shared__ __align__(128) uint8_t dec_smem[];
   const int ws = hd + 2;
-  float* Qs = reinterpret_cast<float*>(dec_smem);                 // [RW][hd]
-  float* Ps = Qs + RW * hd;                                       // [DEC_WARPS][RW][64]
+  const int qp = decode_query_pitch(hd);                          // query row pitch (see qoff)
+  float* Qs = reinterpret_cast<float*>(dec_smem);                 // [RW][qp]
+  float* Ps = Qs + RW * qp;                                       // [DEC_WARPS][RW][64]
   float* Wp = Ps + DEC_WARPS * RW * 64;                           // [DEC_WARPS][RW][hd + 2]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(Wp + DEC_WARPS * RW * ws);  // [DEC_WARPS]  (offset is a multiple of 8 bytes)
-  const size_t head_bytes = ((size_t)(RW * hd + DEC_WARPS * RW * 64 + DEC_WARPS * RW * ws) * 4 + DEC_WARPS * 8 + 127) / 128 * 128;
+  T* newkv = reinterpret_cast<T*>(Wp + DEC_WARPS * RW * ws);      // [2][hd]: the new token's rotated key and its value
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<float*>(newkv) + 2 * hd);  // [DEC_WARPS]; newkv has room for 2 hd floats
+  const size_t head_bytes = decode_head_bytes(hd);
   const int tile_elems = tk * hd;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   T* Kt = reinterpret_cast<T*>(dec_smem + head_bytes) + (size_t)warp * 2 * tile_elems;  // this warp's K tile, then its V tile
@@ -265,13 +281,64 @@ attn_decode_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ld
   __syncwarp();
   uint32_t phase = 0;
   bool failed = false;
+  // Query floats are read in 16-byte pieces at a per-key rotated chunk; with 8-float chunks (bfloat16
+  // keys) chunks four apart would share banks, so every 32 floats are followed by 4 of padding.
+  auto qoff = [&](int d) { return VEC == 8 ? d + ((d >> 5) << 2) : d; };
+  const int pos = nkeys - 1;
+  const int half = hd >> 1;
+  const bool fused = cos_t != nullptr;
+  const int tpos = min(pos, max_pos - 1);
+  const bool owner = fused && (pos / PAGE) / per_split == split;   // this block's pages include the new token's
+  if (fused && pos >= max_pos && threadIdx.x == 0 && err) atomicOr(err, ERR_POSITION_RANGE);
+  auto rotated = [&](const T* row, int d) {   // element d of the rotated head `row`
+    const int j = d < half ? d : d - half;
+    const float c = cos_t[(size_t)tpos * half + j], sn = sin_t[(size_t)tpos * half + j];
+    const float self = to_f32(row[d]), other = to_f32(row[d < half ? d + half : d - half]);
+    const float y = d < half ? self * c - other * sn : self * c + other * sn;
+    return to_f32(from_f32<T>(y));
+  };
+  if (owner) {
+    const int page = pages[pos / PAGE];
+    const T* krow = q + (size_t)seq * ldq + (size_t)(nh + kvh) * hd;
+    const T* vrow = q + (size_t)seq * ldq + (size_t)(nh + nkv + kvh) * hd;
+    if (page < 0) {
+      if (threadIdx.x == 0 && err) atomicOr(err, ERR_PAGE_RANGE);
+    }
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+      const T kd = from_f32<T>(rotated(krow, d));
+      newkv[d] = kd;
+      newkv[hd + d] = vrow[d];
+      if (page >= 0) {
+        const size_t dst = (((size_t)page * nkv + kvh) * PAGE + pos % PAGE) * hd + d;
+        kcache[dst] = kd;
+        vcache[dst] = vrow[d];
+      }
+    }
+  }
+  auto issue_tile = [&](int t) {   // lane 0: start the two bulk copies of tile t into this warp's buffers
+    const int pg = p_begin + t / tiles_per_page, sub = t - (t / tiles_per_page) * tiles_per_page;
+    const size_t src = (((size_t)pages[pg] * nkv + kvh) * PAGE + (size_t)sub * tk) * hd;
+    const uint32_t bytes = (uint32_t)(tile_elems * sizeof(T));
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // earlier reads of the buffers are done
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(2 * bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dec_smem_u32(Kt)), "l"(kcache + src), "r"(bytes), "r"(bar) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dec_smem_u32(Vt)), "l"(vcache + src), "r"(bytes), "r"(bar) : "memory");
+  };
+  bool pre_issued = false;
+  if (warp < n_tiles && (p_begin * PAGE + warp * tk) < nkeys) {   // the first tile is on its way while the queries are staged
+    if (lane == 0) issue_tile(warp);
+    pre_issued = true;
+  }
 
   for (int h0 = 0; h0 < g; h0 += RW) {     // chunks of RW query heads of this kv head
     const int rows = min(RW, g - h0);
     __syncthreads();
     for (int i = threadIdx.x; i < rows * hd; i += blockDim.x) {
       const int r = i / hd, d = i - r * hd;
-      Qs[i] = to_f32(q[(size_t)seq * ldq + (kvh * g + h0 + r) * hd + d]);
+      const T* qrow = q + (size_t)seq * ldq + (size_t)(kvh * g + h0 + r) * hd;
+      Qs[r * qp + qoff(d)] = fused ? rotated(qrow, d) : to_f32(qrow[d]);
     }
     __syncthreads();
     float m[RW], l[RW], acc[RW][NP][2];
@@ -287,16 +354,8 @@ attn_decode_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ld
       const int key0 = pg * PAGE + sub * tk;
       if (key0 >= nkeys) break;            // later tiles of the last page hold no key (tiles ascend)
       const int valid = min(tk, nkeys - key0);
-      const size_t src = (((size_t)pages[pg] * nkv + kvh) * PAGE + (size_t)sub * tk) * hd;
-      if (lane == 0) {
-        const uint32_t bytes = (uint32_t)(tile_elems * sizeof(T));
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // earlier reads of the buffers are done
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(2 * bytes) : "memory");
-        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                     ::"r"(dec_smem_u32(Kt)), "l"(kcache + src), "r"(bytes), "r"(bar) : "memory");
-        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                     ::"r"(dec_smem_u32(Vt)), "l"(vcache + src), "r"(bytes), "r"(bar) : "memory");
-      }
+      if (pre_issued) pre_issued = false;   // this tile's copies were started before the queries were staged
+      else if (lane == 0) issue_tile(t);
       {  // bounded wait for the two copies
         const long long t0 = clock64();
         bool done = dec_mbar_try(bar, phase);
@@ -307,6 +366,13 @@ attn_decode_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ld
         failed = !__all_sync(0xffffffffu, done);
         if (failed) break;
         phase ^= 1;
+      }
+      if (owner && pos >= key0 && pos < key0 + tk) {   // the copy may have read the row before the append landed: put it in by hand
+        for (int d = lane; d < hd; d += 32) {
+          Kt[(size_t)(pos - key0) * hd + d] = newkv[d];
+          Vt[(size_t)(pos - key0) * hd + d] = newkv[hd + d];
+        }
+        __syncwarp();
       }
       // scores
       float s[2][RW];
@@ -325,7 +391,7 @@ attn_decode_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ld
 #pragma unroll
             for (int r = 0; r < RW; ++r) {
               if (r < rows) {
-                const float* qr = Qs + r * hd + cc * VEC;
+                const float* qr = Qs + r * qp + qoff(cc * VEC);
 #pragma unroll
                 for (int v = 0; v < VEC; v += 4) {
                   const float4 qv = *reinterpret_cast<const float4*>(qr + v);
@@ -517,11 +583,11 @@ static int decode_tile_keys(int hd, size_t elem) {
 template <typename T, int NC>
 int launch_decode(const void* q, int ldq, void* out, int ldo, const void* kc, const void* vc, const int32_t* page_table,
                   int table_stride, const int32_t* seq_slot, const int32_t* seq_pos, int n_seqs, int nh, int nkv, int hd,
-                  float scale, int n_splits, float* part_o, float* part_ml, cudaStream_t stream) {
+                  float scale, int n_splits, float* part_o, float* part_ml, cudaStream_t stream,
+                  const float* cos_t = nullptr, const float* sin_t = nullptr, int max_pos = 0) {
   constexpr int NP = NC <= 2 ? 1 : NC / 2;  // pairs of dims per lane: ceil(hd / 64)
   const int tk = decode_tile_keys(hd, sizeof(T));
-  const size_t head = ((size_t)(RW * hd + DEC_WARPS * RW * 64 + DEC_WARPS * RW * (hd + 2)) * 4 + DEC_WARPS * 8 + 127) / 128 * 128;
-  const size_t smem = head + (size_t)DEC_WARPS * 2 * tk * hd * sizeof(T);
+  const size_t smem = decode_head_bytes(hd) + (size_t)DEC_WARPS * 2 * tk * hd * sizeof(T);
   auto kern = attn_decode_kernel<T, NP>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) {
@@ -529,9 +595,10 @@ int launch_decode(const void* q, int ldq, void* out, int ldo, const void* kc, co
     return -2;
   }
   dim3 grid(n_seqs, nkv, n_splits);
-  kern<<<grid, DEC_WARPS * 32, smem, stream>>>((const T*)q, ldq, (T*)out, ldo, (const T*)kc, (const T*)vc, page_table,
-                                              table_stride, seq_slot, seq_pos, nh, nkv, hd, scale, n_splits, tk, part_o,
-                                              part_ml, g_attn_err);
+  // the caches are written only by the fused form (cos_t given), which gets them writable from its caller
+  kern<<<grid, DEC_WARPS * 32, smem, stream>>>((const T*)q, ldq, (T*)out, ldo, (T*)const_cast<void*>(kc), (T*)const_cast<void*>(vc),
+                                              page_table, table_stride, seq_slot, seq_pos, nh, nkv, hd, scale, n_splits, tk,
+                                              part_o, part_ml, g_attn_err, cos_t, sin_t, max_pos);
   if (n_splits > 1) {
     dim3 cgrid(n_seqs, nh);
     attn_decode_combine_kernel<T><<<cgrid, 64, 0, stream>>>(part_o, part_ml, (T*)out, ldo, nh, hd, n_splits);
@@ -604,6 +671,26 @@ extern "C" int edgelm_attn_decode(const void* q, int ldq, void* out, int ldo, co
   EL_ATT_DISPATCH(launch_decode, q, ldq, out, ldo, kcache, vcache, page_table, table_stride, seq_slot, seq_pos, n_seqs, nh,
                   nkv, hd, scale, n_splits, part_o, part_ml, stream);
   EL_LAUNCH_CHECK("attn_decode");
+  return 0;
+}
+
+// Decode attention with rotary positions and the cache append fused in: qkv holds the raw q, k, v
+// projections of each sequence's new token ([n_seqs, (nh + 2 nkv) hd]); the kernel rotates q and k at
+// the token's position with the cos/sin table [max_pos, hd / 2], appends the rotated k and v to the
+// cache (kcache, vcache are written) and attends over the cache including the new token.
+extern "C" int edgelm_attn_decode_rope(const void* qkv, int ldq, void* out, int ldo, void* kcache, void* vcache, int dtype,
+                                       const int32_t* page_table, int table_stride, const int32_t* seq_slot,
+                                       const int32_t* seq_pos, const float* cos_t, const float* sin_t, int max_pos,
+                                       int n_seqs, int nh, int nkv, int hd, float scale, int n_splits, float* part_o,
+                                       float* part_ml, cudaStream_t stream) {
+  if (n_seqs == 0) return 0;
+  if (check_heads("attn_decode_rope", nh, nkv, hd)) return -1;
+  EL_REFUSE(n_splits >= 1 && n_splits <= 65535 && nkv <= 65535, "attn_decode_rope: bad split count %d", n_splits);
+  EL_REFUSE(n_splits == 1 || (part_o && part_ml), "attn_decode_rope: %d splits need the scratch buffers", n_splits);
+  EL_REFUSE(cos_t && sin_t && max_pos > 0, "attn_decode_rope: needs the position table");
+  EL_ATT_DISPATCH(launch_decode, qkv, ldq, out, ldo, kcache, vcache, page_table, table_stride, seq_slot, seq_pos, n_seqs, nh,
+                  nkv, hd, scale, n_splits, part_o, part_ml, stream, cos_t, sin_t, max_pos);
+  EL_LAUNCH_CHECK("attn_decode_rope");
   return 0;
 }
 

@@ -70,10 +70,24 @@ class Attention(Part):
         qkv = ws.alloc((T, (self.nh + 2 * self.nkv) * self.hd), self.dtype)
         with ctx.prof("qkv_proj"):
             linear.matmul(ctx, h, self.w_qkv, qkv)
-        with ctx.prof("rope_kv_append"):
-            self.positions.encode_and_append(ctx, qkv, cache, self.nh, self.nkv)
         a = ws.alloc((T, self.nh * self.hd), self.dtype)
         table = ctx.page_table(cache.group)
+        tables = self.positions.rotation_tables() if hasattr(self.positions, "rotation_tables") else None
+        if ctx.all_single and tables is not None:
+            # one token per sequence: rotation, append and attention in one kernel
+            splits = ctx.decode_splits(self.nkv)
+            part_o = part_ml = None
+            if splits > 1:
+                part_o = ws.alloc((ctx.n_seqs * self.nh * splits * self.hd,), torch.float32)
+                part_ml = ws.alloc((ctx.n_seqs * self.nh * splits * 2,), torch.float32)
+            with ctx.prof("attn_decode"):
+                ops.attn_decode_rope(qkv, a, cache.k, cache.v, table, ctx.seq_index, ctx.seq_pos, tables[0], tables[1],
+                                     ctx.n_seqs, self.nh, self.nkv, self.hd, self.scale, splits, part_o, part_ml)
+            with ctx.prof("o_proj_residual"):
+                linear.matmul(ctx, a, self.w_o, x, epilogue=linear.EPI_RESIDUAL, residual=x)
+            return
+        with ctx.prof("rope_kv_append"):
+            self.positions.encode_and_append(ctx, qkv, cache, self.nh, self.nkv)
         if ctx.all_single:
             splits = ctx.decode_splits(self.nkv)
             part_o = part_ml = None

@@ -29,6 +29,11 @@ class RotaryPositions(Part):
         self.cos = torch.cos(ang).to(torch.float32).to(device).contiguous()
         self.sin = torch.sin(ang).to(torch.float32).to(device).contiguous()
 
+    def rotation_tables(self):
+        """(cos, sin) [positions, head_dim/2] float32: a mixer whose decode kernel rotates and appends
+        by itself asks for these instead of calling encode_and_append."""
+        return self.cos, self.sin
+
     def encode_and_append(self, ctx, qkv, cache, n_heads, n_kv_heads):
         """Rotate the query and key heads of qkv[T, (nh + 2 nkv) hd] in place at each token's
         position; write the rotated keys and the values into the cache entry's pages."""

@@ -586,3 +586,42 @@ def test_attn_prefill_mma_far_key_and_diagonal():
     assert rel_err(out, want) < 1.2e-2
     assert rel_err(out[:, :hd], case.v[0][3, 0].expand(n, hd)) < 5e-2
     assert rel_err(out[:, hd:], case.v[0][p0:p0 + n, 0]) < 5e-2
+
+
+# ----------------------------------------------------------------------------- decode attention with RoPE and append fused
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (9, 3, 64), (3, 1, 32), (12, 2, 128), (2, 2, 48)])
+@pytest.mark.parametrize("n_splits", [1, 5])
+def test_attn_decode_rope_equals_separate_kernels(dtype, nh, nkv, hd, n_splits):
+    o = ops()
+    lengths = [1, 64, 65, 300, 128, 37]          # the new token is the last of each: page edges on both sides
+    B = len(lengths)
+    max_pos = 400
+    cos, sin = plain.rope_angles(np.arange(max_pos), hd, 5000.0)
+    cos_t, sin_t = torch.from_numpy(cos).to(dev()), torch.from_numpy(sin).to(dev())
+    a = PagedCase(o, dtype, lengths, nkv, hd, seed=nh + hd)
+    b = PagedCase(o, dtype, lengths, nkv, hd, seed=nh + hd)   # the same cache twice
+    raw = rnd((B, (nh + 2 * nkv) * hd), dtype, 90)
+    seq_pos = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=dev())
+    tok_seq = torch.arange(B, dtype=torch.int32, device=dev())
+    err = torch.zeros(1, dtype=torch.int32, device=dev())
+    mk = lambda: (torch.full((B * nh * n_splits * hd,), float("nan"), device=dev()), torch.full((B * nh * n_splits * 2,), float("nan"), device=dev()))
+    # separate kernels: rotate + append, then attend
+    q1 = raw.clone()
+    o.rope_kv_append(q1, seq_pos, tok_seq, a.seq_slot, a.table, cos_t, sin_t, a.kcache, a.vcache, nh, nkv, hd, err)
+    want = torch.zeros(B, nh * hd, dtype=dtype, device=dev())
+    po, pm = mk()
+    o.attn_decode(q1, want, a.kcache, a.vcache, a.table, a.seq_slot, seq_pos, B, nh, nkv, hd, 1.0 / math.sqrt(hd), n_splits, po, pm)
+    # fused
+    got = torch.full_like(want, float("nan"))
+    po, pm = mk()
+    o.attn_decode_rope(raw.clone(), got, b.kcache, b.vcache, b.table, b.seq_slot, seq_pos, cos_t, sin_t, B, nh, nkv, hd,
+                       1.0 / math.sqrt(hd), n_splits, po, pm)
+    assert int(err.item()) == 0
+    assert rel_err(got, want) < (1e-6 if dtype == torch.float32 else 4e-3)
+    for s, n in enumerate(lengths):   # the appended rows are the same, nothing else changed
+        for cache_a, cache_b in ((a.kcache, b.kcache), (a.vcache, b.vcache)):
+            page = int(a.table[int(a.seq_slot[s]), (n - 1) // o.PAGE])
+            assert rel_err(cache_b[page, :, (n - 1) % o.PAGE], cache_a[page, :, (n - 1) % o.PAGE]) < (1e-6 if dtype == torch.float32 else 8e-3)
+    same = torch.isclose(a.kcache.float(), b.kcache.float(), rtol=1e-2, atol=1e-2, equal_nan=True)
+    assert bool(same.all())
