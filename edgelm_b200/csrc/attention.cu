@@ -244,7 +244,7 @@ attn_decode_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ld
                    const int32_t* __restrict__ page_table, int table_stride, const int32_t* __restrict__ seq_slot,
                    const int32_t* __restrict__ seq_pos, int nh, int nkv, int hd, float scale, int n_splits, int tk,
                    float* __restrict__ part_o, float* __restrict__ part_ml, int* err,
-                   const float* __restrict__ cos_t, const float* __restrict__ sin_t, int max_pos) {
+                   const float* __restrict__ cos_t, const float* __restrict__ sin_t, int max_pos, int* counters) {
   // cos_t given: q, k, v are the raw projections of the new token; this kernel rotates q and k at
   // the token's position (float32, half-split pairing, rounded to T as the stand-alone kernel
   // stores them) and the block that owns the token's page appends k and v to the cache.
@@ -279,6 +279,8 @@ attn_decode_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ld
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncwarp();
+  pdl_launch_dependents();
+  pdl_wait();  // everything below reads what earlier kernels of the step wrote
   uint32_t phase = 0;
   bool failed = false;
   // Query floats are read in 16-byte pieces at a per-key rotated chunk; with 8-float chunks (bfloat16
@@ -527,6 +529,53 @@ attn_decode_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ld
       }
     }
   }
+  // ---- with a counter per (sequence, kv head): the block that finishes last folds the splits itself,
+  // in the order of the splits, which saves the second kernel; it leaves the counter at zero again
+  if (n_splits > 1 && counters != nullptr) {
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) is_last = atomicAdd(&counters[seq * nkv + kvh], 1) == n_splits - 1;
+    __syncthreads();
+    if (is_last) {
+      __threadfence();
+      // weights of the splits per head in shared memory first (a warp per head, lanes over splits), then
+      // every thread folds its output elements with one independent load per split
+      float* wts = Ps;                                     // [heads of a chunk][n_splits], at most 1024 floats
+      float* linv = Wp;                                    // [heads of a chunk]
+      const int chunk = max(1, min(g, (DEC_WARPS * RW * 64) / n_splits));
+      for (int hc = 0; hc < g; hc += chunk) {
+        const int nhead = min(chunk, g - hc);
+        __syncthreads();
+        for (int hi = warp; hi < nhead; hi += DEC_WARPS) {
+          const size_t base = ((size_t)seq * nh + kvh * g + hc + hi) * n_splits;
+          float mx = -CUDART_INF_F;
+          for (int sp = lane; sp < n_splits; sp += 32) mx = fmaxf(mx, __ldcg(part_ml + (base + sp) * 2));
+          mx = warp_max(mx);
+          float lsum = 0.f;
+          for (int sp = lane; sp < n_splits; sp += 32) {
+            const float ms = __ldcg(part_ml + (base + sp) * 2);
+            const float f = ms == -CUDART_INF_F ? 0.f : expf(ms - mx);  // a split that held no page weighs nothing
+            wts[hi * n_splits + sp] = f;
+            lsum = fmaf(__ldcg(part_ml + (base + sp) * 2 + 1), f, lsum);
+          }
+          lsum = warp_sum(lsum);
+          if (lane == 0) linv[hi] = 1.0f / lsum;
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < nhead * hd; i += blockDim.x) {
+          const int hi = i / hd, d = i - hi * hd;
+          const int head = kvh * g + hc + hi;
+          const size_t base = ((size_t)seq * nh + head) * n_splits;
+          float o = 0.f;
+#pragma unroll 4
+          for (int sp = 0; sp < n_splits; ++sp) o = fmaf(__ldcg(part_o + (base + sp) * hd + d), wts[hi * n_splits + sp], o);
+          out[(size_t)seq * ldo + head * hd + d] = from_f32<T>(o * linv[hi]);
+        }
+      }
+      if (threadIdx.x == 0) counters[seq * nkv + kvh] = 0;
+    }
+  }
 }
 
 template <typename T>
@@ -534,6 +583,8 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, con
                                            T* __restrict__ out, int ldo, int nh, int hd, int n_splits) {
   const int seq = blockIdx.x, head = blockIdx.y;
   const size_t base = ((size_t)seq * nh + head) * n_splits;
+  pdl_launch_dependents();
+  pdl_wait();  // the partials are the previous kernel's
   float M = -CUDART_INF_F;
   for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
@@ -584,7 +635,7 @@ template <typename T, int NC>
 int launch_decode(const void* q, int ldq, void* out, int ldo, const void* kc, const void* vc, const int32_t* page_table,
                   int table_stride, const int32_t* seq_slot, const int32_t* seq_pos, int n_seqs, int nh, int nkv, int hd,
                   float scale, int n_splits, float* part_o, float* part_ml, cudaStream_t stream,
-                  const float* cos_t = nullptr, const float* sin_t = nullptr, int max_pos = 0) {
+                  const float* cos_t = nullptr, const float* sin_t = nullptr, int max_pos = 0, int* counters = nullptr) {
   constexpr int NP = NC <= 2 ? 1 : NC / 2;  // pairs of dims per lane: ceil(hd / 64)
   const int tk = decode_tile_keys(hd, sizeof(T));
   const size_t smem = decode_head_bytes(hd) + (size_t)DEC_WARPS * 2 * tk * hd * sizeof(T);
@@ -596,12 +647,18 @@ int launch_decode(const void* q, int ldq, void* out, int ldo, const void* kc, co
   }
   dim3 grid(n_seqs, nkv, n_splits);
   // the caches are written only by the fused form (cos_t given), which gets them writable from its caller
-  kern<<<grid, DEC_WARPS * 32, smem, stream>>>((const T*)q, ldq, (T*)out, ldo, (T*)const_cast<void*>(kc), (T*)const_cast<void*>(vc),
-                                              page_table, table_stride, seq_slot, seq_pos, nh, nkv, hd, scale, n_splits, tk,
-                                              part_o, part_ml, g_attn_err, cos_t, sin_t, max_pos);
-  if (n_splits > 1) {
+  // both kernels are programmatic dependent launches: their set-up overlaps the tail of the kernel before
+  cudaError_t le = launch_pdl(2, kern, grid, dim3(DEC_WARPS * 32), smem, stream, (const T*)q, ldq, (T*)out, ldo,
+                              (T*)const_cast<void*>(kc), (T*)const_cast<void*>(vc), page_table, table_stride, seq_slot, seq_pos,
+                              nh, nkv, hd, scale, n_splits, tk, part_o, part_ml, g_attn_err, cos_t, sin_t, max_pos, counters);
+  if (le == cudaSuccess && n_splits > 1 && counters == nullptr) {
     dim3 cgrid(n_seqs, nh);
-    attn_decode_combine_kernel<T><<<cgrid, 64, 0, stream>>>(part_o, part_ml, (T*)out, ldo, nh, hd, n_splits);
+    le = launch_pdl(2, attn_decode_combine_kernel<T>, cgrid, dim3(64), 0, stream, (const float*)part_o, (const float*)part_ml,
+                    (T*)out, ldo, nh, hd, n_splits);
+  }
+  if (le != cudaSuccess) {
+    set_error("attn_decode: launch failed: %s", cudaGetErrorString(le));
+    return -2;
   }
   return 0;
 }
@@ -682,14 +739,16 @@ extern "C" int edgelm_attn_decode_rope(const void* qkv, int ldq, void* out, int 
                                        const int32_t* page_table, int table_stride, const int32_t* seq_slot,
                                        const int32_t* seq_pos, const float* cos_t, const float* sin_t, int max_pos,
                                        int n_seqs, int nh, int nkv, int hd, float scale, int n_splits, float* part_o,
-                                       float* part_ml, cudaStream_t stream) {
+                                       float* part_ml, int* counters, cudaStream_t stream) {
+  // counters: n_seqs * nkv int32 that are zero between calls (the kernel leaves them so); with them the
+  // splits are folded by the last block of the main kernel, without them by a second kernel.
   if (n_seqs == 0) return 0;
   if (check_heads("attn_decode_rope", nh, nkv, hd)) return -1;
   EL_REFUSE(n_splits >= 1 && n_splits <= 65535 && nkv <= 65535, "attn_decode_rope: bad split count %d", n_splits);
   EL_REFUSE(n_splits == 1 || (part_o && part_ml), "attn_decode_rope: %d splits need the scratch buffers", n_splits);
   EL_REFUSE(cos_t && sin_t && max_pos > 0, "attn_decode_rope: needs the position table");
   EL_ATT_DISPATCH(launch_decode, qkv, ldq, out, ldo, kcache, vcache, page_table, table_stride, seq_slot, seq_pos, n_seqs, nh,
-                  nkv, hd, scale, n_splits, part_o, part_ml, stream, cos_t, sin_t, max_pos);
+                  nkv, hd, scale, n_splits, part_o, part_ml, stream, cos_t, sin_t, max_pos, counters);
   EL_LAUNCH_CHECK("attn_decode_rope");
   return 0;
 }

@@ -73,6 +73,33 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   return red[32];
 }
 
+// Programmatic dependent launch: a kernel launched with `launch_pdl` may start while the kernel before
+// it on the stream is still running.  It must call `pdl_wait()` before it reads anything an earlier
+// kernel wrote or writes anything an earlier kernel reads; before that point it may only touch what
+// no kernel of the stream writes (weights, tables).  `pdl_launch_dependents()` lets the next kernel
+// start early in turn.  In a kernel launched the ordinary way both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Bit mask of the kernel families launched as programmatic dependent launches (1: few-rows matrix
+// products, 2: decode attention); 0: ordinary launches everywhere.
+int pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(int bit, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (pdl_enabled() & bit) ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 // The cache keeps keys and values in pages of PAGE tokens: [page][kv_head][PAGE][head_dim].
 constexpr int PAGE = 64;
 

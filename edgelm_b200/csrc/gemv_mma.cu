@@ -5,8 +5,9 @@
 // top, eight multiply-adds and eight shared-memory reads per weight and row, is what limits it
 // from 4 rows up.  Here the weights are the 16-row operand of mma.sync.m16n8k16 and the batch is
 // its 8 columns, so the arithmetic disappears behind the loads:
-//   * a block owns 16 output columns (16 rows of W); its 4 warps take the 32-wide K blocks in turn
-//     and their partial 16 x 8 tiles are added in shared memory at the end (fixed order 0..3);
+//   * a block owns 16 output columns (16 rows of W); its warps (4 to 16: more when the output is
+//     narrow, so that one round of loads covers K) take the 32-wide K blocks in turn and their
+//     partial 16 x 8 tiles are added in shared memory at the end, in the order of the warps;
 //   * a lane loads 16 bytes (8 consecutive k) of two weight rows per K block straight from global
 //     memory and uses them as the A fragments of two MMAs; the K index inside a block is permuted
 //     (the same permutation on both operands leaves the sum unchanged) so that those 16 bytes are
@@ -15,13 +16,14 @@
 //     hit distinct banks), optionally produced here as RMSNorm(x) from the float32 residual
 //     stream, rounded to bfloat16 as the stand-alone norm kernel rounds;
 //   * epilogues: store (bfloat16 or float32), += residual (float32), SwiGLU of two weights.
-// K must be a multiple of 8 with 16-byte aligned rows; M <= 16.
+// K must be a multiple of 8 with 16-byte aligned rows; M <= 16.  Launched as a programmatic dependent
+// launch: the first weight loads are issued before the wait for the previous kernel.
 #include "common.cuh"
 
 namespace edgelm {
 
 enum : int { GM_STORE = 0, GM_RESIDUAL = 1, GM_SWIGLU = 2 };
-constexpr int GM_WARPS = 4;
+constexpr int GM_MAX_WARPS = 16;
 constexpr int GM_COLS = 16;  // output columns per block
 
 __device__ __forceinline__ void mma_bf16_16x8x16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -35,14 +37,15 @@ __device__ __forceinline__ void mma_bf16_16x8x16(float* c, uint32_t a0, uint32_t
 __device__ __forceinline__ float gm_silu(float z) { return z / (1.0f + expf(-z)); }
 
 // NT: 8-row tiles of the batch (1: M <= 8, 2: M <= 16).  NORM: activations = RMSNorm(x).
-template <int EPI, typename TOut, int NT, bool NORM>
-__global__ void __launch_bounds__(GM_WARPS * 32)
+template <int EPI, typename TOut, int NT, bool NORM, int MAXW>  // MAXW: the most warps a block is launched with
+__global__ void __launch_bounds__(MAXW * 32)
 gemv_mma_kernel(const __nv_bfloat16* __restrict__ act, int lda, const float* __restrict__ x,
                 const float* __restrict__ norm_w, float eps, const __nv_bfloat16* __restrict__ W,
                 const __nv_bfloat16* __restrict__ W2, TOut* out, int ldo, const float* residual, int M, int N, int K,
                 int pitch /* bfloat16 elements per activation row in shared memory */) {
   constexpr int NW = EPI == GM_SWIGLU ? 2 : 1;
   constexpr int ROWS = 8 * NT;
+  const int GM_WARPS = blockDim.x >> 5;  // the block's warps share the K blocks
   extern __shared__ __align__(16) uint8_t gm_smem[];
   __nv_bfloat16* As = reinterpret_cast<__nv_bfloat16*>(gm_smem);                       // [ROWS][pitch]
   float* red = reinterpret_cast<float*>(gm_smem + (size_t)ROWS * pitch * 2);           // [GM_WARPS][NW][NT][32][4]
@@ -66,6 +69,8 @@ gemv_mma_kernel(const __nv_bfloat16* __restrict__ act, int lda, const float* __r
     }
   }
 
+  pdl_launch_dependents();
+  pdl_wait();  // from here on: activations that the kernel before this one wrote
   // ---- activations into shared memory (rows >= M are zero)
   if (NORM) {
     for (int r = warp; r < ROWS; r += GM_WARPS) {
@@ -154,7 +159,7 @@ gemv_mma_kernel(const __nv_bfloat16* __restrict__ act, int lda, const float* __r
     }
   }
 
-  // ---- add the warps' partial tiles (order 0..3), then the epilogue by warp 0
+  // ---- add the warps' partial tiles (in the order of the warps), then the epilogue by warp 0
   float* mine = red + (size_t)warp * NW * NT * 128;
 #pragma unroll
   for (int w = 0; w < NW; ++w)
@@ -204,19 +209,34 @@ static int launch_gemv_mma(const void* act, int lda, const float* x, const float
                            cudaStream_t stream) {
   constexpr int NW = EPI == GM_SWIGLU ? 2 : 1;
   const int pitch = act_pitch(K);
+  // warps per block: wide outputs fill the device with blocks and want few warps; narrow ones get up to
+  // 16 warps, about two K blocks each, so that a single round of loads is in flight per warp
+  const int n_kb = (K + 31) / 32, blocks = (N + GM_COLS - 1) / GM_COLS;
+  int GM_WARPS = 4;
+  if (blocks < 2 * 148) {
+    while (GM_WARPS < GM_MAX_WARPS && GM_WARPS * 2 <= (n_kb + 1) / 2) GM_WARPS *= 2;
+  }
   const size_t smem = (size_t)8 * NT * pitch * 2 + (size_t)GM_WARPS * NW * NT * 128 * 4 + 8 * NT * 4;
-  auto kern = gemv_mma_kernel<EPI, TOut, NT, NORM>;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) {
-      set_error("gemv_mma: %zu bytes of shared memory refused (K = %d): %s", smem, K, cudaGetErrorString(e));
+  auto go = [&](auto kern) -> int {
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) {
+        set_error("gemv_mma: %zu bytes of shared memory refused (K = %d): %s", smem, K, cudaGetErrorString(e));
+        return -2;
+      }
+    }
+    cudaError_t le = launch_pdl(1, kern, dim3((N + GM_COLS - 1) / GM_COLS), dim3(GM_WARPS * 32), smem, stream,
+                                (const __nv_bfloat16*)act, lda, x, norm_w, eps, (const __nv_bfloat16*)W, (const __nv_bfloat16*)W2,
+                                (TOut*)out, ldo, residual, M, N, K, pitch);
+    if (le != cudaSuccess) {
+      set_error("gemv_mma: launch failed: %s", cudaGetErrorString(le));
       return -2;
     }
-  }
-  kern<<<(N + GM_COLS - 1) / GM_COLS, GM_WARPS * 32, smem, stream>>>((const __nv_bfloat16*)act, lda, x, norm_w, eps,
-                                                                    (const __nv_bfloat16*)W, (const __nv_bfloat16*)W2,
-                                                                    (TOut*)out, ldo, residual, M, N, K, pitch);
-  return 0;
+    return 0;
+  };
+  if (GM_WARPS <= 4) return go(gemv_mma_kernel<EPI, TOut, NT, NORM, 4>);
+  if (GM_WARPS <= 8) return go(gemv_mma_kernel<EPI, TOut, NT, NORM, 8>);
+  return go(gemv_mma_kernel<EPI, TOut, NT, NORM, 16>);
 }
 
 }  // namespace edgelm

@@ -7,6 +7,7 @@ without the library, or without a device of compute capability 10.x, importing t
 raises.
 """
 import ctypes
+import os
 import threading
 
 import torch
@@ -41,6 +42,8 @@ def lib():
                 except OSError as e:  # pragma: no cover
                     raise KernelError(f"edgelm_b200: cannot load the kernel library {path}: {e}") from e
                 loaded.edgelm_last_error.restype = ctypes.c_char_p
+                if os.environ.get("EDGELM_PDL") is not None:
+                    loaded.edgelm_set_pdl(int(os.environ["EDGELM_PDL"]))
                 _lib = loaded
     return _lib
 
@@ -276,7 +279,7 @@ def attn_decode(qkv, out, kcache, vcache, page_table, seq_slot, seq_pos, n_seqs,
 
 
 def attn_decode_rope(qkv, out, kcache, vcache, page_table, seq_slot, seq_pos, cos, sin, n_seqs, nh, nkv, hd, scale,
-                     n_splits=1, part_o=None, part_ml=None):
+                     n_splits=1, part_o=None, part_ml=None, counters=None):
     """Decode attention with RoPE and the cache append fused in: `qkv` holds the raw projections of one
     new token per sequence; the rotated keys and the values are written into the cache pages."""
     _need(qkv.dtype == out.dtype == kcache.dtype and qkv.stride(1) == 1 and out.stride(1) == 1, "attn_decode_rope: layout")
@@ -284,13 +287,17 @@ def attn_decode_rope(qkv, out, kcache, vcache, page_table, seq_slot, seq_pos, co
     _need(cos.dtype == torch.float32 and cos.shape[1] == hd // 2 and cos.is_contiguous() and sin.shape == cos.shape and sin.is_contiguous(), "attn_decode_rope: table layout")
     for t, n in ((page_table, "page_table"), (seq_slot, "seq_slot"), (seq_pos, "seq_pos")):
         _i32(t, n)
+    if counters is not None:
+        _i32(counters, "counters")
+        _need(counters.numel() >= n_seqs * nkv, "attn_decode_rope: one counter per sequence and kv head")
     if n_splits > 1:
         _need(part_o is not None and part_o.dtype == torch.float32 and part_o.numel() >= n_seqs * nh * n_splits * hd, "attn_decode_rope: part_o too small")
         _need(part_ml is not None and part_ml.dtype == torch.float32 and part_ml.numel() >= n_seqs * nh * n_splits * 2, "attn_decode_rope: part_ml too small")
     _check(lib().edgelm_attn_decode_rope(_p(qkv), qkv.stride(0), _p(out), out.stride(0), _p(kcache), _p(vcache), _dt(qkv),
                                          _p(page_table), page_table.stride(0), _p(seq_slot), _p(seq_pos), _p(cos), _p(sin),
                                          cos.shape[0], n_seqs, nh, nkv, hd, ctypes.c_float(scale), n_splits, _p(part_o),
-                                         _p(part_ml), _stream()), launches=2 if n_splits > 1 else 1)
+                                         _p(part_ml), _p(counters), _stream()),
+           launches=2 if (n_splits > 1 and counters is None) else 1)
 
 
 def attn_set_error_word(err):

@@ -15,7 +15,16 @@ void set_error(const char* fmt, ...) {
   va_end(ap);
 }
 
+static int g_pdl = 0;
+int pdl_enabled() { return g_pdl; }
+
 }  // namespace edgelm
+
+// Switch programmatic dependent launch of the decode kernels on (1, the default) or off (0).
+extern "C" int edgelm_set_pdl(int on) {
+  edgelm::g_pdl = on;
+  return 0;
+}
 
 // Message of the last refused or failed call of this thread.
 extern "C" const char* edgelm_last_error() { return edgelm::g_error; }

@@ -80,9 +80,12 @@ class Attention(Part):
             if splits > 1:
                 part_o = ws.alloc((ctx.n_seqs * self.nh * splits * self.hd,), torch.float32)
                 part_ml = ws.alloc((ctx.n_seqs * self.nh * splits * 2,), torch.float32)
+            # the splits are folded by a second small kernel: measured faster than handing the fold to the last
+            # block of the main kernel through `ctx.zero_counters` (1.11 ms against 1.17 ms per step at batch 8)
+            counters = None
             with ctx.prof("attn_decode"):
                 ops.attn_decode_rope(qkv, a, cache.k, cache.v, table, ctx.seq_index, ctx.seq_pos, tables[0], tables[1],
-                                     ctx.n_seqs, self.nh, self.nkv, self.hd, self.scale, splits, part_o, part_ml)
+                                     ctx.n_seqs, self.nh, self.nkv, self.hd, self.scale, splits, part_o, part_ml, counters)
             with ctx.prof("o_proj_residual"):
                 linear.matmul(ctx, a, self.w_o, x, epilogue=linear.EPI_RESIDUAL, residual=x)
             return

@@ -15,7 +15,7 @@ from ..csrc import ops
 EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU = ops.EPI_STORE, ops.EPI_RESIDUAL, ops.EPI_SWIGLU
 
 FEW_ROWS = 16  # up to here one pass over the weights with all rows in shared memory is bandwidth-bound already
-MMA_MIN_ROWS = 3        # below, narrow outputs run faster on the CUDA-core kernel (more blocks, no tile padding)
+MMA_MIN_ROWS = 1        # rows from which the tensor-core few-rows kernel is used (measured: never slower)
 MMA_WIDE_COLUMNS = 8192  # from here on (the vocabulary) the tensor-core kernel wins at any row count
 
 

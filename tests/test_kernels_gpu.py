@@ -619,6 +619,16 @@ def test_attn_decode_rope_equals_separate_kernels(dtype, nh, nkv, hd, n_splits):
                        1.0 / math.sqrt(hd), n_splits, po, pm)
     assert int(err.item()) == 0
     assert rel_err(got, want) < (1e-6 if dtype == torch.float32 else 4e-3)
+    # with counters the last block folds the splits itself (sums in another fixed order); the counters are zero again
+    c = PagedCase(o, dtype, lengths, nkv, hd, seed=nh + hd)
+    counters = torch.zeros(B * nkv, dtype=torch.int32, device=dev())
+    for _ in range(2):
+        got2 = torch.full_like(want, float("nan"))
+        po, pm = mk()
+        o.attn_decode_rope(raw.clone(), got2, c.kcache, c.vcache, c.table, c.seq_slot, seq_pos, cos_t, sin_t, B, nh, nkv, hd,
+                           1.0 / math.sqrt(hd), n_splits, po, pm, counters)
+        assert rel_err(got2, got) < (1e-6 if dtype == torch.float32 else 4e-3)
+        assert int(counters.abs().sum()) == 0
     for s, n in enumerate(lengths):   # the appended rows are the same, nothing else changed
         for cache_a, cache_b in ((a.kcache, b.kcache), (a.vcache, b.vcache)):
             page = int(a.table[int(a.seq_slot[s]), (n - 1) // o.PAGE])
