@@ -12,6 +12,9 @@
 //   * O += P V: the probabilities go from accumulator layout straight to A fragments (rounded to
 //     bfloat16), V fragments by ldmatrix.trans.
 // A page whose first key lies beyond every row of a warp is skipped by that warp.
+// Long rows need more warps than four: with NG warp groups per block, group i visits the pages i,
+// i + NG, ... with shared-memory stages of its own and a named barrier of its own; at the end the
+// groups' partial (max, sum, output) are merged in shared memory in the order of the groups.
 // Takes head sizes 32, 64, 96, 128; others run on the CUDA-core kernel of attention.cu.
 #include <math_constants.h>
 
@@ -44,8 +47,8 @@ __device__ __forceinline__ uint32_t pm_pack(float a, float b) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-template <int HDT>  // head size / 16, even
-__global__ void __launch_bounds__(PM_WARPS * 32)
+template <int HDT, int NG>  // head size / 16 (even); warp groups that share the pages of a tile
+__global__ void __launch_bounds__(PM_WARPS * 32 * NG)
 attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat16* __restrict__ out, int ldo,
                         const __nv_bfloat16* __restrict__ kcache, const __nv_bfloat16* __restrict__ vcache,
                         const int32_t* __restrict__ page_table, int table_stride, const int32_t* __restrict__ seq_slot,
@@ -56,12 +59,13 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
   constexpr int PITCH = HD + 8;             // elements: 16 bytes of padding per row
   constexpr int CHUNKS = HD / 8;            // 16-byte chunks per row
   extern __shared__ __align__(16) uint8_t pm_raw[];
-  __nv_bfloat16* sm = reinterpret_cast<__nv_bfloat16*>(pm_raw);  // [2 stages][K: 64 x PITCH | V: 64 x PITCH]
   constexpr int STAGE = 2 * PAGE * PITCH;
+  const int group = threadIdx.x / (PM_WARPS * 32), gtid = threadIdx.x % (PM_WARPS * 32);
+  __nv_bfloat16* sm = reinterpret_cast<__nv_bfloat16*>(pm_raw) + (size_t)group * 2 * STAGE;  // this group's [2 stages][K: 64 x PITCH | V: 64 x PITCH]
 
   const int tile = blockIdx.x, head = blockIdx.y;
   const int g = nh / nkv, kvh = head / g;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gid = lane >> 2, tig = lane & 3;
+  const int lane = threadIdx.x & 31, warp = (threadIdx.x >> 5) % PM_WARPS, gid = lane >> 2, tig = lane & 3;
   const int seq = tile_seq[tile], tok0 = tile_tok0[tile], ntok = tile_ntok[tile], pos0 = tile_pos0[tile];
   const int32_t* pages = page_table + (size_t)seq_slot[seq] * table_stride;
   const int nkeys_block = pos0 + ntok;      // keys 0 .. pos0 + ntok - 1
@@ -78,7 +82,7 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
     const int valid = min(PAGE, nkeys_block - pg * PAGE);
     __nv_bfloat16* ks = sm + stage * STAGE;
     __nv_bfloat16* vs = ks + PAGE * PITCH;
-    for (int i = threadIdx.x; i < PAGE * CHUNKS; i += blockDim.x) {
+    for (int i = gtid; i < PAGE * CHUNKS; i += PM_WARPS * 32) {
       const int r = i / CHUNKS, c = i - r * CHUNKS;
       const int bytes = r < valid ? 16 : 0;   // rows past the last key: zero fill, nothing is read
       pm_cp16(pm_smem(ks + r * PITCH + c * 8), kp + r * HD + c * 8, bytes);
@@ -106,16 +110,20 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
   for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float mA = -CUDART_INF_F, mB = -CUDART_INF_F, lA = 0.f, lB = 0.f;
 
-  load_page(0, 0);
-  for (int pg = 0; pg < n_pages; ++pg) {
-    const int stage = pg & 1;
-    if (pg + 1 < n_pages) {
-      load_page(pg + 1, stage ^ 1);
+  auto group_sync = [&]() {   // the 128 threads of this group (barrier 0 is __syncthreads)
+    if (NG == 1) __syncthreads();
+    else asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "r"(PM_WARPS * 32) : "memory");
+  };
+  if (group < n_pages) load_page(group, 0);
+  for (int pg = group, it = 0; pg < n_pages; pg += NG, ++it) {
+    const int stage = it & 1;
+    if (pg + NG < n_pages) {
+      load_page(pg + NG, stage ^ 1);
       asm volatile("cp.async.wait_group 1;" ::: "memory");
     } else {
       asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
-    __syncthreads();
+    group_sync();
     if (pg * PAGE <= warp_limit) {   // else: no row of this warp sees this page
       const __nv_bfloat16* ks = sm + stage * STAGE;
       const __nv_bfloat16* vs = ks + PAGE * PITCH;
@@ -196,7 +204,50 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
         }
       }
     }
-    __syncthreads();  // this stage is free for the page after next
+    group_sync();  // this stage is free for the page after next
+  }
+  if (NG > 1) {
+    // ---- merge the groups: groups 1.. leave (max, sum, output) in shared memory, group 0 folds them in order
+    __syncthreads();
+    float* mg = reinterpret_cast<float*>(pm_raw);            // [NG - 1][64 rows][HD + 2]
+    constexpr int MP = HD + 2;
+    if (group > 0) {
+      float* a = mg + ((size_t)(group - 1) * PM_ROWS + rowA) * MP;
+      float* b = mg + ((size_t)(group - 1) * PM_ROWS + rowB) * MP;
+#pragma unroll
+      for (int dt = 0; dt < HD / 8; ++dt) {
+        a[dt * 8 + tig * 2] = o[dt][0];
+        a[dt * 8 + tig * 2 + 1] = o[dt][1];
+        b[dt * 8 + tig * 2] = o[dt][2];
+        b[dt * 8 + tig * 2 + 1] = o[dt][3];
+      }
+      if (tig == 0) {
+        a[HD] = mA;
+        a[HD + 1] = lA;
+        b[HD] = mB;
+        b[HD + 1] = lB;
+      }
+    }
+    __syncthreads();
+    if (group > 0) return;
+    for (int gsrc = 1; gsrc < NG; ++gsrc) {
+      const float* a = mg + ((size_t)(gsrc - 1) * PM_ROWS + rowA) * MP;
+      const float* b = mg + ((size_t)(gsrc - 1) * PM_ROWS + rowB) * MP;
+      const float nmA = fmaxf(mA, a[HD]), nmB = fmaxf(mB, b[HD]);
+      const float refA = nmA == -CUDART_INF_F ? 0.f : nmA, refB = nmB == -CUDART_INF_F ? 0.f : nmB;
+      const float fA0 = expf(mA - refA), fA1 = expf(a[HD] - refA), fB0 = expf(mB - refB), fB1 = expf(b[HD] - refB);
+      lA = lA * fA0 + a[HD + 1] * fA1;
+      lB = lB * fB0 + b[HD + 1] * fB1;
+      mA = nmA;
+      mB = nmB;
+#pragma unroll
+      for (int dt = 0; dt < HD / 8; ++dt) {
+        o[dt][0] = o[dt][0] * fA0 + a[dt * 8 + tig * 2] * fA1;
+        o[dt][1] = o[dt][1] * fA0 + a[dt * 8 + tig * 2 + 1] * fA1;
+        o[dt][2] = o[dt][2] * fB0 + b[dt * 8 + tig * 2] * fB1;
+        o[dt][3] = o[dt][3] * fB0 + b[dt * 8 + tig * 2 + 1] * fB1;
+      }
+    }
   }
   const float invA = 1.0f / lA, invB = 1.0f / lB;
 #pragma unroll
@@ -207,24 +258,50 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
   }
 }
 
-template <int HDT>
-static int launch_prefill_mma(const void* q, int ldq, void* out, int ldo, const void* kc, const void* vc,
-                              const int32_t* page_table, int table_stride, const int32_t* seq_slot, const int32_t* tile_seq,
-                              const int32_t* tile_tok0, const int32_t* tile_ntok, const int32_t* tile_pos0, int n_tiles,
-                              int nh, int nkv, float scale, cudaStream_t stream) {
+template <int HDT, int NG>
+static int launch_prefill_mma_ng(const void* q, int ldq, void* out, int ldo, const void* kc, const void* vc,
+                                 const int32_t* page_table, int table_stride, const int32_t* seq_slot, const int32_t* tile_seq,
+                                 const int32_t* tile_tok0, const int32_t* tile_ntok, const int32_t* tile_pos0, int n_tiles,
+                                 int nh, int nkv, float scale, cudaStream_t stream) {
   constexpr int HD = HDT * 16;
-  const size_t smem = (size_t)2 * 2 * PAGE * (HD + 8) * 2;
-  auto kern = attn_prefill_mma_kernel<HDT>;
+  const size_t smem = (size_t)NG * 2 * 2 * PAGE * (HD + 8) * 2;
+  auto kern = attn_prefill_mma_kernel<HDT, NG>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) {
     set_error("attn_prefill_mma: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
     return -2;
   }
   dim3 grid(n_tiles, nh);
-  kern<<<grid, PM_WARPS * 32, smem, stream>>>((const __nv_bfloat16*)q, ldq, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)kc,
-                                             (const __nv_bfloat16*)vc, page_table, table_stride, seq_slot, tile_seq, tile_tok0,
-                                             tile_ntok, tile_pos0, nh, nkv, scale);
+  kern<<<grid, PM_WARPS * 32 * NG, smem, stream>>>((const __nv_bfloat16*)q, ldq, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)kc,
+                                                  (const __nv_bfloat16*)vc, page_table, table_stride, seq_slot, tile_seq, tile_tok0,
+                                                  tile_ntok, tile_pos0, nh, nkv, scale);
   return 0;
+}
+
+// Warp groups per block: one when the grid fills the device by itself or rows are short; two or four when
+// few blocks walk many pages each (a single long prompt).
+static int prefill_groups(int n_tiles, int nh, int max_keys, int hd, int force) {
+  if (force == 1 || force == 2 || force == 4) return (force == 4 && hd > 64) ? 2 : force;
+  const long long blocks = (long long)n_tiles * nh;
+  const int pages = (max_keys + PAGE - 1) / PAGE;
+  if (pages >= 16 && blocks < 2 * 148 * 2 && hd <= 64) return 4;
+  if (pages >= 6 && blocks < 4 * 148 * 2) return 2;
+  return 1;
+}
+
+template <int HDT>
+static int launch_prefill_mma(int groups, const void* q, int ldq, void* out, int ldo, const void* kc, const void* vc,
+                              const int32_t* page_table, int table_stride, const int32_t* seq_slot, const int32_t* tile_seq,
+                              const int32_t* tile_tok0, const int32_t* tile_ntok, const int32_t* tile_pos0, int n_tiles,
+                              int nh, int nkv, float scale, cudaStream_t stream) {
+#define EL_PM(NG) launch_prefill_mma_ng<HDT, NG>(q, ldq, out, ldo, kc, vc, page_table, table_stride, seq_slot, tile_seq, tile_tok0, tile_ntok, tile_pos0, n_tiles, nh, nkv, scale, stream)
+  if (groups == 4) {
+    if constexpr (HDT <= 4) return EL_PM(4);
+    else return EL_PM(2);
+  }
+  if (groups == 2) return EL_PM(2);
+  return EL_PM(1);
+#undef EL_PM
 }
 
 }  // namespace edgelm
@@ -243,18 +320,21 @@ extern "C" int edgelm_attn_prefill_mma(const void* q, int ldq, void* out, int ld
                                        const int32_t* page_table, int table_stride, const int32_t* seq_slot,
                                        const int32_t* tile_seq, const int32_t* tile_tok0, const int32_t* tile_ntok,
                                        const int32_t* tile_pos0, int n_tiles, int nh, int nkv, int hd, float scale,
-                                       cudaStream_t stream) {
+                                       int max_keys, int force_groups, cudaStream_t stream) {
+  // max_keys: the most keys a tile attends over (a hint for how many warp groups share a tile's pages);
+  // force_groups: 0 to choose, or 1, 2, 4.
   if (n_tiles == 0) return 0;
   EL_REFUSE(nh > 0 && nkv > 0 && nh % nkv == 0, "attn_prefill_mma: %d query heads are not a multiple of %d key/value heads", nh, nkv);
   EL_REFUSE(edgelm_attn_prefill_mma_takes(hd), "attn_prefill_mma: head size %d (takes 32, 64, 96, 128)", hd);
   EL_REFUSE(ldq % 2 == 0 && ldo % 2 == 0 && (uintptr_t)q % 4 == 0 && (uintptr_t)out % 4 == 0, "attn_prefill_mma: rows must be 4-byte aligned");
   EL_REFUSE(n_tiles > 0 && nh <= 65535, "attn_prefill_mma: bad grid");
+  const int groups = prefill_groups(n_tiles, nh, max_keys, hd, force_groups);
   int rc = 0;
   switch (hd / 16) {
-    case 2: rc = launch_prefill_mma<2>(q, ldq, out, ldo, kcache, vcache, page_table, table_stride, seq_slot, tile_seq, tile_tok0, tile_ntok, tile_pos0, n_tiles, nh, nkv, scale, stream); break;
-    case 4: rc = launch_prefill_mma<4>(q, ldq, out, ldo, kcache, vcache, page_table, table_stride, seq_slot, tile_seq, tile_tok0, tile_ntok, tile_pos0, n_tiles, nh, nkv, scale, stream); break;
-    case 6: rc = launch_prefill_mma<6>(q, ldq, out, ldo, kcache, vcache, page_table, table_stride, seq_slot, tile_seq, tile_tok0, tile_ntok, tile_pos0, n_tiles, nh, nkv, scale, stream); break;
-    case 8: rc = launch_prefill_mma<8>(q, ldq, out, ldo, kcache, vcache, page_table, table_stride, seq_slot, tile_seq, tile_tok0, tile_ntok, tile_pos0, n_tiles, nh, nkv, scale, stream); break;
+    case 2: rc = launch_prefill_mma<2>(groups, q, ldq, out, ldo, kcache, vcache, page_table, table_stride, seq_slot, tile_seq, tile_tok0, tile_ntok, tile_pos0, n_tiles, nh, nkv, scale, stream); break;
+    case 4: rc = launch_prefill_mma<4>(groups, q, ldq, out, ldo, kcache, vcache, page_table, table_stride, seq_slot, tile_seq, tile_tok0, tile_ntok, tile_pos0, n_tiles, nh, nkv, scale, stream); break;
+    case 6: rc = launch_prefill_mma<6>(groups, q, ldq, out, ldo, kcache, vcache, page_table, table_stride, seq_slot, tile_seq, tile_tok0, tile_ntok, tile_pos0, n_tiles, nh, nkv, scale, stream); break;
+    case 8: rc = launch_prefill_mma<8>(groups, q, ldq, out, ldo, kcache, vcache, page_table, table_stride, seq_slot, tile_seq, tile_tok0, tile_ntok, tile_pos0, n_tiles, nh, nkv, scale, stream); break;
   }
   if (rc) return rc;
   EL_LAUNCH_CHECK("attn_prefill_mma");

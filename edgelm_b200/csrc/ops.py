@@ -252,7 +252,7 @@ def attn_prefill_mma_takes(dtype, hd):
 
 
 def attn_prefill_mma(qkv, out, kcache, vcache, page_table, seq_slot, tile_seq, tile_tok0, tile_ntok, tile_pos0, n_tiles,
-                     nh, nkv, hd, scale):
+                     nh, nkv, hd, scale, max_keys=0, force_groups=0):
     """Causal attention of new tokens over the paged cache on mma.sync tensor cores; tiles of at most 64 tokens."""
     _need(qkv.dtype == out.dtype == kcache.dtype == torch.bfloat16 and qkv.stride(1) == 1 and out.stride(1) == 1, "attn_prefill_mma: layout")
     for t, n in ((page_table, "page_table"), (seq_slot, "seq_slot"), (tile_seq, "tile_seq"), (tile_tok0, "tile_tok0"),
@@ -260,7 +260,8 @@ def attn_prefill_mma(qkv, out, kcache, vcache, page_table, seq_slot, tile_seq, t
         _i32(t, n)
     _check(lib().edgelm_attn_prefill_mma(_p(qkv), qkv.stride(0), _p(out), out.stride(0), _p(kcache), _p(vcache),
                                          _p(page_table), page_table.stride(0), _p(seq_slot), _p(tile_seq), _p(tile_tok0),
-                                         _p(tile_ntok), _p(tile_pos0), n_tiles, nh, nkv, hd, ctypes.c_float(scale), _stream()))
+                                         _p(tile_ntok), _p(tile_pos0), n_tiles, nh, nkv, hd, ctypes.c_float(scale), int(max_keys),
+                                         int(force_groups), _stream()))
 
 
 def attn_decode(qkv, out, kcache, vcache, page_table, seq_slot, seq_pos, n_seqs, nh, nkv, hd, scale, n_splits=1,

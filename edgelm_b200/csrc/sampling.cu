@@ -29,12 +29,40 @@ argmax_rows_kernel(const float* __restrict__ logits, int ld, int vocab, int32_t*
   const float* row = logits + (size_t)blockIdx.x * ld;
   float best = -CUDART_INF_F;
   int idx = 0x7fffffff;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-    const float v = row[i];
-    if (v > best || (idx == 0x7fffffff && !(v != v))) {  // strict: the first maximum of this thread's indices
+  auto take = [&](float v, int i) {  // strict >: the first maximum among this thread's ascending indices
+    if (v > best || (idx == 0x7fffffff && !(v != v))) {
       best = v;
       idx = i;
     }
+  };
+  if (((uintptr_t)row & 15) == 0) {
+    // 16-byte loads, four in flight per thread: the row is read at memory speed, not at one latency per element
+    const int n4 = vocab >> 2;
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+    int i = threadIdx.x;
+    for (; i + 3 * (int)blockDim.x < n4; i += 4 * blockDim.x) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = row4[i + u * blockDim.x];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int b = (i + u * blockDim.x) * 4;
+        take(v[u].x, b);
+        take(v[u].y, b + 1);
+        take(v[u].z, b + 2);
+        take(v[u].w, b + 3);
+      }
+    }
+    for (; i < n4; i += blockDim.x) {
+      const float4 v = row4[i];
+      take(v.x, i * 4);
+      take(v.y, i * 4 + 1);
+      take(v.z, i * 4 + 2);
+      take(v.w, i * 4 + 3);
+    }
+    for (int j = (n4 << 2) + threadIdx.x; j < vocab; j += blockDim.x) take(row[j], j);
+  } else {
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) take(row[i], i);
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {

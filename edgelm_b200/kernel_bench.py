@@ -104,7 +104,7 @@ def main(argv=None):
             "rmsnorm": lambda l: o.rmsnorm(x, nw, 1e-5, h),
             "qkv_proj": lambda l: o.gemm_tc(h, wq[l], qkv, err),
             "rope_kv_append": lambda l: o.rope_kv_append(qkv, tokpos, tokseq, seq, table, cos, sin, kc[l], vc[l], nh, nkv, hd, err),
-            "attn_prefill": lambda l: o.attn_prefill_mma(qkv, att, kc[l], vc[l], table, seq, t_seq, t_tok0, t_ntok, t_pos0, nt, nh, nkv, hd, scale),
+            "attn_prefill": lambda l: o.attn_prefill_mma(qkv, att, kc[l], vc[l], table, seq, t_seq, t_tok0, t_ntok, t_pos0, nt, nh, nkv, hd, scale, max_keys=T),
             "o_proj_residual": lambda l: o.gemm_tc(att, wo[l], x, err, epilogue=o.EPI_RESIDUAL, residual=x),
             "gate_up_swiglu": lambda l: o.gemm_tc(h, wg[l], mid, err, epilogue=o.EPI_SWIGLU, w2=wu[l]),
             "down_proj_residual": lambda l: o.gemm_tc(mid, wd[l], x, err, epilogue=o.EPI_RESIDUAL, residual=x),

@@ -104,7 +104,8 @@ class Attention(Part):
             tiles = ctx.tiles(ops.MMA_PREFILL_TILE)
             with ctx.prof("attn_prefill"):
                 ops.attn_prefill_mma(qkv, a, cache.k, cache.v, table, ctx.seq_index, tiles.seq, tiles.tok0, tiles.ntok,
-                                     tiles.pos0, tiles.count, self.nh, self.nkv, self.hd, self.scale)
+                                     tiles.pos0, tiles.count, self.nh, self.nkv, self.hd, self.scale,
+                                     max_keys=max(p + n for p, n in zip(ctx.seq_first_positions, ctx.seq_lengths)))
         else:
             tiles = ctx.tiles(self.tile_tokens)
             with ctx.prof("attn_prefill"):

@@ -534,8 +534,9 @@ def test_gemv_mma_row_independent_of_batch_and_refusals():
 
 
 # ----------------------------------------------------------------------------- prefill attention on mma.sync (bfloat16)
+@pytest.mark.parametrize("groups", [0, 1, 2, 4])
 @pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 32), (9, 3, 64), (3, 1, 96), (4, 4, 128), (8, 1, 64)])
-def test_attn_prefill_mma(nh, nkv, hd):
+def test_attn_prefill_mma(nh, nkv, hd, groups):
     o = ops()
     assert o.attn_prefill_mma_takes(torch.bfloat16, hd) and not o.attn_prefill_mma_takes(torch.bfloat16, 48)
     assert not o.attn_prefill_mma_takes(torch.float32, hd)
@@ -557,7 +558,8 @@ def test_attn_prefill_mma(nh, nkv, hd):
     mk = lambda x: torch.tensor(x, dtype=torch.int32, device=dev())
     out = torch.full((T, nh * hd), float("nan"), dtype=torch.bfloat16, device=dev())
     o.attn_prefill_mma(qkv, out, case.kcache, case.vcache, case.table, case.seq_slot, mk(tile_seq), mk(tile_tok0),
-                       mk(tile_ntok), mk(tile_pos0), len(tile_seq), nh, nkv, hd, 1.0 / math.sqrt(hd))
+                       mk(tile_ntok), mk(tile_pos0), len(tile_seq), nh, nkv, hd, 1.0 / math.sqrt(hd),
+                       max_keys=max(lengths), force_groups=groups)
     t0 = 0
     for s, (p0, n) in enumerate(seqs):
         want = attention_rows(qkv[t0:t0 + n, :nh * hd].float().cpu(), case.k[s], case.v[s], p0, nh, nkv, hd)
