@@ -578,6 +578,10 @@ attn_decode_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ld
   }
 }
 
+}  // namespace edgelm
+#include "attention_decode_mma.cuh"
+namespace edgelm {
+
 template <typename T>
 __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                            T* __restrict__ out, int ldo, int nh, int hd, int n_splits) {
@@ -637,20 +641,44 @@ int launch_decode(const void* q, int ldq, void* out, int ldo, const void* kc, co
                   float scale, int n_splits, float* part_o, float* part_ml, cudaStream_t stream,
                   const float* cos_t = nullptr, const float* sin_t = nullptr, int max_pos = 0, int* counters = nullptr) {
   constexpr int NP = NC <= 2 ? 1 : NC / 2;  // pairs of dims per lane: ceil(hd / 64)
-  const int tk = decode_tile_keys(hd, sizeof(T));
-  const size_t smem = decode_head_bytes(hd) + (size_t)DEC_WARPS * 2 * tk * hd * sizeof(T);
-  auto kern = attn_decode_kernel<T, NP>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) {
-    set_error("attn_decode: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
-    return -2;
-  }
   dim3 grid(n_seqs, nkv, n_splits);
-  // the caches are written only by the fused form (cos_t given), which gets them writable from its caller
-  // both kernels are programmatic dependent launches: their set-up overlaps the tail of the kernel before
-  cudaError_t le = launch_pdl(2, kern, grid, dim3(DEC_WARPS * 32), smem, stream, (const T*)q, ldq, (T*)out, ldo,
-                              (T*)const_cast<void*>(kc), (T*)const_cast<void*>(vc), page_table, table_stride, seq_slot, seq_pos,
-                              nh, nkv, hd, scale, n_splits, tk, part_o, part_ml, g_attn_err, cos_t, sin_t, max_pos, counters);
+  cudaError_t le = cudaSuccess;
+  bool on_mma = false;
+  if constexpr (sizeof(T) == 2) {
+    // bfloat16 with a head size the MMAs tile (32, 64, 96, 128): the tensor-core kernel; it folds the splits
+    // with the combine kernel only (no counters)
+    if ((hd == 32 || hd == 64 || hd == 96 || hd == 128) && counters == nullptr) {
+      on_mma = true;
+      const size_t smem = decode_mma_head_bytes(hd) + (size_t)DEC_WARPS * 2 * PAGE * (hd + 8) * 2;
+      auto go = [&](auto kern) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        return launch_pdl(2, kern, grid, dim3(DEC_WARPS * 32), smem, stream, (const __nv_bfloat16*)q, ldq, (__nv_bfloat16*)out, ldo,
+                          (__nv_bfloat16*)const_cast<void*>(kc), (__nv_bfloat16*)const_cast<void*>(vc), page_table, table_stride,
+                          seq_slot, seq_pos, nh, nkv, scale, n_splits, part_o, part_ml, g_attn_err, cos_t, sin_t, max_pos);
+      };
+      switch (hd / 16) {
+        case 2: le = go(attn_decode_mma_kernel<2>); break;
+        case 4: le = go(attn_decode_mma_kernel<4>); break;
+        case 6: le = go(attn_decode_mma_kernel<6>); break;
+        default: le = go(attn_decode_mma_kernel<8>); break;
+      }
+    }
+  }
+  if (!on_mma) {
+    const int tk = decode_tile_keys(hd, sizeof(T));
+    const size_t smem = decode_head_bytes(hd) + (size_t)DEC_WARPS * 2 * tk * hd * sizeof(T);
+    auto kern = attn_decode_kernel<T, NP>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) {
+      set_error("attn_decode: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+      return -2;
+    }
+    // both kernels are programmatic dependent launches when that is switched on
+    le = launch_pdl(2, kern, grid, dim3(DEC_WARPS * 32), smem, stream, (const T*)q, ldq, (T*)out, ldo,
+                    (T*)const_cast<void*>(kc), (T*)const_cast<void*>(vc), page_table, table_stride, seq_slot, seq_pos,
+                    nh, nkv, hd, scale, n_splits, tk, part_o, part_ml, g_attn_err, cos_t, sin_t, max_pos, counters);
+  }
   if (le == cudaSuccess && n_splits > 1 && counters == nullptr) {
     dim3 cgrid(n_seqs, nh);
     le = launch_pdl(2, attn_decode_combine_kernel<T>, cgrid, dim3(64), 0, stream, (const float*)part_o, (const float*)part_ml,

@@ -1,0 +1,326 @@
+// Decode attention on the tensor cores (bfloat16 cache): the variant of attn_decode_kernel whose
+// scores and weighted values are mma.sync.m16n8k16 products.  Included by attention.cu, which owns
+// the entry points, the split bookkeeping and the combine kernel.
+//
+// Same decomposition as the CUDA-core kernel: grid (sequence, kv head, split), 4 warps, a warp per
+// 64-key tile, partials folded in shared memory and, across splits, by the combine kernel.  What
+// differs is inside a tile.  The g query heads that share the kv head are the rows of a 16-row A
+// operand (rows from g on are zero), so one tile costs 8 x hd/16 MMAs for the scores and as many
+// for the values instead of thousands of multiply-adds: at batch 64 the kernel was bound by
+// instruction issue, not by memory.  Key and value rows come by one cp.async.bulk per row into
+// rows padded by 16 bytes (all on the warp's mbarrier), so that ldmatrix reads hit distinct banks.
+// Rows of the last tile that lie past the sequence's end are zeroed in shared memory before use.
+#pragma once
+
+namespace edgelm {
+
+__device__ __forceinline__ void dm_mma(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void dm_ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void dm_ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ uint32_t dm_pack(float a, float b) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+constexpr int DM_ROWS = 16;  // query heads of a kv head served in one pass (rows of the A operand)
+
+// Shared memory before the per-warp tiles: queries [16][hd + 8] bfloat16, the new token's key and value,
+// the warps' mbarriers.  (A warp's partial result [16][hd + 2] float goes into its own key tile when its
+// tiles are done: 3 blocks of 4 warps then fit an SM at head size 64.)
+__host__ __device__ inline size_t decode_mma_head_bytes(int hd) {
+  const size_t b = (size_t)DM_ROWS * (hd + 8) * 2 + 2 * (size_t)hd * 2 + DEC_WARPS * 8;
+  return (b + 127) / 128 * 128;
+}
+
+template <int HDT>  // head size / 16 (2, 4, 6, 8: the MMAs pair up K steps and value columns)
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat16* __restrict__ out, int ldo,
+                       __nv_bfloat16* kcache, __nv_bfloat16* vcache, const int32_t* __restrict__ page_table,
+                       int table_stride, const int32_t* __restrict__ seq_slot, const int32_t* __restrict__ seq_pos, int nh,
+                       int nkv, float scale, int n_splits, float* __restrict__ part_o, float* __restrict__ part_ml, int* err,
+                       const float* __restrict__ cos_t, const float* __restrict__ sin_t, int max_pos) {
+  using T = __nv_bfloat16;
+  constexpr int HD = HDT * 16;
+  constexpr int PITCH = HD + 8;          // elements per padded row
+  constexpr int WS = HD + 2;
+  constexpr int TILE = PAGE * PITCH;     // elements of a K (or V) tile in shared memory
+  extern __shared__ __align__(128) uint8_t dm_raw[];
+  T* Qs = reinterpret_cast<T*>(dm_raw);                                        // [16][PITCH]
+  T* newkv = Qs + DM_ROWS * PITCH;                                             // [2][HD]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(newkv + 2 * HD);                // [DEC_WARPS]
+  static_assert(DM_ROWS * WS * 4 <= TILE * 2, "a warp's partial fits its key tile");
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gid = lane >> 2, tig = lane & 3;
+  T* Kt = reinterpret_cast<T*>(dm_raw + decode_mma_head_bytes(HD)) + (size_t)warp * 2 * TILE;
+  T* Vt = Kt + TILE;
+
+  const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  const int g = nh / nkv;
+  const uint32_t bar = dec_smem_u32(&bars[warp]);
+  if (lane == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(1));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  pdl_launch_dependents();
+  pdl_wait();
+  const int nkeys = seq_pos[seq] + 1;
+  const int32_t* pages = page_table + (size_t)seq_slot[seq] * table_stride;
+  const int n_pages = (nkeys + PAGE - 1) / PAGE;
+  const int per_split = (n_pages + n_splits - 1) / n_splits;
+  const int p_begin = split * per_split, p_end = min(n_pages, p_begin + per_split);
+  const int n_tiles = max(0, p_end - p_begin);   // a tile is a whole page here
+  uint32_t phase = 0;
+  bool failed = false;
+
+  const int pos = nkeys - 1, half = HD >> 1;
+  const bool fused = cos_t != nullptr;
+  const int tpos = min(pos, max_pos - 1);
+  const bool owner = fused && (pos / PAGE) / per_split == split;
+  if (fused && pos >= max_pos && threadIdx.x == 0 && err) atomicOr(err, ERR_POSITION_RANGE);
+  auto rotated = [&](const T* row, int d) {
+    const int j = d < half ? d : d - half;
+    const float c = cos_t[(size_t)tpos * half + j], sn = sin_t[(size_t)tpos * half + j];
+    const float self = to_f32(row[d]), other = to_f32(row[d < half ? d + half : d - half]);
+    return __float2bfloat16_rn(d < half ? self * c - other * sn : self * c + other * sn);
+  };
+  if (owner) {
+    const int page = pages[pos / PAGE];
+    const T* krow = q + (size_t)seq * ldq + (size_t)(nh + kvh) * HD;
+    const T* vrow = q + (size_t)seq * ldq + (size_t)(nh + nkv + kvh) * HD;
+    if (page < 0 && threadIdx.x == 0 && err) atomicOr(err, ERR_PAGE_RANGE);
+    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+      const T kd = rotated(krow, d);
+      newkv[d] = kd;
+      newkv[HD + d] = vrow[d];
+      if (page >= 0) {
+        const size_t dst = (((size_t)page * nkv + kvh) * PAGE + pos % PAGE) * HD + d;
+        kcache[dst] = kd;
+        vcache[dst] = vrow[d];
+      }
+    }
+  }
+  auto issue_tile = [&](int t) {   // whole warp: one bulk copy per key row and per value row into padded rows
+    const size_t src = ((size_t)pages[p_begin + t] * nkv + kvh) * PAGE * HD;
+    if (lane == 0) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)(2 * PAGE * HD * 2)) : "memory");
+    }
+    __syncwarp();
+#pragma unroll
+    for (int rr = 0; rr < PAGE; rr += 32) {
+      const int r = rr + lane;
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                   ::"r"(dec_smem_u32(Kt + r * PITCH)), "l"(kcache + src + (size_t)r * HD), "r"((uint32_t)(HD * 2)), "r"(bar) : "memory");
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                   ::"r"(dec_smem_u32(Vt + r * PITCH)), "l"(vcache + src + (size_t)r * HD), "r"((uint32_t)(HD * 2)), "r"(bar) : "memory");
+    }
+  };
+  bool pre_issued = false;
+  if (warp < n_tiles) {   // the first tile is on its way while the queries are staged
+    issue_tile(warp);
+    pre_issued = true;
+  }
+
+  for (int h0 = 0; h0 < g; h0 += DM_ROWS) {   // passes of 16 query heads (one pass unless a kv head serves more)
+    const int rows = min(DM_ROWS, g - h0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < DM_ROWS * HD; i += blockDim.x) {
+      const int r = i / HD, d = i - r * HD;
+      T v = __float2bfloat16_rn(0.f);
+      if (r < rows) {
+        const T* qrow = q + (size_t)seq * ldq + (size_t)(kvh * g + h0 + r) * HD;
+        v = fused ? rotated(qrow, d) : qrow[d];
+      }
+      Qs[r * PITCH + d] = v;
+    }
+    __syncthreads();
+    uint32_t qa[HDT][4];
+#pragma unroll
+    for (int ks = 0; ks < HDT; ++ks) {
+      const int mi = lane >> 3;  // matrices: (rows 0-7, k 0-7), (rows 8-15, k 0-7), (rows 0-7, k 8-15), (rows 8-15, k 8-15)
+      dm_ldmatrix_x4(dec_smem_u32(Qs + ((mi & 1) * 8 + (lane & 7)) * PITCH + ks * 16 + (mi >> 1) * 8), qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3]);
+    }
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float mA = -CUDART_INF_F, mB = -CUDART_INF_F, lA = 0.f, lB = 0.f;   // rows gid and gid + 8
+
+    for (int t = warp; t < n_tiles && !failed; t += DEC_WARPS) {
+      const int key0 = (p_begin + t) * PAGE;
+      const int valid = min(PAGE, nkeys - key0);
+      if (pre_issued) pre_issued = false;
+      else issue_tile(t);
+      {
+        const long long t0 = clock64();
+        bool done = dec_mbar_try(bar, phase);
+        while (!done) {
+          done = dec_mbar_try(bar, phase);
+          if (!done && clock64() - t0 > DEC_WAIT_CYCLES) break;
+        }
+        failed = !__all_sync(0xffffffffu, done);
+        if (failed) break;
+        phase ^= 1;
+      }
+      if (owner && pos >= key0 && pos < key0 + PAGE) {   // the copy may have read the row before the append landed
+        for (int d = lane; d < HD; d += 32) {
+          Kt[(pos - key0) * PITCH + d] = newkv[d];
+          Vt[(pos - key0) * PITCH + d] = newkv[HD + d];
+        }
+      }
+      if (valid < PAGE) {   // rows past the sequence's end are not this sequence's: zero the values, the scores are masked
+        for (int i = lane; i < (PAGE - valid) * (HD / 8); i += 32) {
+          const int r = valid + i / (HD / 8), c = i - (i / (HD / 8)) * (HD / 8);
+          *reinterpret_cast<uint4*>(Vt + r * PITCH + c * 8) = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(Kt + r * PITCH + c * 8) = make_uint4(0, 0, 0, 0);
+        }
+      }
+      __syncwarp();
+      // ---- scores: 8 tiles of 8 keys
+      float s[8][4];
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+        for (int ks2 = 0; ks2 < HDT; ks2 += 2) {
+          const int mi = lane >> 3;
+          uint32_t b0, b1, b2, b3;
+          dm_ldmatrix_x4(dec_smem_u32(Kt + (nt * 8 + (lane & 7)) * PITCH + (ks2 + (mi >> 1)) * 16 + (mi & 1) * 8), b0, b1, b2, b3);
+          dm_mma(s[nt], qa[ks2][0], qa[ks2][1], qa[ks2][2], qa[ks2][3], b0, b1);
+          dm_mma(s[nt], qa[ks2 + 1][0], qa[ks2 + 1][1], qa[ks2 + 1][2], qa[ks2 + 1][3], b2, b3);
+        }
+      }
+      float mxA = -CUDART_INF_F, mxB = -CUDART_INF_F;
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        const int key = nt * 8 + tig * 2;
+        s[nt][0] = key < valid ? s[nt][0] * scale : -CUDART_INF_F;
+        s[nt][1] = key + 1 < valid ? s[nt][1] * scale : -CUDART_INF_F;
+        s[nt][2] = key < valid ? s[nt][2] * scale : -CUDART_INF_F;
+        s[nt][3] = key + 1 < valid ? s[nt][3] * scale : -CUDART_INF_F;
+        mxA = fmaxf(mxA, fmaxf(s[nt][0], s[nt][1]));
+        mxB = fmaxf(mxB, fmaxf(s[nt][2], s[nt][3]));
+      }
+      mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 1));
+      mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 2));
+      mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 1));
+      mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2));
+      const float nmA = fmaxf(mA, mxA), nmB = fmaxf(mB, mxB);   // finite: valid >= 1
+      const float corrA = expf(mA - nmA), corrB = expf(mB - nmB);
+      float sumA = 0.f, sumB = 0.f;
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        s[nt][0] = expf(s[nt][0] - nmA);
+        s[nt][1] = expf(s[nt][1] - nmA);
+        s[nt][2] = expf(s[nt][2] - nmB);
+        s[nt][3] = expf(s[nt][3] - nmB);
+        sumA += s[nt][0] + s[nt][1];
+        sumB += s[nt][2] + s[nt][3];
+      }
+      sumA += __shfl_xor_sync(0xffffffffu, sumA, 1);
+      sumA += __shfl_xor_sync(0xffffffffu, sumA, 2);
+      sumB += __shfl_xor_sync(0xffffffffu, sumB, 1);
+      sumB += __shfl_xor_sync(0xffffffffu, sumB, 2);
+      lA = lA * corrA + sumA;
+      lB = lB * corrB + sumB;
+      mA = nmA;
+      mB = nmB;
+#pragma unroll
+      for (int i = 0; i < HD / 8; ++i) {
+        o[i][0] *= corrA;
+        o[i][1] *= corrA;
+        o[i][2] *= corrB;
+        o[i][3] *= corrB;
+      }
+      // ---- values: 4 steps of 16 keys
+#pragma unroll
+      for (int kt = 0; kt < 4; ++kt) {
+        const uint32_t a0 = dm_pack(s[2 * kt][0], s[2 * kt][1]), a1 = dm_pack(s[2 * kt][2], s[2 * kt][3]);
+        const uint32_t a2 = dm_pack(s[2 * kt + 1][0], s[2 * kt + 1][1]), a3 = dm_pack(s[2 * kt + 1][2], s[2 * kt + 1][3]);
+#pragma unroll
+        for (int dt = 0; dt < HD / 8; dt += 2) {
+          const int mi = lane >> 3;
+          uint32_t b0, b1, b2, b3;
+          dm_ldmatrix_x4_trans(dec_smem_u32(Vt + (kt * 16 + (mi & 1) * 8 + (lane & 7)) * PITCH + (dt + (mi >> 1)) * 8), b0, b1, b2, b3);
+          dm_mma(o[dt], a0, a1, a2, a3, b0, b1);
+          dm_mma(o[dt + 1], a0, a1, a2, a3, b2, b3);
+        }
+      }
+      __syncwarp();
+    }
+    if (failed) {
+      if (lane == 0 && err) atomicOr(err, ERR_WAIT_TIMEOUT);
+      mA = mB = lA = lB = CUDART_NAN_F;
+    }
+    // ---- warps -> shared memory (each into its own key tile, which it no longer reads): rows gid and gid + 8
+    auto partial = [&](int w) { return reinterpret_cast<float*>(dm_raw + decode_mma_head_bytes(HD)) + (size_t)w * 2 * TILE / 2; };
+    __syncwarp();
+    {
+      float* wa = partial(warp) + gid * WS;
+      float* wb = partial(warp) + (gid + 8) * WS;
+#pragma unroll
+      for (int dt = 0; dt < HD / 8; ++dt) {
+        wa[dt * 8 + tig * 2] = o[dt][0];
+        wa[dt * 8 + tig * 2 + 1] = o[dt][1];
+        wb[dt * 8 + tig * 2] = o[dt][2];
+        wb[dt * 8 + tig * 2 + 1] = o[dt][3];
+      }
+      if (tig == 0) {
+        wa[HD] = mA;
+        wa[HD + 1] = lA;
+        wb[HD] = mB;
+        wb[HD + 1] = lB;
+      }
+    }
+    __syncthreads();
+    // ---- fold the warps in the order 0..3: threads over (row, pair of dims)
+    for (int i = threadIdx.x; i < rows * (HD / 2); i += blockDim.x) {
+      const int r = i / (HD / 2), d = (i - r * (HD / 2)) * 2;
+      float M = -CUDART_INF_F;
+      bool bad = false;
+      for (int w = 0; w < DEC_WARPS; ++w) {
+        const float mw = partial(w)[r * WS + HD];
+        bad = bad || (mw != mw);
+        M = fmaxf(M, mw);
+      }
+      float L = 0.f, o0 = 0.f, o1 = 0.f;
+      if (M != -CUDART_INF_F && !bad) {
+        for (int w = 0; w < DEC_WARPS; ++w) {
+          const float* p = partial(w) + r * WS;
+          if (p[HD] == -CUDART_INF_F) continue;
+          const float f = expf(p[HD] - M);
+          L = fmaf(p[HD + 1], f, L);
+          o0 = fmaf(p[d], f, o0);
+          o1 = fmaf(p[d + 1], f, o1);
+        }
+      }
+      if (bad) {
+        M = 0.f;
+        L = CUDART_NAN_F;
+      }
+      const int head = kvh * g + h0 + r;
+      if (n_splits == 1) {
+        const float inv = 1.0f / L;
+        *reinterpret_cast<__nv_bfloat162*>(out + (size_t)seq * ldo + head * HD + d) = __floats2bfloat162_rn(o0 * inv, o1 * inv);
+      } else {
+        const size_t pi = ((size_t)seq * nh + head) * n_splits + split;
+        part_o[pi * HD + d] = o0;
+        part_o[pi * HD + d + 1] = o1;
+        if (d == 0) {
+          part_ml[pi * 2] = M;
+          part_ml[pi * 2 + 1] = L;
+        }
+      }
+    }
+  }
+}
+
+}  // namespace edgelm
