@@ -627,6 +627,7 @@ int launch_prefill(const void* q, int ldq, void* out, int ldo, const void* kc, c
 // Device error word that decode attention reports a copy that never arrived to (may stay null:
 // the affected rows are then NaN, which no caller can overlook).
 static int* g_attn_err = nullptr;
+static int g_decode_cuda_cores = 0;  // 1: decode attention on the CUDA-core kernel even where the tensor-core one applies
 
 // Keys per tile: the largest power of two up to 64 whose K rows fit DEC_TILE_BYTES.
 static int decode_tile_keys(int hd, size_t elem) {
@@ -645,9 +646,11 @@ int launch_decode(const void* q, int ldq, void* out, int ldo, const void* kc, co
   cudaError_t le = cudaSuccess;
   bool on_mma = false;
   if constexpr (sizeof(T) == 2) {
-    // bfloat16 with a head size the MMAs tile (32, 64, 96, 128): the tensor-core kernel; it folds the splits
-    // with the combine kernel only (no counters)
-    if ((hd == 32 || hd == 64 || hd == 96 || hd == 128) && counters == nullptr) {
+    // bfloat16 with a head size the MMAs tile (32, 64, 96, 128) and several query heads per kv head: the
+    // tensor-core kernel (with one query head per kv head the CUDA-core kernel has as little arithmetic and
+    // fewer, larger copies: measured 46 against 52 us at 32/32 heads).  It folds the splits with the combine
+    // kernel only (no counters).
+    if ((hd == 32 || hd == 64 || hd == 96 || hd == 128) && nh / nkv >= 2 && counters == nullptr && !g_decode_cuda_cores) {
       on_mma = true;
       const size_t smem = decode_mma_head_bytes(hd) + (size_t)DEC_WARPS * 2 * PAGE * (hd + 8) * 2;
       auto go = [&](auto kern) {
@@ -735,6 +738,12 @@ extern "C" int edgelm_attn_prefill(const void* q, int ldq, void* out, int ldo, c
   EL_ATT_DISPATCH(launch_prefill, q, ldq, out, ldo, kcache, vcache, page_table, table_stride, seq_slot, tile_seq, tile_tok0,
                   tile_ntok, tile_pos0, n_tiles, max_tile_tokens, nh, nkv, hd, scale, stream);
   EL_LAUNCH_CHECK("attn_prefill");
+  return 0;
+}
+
+// 1: decode attention runs on the CUDA-core kernel for every dtype and head size (for comparisons); 0: default.
+extern "C" int edgelm_attn_decode_on_cuda_cores(int on) {
+  g_decode_cuda_cores = on ? 1 : 0;
   return 0;
 }
 

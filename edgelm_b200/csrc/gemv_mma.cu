@@ -25,6 +25,7 @@ namespace edgelm {
 enum : int { GM_STORE = 0, GM_RESIDUAL = 1, GM_SWIGLU = 2 };
 constexpr int GM_MAX_WARPS = 16;
 constexpr int GM_COLS = 16;  // output columns per block
+constexpr int GM_K_CHUNK = 4096;  // columns of the activations in shared memory at a time
 
 __device__ __forceinline__ void mma_bf16_16x8x16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                                  uint32_t b1) {
@@ -42,7 +43,8 @@ __global__ void __launch_bounds__(MAXW * 32)
 gemv_mma_kernel(const __nv_bfloat16* __restrict__ act, int lda, const float* __restrict__ x,
                 const float* __restrict__ norm_w, float eps, const __nv_bfloat16* __restrict__ W,
                 const __nv_bfloat16* __restrict__ W2, TOut* out, int ldo, const float* residual, int M, int N, int K,
-                int pitch /* bfloat16 elements per activation row in shared memory */) {
+                int pitch /* bfloat16 elements per activation row in shared memory */,
+                int kc /* columns of the activations staged at a time: a multiple of 32 */) {
   constexpr int NW = EPI == GM_SWIGLU ? 2 : 1;
   constexpr int ROWS = 8 * NT;
   const int GM_WARPS = blockDim.x >> 5;  // the block's warps share the K blocks
@@ -87,33 +89,6 @@ gemv_mma_kernel(const __nv_bfloat16* __restrict__ act, int lda, const float* __r
     }
     __syncthreads();
   }
-  const int kvec = K / 8;
-  for (int i = threadIdx.x; i < ROWS * kvec; i += blockDim.x) {
-    const int r = i / kvec, k = (i - r * kvec) * 8;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < M) {
-      if (NORM) {
-        const float s = inv[r];
-        const float4 x0 = *reinterpret_cast<const float4*>(x + (size_t)r * K + k);
-        const float4 x1 = *reinterpret_cast<const float4*>(x + (size_t)r * K + k + 4);
-        const float4 w0 = *reinterpret_cast<const float4*>(norm_w + k);
-        const float4 w1 = *reinterpret_cast<const float4*>(norm_w + k + 4);
-        __nv_bfloat162 h0 = __floats2bfloat162_rn(x0.x * s * w0.x, x0.y * s * w0.y);
-        __nv_bfloat162 h1 = __floats2bfloat162_rn(x0.z * s * w0.z, x0.w * s * w0.w);
-        __nv_bfloat162 h2 = __floats2bfloat162_rn(x1.x * s * w1.x, x1.y * s * w1.y);
-        __nv_bfloat162 h3 = __floats2bfloat162_rn(x1.z * s * w1.z, x1.w * s * w1.w);
-        v.x = *reinterpret_cast<uint32_t*>(&h0);
-        v.y = *reinterpret_cast<uint32_t*>(&h1);
-        v.z = *reinterpret_cast<uint32_t*>(&h2);
-        v.w = *reinterpret_cast<uint32_t*>(&h3);
-      } else {
-        v = *reinterpret_cast<const uint4*>(act + (size_t)r * lda + k);
-      }
-    }
-    *reinterpret_cast<uint4*>(As + (size_t)r * pitch + k) = v;
-  }
-  __syncthreads();
-
   float acc[NW][NT][4];
 #pragma unroll
   for (int w = 0; w < NW; ++w)
@@ -123,37 +98,69 @@ gemv_mma_kernel(const __nv_bfloat16* __restrict__ act, int lda, const float* __r
       for (int j = 0; j < 4; ++j) acc[w][t][j] = 0.f;
 
   constexpr int UN = 4;  // K blocks whose weight loads are in flight together
-  for (int kb0 = warp; kb0 < n_kb; kb0 += GM_WARPS * UN) {
-    uint4 wa[UN][NW], wb[UN][NW];
-#pragma unroll
-    for (int u = 0; u < UN; ++u) {
-      const int kb = kb0 + u * GM_WARPS;
-      const int k = kb * 32 + tig * 8;
-      const bool ok = kb < n_kb && k < K;
-#pragma unroll
-      for (int w = 0; w < NW; ++w) {
-        if (u == 0 && kb0 == warp) {
-          wa[u][w] = pa[w];
-          wb[u][w] = pb[w];
+  for (int kc0 = 0; kc0 < K; kc0 += kc) {   // K in chunks whose activations fit shared memory (one chunk for the usual sizes)
+    const int kn = min(kc, K - kc0);
+    if (kc0) __syncthreads();               // the previous chunk's activations are used up
+    const int kvec = kn / 8;
+    for (int i = threadIdx.x; i < ROWS * kvec; i += blockDim.x) {
+      const int r = i / kvec, k = kc0 + (i - r * kvec) * 8;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (r < M) {
+        if (NORM) {
+          const float s = inv[r];
+          const float4 x0 = *reinterpret_cast<const float4*>(x + (size_t)r * K + k);
+          const float4 x1 = *reinterpret_cast<const float4*>(x + (size_t)r * K + k + 4);
+          const float4 w0 = *reinterpret_cast<const float4*>(norm_w + k);
+          const float4 w1 = *reinterpret_cast<const float4*>(norm_w + k + 4);
+          __nv_bfloat162 h0 = __floats2bfloat162_rn(x0.x * s * w0.x, x0.y * s * w0.y);
+          __nv_bfloat162 h1 = __floats2bfloat162_rn(x0.z * s * w0.z, x0.w * s * w0.w);
+          __nv_bfloat162 h2 = __floats2bfloat162_rn(x1.x * s * w1.x, x1.y * s * w1.y);
+          __nv_bfloat162 h3 = __floats2bfloat162_rn(x1.z * s * w1.z, x1.w * s * w1.w);
+          v.x = *reinterpret_cast<uint32_t*>(&h0);
+          v.y = *reinterpret_cast<uint32_t*>(&h1);
+          v.z = *reinterpret_cast<uint32_t*>(&h2);
+          v.w = *reinterpret_cast<uint32_t*>(&h3);
         } else {
-          const __nv_bfloat16* Wp = w == 0 ? W : W2;
-          wa[u][w] = ok ? *reinterpret_cast<const uint4*>(Wp + (size_t)ra * K + k) : make_uint4(0, 0, 0, 0);
-          wb[u][w] = ok ? *reinterpret_cast<const uint4*>(Wp + (size_t)rb * K + k) : make_uint4(0, 0, 0, 0);
+          v = *reinterpret_cast<const uint4*>(act + (size_t)r * lda + k);
         }
       }
+      *reinterpret_cast<uint4*>(As + (size_t)r * pitch + (k - kc0)) = v;
     }
+    __syncthreads();
+
+    const int kb_begin = kc0 / 32, kb_end = (kc0 + kn + 31) / 32;
+    for (int kb0 = kb_begin + warp; kb0 < kb_end; kb0 += GM_WARPS * UN) {
+      uint4 wa[UN][NW], wb[UN][NW];
 #pragma unroll
-    for (int u = 0; u < UN; ++u) {
-      const int kb = kb0 + u * GM_WARPS;
-      const int k = kb * 32 + tig * 8;
-      const bool ok = kb < n_kb && k < K;
-#pragma unroll
-      for (int t = 0; t < NT; ++t) {
-        const uint4 av = ok ? *reinterpret_cast<const uint4*>(As + (size_t)(t * 8 + gid) * pitch + k) : make_uint4(0, 0, 0, 0);
+      for (int u = 0; u < UN; ++u) {
+        const int kb = kb0 + u * GM_WARPS;
+        const int k = kb * 32 + tig * 8;
+        const bool ok = kb < kb_end && k < K;
 #pragma unroll
         for (int w = 0; w < NW; ++w) {
-          mma_bf16_16x8x16(acc[w][t], wa[u][w].x, wb[u][w].x, wa[u][w].y, wb[u][w].y, av.x, av.y);
-          mma_bf16_16x8x16(acc[w][t], wa[u][w].z, wb[u][w].z, wa[u][w].w, wb[u][w].w, av.z, av.w);
+          if (u == 0 && kb0 == warp) {
+            wa[u][w] = pa[w];
+            wb[u][w] = pb[w];
+          } else {
+            const __nv_bfloat16* Wp = w == 0 ? W : W2;
+            wa[u][w] = ok ? *reinterpret_cast<const uint4*>(Wp + (size_t)ra * K + k) : make_uint4(0, 0, 0, 0);
+            wb[u][w] = ok ? *reinterpret_cast<const uint4*>(Wp + (size_t)rb * K + k) : make_uint4(0, 0, 0, 0);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UN; ++u) {
+        const int kb = kb0 + u * GM_WARPS;
+        const int k = kb * 32 + tig * 8;
+        const bool ok = kb < kb_end && k < K;
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+          const uint4 av = ok ? *reinterpret_cast<const uint4*>(As + (size_t)(t * 8 + gid) * pitch + (k - kc0)) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+          for (int w = 0; w < NW; ++w) {
+            mma_bf16_16x8x16(acc[w][t], wa[u][w].x, wb[u][w].x, wa[u][w].y, wb[u][w].y, av.x, av.y);
+            mma_bf16_16x8x16(acc[w][t], wa[u][w].z, wb[u][w].z, wa[u][w].w, wb[u][w].w, av.z, av.w);
+          }
         }
       }
     }
@@ -208,7 +215,8 @@ static int launch_gemv_mma(const void* act, int lda, const float* x, const float
                            const void* W2, void* out, int ldo, const float* residual, int M, int N, int K,
                            cudaStream_t stream) {
   constexpr int NW = EPI == GM_SWIGLU ? 2 : 1;
-  const int pitch = act_pitch(K);
+  const int kc = K <= GM_K_CHUNK ? (K + 31) / 32 * 32 : GM_K_CHUNK;
+  const int pitch = act_pitch(kc);
   // warps per block: wide outputs fill the device with blocks and want few warps; narrow ones get up to
   // 16 warps, about two K blocks each, so that a single round of loads is in flight per warp
   const int n_kb = (K + 31) / 32, blocks = (N + GM_COLS - 1) / GM_COLS;
@@ -227,7 +235,7 @@ static int launch_gemv_mma(const void* act, int lda, const float* x, const float
     }
     cudaError_t le = launch_pdl(1, kern, dim3((N + GM_COLS - 1) / GM_COLS), dim3(GM_WARPS * 32), smem, stream,
                                 (const __nv_bfloat16*)act, lda, x, norm_w, eps, (const __nv_bfloat16*)W, (const __nv_bfloat16*)W2,
-                                (TOut*)out, ldo, residual, M, N, K, pitch);
+                                (TOut*)out, ldo, residual, M, N, K, pitch, kc);
     if (le != cudaSuccess) {
       set_error("gemv_mma: launch failed: %s", cudaGetErrorString(le));
       return -2;
@@ -243,10 +251,9 @@ static int launch_gemv_mma(const void* act, int lda, const float* x, const float
 
 using namespace edgelm;
 
-// 1 if the kernel takes these operands, else 0: bfloat16, M <= 16, K a multiple of 8 (and small enough
-// for all rows to sit in shared memory), 16-byte aligned rows.
+// 1 if the kernel takes these operands, else 0: bfloat16, M <= 16, K a multiple of 8, 16-byte aligned rows.
 extern "C" int edgelm_gemv_mma_takes(const void* act, int lda, const void* w, const void* w2, int M, int K, int normed) {
-  bool ok = M >= 1 && M <= 16 && K > 0 && K % 8 == 0 && K <= 6144 && (uintptr_t)w % 16 == 0 &&
+  bool ok = M >= 1 && M <= 16 && K > 0 && K % 8 == 0 && (uintptr_t)w % 16 == 0 &&
             (w2 == nullptr || (uintptr_t)w2 % 16 == 0) && (uintptr_t)act % 16 == 0;
   if (!normed) ok = ok && lda % 8 == 0;
   return ok ? 1 : 0;
@@ -258,7 +265,7 @@ extern "C" int edgelm_gemv_mma(const void* act, int lda, const float* norm_w, fl
   if (M == 0) return 0;
   const bool normed = norm_w != nullptr;
   EL_REFUSE(N > 0 && ldo >= N && (normed || lda >= K), "gemv_mma: bad sizes M=%d N=%d K=%d lda=%d ldo=%d", M, N, K, lda, ldo);
-  EL_REFUSE(edgelm_gemv_mma_takes(act, lda, w, w2, M, K, normed ? 1 : 0), "gemv_mma: takes M <= 16, K a multiple of 8 up to 6144, 16-byte aligned rows (M=%d K=%d)", M, K);
+  EL_REFUSE(edgelm_gemv_mma_takes(act, lda, w, w2, M, K, normed ? 1 : 0), "gemv_mma: takes M <= 16, K a multiple of 8, 16-byte aligned rows (M=%d K=%d)", M, K);
   EL_REFUSE(epilogue != GM_SWIGLU || w2 != nullptr, "gemv_mma: SwiGLU needs the second weight");
   EL_REFUSE(epilogue != GM_RESIDUAL || (residual != nullptr && out_dtype == DT_F32), "gemv_mma: residual epilogue needs a float32 residual and output");
   const float* x = normed ? (const float*)act : nullptr;

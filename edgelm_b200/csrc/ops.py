@@ -42,6 +42,8 @@ def lib():
                 except OSError as e:  # pragma: no cover
                     raise KernelError(f"edgelm_b200: cannot load the kernel library {path}: {e}") from e
                 loaded.edgelm_last_error.restype = ctypes.c_char_p
+                if os.environ.get("EDGELM_DECODE_CUDA_CORES") is not None:
+                    loaded.edgelm_attn_decode_on_cuda_cores(int(os.environ["EDGELM_DECODE_CUDA_CORES"]))
                 if os.environ.get("EDGELM_PDL") is not None:
                     loaded.edgelm_set_pdl(int(os.environ["EDGELM_PDL"]))
                 _lib = loaded
@@ -165,7 +167,7 @@ def gemv(a, w, out, epilogue=EPI_STORE, w2=None, residual=None, norm_weight=None
 
 def gemv_mma_takes(a, w, w2=None, normed=False):
     """Whether the tensor-core few-rows kernel takes these operands: bfloat16 weights, at most 16 rows,
-    K a multiple of 8 up to 6144, aligned rows.  With `normed`, `a` is the float32 residual stream."""
+    K a multiple of 8, aligned rows.  With `normed`, `a` is the float32 residual stream."""
     if w.dtype != torch.bfloat16 or not w.is_contiguous() or a.stride(1) != 1:
         return False
     if normed and (a.dtype != torch.float32 or not a.is_contiguous()):

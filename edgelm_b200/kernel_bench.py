@@ -79,7 +79,6 @@ def main(argv=None):
         po = torch.empty(B * nh * splits * hd, device=d)
         pm = torch.empty(B * nh * splits * 2, device=d)
         few = B <= 16
-        mm = (lambda a, w, out, **k: o.gemv_mma(a, w, out, **k)) if few else None
         cases = {
             "qkv_normed": lambda l: o.gemv_mma(x, wq[l], qkv, norm_weight=nw, eps=1e-5) if few else o.gemm_tc(h, wq[l], qkv, err),
             "rope_kv_append": lambda l: o.rope_kv_append(qkv, tokpos, tokseq, seq, table, cos, sin, kc[l], vc[l], nh, nkv, hd, err),

@@ -104,8 +104,10 @@ def test_random_model_dir_round_trip(tmp_path):
     assert set(t) == set(exp) and all(tuple(t[n].shape) == tuple(s) for n, s in exp.items())
     assert all(v.dtype == torch.bfloat16 for v in t.values())
     assert abs(float(t["model.norm.weight"].float().mean()) - 1) < 0.05 and abs(float(t["lm_head.weight"].float().mean())) < 0.01
-    d2 = H.make_model_dir(tmp_path / "again", "tiny_b") if (tmp_path / "again").mkdir() is None else None
-    assert all(torch.equal(t[n], read_dir(d2)[n]) for n in t)  # same seed, same bits
+    (tmp_path / "again").mkdir()
+    d2 = H.make_model_dir(tmp_path / "again", "tiny_b")
+    again = read_dir(d2)
+    assert all(torch.equal(t[n], again[n]) for n in t)  # same seed, same bits
     d32 = H.make_model_dir(tmp_path, "tiny_b", "float32")
     t32 = load_checked(d32, exp)
     assert all(v.dtype == torch.float32 for v in t32.values())  # stored in 32 bits, kept in 32 bits

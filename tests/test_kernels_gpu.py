@@ -475,7 +475,7 @@ def test_gemv_refuses_unaligned():
 
 # ----------------------------------------------------------------------------- few-rows kernel on mma.sync (bfloat16 decode)
 @pytest.mark.parametrize("M,N,K", [(1, 576, 576), (8, 960, 576), (3, 37, 96), (9, 130, 160), (16, 4000, 64), (5, 397, 200),
-                                     (8, 100, 6144), (2, 3000, 2048), (7, 16, 8), (13, 31, 40)])
+                                     (8, 100, 6144), (2, 3000, 2048), (7, 16, 8), (13, 31, 40), (8, 64, 8192), (11, 40, 9000)])
 def test_gemv_mma_epilogues(M, N, K):
     o = ops()
     a = rnd((M, K), torch.bfloat16, 70)
@@ -499,7 +499,7 @@ def test_gemv_mma_epilogues(M, N, K):
     assert rel_err(sw, want / (1 + torch.exp(-want)) * u) < 1.6e-2
 
 
-@pytest.mark.parametrize("M,N,K,eps", [(8, 960, 576, 1e-5), (1, 200, 96, 1e-6), (12, 64, 2048, 1e-5), (3, 50, 4104, 1e-3)])
+@pytest.mark.parametrize("M,N,K,eps", [(8, 960, 576, 1e-5), (1, 200, 96, 1e-6), (12, 64, 2048, 1e-5), (3, 50, 4104, 1e-3), (5, 48, 8200, 1e-5)])
 def test_gemv_mma_with_norm_prologue(M, N, K, eps):
     o = ops()
     x = rnd((M, K), torch.float32, 74, 2.0)
