@@ -17,7 +17,12 @@ TINY_B = dict(model_type="llama", architectures=["LlamaForCausalLM"], vocab_size
               intermediate_size=200, num_hidden_layers=3, num_attention_heads=3, num_key_value_heads=1, head_dim=32,
               max_position_embeddings=256, rope_theta=100000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
               bos_token_id=1, eos_token_id=2)
-TINY = {"tiny_a": (TINY_A, 0, 0.09), "tiny_b": (TINY_B, 2, 0.07)}  # config, seed, sigma (large enough for logits of order 1)
+# widths that no vector load divides (50 = 2 * 25, 70, 101): every matrix product takes its any-size path
+TINY_C = dict(model_type="llama", architectures=["LlamaForCausalLM"], vocab_size=101, hidden_size=50,
+              intermediate_size=70, num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=3, head_dim=48,
+              max_position_embeddings=160, rope_theta=777.0, rms_norm_eps=3e-4, tie_word_embeddings=True,
+              bos_token_id=0, eos_token_id=1)
+TINY = {"tiny_a": (TINY_A, 0, 0.09), "tiny_b": (TINY_B, 2, 0.07), "tiny_c": (TINY_C, 5, 0.1)}  # config, seed, sigma (large enough for logits of order 1)
 
 TOL = {"float32": 2e-5, "bfloat16": 3e-2}
 

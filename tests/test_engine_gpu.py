@@ -9,7 +9,7 @@ import plain_llama as plain
 
 pytestmark = pytest.mark.gpu
 
-NAMES = ["tiny_a", "tiny_b"]
+NAMES = ["tiny_a", "tiny_b", "tiny_c"]
 DTYPES = ["float32", "bfloat16"]
 
 

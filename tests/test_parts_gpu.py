@@ -262,3 +262,106 @@ def test_cli_commands(tmp_path, capsys):
     rows = [json.loads(l) for l in capsys.readouterr().out.strip().splitlines()]
     assert [r["batch"] for r in rows] == [1, 3] and all(r["decode_tok_s"] > 0 for r in rows)
     assert main(["run", "-m", str(tmp_path / "nowhere")]) == 1
+
+
+# ----------------------------------------------------------------------------- a layer that reads another layer's cache
+def _register_reader():
+    """A mixer without a cache of its own: it averages the VALUES that an earlier attention layer left in
+    its cache (kv head 0, all positions up to the token's own) and projects the mean.  The schedule names
+    the entry whose cache it reads."""
+    from edgelm_b200.config import register_architecture
+    from edgelm_b200.config.base import LayerSpec, ModelPlan, PartSpec, ScheduleEntry
+    from edgelm_b200.parts import Part, register_mixer
+    from edgelm_b200.parts.registry import MIXERS
+
+    if "toy_value_reader" in MIXERS:
+        return
+
+    @register_mixer("toy_value_reader")
+    class ValueReader(Part):
+        def __init__(self, spec, env):
+            self.dim, self.hd, self.name = spec["dim"], spec["head_dim"], spec["name"]
+            self.w = None
+
+        def weight_shapes(self, prefix):
+            return {prefix + self.name: (self.dim, self.hd)}
+
+        def load(self, tensors, prefix, device):
+            self.w = tensors[prefix + self.name].to(device=device, dtype=torch.float32)
+
+        def forward(self, ctx, h, x, cache):
+            table = ctx.page_table(cache.group).long()      # [sequences, pages]: rows of the other entry's group
+            v = cache.v                                      # [pages, kv_heads, 64, head_dim] of the entry it reads
+            t0 = 0
+            for i, (n, p0) in enumerate(zip(ctx.seq_lengths, ctx.seq_first_positions)):
+                pos = torch.arange(p0 + n, device=x.device)
+                rows = v[table[i, pos // 64], 0, pos % 64].float()          # values of positions 0 .. p0 + n - 1
+                means = torch.cumsum(rows, 0)[p0:] / (pos[p0:] + 1).unsqueeze(1)
+                x[t0:t0 + n] += means @ self.w.T
+                t0 += n
+
+    @register_architecture("ToyReaderForCausalLM", model_type="toy_reader")
+    class ReaderConfig:
+        def __init__(self, d):
+            self.d = d
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d)
+
+        def plan(self):
+            d = self.d
+            D, V = d["width"], d["vocab_size"]
+            norm = lambda name: PartSpec("rmsnorm", {"dim": D, "eps": 1e-5, "name": name})
+            att = PartSpec("attention", {"hidden_size": D, "num_heads": 2, "num_kv_heads": 2, "head_dim": 16,
+                                         "positions": PartSpec("rope", {"head_dim": 16, "theta": 1000.0, "max_positions": 256}),
+                                         "names": {"q": "q.weight", "k": "k.weight", "v": "v.weight", "o": "o.weight"}})
+            reader = PartSpec("toy_value_reader", {"dim": D, "head_dim": 16, "name": "read.weight"})
+            ffn = PartSpec("swiglu", {"hidden_size": D, "intermediate_size": 24,
+                                      "names": {"gate": "g.weight", "up": "u.weight", "down": "d.weight"}})
+            layers = (LayerSpec("a.", "prenorm", att, norm("n1.weight"), ffn, norm("n2.weight")),
+                      LayerSpec("r.", "prenorm", reader, norm("n1.weight"), ffn, norm("n2.weight")))
+            return ModelPlan(hidden_size=D, vocab_size=V, max_positions=256,
+                             embedding=PartSpec("embedding", {"vocab_size": V, "dim": D, "name": "emb.weight"}),
+                             layers=layers, schedule=(ScheduleEntry(0), ScheduleEntry(1, reads_cache_of=0)),
+                             final_norm=norm("final.weight"),
+                             head=PartSpec("lm_head", {"vocab_size": V, "dim": D, "tied_to": None, "name": "head.weight"}))
+
+
+def test_a_layer_reads_another_layers_cache(tmp_path):
+    _register_reader()
+    from edgelm_b200.config import read_config
+    from edgelm_b200.engine.engine import Engine, load_model
+    from edgelm_b200.engine.model import expected_weights
+    from edgelm_b200.weights import random_tensors, read_dir, write_file
+    d = {"architectures": ["ToyReaderForCausalLM"], "vocab_size": 41, "width": 32}
+    folder = tmp_path / "reader"
+    folder.mkdir()
+    (folder / "config.json").write_text(json.dumps(d))
+    exp = expected_weights(read_config(str(folder)).plan())
+    write_file(str(folder / "model.safetensors"), random_tensors(exp, seed=3, sigma=0.2, dtype=torch.float32))
+    eng = Engine(load_model(str(folder), "float32"), max_tokens=512)
+    assert len(eng.cache.kv_groups) == 1 and eng.cache.kv_groups[0].n_entries == 1 and eng.cache.entries[1] is None
+    W = {k: v.float().numpy() for k, v in read_dir(str(folder)).items()}
+
+    def plain_model(tokens):
+        x = plain.embed(W["emb.weight"], tokens)
+        h = plain.rmsnorm(x, W["a.n1.weight"], 1e-5)
+        pos = np.arange(len(x))
+        q = plain.rope(h @ W["a.q.weight"].T, pos, 2, 16, 1000.0)
+        k = plain.rope(h @ W["a.k.weight"].T, pos, 2, 16, 1000.0)
+        v = h @ W["a.v.weight"].T
+        x = x + plain.attention(q, k, v, 2, 2, 16) @ W["a.o.weight"].T
+        x = x + plain.swiglu_mlp(plain.rmsnorm(x, W["a.n2.weight"], 1e-5), W["a.g.weight"], W["a.u.weight"], W["a.d.weight"])
+        means = np.cumsum(v[:, :16], axis=0) / (pos + 1)[:, None]          # kv head 0 of the attention layer's values
+        x = x + means.astype(np.float32) @ W["r.read.weight"].T
+        x = x + plain.swiglu_mlp(plain.rmsnorm(x, W["r.n2.weight"], 1e-5), W["r.g.weight"], W["r.u.weight"], W["r.d.weight"])
+        return plain.rmsnorm(x, W["final.weight"], 1e-5) @ W["head.weight"].T
+
+    reqs = [[int(v) for v in np.random.default_rng(10 + i).integers(0, 41, size=n)] for i, n in enumerate([70, 9, 130])]
+    for r in reqs:
+        want = plain_model(r)
+        assert H.rel_err(H.run_whole(eng, r), want) < 5e-5
+        assert H.rel_err(H.run_tail_one_by_one(eng, r, 8), want) < 5e-5
+    for r, g in zip(reqs, H.run_batches(eng, reqs, batch_size=2, decode_tail=4)):
+        assert H.rel_err(g, plain_model(r)) < 5e-5
