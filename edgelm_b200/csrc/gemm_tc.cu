@@ -31,7 +31,7 @@ enum : int { TC_EPI_STORE = 0, TC_EPI_RESIDUAL = 1, TC_EPI_SWIGLU = 2 };
 
 constexpr int TC_BM = 128;   // rows of `a` per tile = lanes of tensor memory
 constexpr int TC_BK = 64;    // 64 bfloat16 = one 128-byte swizzle row
-constexpr int TC_STAGES = 3;
+constexpr int TC_STAGES = 3;   // ring stages of the one-tile kernel (48 KB stages: 144 KB)
 constexpr int TC_THREADS = 192;
 constexpr long long TC_WAIT_CYCLES = 2000000000LL;
 
@@ -131,6 +131,46 @@ template <> struct OutVec<__nv_bfloat16> {
   }
 };
 
+// The epilogue of the 32 columns of one row that a thread holds after tcgen05.ld: 16-byte loads of the
+// residual and 16-byte stores where the row allows them, element by element at the ragged edge.  (Going
+// through shared memory to make a warp's accesses run along rows was measured: twice as slow, the scalar
+// instructions cost more than the scattered vectors.)
+template <int EPI, typename TOut>
+__device__ __forceinline__ void epilogue_piece(const uint32_t* r, const uint32_t* r2, TOut* out, int ldo,
+                                               const float* residual, int row, int col0, int M, int N, int vec_ok) {
+  if (row >= M) return;
+  const size_t base = (size_t)row * ldo + col0;
+  const bool full = vec_ok && (col0 + 32 <= N);
+#pragma unroll
+  for (int j0 = 0; j0 < 32; j0 += 8) {
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float acc = __uint_as_float(r[j0 + j]);
+      if (EPI == TC_EPI_SWIGLU) v[j] = silu_tc(acc) * __uint_as_float(r2[j0 + j]);
+      else v[j] = acc;
+    }
+    if (full) {
+      if (EPI == TC_EPI_RESIDUAL) {
+        const float4 a = *reinterpret_cast<const float4*>(residual + base + j0);
+        const float4 b = *reinterpret_cast<const float4*>(residual + base + j0 + 4);
+        v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
+        v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+      }
+      OutVec<TOut>::store8(out + base + j0, v);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (col0 + j0 + j < N) {
+          float x = v[j];
+          if (EPI == TC_EPI_RESIDUAL) x += residual[base + j0 + j];
+          out[base + j0 + j] = from_f32<TOut>(x);
+        }
+      }
+    }
+  }
+}
+
 template <int BN, int EPI, typename TOut>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -213,7 +253,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(tmem_full_bar), 0, abort_flag, err));  // one decision per warp
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ok) {
-      const int row = m0 + q * 32 + lane;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         if (n0 + c0 >= N) break;  // uniform over the block
@@ -222,39 +261,147 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         tmem_ld32(taddr, r);
         if (NB == 2) tmem_ld32(taddr + BN, r2);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (row < M) {
-          const size_t base = (size_t)row * ldo + n0 + c0;
-          const bool full = vec_ok && (n0 + c0 + 32 <= N);
-#pragma unroll
-          for (int j0 = 0; j0 < 32; j0 += 8) {
-            float v[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float acc = __uint_as_float(r[j0 + j]);
-              if (EPI == TC_EPI_SWIGLU) v[j] = silu_tc(acc) * __uint_as_float(r2[j0 + j]);
-              else v[j] = acc;
-            }
-            if (full) {
-              if (EPI == TC_EPI_RESIDUAL) {
-                const float4 a = *reinterpret_cast<const float4*>(residual + base + j0);
-                const float4 b = *reinterpret_cast<const float4*>(residual + base + j0 + 4);
-                v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
-                v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
-              }
-              OutVec<TOut>::store8(out + base + j0, v);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                if (n0 + c0 + j0 + j < N) {
-                  float x = v[j];
-                  if (EPI == TC_EPI_RESIDUAL) x += residual[base + j0 + j];
-                  out[base + j0 + j] = from_f32<TOut>(x);
-                }
-              }
-            }
-          }
+        epilogue_piece<EPI, TOut>(r, r2, out, ldo, residual, m0 + q * 32 + lane, n0 + c0, M, N, vec_ok);
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------- persistent form
+// One CTA per SM walks the tiles tile = blockIdx.x, blockIdx.x + gridDim.x, ... (row tiles fastest, so
+// that the CTAs running together share the weight tiles in L2).  The shared-memory ring runs on across
+// tiles, and the accumulator has two stages in tensor memory: while the epilogue warps drain tile i
+// (tcgen05.ld, epilogue, stores) the MMA warp already accumulates tile i + 1 into the other stage.
+// Barriers: full/empty per ring stage as above, tmem_full/tmem_empty per accumulator stage (the
+// epilogue's four warps each arrive once on tmem_empty when their rows are read).
+constexpr int TCP_STAGES = 4;
+
+template <int BN, int EPI, typename TOut>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                          const __grid_constant__ CUtensorMap map_b2, TOut* out, int ldo, const float* residual,
+                          int M, int N, int K, int vec_ok, int* err) {
+  constexpr int NB = EPI == TC_EPI_SWIGLU ? 2 : 1;
+  constexpr int A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
+  constexpr int STAGE_BYTES = A_BYTES + NB * B_BYTES;
+  constexpr uint32_t ACC_COLS = NB * BN;          // columns of one accumulator stage
+  constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;    // two stages: 256
+  static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "tensor memory columns: a power of two");
+  static_assert(STAGE_BYTES % 1024 == 0, "stages keep the 1024-byte alignment of swizzled tiles");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TCP_STAGES * STAGE_BYTES);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + TCP_STAGES;
+  uint64_t* tmem_full_bar = bars + 2 * TCP_STAGES;       // [2]
+  uint64_t* tmem_empty_bar = bars + 2 * TCP_STAGES + 2;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * TCP_STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (N + BN - 1) / BN;
+  const int n_tiles = tiles_m * tiles_n;
+  const int n_k = (K + TC_BK - 1) / TC_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < TCP_STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&tmem_full_bar[a]), 1);
+      mbar_init(smem_u32(&tmem_empty_bar[a]), 4);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * BN;
+        for (int i = 0; i < n_k; ++i, ++it) {
+          const int s = it % TCP_STAGES;
+          ok = mbar_wait(smem_u32(&empty_bar[s]), ((it / TCP_STAGES) & 1) ^ 1, abort_flag, err);
+          if (!ok) break;
+          const uint32_t bar = smem_u32(&full_bar[s]);
+          mbar_expect_tx(bar, STAGE_BYTES);
+          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+          tma_load_2d(sa, &map_a, bar, i * TC_BK, m0);
+          tma_load_2d(sa + A_BYTES, &map_b, bar, i * TC_BK, n0);
+          if (NB == 2) tma_load_2d(sa + A_BYTES + B_BYTES, &map_b2, bar, i * TC_BK, n0);
         }
       }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(TC_BM, BN);
+      int it = 0, ti = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++ti) {
+        const int as = ti & 1;
+        ok = mbar_wait(smem_u32(&tmem_empty_bar[as]), ((ti >> 1) & 1) ^ 1, abort_flag, err);  // the epilogue has drained this stage
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t acc_addr = tmem_base + (uint32_t)as * ACC_COLS;
+        for (int i = 0; i < n_k; ++i, ++it) {
+          const int s = it % TCP_STAGES;
+          ok = mbar_wait(smem_u32(&full_bar[s]), (it / TCP_STAGES) & 1, abort_flag, err);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+          const uint64_t da = umma_desc(sa), db = umma_desc(sa + A_BYTES), db2 = umma_desc(sa + A_BYTES + B_BYTES);
+#pragma unroll
+          for (int k = 0; k < TC_BK / 16; ++k) {
+            const uint32_t acc = (i | k) != 0;
+            umma_f16(acc_addr, da + 2 * k, db + 2 * k, idesc, acc);
+            if (NB == 2) umma_f16(acc_addr + BN, da + 2 * k, db2 + 2 * k, idesc, acc);
+          }
+          umma_commit(smem_u32(&empty_bar[s]));
+        }
+        if (ok) umma_commit(smem_u32(&tmem_full_bar[as]));
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    int ti = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++ti) {
+      const int as = ti & 1;
+      const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * BN;
+      const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&tmem_full_bar[as]), (ti >> 1) & 1, abort_flag, err));
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (!ok) break;
+      const uint32_t acc_addr = tmem_base + (uint32_t)as * ACC_COLS + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (n0 + c0 >= N) break;
+        uint32_t r[32], r2[32];
+        tmem_ld32(acc_addr + (uint32_t)c0, r);
+        if (NB == 2) tmem_ld32(acc_addr + (uint32_t)c0 + BN, r2);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        epilogue_piece<EPI, TOut>(r, r2, out, ldo, residual, m0 + q * 32 + lane, n0 + c0, M, N, vec_ok);
+      }
+      // this warp's rows of the stage are in registers or stored: hand the stage back to the MMA warp
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&tmem_empty_bar[as])) : "memory");
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -324,10 +471,38 @@ static int tensor_map(const void* ptr, int rows, int cols, int ld, int box_rows,
   return 0;
 }
 
+// Which kernel runs a product: by default (auto) wide outputs with a long K go to the persistent kernel with
+// 128 x 256 tiles and two accumulator stages (1.10 to 1.16 PFLOP/s at 2048 x 8192 x 2048 against 0.88 to 0.91
+// of the other), everything else to the one-tile-per-CTA kernel with 128 x 128 tiles, two CTAs per SM (the
+// persistent kernel with narrow tiles starves on shared-memory bandwidth: 0.68 to 0.78).  Forced for comparisons.
+static int g_tc_auto = 1, g_tc_persistent = 1, g_tc_wide = 1;
+
 template <int BN, int EPI, typename TOut>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, void* out, int ldo,
-                     const float* residual, int M, int N, int K, int vec_ok, int* err, cudaStream_t stream) {
+                     const float* residual, int M, int N, int K, int vec_ok, int* err, cudaStream_t stream, bool persistent) {
   constexpr int NB = EPI == TC_EPI_SWIGLU ? 2 : 1;
+  if (persistent) {
+    constexpr int smem = TCP_STAGES * (TC_BM * TC_BK * 2 + NB * BN * TC_BK * 2) + 1024 + 256;
+    auto kern = gemm_tc_persistent_kernel<BN, EPI, TOut>;
+    static bool configured = false;
+    static int n_sms = 0;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) {
+        set_error("gemm_tc: %d bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+        return -2;
+      }
+      int dev = 0;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
+      if (n_sms <= 0) n_sms = 148;
+      configured = true;
+    }
+    const int tiles = ((N + BN - 1) / BN) * ((M + TC_BM - 1) / TC_BM);
+    const int grid = tiles < n_sms ? tiles : n_sms;
+    kern<<<grid, TC_THREADS, smem, stream>>>(ma, mb, mb2, (TOut*)out, ldo, residual, M, N, K, vec_ok, err);
+    return 0;
+  }
   constexpr int smem = TC_STAGES * (TC_BM * TC_BK * 2 + NB * BN * TC_BK * 2) + 1024 + 256;
   auto kern = gemm_tc_kernel<BN, EPI, TOut>;
   static bool configured = false;
@@ -348,6 +523,18 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
 
 using namespace edgelm;
 
+// Negative: choose per product (default).  Else bit 0: the persistent kernel; bit 1: narrow tiles only.
+extern "C" int edgelm_gemm_tc_persistent(int on) {
+  if (on < 0) {
+    g_tc_auto = 1;
+    return 0;
+  }
+  g_tc_auto = 0;
+  g_tc_persistent = on & 1;
+  g_tc_wide = (on >> 1) & 1 ? 0 : 1;   // bit 1 set: narrow tiles only
+  return 0;
+}
+
 // 1 if the tensor-core kernel takes these operands (alignment and pitch rules of TMA), else 0.
 extern "C" int edgelm_gemm_tc_takes(const void* a, int lda, const void* w, const void* w2, int K) {
   const bool ok = K > 0 && K % 8 == 0 && lda % 8 == 0 && (uintptr_t)a % 16 == 0 && (uintptr_t)w % 16 == 0 &&
@@ -365,7 +552,12 @@ extern "C" int edgelm_gemm_tc(const void* a, int lda, const void* w, const void*
   EL_REFUSE(epilogue != TC_EPI_RESIDUAL || (residual != nullptr && out_dtype == DT_F32), "gemm_tc: residual epilogue needs a float32 residual and output");
   EL_REFUSE(err != nullptr, "gemm_tc: needs the error word");
   EL_REFUSE((M + TC_BM - 1) / TC_BM <= 65535, "gemm_tc: too many rows (%d)", M);
-  const int bn = epilogue == TC_EPI_SWIGLU ? 64 : 128;
+  // wide tiles (128 x 256, or 2 x 128 for SwiGLU) when the output is wide enough to fill the device with
+  // them: twice the multiply-adds per byte that comes through shared memory
+  const long long wide_tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((N + (epilogue == TC_EPI_SWIGLU ? 127 : 255)) / (epilogue == TC_EPI_SWIGLU ? 128 : 256));
+  const bool wide = g_tc_auto ? (wide_tiles >= 120 && N >= 1024 && K >= 1024 && epilogue != TC_EPI_RESIDUAL) : (g_tc_wide && wide_tiles >= 120 && N >= 1024);
+  const bool persistent = g_tc_auto ? wide : g_tc_persistent != 0;
+  const int bn = epilogue == TC_EPI_SWIGLU ? (wide ? 128 : 64) : (wide ? 256 : 128);
   CUtensorMap ma, mb, mb2;
   if (tensor_map(a, M, K, lda, TC_BM, &ma)) return -1;
   if (tensor_map(w, N, K, K, bn, &mb)) return -1;
@@ -375,14 +567,25 @@ extern "C" int edgelm_gemm_tc(const void* a, int lda, const void* w, const void*
   const int vec_ok = ((uintptr_t)out % 16 == 0) && ((size_t)ldo * esz % 16 == 0) &&
                      (residual == nullptr || (uintptr_t)residual % 16 == 0);
   int rc = 0;
-  if (epilogue == TC_EPI_STORE && out_dtype == DT_BF16)
-    rc = launch_tc<128, TC_EPI_STORE, __nv_bfloat16>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream);
+  if (wide) {
+    if (epilogue == TC_EPI_STORE && out_dtype == DT_BF16)
+      rc = launch_tc<256, TC_EPI_STORE, __nv_bfloat16>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent);
+    else if (epilogue == TC_EPI_STORE && out_dtype == DT_F32)
+      rc = launch_tc<256, TC_EPI_STORE, float>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent);
+    else if (epilogue == TC_EPI_RESIDUAL)
+      rc = launch_tc<256, TC_EPI_RESIDUAL, float>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent);
+    else if (epilogue == TC_EPI_SWIGLU && out_dtype == DT_BF16)
+      rc = launch_tc<128, TC_EPI_SWIGLU, __nv_bfloat16>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent);
+    else
+      EL_REFUSE(false, "gemm_tc: unsupported epilogue %d with output dtype %d", epilogue, out_dtype);
+  } else if (epilogue == TC_EPI_STORE && out_dtype == DT_BF16)
+    rc = launch_tc<128, TC_EPI_STORE, __nv_bfloat16>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent);
   else if (epilogue == TC_EPI_STORE && out_dtype == DT_F32)
-    rc = launch_tc<128, TC_EPI_STORE, float>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream);
+    rc = launch_tc<128, TC_EPI_STORE, float>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent);
   else if (epilogue == TC_EPI_RESIDUAL)
-    rc = launch_tc<128, TC_EPI_RESIDUAL, float>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream);
+    rc = launch_tc<128, TC_EPI_RESIDUAL, float>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent);
   else if (epilogue == TC_EPI_SWIGLU && out_dtype == DT_BF16)
-    rc = launch_tc<64, TC_EPI_SWIGLU, __nv_bfloat16>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream);
+    rc = launch_tc<64, TC_EPI_SWIGLU, __nv_bfloat16>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent);
   else
     EL_REFUSE(false, "gemm_tc: unsupported epilogue %d with output dtype %d", epilogue, out_dtype);
   if (rc) return rc;

@@ -357,7 +357,7 @@ def test_sample_topk_matches_plain(vocab, temp, k, seed):
 
 # ----------------------------------------------------------------------------- GEMM (tcgen05 tensor cores)
 TC_SHAPES = [(128, 128, 64), (17, 64, 72), (129, 192, 576), (300, 100, 200), (256, 960, 576), (2048, 576, 1536),
-             (64, 397, 96), (130, 49, 8), (1000, 130, 136)]
+             (64, 397, 96), (130, 49, 8), (1000, 130, 136), (2048, 2048, 256), (1920, 2050, 200)]  # the last two: 128 x 256 tiles
 
 
 @pytest.mark.parametrize("M,N,K", TC_SHAPES)
