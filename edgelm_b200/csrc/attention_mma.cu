@@ -74,6 +74,8 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
   const int limA = rowA < ntok ? pos0 + rowA : -1;         // last key a row may see; -1: no such row
   const int limB = rowB < ntok ? pos0 + rowB : -1;
   const int warp_limit = min(ntok - 1, warp * 16 + 15) >= warp * 16 ? pos0 + min(ntok - 1, warp * 16 + 15) : -1;
+  const int warp_min_limit = warp * 16 < ntok ? pos0 + warp * 16 : -1;   // what the warp's first row sees: pages up to here need no mask
+  const float scale2 = scale * 1.4426950408889634f;                     // scores in units of log 2
 
   auto load_page = [&](int pg, int stage) {
     const int page = pages[pg];
@@ -143,15 +145,25 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
           pm_mma(s[nt], qa[ks2 + 1][0], qa[ks2 + 1][1], qa[ks2 + 1][2], qa[ks2 + 1][3], b2, b3);
         }
       }
-      // ---- scale, causal mask, running max and sum (float32)
+      // ---- scale, causal mask, running max and sum (float32).  Scores are kept in units of log 2
+      // (scale * log2(e) folded into one multiply), so that the exponentials are bare exp2; a page that
+      // every row of the warp sees in full needs no mask.
+      const bool masked = pg * PAGE + PAGE - 1 > warp_min_limit;
       float mxA = -CUDART_INF_F, mxB = -CUDART_INF_F;
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
         const int key = pg * PAGE + nt * 8 + tig * 2;
-        s[nt][0] = key <= limA ? s[nt][0] * scale : -CUDART_INF_F;
-        s[nt][1] = key + 1 <= limA ? s[nt][1] * scale : -CUDART_INF_F;
-        s[nt][2] = key <= limB ? s[nt][2] * scale : -CUDART_INF_F;
-        s[nt][3] = key + 1 <= limB ? s[nt][3] * scale : -CUDART_INF_F;
+        if (masked) {
+          s[nt][0] = key <= limA ? s[nt][0] * scale2 : -CUDART_INF_F;
+          s[nt][1] = key + 1 <= limA ? s[nt][1] * scale2 : -CUDART_INF_F;
+          s[nt][2] = key <= limB ? s[nt][2] * scale2 : -CUDART_INF_F;
+          s[nt][3] = key + 1 <= limB ? s[nt][3] * scale2 : -CUDART_INF_F;
+        } else {
+          s[nt][0] *= scale2;
+          s[nt][1] *= scale2;
+          s[nt][2] *= scale2;
+          s[nt][3] *= scale2;
+        }
         mxA = fmaxf(mxA, fmaxf(s[nt][0], s[nt][1]));
         mxB = fmaxf(mxB, fmaxf(s[nt][2], s[nt][3]));
       }
@@ -161,14 +173,14 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
       mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2));
       const float nmA = fmaxf(mA, mxA), nmB = fmaxf(mB, mxB);
       const float refA = nmA == -CUDART_INF_F ? 0.f : nmA, refB = nmB == -CUDART_INF_F ? 0.f : nmB;  // a row that sees no key yet
-      const float corrA = expf(mA - refA), corrB = expf(mB - refB);  // exp(-inf) = 0 on the first page
+      const float corrA = exp2f(mA - refA), corrB = exp2f(mB - refB);  // exp2(-inf) = 0 on the first page
       float sumA = 0.f, sumB = 0.f;
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
-        s[nt][0] = expf(s[nt][0] - refA);
-        s[nt][1] = expf(s[nt][1] - refA);
-        s[nt][2] = expf(s[nt][2] - refB);
-        s[nt][3] = expf(s[nt][3] - refB);
+        s[nt][0] = exp2f(s[nt][0] - refA);
+        s[nt][1] = exp2f(s[nt][1] - refA);
+        s[nt][2] = exp2f(s[nt][2] - refB);
+        s[nt][3] = exp2f(s[nt][3] - refB);
         sumA += s[nt][0] + s[nt][1];
         sumB += s[nt][2] + s[nt][3];
       }
@@ -180,12 +192,14 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
       lB = lB * corrB + sumB;
       mA = nmA;
       mB = nmB;
+      if (__any_sync(0xffffffffu, corrA != 1.f || corrB != 1.f)) {   // some row's maximum moved: rescale what is gathered
 #pragma unroll
-      for (int i = 0; i < HD / 8; ++i) {
-        o[i][0] *= corrA;
-        o[i][1] *= corrA;
-        o[i][2] *= corrB;
-        o[i][3] *= corrB;
+        for (int i = 0; i < HD / 8; ++i) {
+          o[i][0] *= corrA;
+          o[i][1] *= corrA;
+          o[i][2] *= corrB;
+          o[i][3] *= corrB;
+        }
       }
       // ---- O += P V : 4 steps of 16 keys
 #pragma unroll
@@ -235,7 +249,7 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
       const float* b = mg + ((size_t)(gsrc - 1) * PM_ROWS + rowB) * MP;
       const float nmA = fmaxf(mA, a[HD]), nmB = fmaxf(mB, b[HD]);
       const float refA = nmA == -CUDART_INF_F ? 0.f : nmA, refB = nmB == -CUDART_INF_F ? 0.f : nmB;
-      const float fA0 = expf(mA - refA), fA1 = expf(a[HD] - refA), fB0 = expf(mB - refB), fB1 = expf(b[HD] - refB);
+      const float fA0 = exp2f(mA - refA), fA1 = exp2f(a[HD] - refA), fB0 = exp2f(mB - refB), fB1 = exp2f(b[HD] - refB);
       lA = lA * fA0 + a[HD + 1] * fA1;
       lB = lB * fB0 + b[HD + 1] * fB1;
       mA = nmA;

@@ -135,9 +135,26 @@ template <> struct OutVec<__nv_bfloat16> {
 // residual and 16-byte stores where the row allows them, element by element at the ragged edge.  (Going
 // through shared memory to make a warp's accesses run along rows was measured: twice as slow, the scalar
 // instructions cost more than the scattered vectors.)
+// The residual of a piece, fetched ahead of the accumulator it will be added to (it does not depend on the
+// MMAs): 32 floats of the thread's row, valid only where the vector path applies.
+struct ResidualAhead {
+  float4 v[8];
+  bool have;
+};
+__device__ __forceinline__ void fetch_residual(ResidualAhead& ra, const float* residual, int ldo, int row, int col0, int M,
+                                               int N, int vec_ok) {
+  ra.have = residual != nullptr && vec_ok && row < M && col0 + 32 <= N;
+  if (ra.have) {
+    const float4* p = reinterpret_cast<const float4*>(residual + (size_t)row * ldo + col0);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ra.v[i] = p[i];
+  }
+}
+
 template <int EPI, typename TOut>
 __device__ __forceinline__ void epilogue_piece(const uint32_t* r, const uint32_t* r2, TOut* out, int ldo,
-                                               const float* residual, int row, int col0, int M, int N, int vec_ok) {
+                                               const float* residual, int row, int col0, int M, int N, int vec_ok,
+                                               const ResidualAhead* ahead = nullptr) {
   if (row >= M) return;
   const size_t base = (size_t)row * ldo + col0;
   const bool full = vec_ok && (col0 + 32 <= N);
@@ -152,8 +169,9 @@ __device__ __forceinline__ void epilogue_piece(const uint32_t* r, const uint32_t
     }
     if (full) {
       if (EPI == TC_EPI_RESIDUAL) {
-        const float4 a = *reinterpret_cast<const float4*>(residual + base + j0);
-        const float4 b = *reinterpret_cast<const float4*>(residual + base + j0 + 4);
+        const bool pre = ahead != nullptr && ahead->have;
+        const float4 a = pre ? ahead->v[j0 / 4] : *reinterpret_cast<const float4*>(residual + base + j0);
+        const float4 b = pre ? ahead->v[j0 / 4 + 1] : *reinterpret_cast<const float4*>(residual + base + j0 + 4);
         v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
         v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
       }
@@ -250,18 +268,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
   } else {
     const int q = warp & 3;  // a warp reads the 32 lanes of tensor memory that its index modulo 4 selects
+    ResidualAhead ra[2];
+    ra[0].have = ra[1].have = false;
+    if (EPI == TC_EPI_RESIDUAL) fetch_residual(ra[0], residual, ldo, m0 + q * 32 + lane, n0, M, N, vec_ok);  // while the MMAs run
     const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(tmem_full_bar), 0, abort_flag, err));  // one decision per warp
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ok) {
-#pragma unroll 1
+#pragma unroll
       for (int c0 = 0; c0 < BN; c0 += 32) {
         if (n0 + c0 >= N) break;  // uniform over the block
         uint32_t r[32], r2[32];
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
         tmem_ld32(taddr, r);
         if (NB == 2) tmem_ld32(taddr + BN, r2);
+        if (EPI == TC_EPI_RESIDUAL && c0 + 32 < BN)   // the next piece's residual is on its way while this one is finished
+          fetch_residual(ra[((c0 >> 5) + 1) & 1], residual, ldo, m0 + q * 32 + lane, n0 + c0 + 32, M, N, vec_ok);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        epilogue_piece<EPI, TOut>(r, r2, out, ldo, residual, m0 + q * 32 + lane, n0 + c0, M, N, vec_ok);
+        epilogue_piece<EPI, TOut>(r, r2, out, ldo, residual, m0 + q * 32 + lane, n0 + c0, M, N, vec_ok, &ra[(c0 >> 5) & 1]);
       }
     }
   }
