@@ -28,6 +28,7 @@ def main(argv=None):
     ap.add_argument("--layers", type=int, default=None, help="layers' worth of distinct weights to cycle through")
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--only", default=None, help="run only the kernels whose name contains this")
+    ap.add_argument("--no-fuse-norm", action="store_true", help="decode: the projections read a normalised input instead of computing the norm")
     ap.add_argument("--plain", action="store_true", help="eager launches, no graph and no timing (for profilers)")
     args = ap.parse_args(argv)
 
@@ -80,11 +81,11 @@ def main(argv=None):
         pm = torch.empty(B * nh * splits * 2, device=d)
         few = B <= 16
         cases = {
-            "qkv_normed": lambda l: o.gemv_mma(x, wq[l], qkv, norm_weight=nw, eps=1e-5) if few else o.gemm_tc(h, wq[l], qkv, err),
+            "qkv_normed": lambda l: (o.gemv_mma(h, wq[l], qkv) if args.no_fuse_norm else o.gemv_mma(x, wq[l], qkv, norm_weight=nw, eps=1e-5)) if few else o.gemm_tc(h, wq[l], qkv, err),
             "rope_kv_append": lambda l: o.rope_kv_append(qkv, tokpos, tokseq, seq, table, cos, sin, kc[l], vc[l], nh, nkv, hd, err),
             "attn_decode": lambda l: o.attn_decode(qkv, att, kc[l], vc[l], table, seq, pos, B, nh, nkv, hd, scale, splits, po, pm),
             "o_proj_residual": lambda l: o.gemv_mma(att, wo[l], x, epilogue=o.EPI_RESIDUAL, residual=x) if few else o.gemm_tc(att, wo[l], x, err, epilogue=o.EPI_RESIDUAL, residual=x),
-            "gate_up_swiglu_normed": lambda l: o.gemv_mma(x, wg[l], mid, epilogue=o.EPI_SWIGLU, w2=wu[l], norm_weight=nw, eps=1e-5) if few else o.gemm_tc(h, wg[l], mid, err, epilogue=o.EPI_SWIGLU, w2=wu[l]),
+            "gate_up_swiglu_normed": lambda l: (o.gemv_mma(h, wg[l], mid, epilogue=o.EPI_SWIGLU, w2=wu[l]) if args.no_fuse_norm else o.gemv_mma(x, wg[l], mid, epilogue=o.EPI_SWIGLU, w2=wu[l], norm_weight=nw, eps=1e-5)) if few else o.gemm_tc(h, wg[l], mid, err, epilogue=o.EPI_SWIGLU, w2=wu[l]),
             "down_proj_residual": lambda l: o.gemv_mma(mid, wd[l], x, epilogue=o.EPI_RESIDUAL, residual=x) if few else o.gemm_tc(mid, wd[l], x, err, epilogue=o.EPI_RESIDUAL, residual=x),
             "rmsnorm": lambda l: o.rmsnorm(x, nw, 1e-5, h),
             "lm_head": lambda l: o.gemv_mma(h, emb, logits) if few else o.gemm_tc(h, emb, logits, err),

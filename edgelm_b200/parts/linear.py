@@ -16,6 +16,7 @@ EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU = ops.EPI_STORE, ops.EPI_RESIDUAL, ops.EPI_S
 
 FEW_ROWS = 16  # up to here one pass over the weights with all rows in shared memory is bandwidth-bound already
 MMA_MIN_ROWS = 1        # rows from which the tensor-core few-rows kernel is used (measured: never slower)
+FUSE_NORM_MAX_WIDTH = 1024  # every block of a few-rows product recomputes a fused norm: worth it for narrow models only
 MMA_WIDE_COLUMNS = 8192  # from here on (the vocabulary) the tensor-core kernel wins at any row count
 
 
@@ -50,7 +51,7 @@ def matmul(ctx, a, w, out, epilogue=EPI_STORE, w2=None, residual=None):
     the tensor-core kernel's bounded waits report to."""
     rows = a.shape[0]
     if isinstance(a, NormedInput):
-        if rows <= FEW_ROWS and a._t is None:
+        if rows <= FEW_ROWS and a._t is None and a.x.shape[1] <= FUSE_NORM_MAX_WIDTH:
             if _few_rows_on_mma(rows, w.shape[0]) and ops.gemv_mma_takes(a.x, w, w2, normed=True):
                 ops.gemv_mma(a.x, w, out, epilogue=epilogue, w2=w2, residual=residual, norm_weight=a.norm.weight, eps=a.norm.eps)
                 return
