@@ -25,20 +25,52 @@ __global__ void embed_gather_kernel(const int32_t* __restrict__ ids, const TW* _
 // y[r,:] = x[src(r),:] * (1 / sqrt(mean(x^2) + eps)) * w, statistics in float32.
 // `rows_idx` (may be null) picks the source row of each output row: the gather of the
 // wanted positions before the final norm.
-template <typename TOut>
+template <typename TOut> struct NormStore;
+template <> struct NormStore<float> {
+  static __device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+  }
+};
+template <> struct NormStore<__nv_bfloat16> {
+  static __device__ __forceinline__ void store4(__nv_bfloat16* p, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 u;
+    u.x = *reinterpret_cast<uint32_t*>(&lo);
+    u.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = u;
+  }
+};
+
+// VEC: rows are read and written four elements at a time (dim a multiple of 4, 16-byte aligned rows).
+template <typename TOut, bool VEC>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, TOut* __restrict__ y,
                                const int32_t* __restrict__ rows_idx, int dim, float eps) {
   __shared__ float red[33];
   const int r = blockIdx.x;
   const float* xr = x + (size_t)(rows_idx ? rows_idx[r] : r) * dim;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
-    const float v = xr[i];
-    ss = fmaf(v, v, ss);
+  if (VEC) {
+    for (int i = threadIdx.x * 4; i < dim; i += blockDim.x * 4) {
+      const float4 v = *reinterpret_cast<const float4*>(xr + i);
+      ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+    }
+  } else {
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+      const float v = xr[i];
+      ss = fmaf(v, v, ss);
+    }
   }
   ss = block_sum(ss, red);
   const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
-  for (int i = threadIdx.x; i < dim; i += blockDim.x) y[(size_t)r * dim + i] = from_f32<TOut>(xr[i] * inv * w[i]);
+  if (VEC) {
+    for (int i = threadIdx.x * 4; i < dim; i += blockDim.x * 4) {
+      const float4 v = *reinterpret_cast<const float4*>(xr + i);
+      const float4 g = *reinterpret_cast<const float4*>(w + i);
+      NormStore<TOut>::store4(y + (size_t)r * dim + i, v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w);
+    }
+  } else {
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) y[(size_t)r * dim + i] = from_f32<TOut>(xr[i] * inv * w[i]);
+  }
 }
 
 // ---------------------------------------------------------------- RoPE + cache append
@@ -119,11 +151,14 @@ extern "C" int edgelm_rmsnorm(const float* x, const float* w, void* y, int out_d
   if (rows == 0) return 0;
   EL_REFUSE(rows > 0 && dim > 0, "rmsnorm: bad sizes rows=%d dim=%d", rows, dim);
   const int threads = dim >= 1024 ? 256 : 128;
-  if (out_dtype == DT_F32)
-    rmsnorm_kernel<float><<<rows, threads, 0, stream>>>(x, w, (float*)y, rows_idx, dim, eps);
-  else if (out_dtype == DT_BF16)
-    rmsnorm_kernel<__nv_bfloat16><<<rows, threads, 0, stream>>>(x, w, (__nv_bfloat16*)y, rows_idx, dim, eps);
-  else
+  const bool vec = dim % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)y % 16 == 0;
+  if (out_dtype == DT_F32) {
+    if (vec) rmsnorm_kernel<float, true><<<rows, threads, 0, stream>>>(x, w, (float*)y, rows_idx, dim, eps);
+    else rmsnorm_kernel<float, false><<<rows, threads, 0, stream>>>(x, w, (float*)y, rows_idx, dim, eps);
+  } else if (out_dtype == DT_BF16) {
+    if (vec) rmsnorm_kernel<__nv_bfloat16, true><<<rows, threads, 0, stream>>>(x, w, (__nv_bfloat16*)y, rows_idx, dim, eps);
+    else rmsnorm_kernel<__nv_bfloat16, false><<<rows, threads, 0, stream>>>(x, w, (__nv_bfloat16*)y, rows_idx, dim, eps);
+  } else
     EL_REFUSE(false, "rmsnorm: unknown dtype code %d", out_dtype);
   EL_LAUNCH_CHECK("rmsnorm");
   return 0;
