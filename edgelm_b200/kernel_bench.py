@@ -28,6 +28,7 @@ def main(argv=None):
     ap.add_argument("--layers", type=int, default=None, help="layers' worth of distinct weights to cycle through")
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--only", default=None, help="run only the kernels whose name contains this")
+    ap.add_argument("--splits", type=int, default=0, help="decode: blocks per (sequence, kv head) of the attention")
     ap.add_argument("--no-fuse-norm", action="store_true", help="decode: the projections read a normalised input instead of computing the norm")
     ap.add_argument("--plain", action="store_true", help="eager launches, no graph and no timing (for profilers)")
     args = ap.parse_args(argv)
@@ -76,7 +77,7 @@ def main(argv=None):
     if decode:
         pos = torch.full((B,), ctx_len - 1, dtype=torch.int32, device=d)
         tokpos, tokseq = pos.clone(), seq.clone()
-        splits = min(64, max(1, (2 * 148 + B * nkv - 1) // (B * nkv)))
+        splits = args.splits or min(64, max(1, (2 * 148 + B * nkv - 1) // (B * nkv)))
         po = torch.empty(B * nh * splits * hd, device=d)
         pm = torch.empty(B * nh * splits * 2, device=d)
         few = B <= 16
