@@ -11,27 +11,9 @@
 // rows padded by 16 bytes (all on the warp's mbarrier), so that ldmatrix reads hit distinct banks.
 // Rows of the last tile that lie past the sequence's end are zeroed in shared memory before use.
 #pragma once
+#include "attention_tile_mma.cuh"
 
 namespace edgelm {
-
-__device__ __forceinline__ void dm_mma(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void dm_ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-__device__ __forceinline__ void dm_ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-__device__ __forceinline__ uint32_t dm_pack(float a, float b) {
-  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<const uint32_t*>(&v);
-}
-
-constexpr int DM_ROWS = 16;  // query heads of a kv head served in one pass (rows of the A operand)
 
 // Shared memory before the per-warp tiles: queries [16][hd + 8] bfloat16, the new token's key and value,
 // the warps' mbarriers.  (A warp's partial result [16][hd + 2] float goes into its own key tile when its
@@ -144,11 +126,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat
     }
     __syncthreads();
     uint32_t qa[HDT][4];
-#pragma unroll
-    for (int ks = 0; ks < HDT; ++ks) {
-      const int mi = lane >> 3;  // matrices: (rows 0-7, k 0-7), (rows 8-15, k 0-7), (rows 0-7, k 8-15), (rows 8-15, k 8-15)
-      dm_ldmatrix_x4(dec_smem_u32(Qs + ((mi & 1) * 8 + (lane & 7)) * PITCH + ks * 16 + (mi >> 1) * 8), qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3]);
-    }
+    dm_load_queries<HDT>(Qs, qa);
     float o[HD / 8][4];
 #pragma unroll
     for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
@@ -184,76 +162,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat
         }
       }
       __syncwarp();
-      // ---- scores: 8 tiles of 8 keys
-      float s[8][4];
-#pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
-#pragma unroll
-        for (int ks2 = 0; ks2 < HDT; ks2 += 2) {
-          const int mi = lane >> 3;
-          uint32_t b0, b1, b2, b3;
-          dm_ldmatrix_x4(dec_smem_u32(Kt + (nt * 8 + (lane & 7)) * PITCH + (ks2 + (mi >> 1)) * 16 + (mi & 1) * 8), b0, b1, b2, b3);
-          dm_mma(s[nt], qa[ks2][0], qa[ks2][1], qa[ks2][2], qa[ks2][3], b0, b1);
-          dm_mma(s[nt], qa[ks2 + 1][0], qa[ks2 + 1][1], qa[ks2 + 1][2], qa[ks2 + 1][3], b2, b3);
-        }
-      }
-      float mxA = -CUDART_INF_F, mxB = -CUDART_INF_F;
-#pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        const int key = nt * 8 + tig * 2;
-        s[nt][0] = key < valid ? s[nt][0] * scale : -CUDART_INF_F;
-        s[nt][1] = key + 1 < valid ? s[nt][1] * scale : -CUDART_INF_F;
-        s[nt][2] = key < valid ? s[nt][2] * scale : -CUDART_INF_F;
-        s[nt][3] = key + 1 < valid ? s[nt][3] * scale : -CUDART_INF_F;
-        mxA = fmaxf(mxA, fmaxf(s[nt][0], s[nt][1]));
-        mxB = fmaxf(mxB, fmaxf(s[nt][2], s[nt][3]));
-      }
-      mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 1));
-      mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 2));
-      mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 1));
-      mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2));
-      const float nmA = fmaxf(mA, mxA), nmB = fmaxf(mB, mxB);   // finite: valid >= 1
-      const float corrA = expf(mA - nmA), corrB = expf(mB - nmB);
-      float sumA = 0.f, sumB = 0.f;
-#pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        s[nt][0] = expf(s[nt][0] - nmA);
-        s[nt][1] = expf(s[nt][1] - nmA);
-        s[nt][2] = expf(s[nt][2] - nmB);
-        s[nt][3] = expf(s[nt][3] - nmB);
-        sumA += s[nt][0] + s[nt][1];
-        sumB += s[nt][2] + s[nt][3];
-      }
-      sumA += __shfl_xor_sync(0xffffffffu, sumA, 1);
-      sumA += __shfl_xor_sync(0xffffffffu, sumA, 2);
-      sumB += __shfl_xor_sync(0xffffffffu, sumB, 1);
-      sumB += __shfl_xor_sync(0xffffffffu, sumB, 2);
-      lA = lA * corrA + sumA;
-      lB = lB * corrB + sumB;
-      mA = nmA;
-      mB = nmB;
-#pragma unroll
-      for (int i = 0; i < HD / 8; ++i) {
-        o[i][0] *= corrA;
-        o[i][1] *= corrA;
-        o[i][2] *= corrB;
-        o[i][3] *= corrB;
-      }
-      // ---- values: 4 steps of 16 keys
-#pragma unroll
-      for (int kt = 0; kt < 4; ++kt) {
-        const uint32_t a0 = dm_pack(s[2 * kt][0], s[2 * kt][1]), a1 = dm_pack(s[2 * kt][2], s[2 * kt][3]);
-        const uint32_t a2 = dm_pack(s[2 * kt + 1][0], s[2 * kt + 1][1]), a3 = dm_pack(s[2 * kt + 1][2], s[2 * kt + 1][3]);
-#pragma unroll
-        for (int dt = 0; dt < HD / 8; dt += 2) {
-          const int mi = lane >> 3;
-          uint32_t b0, b1, b2, b3;
-          dm_ldmatrix_x4_trans(dec_smem_u32(Vt + (kt * 16 + (mi & 1) * 8 + (lane & 7)) * PITCH + (dt + (mi >> 1)) * 8), b0, b1, b2, b3);
-          dm_mma(o[dt], a0, a1, a2, a3, b0, b1);
-          dm_mma(o[dt + 1], a0, a1, a2, a3, b2, b3);
-        }
-      }
+      dm_tile_update<HDT>(Kt, Vt, qa, valid, scale, o, mA, mB, lA, lB);
       __syncwarp();
     }
     if (failed) {

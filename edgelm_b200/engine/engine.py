@@ -243,7 +243,11 @@ class Engine:
 
     def check_device_errors(self):
         """Raise if a kernel flagged bad input since the last check (synchronises)."""
-        ops.read_error_word(self.err)
+        try:
+            ops.read_error_word(self.err)
+        except ops.KernelError:
+            self.model.reset_after_device_error()
+            raise
 
     # ------------------------------------------------------------------ sampled steps (generation)
     def prefill_sampled(self, slots, prompts, params):

@@ -10,6 +10,7 @@ import torch
 from ..config.base import ConfigError, ModelPlan
 from ..parts import registry as part_registry
 from ..parts.base import nbytes
+from .profiler import NULL_PROFILER
 
 
 class DecoderModel:
@@ -28,6 +29,8 @@ class DecoderModel:
         self.head = env.build("head", plan.head)
         self.schedule = plan.schedule
         self.device = None
+        self.fuse_decode = True      # small decode steps run fused runs of layers as one kernel each
+        self._decode_runs = None
         for i, e in enumerate(self.schedule):
             need = self.layers[e.layer].cache_need()
             if e.reads_cache_of is not None and need is not None and not getattr(self.layers[e.layer].mixer, "reads_foreign_cache", False):
@@ -60,7 +63,20 @@ class DecoderModel:
             self.head.load(tensors, "", device, tied_table=self.embedding.table)
         else:
             self.head.load(tensors, "", device)
+        self._decode_runs = None
         return self
+
+    def decode_runs(self):
+        """The schedule cut into runs that the fused decode kernel takes and single entries (planned once)."""
+        if self._decode_runs is None:
+            from .fusion import plan_decode_runs
+            self._decode_runs = plan_decode_runs(self)
+        return self._decode_runs
+
+    def reset_after_device_error(self):
+        for stack, _ in (self._decode_runs or ()):
+            if stack is not None:
+                stack.reset()
 
     # ------------------------------------------------------------------ cache and workspace
     def cache_needs(self):
@@ -109,9 +125,15 @@ class DecoderModel:
         x = ws.alloc((T, self.plan.hidden_size), torch.float32)
         with ctx.prof("embedding"):
             self.embedding.forward(ctx, x)
-        for i, e in enumerate(self.schedule):
-            entry = cache.entries[e.reads_cache_of if e.reads_cache_of is not None else i]
-            self.layers[e.layer].forward(ctx, x, entry)
+        fused = self.fuse_decode and ctx.all_single and self.dtype == torch.bfloat16 and ctx.prof is NULL_PROFILER
+        for stack, indices in (self.decode_runs() if fused else [(None, range(len(self.schedule)))]):
+            if stack is not None and stack.takes(ctx):
+                stack.run(ctx, cache, x)
+                continue
+            for i in indices:
+                e = self.schedule[i]
+                entry = cache.entries[e.reads_cache_of if e.reads_cache_of is not None else i]
+                self.layers[e.layer].forward(ctx, x, entry)
         if R:
             with ws.frame():
                 xn = ws.alloc((R, self.plan.hidden_size), self.dtype)

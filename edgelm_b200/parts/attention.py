@@ -44,6 +44,13 @@ class Attention(Part):
         self.w_o = as_matrix(tensors[prefix + n["o"]], self.dtype, device)
         self.positions.load(tensors, prefix, device)
 
+    def decode_fusion(self):
+        if not hasattr(self.positions, "rotation_tables"):
+            return None
+        cos, sin = self.positions.rotation_tables()
+        return {"kind": "attention_rope", "w_qkv": self.w_qkv, "w_o": self.w_o, "num_heads": self.nh, "num_kv_heads": self.nkv,
+                "head_dim": self.hd, "scale": self.scale, "cos": cos, "sin": sin}
+
     def cache_need(self):
         return KVNeed(self.nkv, self.hd)
 

@@ -60,6 +60,12 @@ class Part:
     def cache_need(self):
         return None
 
+    def decode_fusion(self):
+        """What a fused decode kernel needs to know to do this part's work itself: a dict with a "kind" and the
+        part's tensors and constants, or None (the default) if the part only runs through its own `forward`.
+        The engine's fusion pass reads these once the weights are loaded; a part never sees the fused kernel."""
+        return None
+
     def tile_sizes(self):
         """Sizes of attention tiles (`ctx.tiles(n)`) this part will ask for: the engine lays them out
         with the step's metadata, which is what lets a whole step be replayed from a CUDA graph."""

@@ -22,7 +22,12 @@ TINY_C = dict(model_type="llama", architectures=["LlamaForCausalLM"], vocab_size
               intermediate_size=70, num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=3, head_dim=48,
               max_position_embeddings=160, rope_theta=777.0, rms_norm_eps=3e-4, tie_word_embeddings=True,
               bos_token_id=0, eos_token_id=1)
-TINY = {"tiny_a": (TINY_A, 0, 0.09), "tiny_b": (TINY_B, 2, 0.07), "tiny_c": (TINY_C, 5, 0.1)}  # config, seed, sigma (large enough for logits of order 1)
+# sizes the fused decode kernel takes (head size 64), and room for contexts of several attention chunks
+TINY_D = dict(model_type="llama", architectures=["LlamaForCausalLM"], vocab_size=300, hidden_size=72,
+              intermediate_size=88, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+              max_position_embeddings=1200, rope_theta=50000.0, rms_norm_eps=2e-5, tie_word_embeddings=False,
+              bos_token_id=0, eos_token_id=1)
+TINY = {"tiny_a": (TINY_A, 0, 0.09), "tiny_b": (TINY_B, 2, 0.07), "tiny_c": (TINY_C, 5, 0.1), "tiny_d": (TINY_D, 8, 0.08)}  # config, seed, sigma (large enough for logits of order 1)
 
 TOL = {"float32": 2e-5, "bfloat16": 3e-2}
 

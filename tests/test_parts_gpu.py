@@ -311,19 +311,24 @@ def _register_reader():
 
         def plan(self):
             d = self.d
-            D, V = d["width"], d["vocab_size"]
+            D, V, hd = d["width"], d["vocab_size"], d.get("head_dim", 16)
             norm = lambda name: PartSpec("rmsnorm", {"dim": D, "eps": 1e-5, "name": name})
-            att = PartSpec("attention", {"hidden_size": D, "num_heads": 2, "num_kv_heads": 2, "head_dim": 16,
-                                         "positions": PartSpec("rope", {"head_dim": 16, "theta": 1000.0, "max_positions": 256}),
-                                         "names": {"q": "q.weight", "k": "k.weight", "v": "v.weight", "o": "o.weight"}})
-            reader = PartSpec("toy_value_reader", {"dim": D, "head_dim": 16, "name": "read.weight"})
-            ffn = PartSpec("swiglu", {"hidden_size": D, "intermediate_size": 24,
-                                      "names": {"gate": "g.weight", "up": "u.weight", "down": "d.weight"}})
-            layers = (LayerSpec("a.", "prenorm", att, norm("n1.weight"), ffn, norm("n2.weight")),
-                      LayerSpec("r.", "prenorm", reader, norm("n1.weight"), ffn, norm("n2.weight")))
+            rope = PartSpec("rope", {"head_dim": hd, "theta": 1000.0, "max_positions": 256})
+            names = {"q": "q.weight", "k": "k.weight", "v": "v.weight", "o": "o.weight"}
+            att = PartSpec("attention", {"hidden_size": D, "num_heads": 2, "num_kv_heads": 2, "head_dim": hd, "positions": rope, "names": names})
+            reader = PartSpec("toy_value_reader", {"dim": D, "head_dim": hd, "name": "read.weight"})
+            ffn = lambda inter: PartSpec("swiglu", {"hidden_size": D, "intermediate_size": inter,
+                                                    "names": {"gate": "g.weight", "up": "u.weight", "down": "d.weight"}})
+            layers = (LayerSpec("a.", "prenorm", att, norm("n1.weight"), ffn(24), norm("n2.weight")),
+                      LayerSpec("r.", "prenorm", reader, norm("n1.weight"), ffn(24), norm("n2.weight")))
+            schedule = (ScheduleEntry(0), ScheduleEntry(1, reads_cache_of=0))
+            if d.get("third_layer"):   # another attention layer, with other head counts and another width inside
+                att3 = PartSpec("attention", {"hidden_size": D, "num_heads": 3, "num_kv_heads": 1, "head_dim": hd, "positions": rope, "names": names})
+                layers += (LayerSpec("c.", "prenorm", att3, norm("n1.weight"), ffn(40), norm("n2.weight")),)
+                schedule += (ScheduleEntry(2),)
             return ModelPlan(hidden_size=D, vocab_size=V, max_positions=256,
                              embedding=PartSpec("embedding", {"vocab_size": V, "dim": D, "name": "emb.weight"}),
-                             layers=layers, schedule=(ScheduleEntry(0), ScheduleEntry(1, reads_cache_of=0)),
+                             layers=layers, schedule=schedule,
                              final_norm=norm("final.weight"),
                              head=PartSpec("lm_head", {"vocab_size": V, "dim": D, "tied_to": None, "name": "head.weight"}))
 
@@ -365,3 +370,35 @@ def test_a_layer_reads_another_layers_cache(tmp_path):
         assert H.rel_err(H.run_tail_one_by_one(eng, r, 8), want) < 5e-5
     for r, g in zip(reqs, H.run_batches(eng, reqs, batch_size=2, decode_tail=4)):
         assert H.rel_err(g, plain_model(r)) < 5e-5
+
+
+def test_fusion_pass_cuts_the_schedule_around_a_layer_it_cannot_take(tmp_path):
+    """Attention layer, a toy layer that reads the first one's cache, attention layer with other head counts: in
+    bfloat16 the decode steps run the first and the third as fused kernels and the toy layer through its own
+    forward; the logits are those of the same engine with the fusion off."""
+    _register_reader()
+    from edgelm_b200.config import read_config
+    from edgelm_b200.engine.engine import Engine, load_model
+    from edgelm_b200.engine.model import expected_weights
+    from edgelm_b200.weights import random_tensors, write_file
+    d = {"architectures": ["ToyReaderForCausalLM"], "vocab_size": 41, "width": 32, "head_dim": 32, "third_layer": True}
+    folder = tmp_path / "sandwich"
+    folder.mkdir()
+    (folder / "config.json").write_text(json.dumps(d))
+    exp = expected_weights(read_config(str(folder)).plan())
+    write_file(str(folder / "model.safetensors"), random_tensors(exp, seed=4, sigma=0.2, dtype=torch.float32))
+    model = load_model(str(folder), "bfloat16")
+    eng = Engine(model, max_tokens=1024)
+    runs = model.decode_runs()
+    assert [(s is not None, list(i)) for s, i in runs] == [(True, [0]), (False, [1]), (True, [2])]
+    assert runs[0][0].fusions[0]["num_heads"] == 2 and runs[2][0].fusions[0]["num_heads"] == 3 and runs[2][0].max_inter == 40
+    reqs = [[int(v) for v in np.random.default_rng(20 + i).integers(0, 41, size=n)] for i, n in enumerate([70, 9, 130, 64])]
+    got = {}
+    for fuse in (True, False):
+        model.fuse_decode = fuse
+        got[fuse] = [H.run_tail_one_by_one(eng, r, 12) for r in reqs] + H.run_batches(eng, reqs, batch_size=3, decode_tail=6)
+    for a, b in zip(got[True], got[False]):
+        assert np.isfinite(a).all() and H.rel_err(a, b) < 2e-2
+    # float32 keeps to the parts' own kernels
+    assert all(s is None for s, _ in load_model(str(folder), "float32").decode_runs())
+    eng.check_device_errors()
