@@ -646,11 +646,12 @@ int launch_decode(const void* q, int ldq, void* out, int ldo, const void* kc, co
   cudaError_t le = cudaSuccess;
   bool on_mma = false;
   if constexpr (sizeof(T) == 2) {
-    // bfloat16 with a head size the MMAs tile (32, 64, 96, 128) and several query heads per kv head: the
-    // tensor-core kernel (with one query head per kv head the CUDA-core kernel has as little arithmetic and
-    // fewer, larger copies: measured 46 against 52 us at 32/32 heads).  It folds the splits with the combine
-    // kernel only (no counters).
-    if ((hd == 32 || hd == 64 || hd == 96 || hd == 128) && nh / nkv >= 2 && counters == nullptr && !g_decode_cuda_cores) {
+    // bfloat16 with a head size the MMAs tile (32, 64, 96, 128): the tensor-core kernel, whatever the number of
+    // query heads a kv head (with one, 15 of the 16 rows are zero, but the kernel is bound by the cache's bytes:
+    // measured at 32/32 heads, 1,500 keys, batch 64: 136 us against the CUDA-core kernel's 210 us).  It folds the
+    // splits with the combine kernel only (no counters).
+    const bool aligned = ldq % 8 == 0 && (uintptr_t)q % 16 == 0;   // it reads the query rows 16 bytes at a time
+    if ((hd == 32 || hd == 64 || hd == 96 || hd == 128) && counters == nullptr && !g_decode_cuda_cores && aligned) {
       on_mma = true;
       const size_t smem = decode_mma_head_bytes(hd) + (size_t)DEC_WARPS * 2 * PAGE * (hd + 8) * 2;
       auto go = [&](auto kern) {

@@ -7,9 +7,10 @@
 // differs is inside a tile.  The g query heads that share the kv head are the rows of a 16-row A
 // operand (rows from g on are zero), so one tile costs 8 x hd/16 MMAs for the scores and as many
 // for the values instead of thousands of multiply-adds: at batch 64 the kernel was bound by
-// instruction issue, not by memory.  Key and value rows come by one cp.async.bulk per row into
-// rows padded by 16 bytes (all on the warp's mbarrier), so that ldmatrix reads hit distinct banks.
-// Rows of the last tile that lie past the sequence's end are zeroed in shared memory before use.
+// instruction issue, not by memory.  Key and value rows come by 16-byte cp.async into rows padded by
+// 16 bytes (each lane's share arriving on the warp's mbarrier), so that ldmatrix reads hit distinct
+// banks; a bulk copy per row, 128 small requests a tile, was bound by their issue.  Value rows of the
+// last tile that lie past the sequence's end are zeroed in shared memory before use.
 #pragma once
 #include "attention_tile_mma.cuh"
 
@@ -48,7 +49,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat
   const int g = nh / nkv;
   const uint32_t bar = dec_smem_u32(&bars[warp]);
   if (lane == 0) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(1));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(32));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncwarp();
@@ -68,43 +69,20 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat
   const int tpos = min(pos, max_pos - 1);
   const bool owner = fused && (pos / PAGE) / per_split == split;
   if (fused && pos >= max_pos && threadIdx.x == 0 && err) atomicOr(err, ERR_POSITION_RANGE);
-  auto rotated = [&](const T* row, int d) {
-    const int j = d < half ? d : d - half;
-    const float c = cos_t[(size_t)tpos * half + j], sn = sin_t[(size_t)tpos * half + j];
-    const float self = to_f32(row[d]), other = to_f32(row[d < half ? d + half : d - half]);
-    return __float2bfloat16_rn(d < half ? self * c - other * sn : self * c + other * sn);
-  };
+  int new_page = -1;
   if (owner) {
-    const int page = pages[pos / PAGE];
-    const T* krow = q + (size_t)seq * ldq + (size_t)(nh + kvh) * HD;
-    const T* vrow = q + (size_t)seq * ldq + (size_t)(nh + nkv + kvh) * HD;
-    if (page < 0 && threadIdx.x == 0 && err) atomicOr(err, ERR_PAGE_RANGE);
-    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-      const T kd = rotated(krow, d);
-      newkv[d] = kd;
-      newkv[HD + d] = vrow[d];
-      if (page >= 0) {
-        const size_t dst = (((size_t)page * nkv + kvh) * PAGE + pos % PAGE) * HD + d;
-        kcache[dst] = kd;
-        vcache[dst] = vrow[d];
-      }
-    }
+    new_page = pages[pos / PAGE];
+    if (new_page < 0 && threadIdx.x == 0 && err) atomicOr(err, ERR_PAGE_RANGE);
   }
-  auto issue_tile = [&](int t) {   // whole warp: one bulk copy per key row and per value row into padded rows
+  auto issue_tile = [&](int t) {   // whole warp: 16-byte asynchronous copies into padded rows, a lane's share arriving on the warp's mbarrier
     const size_t src = ((size_t)pages[p_begin + t] * nkv + kvh) * PAGE * HD;
-    if (lane == 0) {
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)(2 * PAGE * HD * 2)) : "memory");
-    }
-    __syncwarp();
 #pragma unroll
-    for (int rr = 0; rr < PAGE; rr += 32) {
-      const int r = rr + lane;
-      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                   ::"r"(dec_smem_u32(Kt + r * PITCH)), "l"(kcache + src + (size_t)r * HD), "r"((uint32_t)(HD * 2)), "r"(bar) : "memory");
-      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                   ::"r"(dec_smem_u32(Vt + r * PITCH)), "l"(vcache + src + (size_t)r * HD), "r"((uint32_t)(HD * 2)), "r"(bar) : "memory");
+    for (int i = lane; i < PAGE * (HD / 8); i += 32) {
+      const int r = i / (HD / 8), c = (i - r * (HD / 8)) * 8;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dec_smem_u32(Kt + r * PITCH + c)), "l"(kcache + src + (size_t)r * HD + c) : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dec_smem_u32(Vt + r * PITCH + c)), "l"(vcache + src + (size_t)r * HD + c) : "memory");
     }
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
   };
   bool pre_issued = false;
   if (warp < n_tiles) {   // the first tile is on its way while the queries are staged
@@ -115,14 +93,32 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat
   for (int h0 = 0; h0 < g; h0 += DM_ROWS) {   // passes of 16 query heads (one pass unless a kv head serves more)
     const int rows = min(DM_ROWS, g - h0);
     __syncthreads();
-    for (int i = threadIdx.x; i < DM_ROWS * HD; i += blockDim.x) {
-      const int r = i / HD, d = i - r * HD;
-      T v = __float2bfloat16_rn(0.f);
-      if (r < rows) {
-        const T* qrow = q + (size_t)seq * ldq + (size_t)(kvh * g + h0 + r) * HD;
-        v = fused ? rotated(qrow, d) : qrow[d];
+    // rows 0 .. rows - 1: the query heads of this pass (rotated when fused; rows from there on are zero); rows 16 and
+    // 17, in the block that holds the new token and on the first pass: its rotated key and its value, for the cache
+    // and for this block's own tile.  An item is eight dims of a row's first half with their partners in the second.
+    for (int i = threadIdx.x; i < DM_ROWS * (HD / 8); i += blockDim.x) {
+      const int r = i / (HD / 8), c = (i - r * (HD / 8)) * 8;
+      if (r >= rows) *reinterpret_cast<uint4*>(Qs + r * PITCH + c) = make_uint4(0, 0, 0, 0);
+    }
+    const T* tok = q + (size_t)seq * ldq;
+    for (int i = threadIdx.x; i < (rows + (owner && h0 == 0 ? 2 : 0)) * (HD / 16); i += blockDim.x) {
+      const int rr = i / (HD / 16), d = (i - rr * (HD / 16)) * 8;
+      const int r = rr < rows ? rr : DM_ROWS + (rr - rows);
+      const T* row = r < DM_ROWS ? tok + (size_t)(kvh * g + h0 + r) * HD : tok + (size_t)(nh + (r - DM_ROWS) * nkv + kvh) * HD;
+      uint4 lo = *reinterpret_cast<const uint4*>(row + d), hi = *reinterpret_cast<const uint4*>(row + half + d);
+      if (fused && r != DM_ROWS + 1) dm_rotate8(lo, hi, cos_t + (size_t)tpos * half, sin_t + (size_t)tpos * half, d);
+      if (r < DM_ROWS) {
+        *reinterpret_cast<uint4*>(Qs + r * PITCH + d) = lo;
+        *reinterpret_cast<uint4*>(Qs + r * PITCH + half + d) = hi;
+      } else {
+        *reinterpret_cast<uint4*>(newkv + (r - DM_ROWS) * HD + d) = lo;
+        *reinterpret_cast<uint4*>(newkv + (r - DM_ROWS) * HD + half + d) = hi;
+        if (new_page >= 0) {
+          T* dst = (r == DM_ROWS ? kcache : vcache) + (((size_t)new_page * nkv + kvh) * PAGE + pos % PAGE) * HD;
+          *reinterpret_cast<uint4*>(dst + d) = lo;
+          *reinterpret_cast<uint4*>(dst + half + d) = hi;
+        }
       }
-      Qs[r * PITCH + d] = v;
     }
     __syncthreads();
     uint32_t qa[HDT][4];
@@ -154,11 +150,11 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat
           Vt[(pos - key0) * PITCH + d] = newkv[HD + d];
         }
       }
-      if (valid < PAGE) {   // rows past the sequence's end are not this sequence's: zero the values, the scores are masked
+      if (valid < PAGE) {   // rows past the sequence's end are not this sequence's: their scores are masked whatever the
+        // keys hold and their weights are exactly zero; zero values keep a stale NaN from meeting them
         for (int i = lane; i < (PAGE - valid) * (HD / 8); i += 32) {
           const int r = valid + i / (HD / 8), c = i - (i / (HD / 8)) * (HD / 8);
           *reinterpret_cast<uint4*>(Vt + r * PITCH + c * 8) = make_uint4(0, 0, 0, 0);
-          *reinterpret_cast<uint4*>(Kt + r * PITCH + c * 8) = make_uint4(0, 0, 0, 0);
         }
       }
       __syncwarp();

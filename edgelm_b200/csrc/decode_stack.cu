@@ -624,22 +624,7 @@ __device__ __forceinline__ void ds_attention(uint8_t* head, uint8_t* tiles, uint
       const int r = rr < g ? rr : DM_ROWS + (rr - g);
       const T* row = r < DM_ROWS ? tok + (size_t)(kvh * g + r) * HD : tok + (size_t)(nh + (r - DM_ROWS) * nkv + kvh) * HD;
       uint4 lo = __ldcg(reinterpret_cast<const uint4*>(row + d)), hi = __ldcg(reinterpret_cast<const uint4*>(row + half + d));
-      if (r != DM_ROWS + 1) {   // rotate: (a, b) -> (a cos - b sin, b cos + a sin) for the pairs (d, d + half)
-        const float4 c0 = *reinterpret_cast<const float4*>(L.cos_t + (size_t)tpos * half + d), c1 = *reinterpret_cast<const float4*>(L.cos_t + (size_t)tpos * half + d + 4);
-        const float4 s0 = *reinterpret_cast<const float4*>(L.sin_t + (size_t)tpos * half + d), s1 = *reinterpret_cast<const float4*>(L.sin_t + (size_t)tpos * half + d + 4);
-        const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w}, sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-        const __nv_bfloat16* pl = reinterpret_cast<const __nv_bfloat16*>(&lo);
-        const __nv_bfloat16* ph = reinterpret_cast<const __nv_bfloat16*>(&hi);
-        __nv_bfloat16 ol[8], oh[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float av = to_f32(pl[j]), bv = to_f32(ph[j]);
-          ol[j] = __float2bfloat16_rn(av * cs[j] - bv * sn[j]);
-          oh[j] = __float2bfloat16_rn(bv * cs[j] + av * sn[j]);
-        }
-        lo = *reinterpret_cast<const uint4*>(ol);
-        hi = *reinterpret_cast<const uint4*>(oh);
-      }
+      if (r != DM_ROWS + 1) dm_rotate8(lo, hi, L.cos_t + (size_t)tpos * half, L.sin_t + (size_t)tpos * half, d);
       if (r < DM_ROWS) {
         *reinterpret_cast<uint4*>(Qs + r * PITCH + d) = lo;
         *reinterpret_cast<uint4*>(Qs + r * PITCH + half + d) = hi;
