@@ -193,7 +193,11 @@ template <int BN, int EPI, typename TOut>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_b2, TOut* out, int ldo, const float* residual,
-               int M, int N, int K, int vec_ok, int* err) {
+               int M, int N, int K, int vec_ok, int* err, int k_splits, float* partial) {
+  // k_splits > 1: block z of the grid accumulates its share of K only and leaves the raw sums in
+  // `partial` [split][weight][M][N] (float32); splitk_reduce_kernel adds the splits in their order and
+  // applies the epilogue.  For products of few tiles and long K (decoding 17 to 128 sequences), which
+  // would otherwise run on a handful of SMs.
   constexpr int NB = EPI == TC_EPI_SWIGLU ? 2 : 1;
   constexpr int A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
   constexpr int STAGE_BYTES = A_BYTES + NB * B_BYTES;
@@ -212,7 +216,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN;
-  const int n_k = (K + TC_BK - 1) / TC_BK;
+  const int n_k_all = (K + TC_BK - 1) / TC_BK;
+  const int k_per = (n_k_all + k_splits - 1) / k_splits;
+  const int k_first = blockIdx.z * k_per;
+  const int n_k = max(0, min(n_k_all, k_first + k_per) - k_first);   // (the host picks splits that all get a share)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < TC_STAGES; ++s) {
@@ -240,9 +247,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint32_t bar = smem_u32(&full_bar[s]);
         mbar_expect_tx(bar, STAGE_BYTES);
         const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
-        tma_load_2d(sa, &map_a, bar, i * TC_BK, m0);
-        tma_load_2d(sa + A_BYTES, &map_b, bar, i * TC_BK, n0);
-        if (NB == 2) tma_load_2d(sa + A_BYTES + B_BYTES, &map_b2, bar, i * TC_BK, n0);
+        tma_load_2d(sa, &map_a, bar, (k_first + i) * TC_BK, m0);
+        tma_load_2d(sa + A_BYTES, &map_b, bar, (k_first + i) * TC_BK, n0);
+        if (NB == 2) tma_load_2d(sa + A_BYTES + B_BYTES, &map_b2, bar, (k_first + i) * TC_BK, n0);
       }
     }
   } else if (warp == 1) {
@@ -270,7 +277,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int q = warp & 3;  // a warp reads the 32 lanes of tensor memory that its index modulo 4 selects
     ResidualAhead ra[2];
     ra[0].have = ra[1].have = false;
-    if (EPI == TC_EPI_RESIDUAL) fetch_residual(ra[0], residual, ldo, m0 + q * 32 + lane, n0, M, N, vec_ok);  // while the MMAs run
+    if (EPI == TC_EPI_RESIDUAL && k_splits == 1) fetch_residual(ra[0], residual, ldo, m0 + q * 32 + lane, n0, M, N, vec_ok);  // while the MMAs run
     const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(tmem_full_bar), 0, abort_flag, err));  // one decision per warp
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ok) {
@@ -281,9 +288,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
         tmem_ld32(taddr, r);
         if (NB == 2) tmem_ld32(taddr + BN, r2);
-        if (EPI == TC_EPI_RESIDUAL && c0 + 32 < BN)   // the next piece's residual is on its way while this one is finished
+        if (EPI == TC_EPI_RESIDUAL && k_splits == 1 && c0 + 32 < BN)   // the next piece's residual is on its way while this one is finished
           fetch_residual(ra[((c0 >> 5) + 1) & 1], residual, ldo, m0 + q * 32 + lane, n0 + c0 + 32, M, N, vec_ok);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (k_splits > 1) {   // raw sums of this share of K
+          const int row = m0 + q * 32 + lane;
+          if (row < M) {
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+              float* dst = partial + (((size_t)blockIdx.z * NB + b) * M + row) * N + n0 + c0;
+              const uint32_t* src = b == 0 ? r : r2;
+              if (n0 + c0 + 32 <= N && N % 4 == 0) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                  *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(src[j]), __uint_as_float(src[j + 1]), __uint_as_float(src[j + 2]), __uint_as_float(src[j + 3]));
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (n0 + c0 + j < N) dst[j] = __uint_as_float(src[j]);
+              }
+            }
+          }
+          continue;
+        }
         epilogue_piece<EPI, TOut>(r, r2, out, ldo, residual, m0 + q * 32 + lane, n0 + c0, M, N, vec_ok, &ra[(c0 >> 5) & 1]);
       }
     }
@@ -293,6 +320,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// out = epilogue(sum over the splits, in their order, of the raw sums a split-K launch left).
+template <int EPI, typename TOut>
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, TOut* out, int ldo, const float* residual,
+                                     int M, int N) {
+  constexpr int NB = EPI == TC_EPI_SWIGLU ? 2 : 1;
+  const size_t plane = (size_t)M * N;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < plane; i += (size_t)gridDim.x * blockDim.x) {
+    float a = 0.f, b = 0.f;
+    for (int z = 0; z < splits; ++z) {
+      a += partial[(size_t)z * NB * plane + i];
+      if (NB == 2) b += partial[((size_t)z * NB + 1) * plane + i];
+    }
+    const int m = (int)(i / N), n = (int)(i - (size_t)m * N);
+    const size_t o = (size_t)m * ldo + n;
+    if (EPI == TC_EPI_SWIGLU) out[o] = from_f32<TOut>(silu_tc(a) * b);
+    else if (EPI == TC_EPI_RESIDUAL) out[o] = from_f32<TOut>(residual[o] + a);
+    else out[o] = from_f32<TOut>(a);
   }
 }
 
@@ -500,6 +547,27 @@ static int tensor_map(const void* ptr, int rows, int cols, int ld, int box_rows,
 // persistent kernel with narrow tiles starves on shared-memory bandwidth: 0.68 to 0.78).  Forced for comparisons.
 static int g_tc_auto = 1, g_tc_persistent = 1, g_tc_wide = 1;
 
+// Scratch for split-K launches (set by the caller once; nothing is allocated here): without it no product is split.
+static float* g_splitk_ws = nullptr;
+static size_t g_splitk_bytes = 0;
+static int g_splitk_on = 1;
+static int g_last_launches = 1;   // kernels the last edgelm_gemm_tc call launched (2 when it split K)
+
+// Splits of K for a product of `tiles` one-tile blocks and `n_k` K blocks of 64: none unless the tiles would leave
+// more than half of the SMs idle and K is at least 1,024 (below that the second kernel costs more than the idle
+// SMs: measured at 64 rows, N 960, K 576: 6.1 us whole against 7.7 us split); then enough splits for about one and
+// a half blocks an SM, at least four K blocks each, within the scratch.  Measured at 64 rows: N 2048, K 8192:
+// 60.9 -> 15.5 us; N 2048, K 2048: 16.9 -> 8.5 us; N 576, K 1536: 12.9 -> 9.2 us.
+static int splitk_for(int tiles, int n_k, size_t bytes_per_split) {
+  if (!g_splitk_on || g_splitk_ws == nullptr || tiles >= 74 || n_k < 16) return 1;
+  int s = (222 + tiles - 1) / tiles;
+  if (s > n_k / 4) s = n_k / 4;
+  while (s > 1 && (size_t)s * bytes_per_split > g_splitk_bytes) --s;
+  if (s < 2) return 1;
+  const int k_per = (n_k + s - 1) / s;
+  return (n_k + k_per - 1) / k_per;   // every split gets a share
+}
+
 template <int BN, int EPI, typename TOut>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, void* out, int ldo,
                      const float* residual, int M, int N, int K, int vec_ok, int* err, cudaStream_t stream, bool persistent) {
@@ -523,6 +591,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
     }
     const int tiles = ((N + BN - 1) / BN) * ((M + TC_BM - 1) / TC_BM);
     const int grid = tiles < n_sms ? tiles : n_sms;
+    g_last_launches = 1;
     kern<<<grid, TC_THREADS, smem, stream>>>(ma, mb, mb2, (TOut*)out, ldo, residual, M, N, K, vec_ok, err);
     return 0;
   }
@@ -538,7 +607,15 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
     configured = true;
   }
   dim3 grid((N + BN - 1) / BN, (M + TC_BM - 1) / TC_BM);
-  kern<<<grid, TC_THREADS, smem, stream>>>(ma, mb, mb2, (TOut*)out, ldo, residual, M, N, K, vec_ok, err);
+  const int splits = splitk_for((int)(grid.x * grid.y), (K + TC_BK - 1) / TC_BK, (size_t)NB * M * N * sizeof(float));
+  grid.z = splits;
+  g_last_launches = splits > 1 ? 2 : 1;
+  kern<<<grid, TC_THREADS, smem, stream>>>(ma, mb, mb2, (TOut*)out, ldo, residual, M, N, K, vec_ok, err, splits, g_splitk_ws);
+  if (splits > 1) {
+    const size_t plane = (size_t)M * N;
+    const int blocks = (int)((plane + 255) / 256 < 1184 ? (plane + 255) / 256 : 1184);
+    splitk_reduce_kernel<EPI, TOut><<<blocks, 256, 0, stream>>>(g_splitk_ws, splits, (TOut*)out, ldo, residual, M, N);
+  }
   return 0;
 }
 
@@ -557,6 +634,17 @@ extern "C" int edgelm_gemm_tc_persistent(int on) {
   g_tc_wide = (on >> 1) & 1 ? 0 : 1;   // bit 1 set: narrow tiles only
   return 0;
 }
+
+// Float32 scratch for split-K launches (raw sums of every split); the library only keeps the pointer.  bytes 0: none.
+// `on` 0 switches splitting off (comparisons).
+extern "C" int edgelm_gemm_tc_splitk(float* scratch, size_t bytes, int on) {
+  g_splitk_ws = bytes ? scratch : nullptr;
+  g_splitk_bytes = bytes;
+  g_splitk_on = on;
+  return 0;
+}
+
+extern "C" int edgelm_gemm_tc_last_launches() { return g_last_launches; }
 
 // 1 if the tensor-core kernel takes these operands (alignment and pitch rules of TMA), else 0.
 extern "C" int edgelm_gemm_tc_takes(const void* a, int lda, const void* w, const void* w2, int K) {

@@ -38,7 +38,9 @@ __device__ __forceinline__ void mma_bf16_16x8x16(float* c, uint32_t a0, uint32_t
 __device__ __forceinline__ float gm_silu(float z) { return z / (1.0f + expf(-z)); }
 
 // NT: 8-row tiles of the batch (1: M <= 8, 2: M <= 16).  NORM: activations = RMSNorm(x).
-template <int EPI, typename TOut, int NT, bool NORM, int MAXW>  // MAXW: the most warps a block is launched with
+// MAXW: the most warps a block is launched with.  UN: K blocks whose weight loads a warp has in flight together
+// (4, or 8 for long rows of a single weight: 64 registers of weights either way).
+template <int EPI, typename TOut, int NT, bool NORM, int MAXW, int UN>
 __global__ void __launch_bounds__(MAXW * 32)
 gemv_mma_kernel(const __nv_bfloat16* __restrict__ act, int lda, const float* __restrict__ x,
                 const float* __restrict__ norm_w, float eps, const __nv_bfloat16* __restrict__ W,
@@ -79,6 +81,7 @@ gemv_mma_kernel(const __nv_bfloat16* __restrict__ act, int lda, const float* __r
       float ss = 0.f;
       if (r < M) {
         const float* xr = x + (size_t)r * K;
+#pragma unroll 4
         for (int k = lane * 4; k < K; k += 128) {
           const float4 v = *reinterpret_cast<const float4*>(xr + k);
           ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
@@ -97,34 +100,53 @@ gemv_mma_kernel(const __nv_bfloat16* __restrict__ act, int lda, const float* __r
 #pragma unroll
       for (int j = 0; j < 4; ++j) acc[w][t][j] = 0.f;
 
-  constexpr int UN = 4;  // K blocks whose weight loads are in flight together
   for (int kc0 = 0; kc0 < K; kc0 += kc) {   // K in chunks whose activations fit shared memory (one chunk for the usual sizes)
     const int kn = min(kc, K - kc0);
     if (kc0) __syncthreads();               // the previous chunk's activations are used up
     const int kvec = kn / 8;
-    for (int i = threadIdx.x; i < ROWS * kvec; i += blockDim.x) {
-      const int r = i / kvec, k = kc0 + (i - r * kvec) * 8;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (r < M) {
-        if (NORM) {
-          const float s = inv[r];
-          const float4 x0 = *reinterpret_cast<const float4*>(x + (size_t)r * K + k);
-          const float4 x1 = *reinterpret_cast<const float4*>(x + (size_t)r * K + k + 4);
-          const float4 w0 = *reinterpret_cast<const float4*>(norm_w + k);
-          const float4 w1 = *reinterpret_cast<const float4*>(norm_w + k + 4);
-          __nv_bfloat162 h0 = __floats2bfloat162_rn(x0.x * s * w0.x, x0.y * s * w0.y);
-          __nv_bfloat162 h1 = __floats2bfloat162_rn(x0.z * s * w0.z, x0.w * s * w0.w);
-          __nv_bfloat162 h2 = __floats2bfloat162_rn(x1.x * s * w1.x, x1.y * s * w1.y);
-          __nv_bfloat162 h3 = __floats2bfloat162_rn(x1.z * s * w1.z, x1.w * s * w1.w);
-          v.x = *reinterpret_cast<uint32_t*>(&h0);
-          v.y = *reinterpret_cast<uint32_t*>(&h1);
-          v.z = *reinterpret_cast<uint32_t*>(&h2);
-          v.w = *reinterpret_cast<uint32_t*>(&h3);
-        } else {
-          v = *reinterpret_cast<const uint4*>(act + (size_t)r * lda + k);
+    if (!NORM) {
+      // 16-byte asynchronous copies: all of a thread's pieces are in flight together (one load at a time, a
+      // round trip each, was most of a block's life at K = 2048 and beyond); through L1, where the blocks that
+      // follow on the same SM find them
+      for (int i = threadIdx.x; i < ROWS * kvec; i += blockDim.x) {
+        const int r = i / kvec, k = kc0 + (i - r * kvec) * 8;
+        __nv_bfloat16* dst = As + (size_t)r * pitch + (k - kc0);
+        if (r < M)
+          asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(act + (size_t)r * lda + k) : "memory");
+        else
+          *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+      }
+      asm volatile("cp.async.wait_all;" ::: "memory");
+    } else {
+      for (int i0 = threadIdx.x; i0 < ROWS * kvec; i0 += blockDim.x * 2) {   // two pieces' loads in flight together
+        float4 x0[2], x1[2], w0[2], w1[2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int i = i0 + j * blockDim.x, r = i / kvec, k = kc0 + (i - r * kvec) * 8;
+          const bool ok = i < ROWS * kvec && r < M;
+          x0[j] = ok ? *reinterpret_cast<const float4*>(x + (size_t)r * K + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+          x1[j] = ok ? *reinterpret_cast<const float4*>(x + (size_t)r * K + k + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+          w0[j] = ok ? *reinterpret_cast<const float4*>(norm_w + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+          w1[j] = ok ? *reinterpret_cast<const float4*>(norm_w + k + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int i = i0 + j * blockDim.x, r = i / kvec, k = (i - r * kvec) * 8;
+          if (i < ROWS * kvec) {
+            const float s = r < M ? inv[r] : 0.f;
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(x0[j].x * s * w0[j].x, x0[j].y * s * w0[j].y);
+            __nv_bfloat162 h1 = __floats2bfloat162_rn(x0[j].z * s * w0[j].z, x0[j].w * s * w0[j].w);
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(x1[j].x * s * w1[j].x, x1[j].y * s * w1[j].y);
+            __nv_bfloat162 h3 = __floats2bfloat162_rn(x1[j].z * s * w1[j].z, x1[j].w * s * w1[j].w);
+            uint4 v;
+            v.x = *reinterpret_cast<uint32_t*>(&h0);
+            v.y = *reinterpret_cast<uint32_t*>(&h1);
+            v.z = *reinterpret_cast<uint32_t*>(&h2);
+            v.w = *reinterpret_cast<uint32_t*>(&h3);
+            *reinterpret_cast<uint4*>(As + (size_t)r * pitch + k) = v;
+          }
         }
       }
-      *reinterpret_cast<uint4*>(As + (size_t)r * pitch + (k - kc0)) = v;
     }
     __syncthreads();
 
@@ -220,9 +242,16 @@ static int launch_gemv_mma(const void* act, int lda, const float* x, const float
   // warps per block: wide outputs fill the device with blocks and want few warps; narrow ones get up to
   // 16 warps, about two K blocks each, so that a single round of loads is in flight per warp
   const int n_kb = (K + 31) / 32, blocks = (N + GM_COLS - 1) / GM_COLS;
+  // warps per block: as many (up to 16) as it takes to have all of K in flight in one round of loads, unless the
+  // output is so wide that the device is full of blocks anyway (the vocabulary product); a narrow output gets at
+  // least about two K blocks a warp
+  const bool deep = NW == 1 && n_kb >= 64;   // rows of 2,048 and more of one weight: eight K blocks in flight per warp
+  const int un = deep ? 8 : 4;
   int GM_WARPS = 4;
   if (blocks < 2 * 148) {
     while (GM_WARPS < GM_MAX_WARPS && GM_WARPS * 2 <= (n_kb + 1) / 2) GM_WARPS *= 2;
+  } else if (blocks < 8 * 148) {
+    while (GM_WARPS < GM_MAX_WARPS && n_kb > GM_WARPS * un) GM_WARPS *= 2;
   }
   const size_t smem = (size_t)8 * NT * pitch * 2 + (size_t)GM_WARPS * NW * NT * 128 * 4 + 8 * NT * 4;
   auto go = [&](auto kern) -> int {
@@ -242,9 +271,16 @@ static int launch_gemv_mma(const void* act, int lda, const float* x, const float
     }
     return 0;
   };
-  if (GM_WARPS <= 4) return go(gemv_mma_kernel<EPI, TOut, NT, NORM, 4>);
-  if (GM_WARPS <= 8) return go(gemv_mma_kernel<EPI, TOut, NT, NORM, 8>);
-  return go(gemv_mma_kernel<EPI, TOut, NT, NORM, 16>);
+  if constexpr (NW == 1) {
+    if (deep) {
+      if (GM_WARPS <= 4) return go(gemv_mma_kernel<EPI, TOut, NT, NORM, 4, 8>);
+      if (GM_WARPS <= 8) return go(gemv_mma_kernel<EPI, TOut, NT, NORM, 8, 8>);
+      return go(gemv_mma_kernel<EPI, TOut, NT, NORM, 16, 8>);
+    }
+  }
+  if (GM_WARPS <= 4) return go(gemv_mma_kernel<EPI, TOut, NT, NORM, 4, 4>);
+  if (GM_WARPS <= 8) return go(gemv_mma_kernel<EPI, TOut, NT, NORM, 8, 4>);
+  return go(gemv_mma_kernel<EPI, TOut, NT, NORM, 16, 4>);
 }
 
 }  // namespace edgelm

@@ -204,8 +204,24 @@ def gemm_tc_takes(a, w, out, w2=None):
     return bool(lib().edgelm_gemm_tc_takes(_p(a), a.stride(0), _p(w), _p(w2), a.shape[1]))
 
 
+SPLITK_SCRATCH_BYTES = 32 << 20
+_splitk_scratch = None
+
+
+def _splitk_ready():
+    """The scratch that lets products of few tiles and long K spread over the device (split-K): allocated once, at
+    the first product outside of a graph capture, and handed to the library."""
+    global _splitk_scratch
+    if _splitk_scratch is None and not torch.cuda.is_current_stream_capturing():
+        _splitk_scratch = torch.empty(SPLITK_SCRATCH_BYTES // 4, dtype=torch.float32, device="cuda")
+        on = int(os.environ.get("EDGELM_GEMM_TC_SPLITK", "1"))
+        lib().edgelm_gemm_tc_splitk.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int]
+        lib().edgelm_gemm_tc_splitk(_p(_splitk_scratch), SPLITK_SCRATCH_BYTES, on)
+
+
 def gemm_tc(a, w, out, err, epilogue=EPI_STORE, w2=None, residual=None):
     """out = a @ w.T (+ epilogue) on the tcgen05 tensor cores: bfloat16 operands, float32 accumulation."""
+    _splitk_ready()
     _need(a.dim() == 2 and w.dim() == 2 and out.dim() == 2, "gemm_tc: 2-D operands")
     M, K = a.shape
     N = w.shape[0]
@@ -216,7 +232,8 @@ def gemm_tc(a, w, out, err, epilogue=EPI_STORE, w2=None, residual=None):
     if residual is not None:
         _need(residual.dtype == torch.float32 and residual.shape == out.shape and residual.stride() == out.stride(), "gemm_tc: residual layout")
     _check(lib().edgelm_gemm_tc(_p(a), a.stride(0), _p(w), _p(w2), _p(out), out.stride(0), _p(residual), M, N, K, _dt(out),
-                                epilogue, _p(err), _stream()))
+                                epilogue, _p(err), _stream()), launches=0)
+    count_launches(lib().edgelm_gemm_tc_last_launches())
 
 
 def rope_kv_append(qkv, tok_pos, tok_seq, seq_slot, page_table, cos, sin, kcache, vcache, nh, nkv, hd, err):

@@ -357,7 +357,8 @@ def test_sample_topk_matches_plain(vocab, temp, k, seed):
 
 # ----------------------------------------------------------------------------- GEMM (tcgen05 tensor cores)
 TC_SHAPES = [(128, 128, 64), (17, 64, 72), (129, 192, 576), (300, 100, 200), (256, 960, 576), (2048, 576, 1536),
-             (64, 397, 96), (130, 49, 8), (1000, 130, 136), (2048, 2048, 256), (1920, 2050, 200)]  # the last two: 128 x 256 tiles
+             (64, 397, 96), (130, 49, 8), (1000, 130, 136), (2048, 2048, 256), (1920, 2050, 200),  # the last two: 128 x 256 tiles
+             (64, 2048, 8192), (64, 576, 1536), (100, 397, 1032), (129, 200, 4096)]  # few tiles and long K: split-K
 
 
 @pytest.mark.parametrize("M,N,K", TC_SHAPES)
@@ -386,7 +387,7 @@ def test_gemm_tc_store_and_residual(M, N, K):
     assert rel_err(out32, simt) < 2e-5
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 64, 64), (200, 200, 96), (2048, 1536, 576), (33, 130, 40)])
+@pytest.mark.parametrize("M,N,K", [(128, 64, 64), (200, 200, 96), (2048, 1536, 576), (33, 130, 40), (64, 520, 1024), (40, 1536, 2048)])
 def test_gemm_tc_swiglu(M, N, K):
     o = ops()
     a = rnd((M, K), torch.bfloat16, 53)
