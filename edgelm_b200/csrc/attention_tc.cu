@@ -1,0 +1,349 @@
+// Causal attention of new tokens over the paged cache on the fifth-generation tensor cores
+// (tcgen05): bfloat16, head size 64, any number of heads and groups, any lengths.
+//
+// One CTA takes a tile of up to 128 consecutive tokens of one sequence and one query head, and walks
+// the sequence's keys in blocks of 128 (two pages of the cache) up to the tile's last position:
+//
+//   S   = Q K^T          tcgen05.mma M128 N128 K16 x 4, accumulator in tensor memory (two S buffers)
+//   P   = exp2(S - max)  four softmax warps, a thread a row: tcgen05.ld of its row, float32 running
+//                        maximum and denominator, P rounded to bfloat16 into shared memory in the
+//                        128-byte-swizzled K-major layout the next MMA reads
+//   O_b = P V            tcgen05.mma M128 N64 K16 x 8; V is used as it lies in the cache, [key][dim]:
+//                        the MN-major B operand (rows of 128 bytes = the 64 dims of a key)
+//   O   = O corr + O_b   in the softmax threads' registers (64 floats a row)
+//
+// Roles: warp 0 issues the TMA loads (Q once; K and V of a block as two pages each, two stages),
+// warp 1 allocates tensor memory and issues the MMAs, warps 2-5 and 6-9 are two softmax groups.  The
+// groups take the key blocks in turn (even, odd), each with an S, a P and an O_b of its own and its own
+// running maximum, denominator and output; group 0 merges the two at the end.  So two blocks are in
+// flight in a CTA: the tensor cores work for one group while the other computes exponentials, and an
+// SM sub-partition has two softmax warps to overlap the latencies of tcgen05.ld.  384 of 512 columns
+// of tensor memory (S, S, O_b, O_b).
+// Every wait is bounded as in the matrix-product kernels: a wait that runs out sets ERR_WAIT_TIMEOUT,
+// raises the block's abort flag, and all roles leave; tensor memory is freed in any case.
+//
+// Rows of the tile past its token count compute on whatever the Q box brought (other tokens' rows or
+// zeros) and are not stored.  A block's second page may not exist: the first is loaded twice and the
+// keys are masked.  Value rows past the tile's last position are zeroed in shared memory in the last
+// block, so that a stale NaN cannot meet a zero weight.
+#include <math_constants.h>
+
+#include "tc_common.cuh"
+
+namespace edgelm {
+
+constexpr int AT_ROWS = 128;    // tokens of a tile = lanes of tensor memory
+constexpr int AT_KEYS = 128;    // keys of a block
+constexpr int AT_HD = 64;
+constexpr int AT_THREADS = 320; // TMA warp, MMA warp, two softmax groups of four warps
+constexpr int AT_Q_BYTES = AT_ROWS * AT_HD * 2;          // 16 KB
+constexpr int AT_KV_BYTES = AT_KEYS * AT_HD * 2;         // 16 KB: two pages
+constexpr int AT_P_BYTES = AT_ROWS * AT_KEYS * 2;        // 32 KB: two K-major tiles of 128 x 64
+constexpr int AT_SMEM = AT_Q_BYTES + 4 * AT_KV_BYTES + 2 * AT_P_BYTES + 1024 + 256;
+constexpr uint32_t AT_TMEM_COLS = 512;                   // S of group 0, S of group 1 (128 each), O_b of group 0, of group 1 (64 each)
+constexpr int AT_MERGE_PITCH = AT_HD + 2;                // floats a row hands over when the two groups' results are merged
+
+__device__ __forceinline__ float at_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t at_pack(float a, float b) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// The softmax of one block for one row.  MASKED: the block touches the diagonal (keys past `pos` do not count).
+// Reads the row of S twice from tensor memory (maximum, then exponentials); writes P (bfloat16) into the swizzled
+// K-major tiles; returns the block's maximum-adjusted sum and updates m; `corr` is the factor for what was
+// accumulated before.
+template <bool MASKED>
+__device__ __forceinline__ float at_softmax_block(uint32_t s_addr, uint8_t* p_tiles, int row, int key0, int pos, float scale_log2,
+                                                  float& m, float& corr) {
+  float mx = -CUDART_INF_F;
+#pragma unroll
+  for (int c = 0; c < AT_KEYS / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld32(s_addr + c * 32, r);
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (!MASKED || key0 + c * 32 + i <= pos) mx = fmaxf(mx, __uint_as_float(r[i]));   // (the scale is positive)
+  }
+  const float m_new = fmaxf(m, mx * scale_log2);
+  const float m_use = m_new == -CUDART_INF_F ? 0.f : m_new;   // (a row of the tile's unused tail may see no key)
+  corr = at_exp2(m - m_use);                                  // 0 at the first block
+  m = m_new;
+  float lsum = 0.f;
+#pragma unroll
+  for (int c = 0; c < AT_KEYS / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld32(s_addr + c * 32, r);
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    float p[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const float v = at_exp2(fmaf(__uint_as_float(r[i]), scale_log2, -m_use));
+      p[i] = (!MASKED || key0 + c * 32 + i <= pos) ? v : 0.f;
+      lsum += p[i];
+    }
+    uint8_t* prow = p_tiles + (c >> 1) * (AT_P_BYTES / 2) + row * 128;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int ch = (c & 1) * 4 + u;
+      uint4 w;
+      w.x = at_pack(p[u * 8 + 0], p[u * 8 + 1]);
+      w.y = at_pack(p[u * 8 + 2], p[u * 8 + 3]);
+      w.z = at_pack(p[u * 8 + 4], p[u * 8 + 5]);
+      w.w = at_pack(p[u * 8 + 6], p[u * 8 + 7]);
+      *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = w;
+    }
+  }
+  return lsum;
+}
+
+__global__ void __launch_bounds__(AT_THREADS, 1)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, int ldo,
+                       const int32_t* __restrict__ page_table, int table_stride, int n_pages,
+                       const int32_t* __restrict__ seq_slot, const int32_t* __restrict__ tile_seq,
+                       const int32_t* __restrict__ tile_tok0, const int32_t* __restrict__ tile_ntok,
+                       const int32_t* __restrict__ tile_pos0, int n_tiles, int nh, int nkv, float scale_log2, int* err) {
+  extern __shared__ uint8_t at_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(at_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* q_s = smem;
+  uint8_t* k_s = q_s + AT_Q_BYTES;            // [2][16 KB]
+  uint8_t* v_s = k_s + 2 * AT_KV_BYTES;       // [2][16 KB]
+  uint8_t* p_s = v_s + 2 * AT_KV_BYTES;       // [2 groups][2 tiles][128 rows][128 bytes]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + 2 * AT_P_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;      // [2]
+  uint64_t* v_full = bars + 3;      // [2]
+  uint64_t* k_empty = bars + 5;     // [2]
+  uint64_t* v_empty = bars + 7;     // [2]
+  uint64_t* s_ready = bars + 9;     // [2]
+  uint64_t* p_ready = bars + 11;    // [2] 128 arrivals
+  uint64_t* o_ready = bars + 13;    // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = n_tiles - 1 - (int)blockIdx.x;   // late tiles (long rows of keys) first
+  const int head = blockIdx.y, kvh = head / (nh / nkv);
+  const int seq = tile_seq[tile], tok0 = tile_tok0[tile], ntok = tile_ntok[tile], pos0 = tile_pos0[tile];
+  const int n_keys = pos0 + ntok;                          // keys 0 .. n_keys - 1 are seen by some row of the tile
+  const int n_blk = (n_keys + AT_KEYS - 1) / AT_KEYS;
+  const int n_pg = (n_keys + PAGE - 1) / PAGE;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 15; ++i) mbar_init(smem_u32(&bars[i]), (i == 11 || i == 12) ? 128u : 1u);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(AT_TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_o = tmem_base + 2 * AT_KEYS;   // O_b of group g at + g * AT_HD
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      const int32_t* pages = page_table + (size_t)seq_slot[seq] * table_stride;
+      mbar_expect_tx(smem_u32(q_full), AT_Q_BYTES);
+      tma_load_2d(smem_u32(q_s), &map_q, smem_u32(q_full), head * AT_HD, tok0);
+      for (int j = 0; j < n_blk; ++j) {
+        const int s = j & 1;
+        int p0 = pages[2 * j], p1 = 2 * j + 1 < n_pg ? pages[2 * j + 1] : p0;
+        if (p0 < 0 || p0 >= n_pages || p1 < 0 || p1 >= n_pages) {
+          atomicOr(err, ERR_PAGE_RANGE);
+          p0 = p1 = 0;
+        }
+        const int y0 = (p0 * nkv + kvh) * PAGE, y1 = (p1 * nkv + kvh) * PAGE;
+        if (!mbar_wait(smem_u32(&k_empty[s]), ((j >> 1) & 1) ^ 1, abort_flag, err)) break;
+        mbar_expect_tx(smem_u32(&k_full[s]), AT_KV_BYTES);
+        tma_load_2d(smem_u32(k_s + s * AT_KV_BYTES), &map_k, smem_u32(&k_full[s]), 0, y0);
+        tma_load_2d(smem_u32(k_s + s * AT_KV_BYTES + AT_KV_BYTES / 2), &map_k, smem_u32(&k_full[s]), 0, y1);
+        if (!mbar_wait(smem_u32(&v_empty[s]), ((j >> 1) & 1) ^ 1, abort_flag, err)) break;
+        mbar_expect_tx(smem_u32(&v_full[s]), AT_KV_BYTES);
+        tma_load_2d(smem_u32(v_s + s * AT_KV_BYTES), &map_v, smem_u32(&v_full[s]), 0, y0);
+        tma_load_2d(smem_u32(v_s + s * AT_KV_BYTES + AT_KV_BYTES / 2), &map_v, smem_u32(&v_full[s]), 0, y1);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    // Block j belongs to softmax group j & 1 and uses that group's S, P and O_b.  Order: the scores of blocks 0
+    // and 1, then for every block its P V as soon as its P is there, followed by the scores of block j + 2 into
+    // the S buffer that the group has just finished reading.
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = umma_idesc(AT_ROWS, AT_KEYS);
+      constexpr uint32_t idesc_pv = umma_idesc(AT_ROWS, AT_HD) | (1u << 16);   // B (the values) is MN-major
+      const uint64_t dq = umma_desc(smem_u32(q_s));
+      bool ok = mbar_wait(smem_u32(q_full), 0, abort_flag, err);
+      auto issue_qk = [&](int j) {   // S[j & 1] = Q K_j^T
+        const int s = j & 1;
+        if (!mbar_wait(smem_u32(&k_full[s]), (j >> 1) & 1, abort_flag, err)) return false;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint64_t dk = umma_desc(smem_u32(k_s + s * AT_KV_BYTES));
+#pragma unroll
+        for (int k = 0; k < AT_HD / 16; ++k) umma_f16(tmem_base + (uint32_t)s * AT_KEYS, dq + 2 * k, dk + 2 * k, idesc_qk, k != 0);
+        umma_commit(smem_u32(&s_ready[s]));
+        umma_commit(smem_u32(&k_empty[s]));
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      if (ok && n_blk > 1) ok = issue_qk(1);
+      for (int j = 0; j < n_blk && ok; ++j) {
+        const int s = j & 1;
+        if (!(ok = mbar_wait(smem_u32(&p_ready[s]), (j >> 1) & 1, abort_flag, err))) break;
+        if (!(ok = mbar_wait(smem_u32(&v_full[s]), (j >> 1) & 1, abort_flag, err))) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint64_t dv = umma_desc(smem_u32(v_s + s * AT_KV_BYTES));
+#pragma unroll
+        for (int k = 0; k < AT_KEYS / 16; ++k) {
+          // P: two K-major tiles of 64 keys; V: 16 keys further = 16 rows of 128 bytes further
+          const uint64_t dp = umma_desc(smem_u32(p_s + s * AT_P_BYTES + (k >> 2) * (AT_P_BYTES / 2))) + 2 * (k & 3);
+          umma_f16(tmem_o + (uint32_t)s * AT_HD, dp, dv + (uint64_t)(k * 16 * 128 >> 4), idesc_pv, k != 0);
+        }
+        umma_commit(smem_u32(&o_ready[s]));
+        umma_commit(smem_u32(&v_empty[s]));
+        if (j + 2 < n_blk) ok = issue_qk(j + 2);   // (the group has read S of block j: it has written its P)
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax: two groups, a thread a row, the
+    // groups take the blocks in turn, each with a running maximum, denominator and output of its own
+    const int g = (warp - 2) >> 2, q4 = warp & 3, row = q4 * 32 + lane, pos = pos0 + row;
+    const uint32_t lane_off = (uint32_t)(q4 * 32) << 16;
+    const uint32_t s_addr = tmem_base + lane_off + (uint32_t)g * AT_KEYS, o_addr = tmem_o + lane_off + (uint32_t)g * AT_HD;
+    uint8_t* p_tiles = p_s + g * AT_P_BYTES;
+    float m = -CUDART_INF_F, l = 0.f, corr_prev = 1.f;
+    float o[AT_HD];
+#pragma unroll
+    for (int i = 0; i < AT_HD; ++i) o[i] = 0.f;
+    bool ok = true;
+    auto add_block_output = [&](int u) {   // o = o * corr + (P V of the group's block number u)
+      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&o_ready[g]), u & 1, abort_flag, err))) return false;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+      for (int c = 0; c < AT_HD / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(o_addr + c * 32, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], corr_prev, __uint_as_float(r[i]));
+      }
+      return true;
+    };
+    int u = 0;   // blocks this group has done
+    for (int j = g; j < n_blk; j += 2, ++u) {
+      const int key0 = j * AT_KEYS;
+      if (!(ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&s_ready[g]), u & 1, abort_flag, err)))) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      // the group's block before this one: its output into the registers before P is overwritten (its P V is long done)
+      if (u > 0 && !(ok = add_block_output(u - 1))) break;
+      float corr;
+      const float lsum = key0 + AT_KEYS - 1 > pos0 ? at_softmax_block<true>(s_addr, p_tiles, row, key0, pos, scale_log2, m, corr)
+                                                   : at_softmax_block<false>(s_addr, p_tiles, row, key0, pos, scale_log2, m, corr);
+      // what was accumulated so far is scaled when the next block's output is added
+      if (u > 0) {
+#pragma unroll
+        for (int i = 0; i < AT_HD; ++i) o[i] *= corr;
+      }
+      l = fmaf(l, corr, lsum);
+      corr_prev = 1.f;
+      if (j == n_blk - 1 && n_keys < key0 + AT_KEYS) {
+        // value rows past the tile's last position: every weight on them is zero; make them zero too
+        if (!(ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&v_full[g]), u & 1, abort_flag, err)))) break;
+        const int first = n_keys - key0;   // 1 .. 127
+        for (int i = q4 * 32 + lane; i < (AT_KEYS - first) * 8; i += 128) {
+          const int r = first + (i >> 3);
+          *reinterpret_cast<uint4*>(v_s + g * AT_KV_BYTES + r * 128 + ((i & 7) << 4)) = make_uint4(0, 0, 0, 0);
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&p_ready[g])) : "memory");
+    }
+    if (ok && u > 0) ok = add_block_output(u - 1);
+    // ---- the two groups' results of a row are merged by group 0: group 1 hands over (m, l, o) through the P tiles
+    // (all P V products are done: both groups have read their last O_b)
+    float* hand = reinterpret_cast<float*>(p_s) + (size_t)row * AT_MERGE_PITCH;
+    asm volatile("bar.sync 1, 256;" ::: "memory");   // group 0's P tiles are no longer read either
+    if (g == 1) {
+      hand[0] = m;
+      hand[1] = l;
+#pragma unroll
+      for (int i = 0; i < AT_HD; ++i) hand[2 + i] = o[i];
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    if (g == 0 && ok && row < ntok) {
+      const float m1 = hand[0], l1 = hand[1];
+      const float mm = fmaxf(m, m1);
+      const float f0 = at_exp2(m - mm), f1 = m1 == -CUDART_INF_F ? 0.f : at_exp2(m1 - mm);
+      const float inv = 1.0f / (l * f0 + l1 * f1);
+      __nv_bfloat16* dst = out + (size_t)(tok0 + row) * ldo + head * AT_HD;
+#pragma unroll
+      for (int i = 0; i < AT_HD; i += 8) {
+        float v[8];
+#pragma unroll
+        for (int t = 0; t < 8; ++t) v[t] = (o[i + t] * f0 + hand[2 + i + t] * f1) * inv;
+        uint4 w;
+        w.x = at_pack(v[0], v[1]);
+        w.y = at_pack(v[2], v[3]);
+        w.z = at_pack(v[4], v[5]);
+        w.w = at_pack(v[6], v[7]);
+        *reinterpret_cast<uint4*>(dst + i) = w;
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(AT_TMEM_COLS) : "memory");
+  }
+}
+
+}  // namespace edgelm
+
+using namespace edgelm;
+
+// 1 if the tcgen05 prefill attention takes this head size (bfloat16 is implied), else 0.
+extern "C" int edgelm_attn_prefill_tc_takes(int hd) { return hd == AT_HD ? 1 : 0; }
+
+// qkv [T, (nh + 2 nkv) * 64] bfloat16 with the queries already rotated; keys and values already in the cache.
+// Tiles of at most 128 tokens.
+extern "C" int edgelm_attn_prefill_tc(const void* qkv, int ldq, int n_tokens, void* out, int ldo, const void* kcache,
+                                      const void* vcache, int n_pages, const int32_t* page_table, int table_stride,
+                                      const int32_t* seq_slot, const int32_t* tile_seq, const int32_t* tile_tok0,
+                                      const int32_t* tile_ntok, const int32_t* tile_pos0, int n_tiles, int nh, int nkv, int hd,
+                                      float scale, int* err, cudaStream_t stream) {
+  if (n_tiles == 0) return 0;
+  EL_REFUSE(hd == AT_HD, "attn_prefill_tc: head size %d (takes 64)", hd);
+  EL_REFUSE(nh > 0 && nkv > 0 && nh % nkv == 0 && nh <= 65535, "attn_prefill_tc: %d heads over %d kv heads", nh, nkv);
+  EL_REFUSE(ldq % 8 == 0 && ldo % 8 == 0 && (uintptr_t)qkv % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)kcache % 16 == 0 &&
+                (uintptr_t)vcache % 16 == 0,
+            "attn_prefill_tc: rows and cache must be 16-byte aligned");
+  EL_REFUSE(err != nullptr && n_tokens > 0 && (long long)n_pages * nkv * PAGE < (1LL << 31), "attn_prefill_tc: bad arguments");
+  CUtensorMap mq, mk, mv;
+  if (tensor_map(qkv, n_tokens, ldq, ldq, AT_ROWS, &mq)) return -1;
+  if (tensor_map(kcache, n_pages * nkv * PAGE, AT_HD, AT_HD, PAGE, &mk)) return -1;
+  if (tensor_map(vcache, n_pages * nkv * PAGE, AT_HD, AT_HD, PAGE, &mv)) return -1;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM);
+    EL_REFUSE(e == cudaSuccess, "attn_prefill_tc: %d bytes of shared memory refused: %s", AT_SMEM, cudaGetErrorString(e));
+    configured = true;
+  }
+  const float scale_log2 = scale * 1.4426950408889634f;
+  attn_prefill_tc_kernel<<<dim3(n_tiles, nh), AT_THREADS, AT_SMEM, stream>>>(
+      mq, mk, mv, (__nv_bfloat16*)out, ldo, page_table, table_stride, n_pages, seq_slot, tile_seq, tile_tok0, tile_ntok,
+      tile_pos0, n_tiles, nh, nkv, scale_log2, err);
+  EL_LAUNCH_CHECK("attn_prefill_tc");
+  return 0;
+}

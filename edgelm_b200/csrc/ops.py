@@ -285,6 +285,28 @@ def attn_prefill_mma(qkv, out, kcache, vcache, page_table, seq_slot, tile_seq, t
                                          int(force_groups), _stream()))
 
 
+TC_PREFILL_TILE = 128  # new tokens per tile of the tcgen05 prefill kernel (AT_ROWS in attention_tc.cu)
+
+
+def attn_prefill_tc_takes(dtype, hd):
+    """Whether the tcgen05 prefill attention takes this dtype and head size (bfloat16, 64)."""
+    return dtype == torch.bfloat16 and bool(lib().edgelm_attn_prefill_tc_takes(int(hd)))
+
+
+def attn_prefill_tc(qkv, out, kcache, vcache, page_table, seq_slot, tile_seq, tile_tok0, tile_ntok, tile_pos0, n_tiles,
+                    nh, nkv, hd, scale, err):
+    """Causal attention of new tokens over the paged cache on tcgen05 tensor cores; tiles of at most 128 tokens."""
+    _need(qkv.dtype == out.dtype == kcache.dtype == torch.bfloat16 and qkv.stride(1) == 1 and out.stride(1) == 1, "attn_prefill_tc: layout")
+    _need(kcache.is_contiguous() and vcache.is_contiguous() and kcache.shape[1:] == (nkv, PAGE, hd) and vcache.shape == kcache.shape, "attn_prefill_tc: cache layout")
+    for t, n in ((page_table, "page_table"), (seq_slot, "seq_slot"), (tile_seq, "tile_seq"), (tile_tok0, "tile_tok0"),
+                 (tile_ntok, "tile_ntok"), (tile_pos0, "tile_pos0")):
+        _i32(t, n)
+    _check(lib().edgelm_attn_prefill_tc(_p(qkv), qkv.stride(0), qkv.shape[0], _p(out), out.stride(0), _p(kcache), _p(vcache),
+                                        kcache.shape[0], _p(page_table), page_table.stride(0), _p(seq_slot), _p(tile_seq),
+                                        _p(tile_tok0), _p(tile_ntok), _p(tile_pos0), n_tiles, nh, nkv, hd, ctypes.c_float(scale),
+                                        _p(err), _stream()))
+
+
 def attn_decode(qkv, out, kcache, vcache, page_table, seq_slot, seq_pos, n_seqs, nh, nkv, hd, scale, n_splits=1,
                 part_o=None, part_ml=None):
     """Attention of one new token per sequence over the paged cache, pages dealt to `n_splits` blocks."""

@@ -106,17 +106,24 @@ def main(argv=None):
         nt = (T + 63) // 64
         t_seq, t_tok0 = mk([0] * nt), mk([i * 64 for i in range(nt)])
         t_ntok, t_pos0 = mk([min(64, T - i * 64) for i in range(nt)]), mk([i * 64 for i in range(nt)])
+        nt2 = (T + 127) // 128
+        u_seq, u_tok0 = mk([0] * nt2), mk([i * 128 for i in range(nt2)])
+        u_ntok, u_pos0 = mk([min(128, T - i * 128) for i in range(nt2)]), mk([i * 128 for i in range(nt2)])
         flops = {"qkv_proj": 2 * T * QKV * D, "o_proj_residual": 2 * T * D * nh * hd, "gate_up_swiglu": 4 * T * I * D,
-                 "down_proj_residual": 2 * T * D * I, "attn_prefill": 4 * nh * hd * T * (T + 1) / 2}
+                 "down_proj_residual": 2 * T * D * I, "attn_prefill": 4 * nh * hd * T * (T + 1) / 2,
+                 "attn_prefill_tc": 4 * nh * hd * T * (T + 1) / 2}
         cases = {
             "rmsnorm": lambda l: o.rmsnorm(x, nw, 1e-5, h),
             "qkv_proj": lambda l: o.gemm_tc(h, wq[l], qkv, err),
             "rope_kv_append": lambda l: o.rope_kv_append(qkv, tokpos, tokseq, seq, table, cos, sin, kc[l], vc[l], nh, nkv, hd, err),
             "attn_prefill": lambda l: o.attn_prefill_mma(qkv, att, kc[l], vc[l], table, seq, t_seq, t_tok0, t_ntok, t_pos0, nt, nh, nkv, hd, scale, max_keys=T),
+            "attn_prefill_tc": lambda l: o.attn_prefill_tc(qkv, att, kc[l], vc[l], table, seq, u_seq, u_tok0, u_ntok, u_pos0, nt2, nh, nkv, hd, scale, err),
             "o_proj_residual": lambda l: o.gemm_tc(att, wo[l], x, err, epilogue=o.EPI_RESIDUAL, residual=x),
             "gate_up_swiglu": lambda l: o.gemm_tc(h, wg[l], mid, err, epilogue=o.EPI_SWIGLU, w2=wu[l]),
             "down_proj_residual": lambda l: o.gemm_tc(mid, wd[l], x, err, epilogue=o.EPI_RESIDUAL, residual=x),
         }
+        if not o.attn_prefill_tc_takes(bf, hd):
+            del cases["attn_prefill_tc"]
         print(f"prefill: {args.preset}, {T} tokens, {L} layers of weights")
     for name, fn in cases.items():
         if args.only and args.only not in name:

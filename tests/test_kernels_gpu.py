@@ -591,6 +591,67 @@ def test_attn_prefill_mma_far_key_and_diagonal():
     assert rel_err(out[:, hd:], case.v[0][p0:p0 + n, 0]) < 5e-2
 
 
+# ----------------------------------------------------------------------------- prefill attention on tcgen05 (bfloat16, head size 64)
+def _tc_tiles(seqs, tq):
+    cols = [[], [], [], []]
+    t0 = 0
+    for s, (p0, n) in enumerate(seqs):
+        for a in range(0, n, tq):
+            for c, v in zip(cols, (s, t0 + a, min(tq, n - a), p0 + a)):
+                c.append(v)
+        t0 += n
+    return [torch.tensor(c, dtype=torch.int32, device=dev()) for c in cols]
+
+
+@pytest.mark.parametrize("nh,nkv", [(9, 3), (4, 4), (8, 1), (2, 1)])
+def test_attn_prefill_tc(nh, nkv):
+    o = ops()
+    hd = 64
+    assert o.attn_prefill_tc_takes(torch.bfloat16, 64) and not o.attn_prefill_tc_takes(torch.bfloat16, 128)
+    assert not o.attn_prefill_tc_takes(torch.float32, 64)
+    # (cached before, new tokens): page and block edges on both sides, a tile that spans two diagonal blocks,
+    # a second page that does not exist, several tiles of one sequence
+    seqs = [(0, 5), (0, 70), (64, 1), (100, 129), (63, 2), (0, 64), (30, 200), (0, 128), (127, 130), (0, 600)]
+    lengths = [a + b for a, b in seqs]
+    case = PagedCase(o, torch.bfloat16, lengths, nkv, hd, seed=nh * 10 + nkv)
+    T = sum(b for _, b in seqs)
+    qkv = rnd((T, (nh + 2 * nkv) * hd), torch.bfloat16, 81)
+    tiles = _tc_tiles(seqs, o.TC_PREFILL_TILE)
+    err = torch.zeros(1, dtype=torch.int32, device=dev())
+    out = torch.full((T, nh * hd), float("nan"), dtype=torch.bfloat16, device=dev())
+    o.attn_prefill_tc(qkv, out, case.kcache, case.vcache, case.table, case.seq_slot, *tiles, tiles[0].numel(), nh, nkv, hd,
+                      1.0 / math.sqrt(hd), err)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    t0 = 0
+    for s, (p0, n) in enumerate(seqs):
+        want = attention_rows(qkv[t0:t0 + n, :nh * hd].float().cpu(), case.k[s], case.v[s], p0, nh, nkv, hd)
+        assert rel_err(out[t0:t0 + n], want) < 1.2e-2, (s, p0, n)
+        t0 += n
+
+
+def test_attn_prefill_tc_far_key_and_diagonal():
+    """Scaled queries make one early key, or the token's own key, dominate: a wrong mask, page or value layout shows."""
+    o = ops()
+    nh, nkv, hd, p0, n = 2, 1, 64, 130, 300
+    case = PagedCase(o, torch.bfloat16, [p0 + n], nkv, hd, seed=8)
+    q = torch.zeros(n, (nh + 2 * nkv) * hd)
+    for t in range(n):
+        q[t, :hd] = 12.0 * case.k[0][3, 0]                 # head 0: key 3, far back
+        q[t, hd:2 * hd] = 12.0 * case.k[0][p0 + t, 0]      # head 1: its own position, the last it may see
+    qkv = q.to(torch.bfloat16).to(dev())
+    tiles = _tc_tiles([(p0, n)], o.TC_PREFILL_TILE)
+    err = torch.zeros(1, dtype=torch.int32, device=dev())
+    out = torch.zeros(n, nh * hd, dtype=torch.bfloat16, device=dev())
+    o.attn_prefill_tc(qkv, out, case.kcache, case.vcache, case.table, case.seq_slot, *tiles, tiles[0].numel(), nh, nkv, hd,
+                      1.0 / math.sqrt(hd), err)
+    want = attention_rows(qkv[:, :nh * hd].float().cpu(), case.k[0], case.v[0], p0, nh, nkv, hd)
+    assert int(err.item()) == 0
+    assert rel_err(out, want) < 1.2e-2
+    assert rel_err(out[:, :hd], case.v[0][3, 0].expand(n, hd)) < 5e-2
+    assert rel_err(out[:, hd:], case.v[0][p0:p0 + n, 0]) < 5e-2
+
+
 # ----------------------------------------------------------------------------- decode attention with RoPE and append fused
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (9, 3, 64), (3, 1, 32), (12, 2, 128), (2, 2, 48)])
