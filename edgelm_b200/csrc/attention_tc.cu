@@ -8,17 +8,19 @@
 //   P   = exp2(S - max)  four softmax warps, a thread a row: tcgen05.ld of its row, float32 running
 //                        maximum and denominator, P rounded to bfloat16 into shared memory in the
 //                        128-byte-swizzled K-major layout the next MMA reads
-//   O_b = P V            tcgen05.mma M128 N64 K16 x 8; V is used as it lies in the cache, [key][dim]:
-//                        the MN-major B operand (rows of 128 bytes = the 64 dims of a key)
-//   O   = O corr + O_b   in the softmax threads' registers (64 floats a row)
+//   O  += P V            tcgen05.mma M128 N64 K16 x 8, accumulating in tensor memory over the blocks; V is
+//                        used as it lies in the cache, [key][dim]: the MN-major B operand (rows of 128
+//                        bytes = the 64 dims of a key).  The reference maximum of a row moves only when
+//                        the running maximum has outgrown it by 2^8; then the softmax threads scale
+//                        their rows of O in place (tcgen05.ld, multiply, tcgen05.st)
 //
 // Roles: warp 0 issues the TMA loads (Q once; K and V of a block as two pages each, two stages),
 // warp 1 allocates tensor memory and issues the MMAs, warps 2-5 and 6-9 are two softmax groups.  The
-// groups take the key blocks in turn (even, odd), each with an S, a P and an O_b of its own and its own
-// running maximum, denominator and output; group 0 merges the two at the end.  So two blocks are in
+// groups take the key blocks in turn (even, odd), each with an S, a P and an O of its own and its own
+// reference maximum and denominator; group 0 merges the two at the end.  So two blocks are in
 // flight in a CTA: the tensor cores work for one group while the other computes exponentials, and an
 // SM sub-partition has two softmax warps to overlap the latencies of tcgen05.ld.  384 of 512 columns
-// of tensor memory (S, S, O_b, O_b).
+// of tensor memory (S, S, O, O).
 // Every wait is bounded as in the matrix-product kernels: a wait that runs out sets ERR_WAIT_TIMEOUT,
 // raises the block's abort flag, and all roles leave; tensor memory is freed in any case.
 //
@@ -53,50 +55,66 @@ __device__ __forceinline__ uint32_t at_pack(float a, float b) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// The softmax of one block for one row.  MASKED: the block touches the diagonal (keys past `pos` do not count).
-// Reads the row of S twice from tensor memory (maximum, then exponentials); writes P (bfloat16) into the swizzled
-// K-major tiles; returns the block's maximum-adjusted sum and updates m; `corr` is the factor for what was
-// accumulated before.
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+        "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+        "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
+constexpr float AT_LAZY = 8.f;   // the reference maximum follows the running maximum only when that has grown by more than 2^8
+
+// The softmax of one block for one row: the row of S comes from tensor memory once and stays in registers.
+// MASKED: the block touches the diagonal (keys past `pos` do not count).  P = exp2(S scale - m_ref), rounded to
+// bfloat16, goes into the swizzled K-major tiles; returns its sum.  m_ref is the row's reference maximum: the
+// first block's maximum, replaced by a later block's only when that exceeds it by more than AT_LAZY (P then stays
+// below 2^8, far inside the range of bfloat16 and float32); `rescale` is the factor that replacement puts on
+// what was accumulated before (1 if none): softmax does not depend on the reference, only its rounding does.
 template <bool MASKED>
 __device__ __forceinline__ float at_softmax_block(uint32_t s_addr, uint8_t* p_tiles, int row, int key0, int pos, float scale_log2,
-                                                  float& m, float& corr) {
+                                                  bool first, float& m_ref, float& rescale) {
+  uint32_t r[AT_KEYS];
+#pragma unroll
+  for (int c = 0; c < AT_KEYS / 32; ++c) tmem_ld32(s_addr + c * 32, r + c * 32);
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
   float mx = -CUDART_INF_F;
 #pragma unroll
-  for (int c = 0; c < AT_KEYS / 32; ++c) {
-    uint32_t r[32];
-    tmem_ld32(s_addr + c * 32, r);
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i)
-      if (!MASKED || key0 + c * 32 + i <= pos) mx = fmaxf(mx, __uint_as_float(r[i]));   // (the scale is positive)
+  for (int i = 0; i < AT_KEYS; ++i)
+    if (!MASKED || key0 + i <= pos) mx = fmaxf(mx, __uint_as_float(r[i]));   // (the scale is positive)
+  mx *= scale_log2;
+  rescale = 1.f;
+  if (first) {
+    m_ref = mx;
+  } else if (mx > m_ref + AT_LAZY) {
+    rescale = at_exp2(m_ref - mx);   // (0 if the row has seen no key so far)
+    m_ref = mx;
   }
-  const float m_new = fmaxf(m, mx * scale_log2);
-  const float m_use = m_new == -CUDART_INF_F ? 0.f : m_new;   // (a row of the tile's unused tail may see no key)
-  corr = at_exp2(m - m_use);                                  // 0 at the first block
-  m = m_new;
+  const float m_use = m_ref == -CUDART_INF_F ? 0.f : m_ref;   // (a row of the tile's unused tail may see no key)
   float lsum = 0.f;
 #pragma unroll
   for (int c = 0; c < AT_KEYS / 32; ++c) {
-    uint32_t r[32];
-    tmem_ld32(s_addr + c * 32, r);
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-    float p[32];
+    uint32_t pk[16];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const float v = at_exp2(fmaf(__uint_as_float(r[i]), scale_log2, -m_use));
-      p[i] = (!MASKED || key0 + c * 32 + i <= pos) ? v : 0.f;
-      lsum += p[i];
+    for (int i = 0; i < 32; i += 2) {
+      float p0 = at_exp2(fmaf(__uint_as_float(r[c * 32 + i]), scale_log2, -m_use));
+      float p1 = at_exp2(fmaf(__uint_as_float(r[c * 32 + i + 1]), scale_log2, -m_use));
+      if (MASKED) {
+        if (key0 + c * 32 + i > pos) p0 = 0.f;
+        if (key0 + c * 32 + i + 1 > pos) p1 = 0.f;
+      }
+      lsum += p0 + p1;
+      pk[i >> 1] = at_pack(p0, p1);
     }
     uint8_t* prow = p_tiles + (c >> 1) * (AT_P_BYTES / 2) + row * 128;
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int ch = (c & 1) * 4 + u;
-      uint4 w;
-      w.x = at_pack(p[u * 8 + 0], p[u * 8 + 1]);
-      w.y = at_pack(p[u * 8 + 2], p[u * 8 + 3]);
-      w.z = at_pack(p[u * 8 + 4], p[u * 8 + 5]);
-      w.w = at_pack(p[u * 8 + 6], p[u * 8 + 7]);
-      *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = w;
+      *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = make_uint4(pk[u * 4], pk[u * 4 + 1], pk[u * 4 + 2], pk[u * 4 + 3]);
     }
   }
   return lsum;
@@ -207,7 +225,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int k = 0; k < AT_KEYS / 16; ++k) {
           // P: two K-major tiles of 64 keys; V: 16 keys further = 16 rows of 128 bytes further
           const uint64_t dp = umma_desc(smem_u32(p_s + s * AT_P_BYTES + (k >> 2) * (AT_P_BYTES / 2))) + 2 * (k & 3);
-          umma_f16(tmem_o + (uint32_t)s * AT_HD, dp, dv + (uint64_t)(k * 16 * 128 >> 4), idesc_pv, k != 0);
+          umma_f16(tmem_o + (uint32_t)s * AT_HD, dp, dv + (uint64_t)(k * 16 * 128 >> 4), idesc_pv, (k != 0) || (j >= 2));   // O of the group accumulates over its blocks
         }
         umma_commit(smem_u32(&o_ready[s]));
         umma_commit(smem_u32(&v_empty[s]));
@@ -221,41 +239,31 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t lane_off = (uint32_t)(q4 * 32) << 16;
     const uint32_t s_addr = tmem_base + lane_off + (uint32_t)g * AT_KEYS, o_addr = tmem_o + lane_off + (uint32_t)g * AT_HD;
     uint8_t* p_tiles = p_s + g * AT_P_BYTES;
-    float m = -CUDART_INF_F, l = 0.f, corr_prev = 1.f;
-    float o[AT_HD];
-#pragma unroll
-    for (int i = 0; i < AT_HD; ++i) o[i] = 0.f;
+    float m = -CUDART_INF_F, l = 0.f;   // the row's reference maximum (log2 units) and denominator; its output lives in tensor memory
     bool ok = true;
-    auto add_block_output = [&](int u) {   // o = o * corr + (P V of the group's block number u)
-      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&o_ready[g]), u & 1, abort_flag, err))) return false;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-      for (int c = 0; c < AT_HD / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(o_addr + c * 32, r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], corr_prev, __uint_as_float(r[i]));
-      }
-      return true;
-    };
     int u = 0;   // blocks this group has done
     for (int j = g; j < n_blk; j += 2, ++u) {
       const int key0 = j * AT_KEYS;
       if (!(ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&s_ready[g]), u & 1, abort_flag, err)))) break;
+      // the group's block before this one has been through its P V: P and O are free (that product was issued long ago)
+      if (u > 0 && !(ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&o_ready[g]), (u - 1) & 1, abort_flag, err)))) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      // the group's block before this one: its output into the registers before P is overwritten (its P V is long done)
-      if (u > 0 && !(ok = add_block_output(u - 1))) break;
-      float corr;
-      const float lsum = key0 + AT_KEYS - 1 > pos0 ? at_softmax_block<true>(s_addr, p_tiles, row, key0, pos, scale_log2, m, corr)
-                                                   : at_softmax_block<false>(s_addr, p_tiles, row, key0, pos, scale_log2, m, corr);
-      // what was accumulated so far is scaled when the next block's output is added
-      if (u > 0) {
+      float rescale;
+      const float lsum = key0 + AT_KEYS - 1 > pos0 ? at_softmax_block<true>(s_addr, p_tiles, row, key0, pos, scale_log2, u == 0, m, rescale)
+                                                   : at_softmax_block<false>(s_addr, p_tiles, row, key0, pos, scale_log2, u == 0, m, rescale);
+      if (__any_sync(0xffffffffu, rescale != 1.f)) {   // rare after the first blocks: the warp's rows of O times their factors
 #pragma unroll
-        for (int i = 0; i < AT_HD; ++i) o[i] *= corr;
+        for (int c = 0; c < AT_HD / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(o_addr + c * 32, r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * rescale);
+          tmem_st32(o_addr + c * 32, r);
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       }
-      l = fmaf(l, corr, lsum);
-      corr_prev = 1.f;
+      l = fmaf(l, rescale, lsum);
       if (j == n_blk - 1 && n_keys < key0 + AT_KEYS) {
         // value rows past the tile's last position: every weight on them is zero; make them zero too
         if (!(ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&v_full[g]), u & 1, abort_flag, err)))) break;
@@ -269,7 +277,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&p_ready[g])) : "memory");
     }
-    if (ok && u > 0) ok = add_block_output(u - 1);
+    // ---- the group's output out of tensor memory
+    float o[AT_HD];
+#pragma unroll
+    for (int i = 0; i < AT_HD; ++i) o[i] = 0.f;
+    if (ok && u > 0) {
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&o_ready[g]), (u - 1) & 1, abort_flag, err));
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (ok) {
+        uint32_t r[AT_HD];
+        tmem_ld32(o_addr, r);
+        tmem_ld32(o_addr + 32, r + 32);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int i = 0; i < AT_HD; ++i) o[i] = __uint_as_float(r[i]);
+      }
+    }
     // ---- the two groups' results of a row are merged by group 0: group 1 hands over (m, l, o) through the P tiles
     // (all P V products are done: both groups have read their last O_b)
     float* hand = reinterpret_cast<float*>(p_s) + (size_t)row * AT_MERGE_PITCH;
