@@ -405,7 +405,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 // 128 x 256 tiles and two accumulator stages (1.10 to 1.16 PFLOP/s at 2048 x 8192 x 2048 against 0.88 to 0.91
 // of the other), everything else to the one-tile-per-CTA kernel with 128 x 128 tiles, two CTAs per SM (the
 // persistent kernel with narrow tiles starves on shared-memory bandwidth: 0.68 to 0.78).  Forced for comparisons.
-static int g_tc_auto = 1, g_tc_persistent = 1, g_tc_wide = 1;
+static int g_tc_auto = 1, g_tc_persistent = 1, g_tc_wide = 1, g_tc_narrow = 1;
 
 // Scratch for split-K launches (set by the caller once; nothing is allocated here): without it no product is split.
 static float* g_splitk_ws = nullptr;
@@ -504,6 +504,11 @@ extern "C" int edgelm_gemm_tc_splitk(float* scratch, size_t bytes, int on) {
   return 0;
 }
 
+extern "C" int edgelm_gemm_tc_narrow(int on) {
+  g_tc_narrow = on;
+  return 0;
+}
+
 extern "C" int edgelm_gemm_tc_last_launches() { return g_last_launches; }
 
 // 1 if the tensor-core kernel takes these operands (alignment and pitch rules of TMA), else 0.
@@ -528,7 +533,12 @@ extern "C" int edgelm_gemm_tc(const void* a, int lda, const void* w, const void*
   const long long wide_tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((N + (epilogue == TC_EPI_SWIGLU ? 127 : 255)) / (epilogue == TC_EPI_SWIGLU ? 128 : 256));
   const bool wide = g_tc_auto ? (wide_tiles >= 120 && N >= 1024 && K >= 1024 && epilogue != TC_EPI_RESIDUAL) : (g_tc_wide && wide_tiles >= 120 && N >= 1024);
   const bool persistent = g_tc_auto ? wide : g_tc_persistent != 0;
-  const int bn = epilogue == TC_EPI_SWIGLU ? (wide ? 128 : 64) : (wide ? 256 : 128);
+  // tiles of 64 columns for a single weight when 128-column tiles would not fill one wave of SMs and there are
+  // several row tiles to share a weight tile in L2 (measured at 2,048 rows: N 576, K 576: 11.6 -> 8.8 us; N 576,
+  // K 1536: 16.1 -> 13.5 us; with 256 tiles of 128 columns and K 8192 the narrow tiles lose: 68 -> 107 us)
+  const long long tiles128 = (long long)((M + TC_BM - 1) / TC_BM) * ((N + 127) / 128);
+  const bool narrow = !wide && epilogue != TC_EPI_SWIGLU && g_tc_narrow && tiles128 < 148 && M > TC_BM;
+  const int bn = epilogue == TC_EPI_SWIGLU ? (wide ? 128 : 64) : (wide ? 256 : (narrow ? 64 : 128));
   CUtensorMap ma, mb, mb2;
   if (tensor_map(a, M, K, lda, TC_BM, &ma)) return -1;
   if (tensor_map(w, N, K, K, bn, &mb)) return -1;
@@ -549,7 +559,13 @@ extern "C" int edgelm_gemm_tc(const void* a, int lda, const void* w, const void*
       rc = launch_tc<128, TC_EPI_SWIGLU, __nv_bfloat16>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent);
     else
       EL_REFUSE(false, "gemm_tc: unsupported epilogue %d with output dtype %d", epilogue, out_dtype);
-  } else if (epilogue == TC_EPI_STORE && out_dtype == DT_BF16)
+  } else if (narrow && epilogue == TC_EPI_STORE && out_dtype == DT_BF16)
+    rc = launch_tc<64, TC_EPI_STORE, __nv_bfloat16>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent);
+  else if (narrow && epilogue == TC_EPI_STORE && out_dtype == DT_F32)
+    rc = launch_tc<64, TC_EPI_STORE, float>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent);
+  else if (narrow && epilogue == TC_EPI_RESIDUAL)
+    rc = launch_tc<64, TC_EPI_RESIDUAL, float>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent);
+  else if (epilogue == TC_EPI_STORE && out_dtype == DT_BF16)
     rc = launch_tc<128, TC_EPI_STORE, __nv_bfloat16>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent);
   else if (epilogue == TC_EPI_STORE && out_dtype == DT_F32)
     rc = launch_tc<128, TC_EPI_STORE, float>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent);

@@ -46,6 +46,8 @@ def lib():
                     loaded.edgelm_attn_decode_on_cuda_cores(int(os.environ["EDGELM_DECODE_CUDA_CORES"]))
                 if os.environ.get("EDGELM_GEMM_TC_PERSISTENT") is not None:
                     loaded.edgelm_gemm_tc_persistent(int(os.environ["EDGELM_GEMM_TC_PERSISTENT"]))
+                if os.environ.get("EDGELM_GEMM_TC_NARROW") is not None:
+                    loaded.edgelm_gemm_tc_narrow(int(os.environ["EDGELM_GEMM_TC_NARROW"]))
                 if os.environ.get("EDGELM_PDL") is not None:
                     loaded.edgelm_set_pdl(int(os.environ["EDGELM_PDL"]))
                 _lib = loaded
