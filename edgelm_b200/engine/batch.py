@@ -113,6 +113,7 @@ class BatchBuffers:
         self.seq_index_full = torch.arange(max_seqs, dtype=torch.int32, device=device)
         self.last_bytes = 0
         self._copied = torch.cuda.Event()
+        self._decode = None   # layout of the last step if it was one token per sequence: lets the next one be patched in place
 
     def fill(self, ctx, token_ids, seq_slots, seq_ntok, seq_pos0, want_rows, cache):
         """Lay out the step and copy it; sets every tensor of `ctx` (views of the device buffer)."""
@@ -170,4 +171,39 @@ class BatchBuffers:
                       for ts, n in tile_counts.items()}
         ctx._seq_ntok, ctx._seq_pos0 = [int(x) for x in ntok], [int(x) for x in pos0]
         ctx.seq_slots = view("seq_slots")
+        self._decode = None
+        if T == B and R == B:
+            self._decode = {"slots": list(seq_slots), "pos": [int(x) for x in pos0], "views": views, "words": o,
+                            "held": {g.id: g.n_held[slots].copy() for g in self.groups}, "slot_index": slots}
         return ctx
+
+    def refill_next_token(self, ctx, token_ids, seq_slots, seq_pos0):
+        """The step after a step of one token per sequence, for the same sequences one position further: the
+        staging buffer is patched in place (ids, positions, rows of the page tables that gained a page) instead of
+        being laid out again, and copied.  `ctx` keeps its views.  False if the step is not of that kind."""
+        d = self._decode
+        if d is None or d["slots"] != seq_slots or len(token_ids) != len(seq_slots) or any(p != q + 1 for p, q in zip(seq_pos0, d["pos"])):
+            return False
+        B = len(seq_slots)
+        self._copied.synchronize()  # the previous step's copy has read the staging buffer
+        h, views = self.host_np, d["views"]
+        a = views["token_ids"][0]
+        h[a:a + B] = token_ids
+        a = views["tok_pos"][0]
+        h[a:a + B] += 1
+        a = views["seq_pos"][0]
+        h[a:a + B] += 1
+        for g in self.groups:
+            held = g.n_held[d["slot_index"]]
+            if (held != d["held"][g.id]).any():
+                s = self.stride[g.id]
+                a = views[("table", g.id)][0]
+                h[a:a + B * s] = g.table[d["slot_index"]].reshape(-1)
+                d["held"][g.id] = held.copy()
+        o = d["words"]
+        self.dev[:o].copy_(self.host[:o], non_blocking=True)
+        self._copied.record()
+        self.last_bytes = o * 4
+        d["pos"] = list(seq_pos0)
+        ctx._seq_pos0 = list(seq_pos0)
+        return True

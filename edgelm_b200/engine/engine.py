@@ -283,7 +283,9 @@ class Engine:
                 raise EngineError(f"token id {t} is outside the vocabulary of {vocab}")
             self.cache.reserve(s, 1)
         pos0 = [int(self.cache.length[s]) for s in slots]
-        ctx = self.buffers.fill(self.ctx, list(last_tokens), slots, [1] * B, pos0, list(range(B)), self.cache)
+        ctx = self.ctx
+        if not self.buffers.refill_next_token(ctx, list(last_tokens), list(slots), pos0):
+            ctx = self.buffers.fill(self.ctx, list(last_tokens), list(slots), [1] * B, pos0, list(range(B)), self.cache)
         self.h2d_bytes_last = self.buffers.last_bytes
         key = (B, params.key())
         g = self._graphs.get(key)

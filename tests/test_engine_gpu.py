@@ -201,6 +201,33 @@ def test_greedy_generation_through_entry_point(model_dirs, oracles, name, dtype)
     assert edgelm_b200.generate(None, prompts, n=12, engine=eng2, slots=2, stop=[], ignore_eos=True) == got
 
 
+def test_long_greedy_generation_patches_the_step_in_place(model_dirs, oracles):
+    """float32, 150 tokens from prompts of unequal lengths: consecutive decode steps patch the step's metadata in
+    place (ids, positions, the page-table rows that gain a page) instead of laying it out again; the tokens are
+    the plain implementation's across three page edges."""
+    import edgelm_b200
+    name = "tiny_b"
+    o = oracles[name]
+    prompts = [H.tokens_for(name, n, 170 + i) for i, n in enumerate([60, 3, 64])]
+    eng = edgelm_b200.load_engine(model_dirs[name], dtype="float32", ctx=256, slots=3)
+    calls = {"patched": 0, "laid_out": 0}
+    refill, fill = eng.buffers.refill_next_token, eng.buffers.fill
+
+    def count_refill(*a, **k):
+        ok = refill(*a, **k)
+        calls["patched"] += bool(ok)
+        return ok
+
+    def count_fill(*a, **k):
+        calls["laid_out"] += 1
+        return fill(*a, **k)
+    eng.buffers.refill_next_token, eng.buffers.fill = count_refill, count_fill
+    got = edgelm_b200.generate(None, prompts, n=150, engine=eng, slots=3, stop=[], ignore_eos=True)
+    assert got == [plain.generate(o.cfg, o.W, p, 150, stop_ids=[], ignore_eos=True) for p in prompts]
+    assert calls["patched"] > 100 and calls["laid_out"] < 10
+    eng.cache.check()
+
+
 def test_sampled_generation_and_stop(model_dirs, oracles):
     import edgelm_b200
     name = "tiny_b"
