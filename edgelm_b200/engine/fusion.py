@@ -49,12 +49,14 @@ class DecodeStack:
         self.trace = None    # int64 [layers, 10] when phase stamps are wanted (see ops.decode_stack)
         self._records = {}   # addresses of tables and cache -> packed records on the device (kept: graphs read them)
 
-    # Measured on a B200 (decode steps of SmolLM2-shaped models, contexts of 128 to 2300 tokens): with 7 MB of
-    # weights a layer the fused kernel is 8 to 20 % faster than the parts' kernels at 1 to 16 sequences; with 20 MB
-    # it wins at 1 sequence, ties at 8 and loses at 16; with 100 MB it loses everywhere, because a phase is then
-    # bound by bytes in flight, which the separate kernels' many blocks have more of.
+    # Measured on a B200 (decode steps of SmolLM2-shaped models, contexts of 128 to 2300 tokens, device time per
+    # step, fused against the parts' own kernels): 7 MB of weights a layer: 0.78 against 0.90 to 0.97 ms at 1 sequence,
+    # 0.95 against 1.01 at 8, 1.41 against 1.30 at 16; 20 MB a layer: 1.02 against 1.12 to 1.20 at 1 sequence, 1.47
+    # against 1.30 at 8; 100 MB a layer: slower at every batch.  A phase of the fused kernel costs about as much
+    # whatever it computes (round trips through L2 and a grid barrier); the separate kernels have more blocks and
+    # more bytes in flight, which wins as soon as a phase has real work.
     MAX_LAYER_BYTES = 24 << 20
-    MAX_LAYER_BYTES_TIMES_SEQS = 160 << 20
+    MAX_LAYER_BYTES_TIMES_SEQS = 64 << 20
 
     def takes(self, ctx):
         if not (ctx.all_single and 1 <= ctx.n_seqs <= ops.DECODE_STACK_MAX_SEQS):
