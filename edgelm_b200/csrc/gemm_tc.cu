@@ -25,7 +25,8 @@ namespace edgelm {
 enum : int { TC_EPI_STORE = 0, TC_EPI_RESIDUAL = 1, TC_EPI_SWIGLU = 2 };
 
 constexpr int TC_BM = 128;   // rows of `a` per tile = lanes of tensor memory
-constexpr int TC_STAGES = 3;   // ring stages of the one-tile kernel (48 KB stages: 144 KB)
+constexpr int TC_STAGES = 3;   // ring stages of the one-tile kernel when several blocks share an SM (48 KB stages: 144 KB)
+constexpr int TC_DEEP_BYTES = 192 * 1024;   // ring of the one-tile kernel when the grid is at most one block an SM
 constexpr int TC_THREADS = 192;
 __device__ __forceinline__ float silu_tc(float z) { return z / (1.0f + expf(-z)); }
 
@@ -107,7 +108,7 @@ __device__ __forceinline__ void epilogue_piece(const uint32_t* r, const uint32_t
   }
 }
 
-template <int BN, int EPI, typename TOut>
+template <int BN, int EPI, typename TOut, int STAGES>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_b2, TOut* out, int ldo, const float* residual,
@@ -125,11 +126,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TC_STAGES * STAGE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
   uint64_t* full_bar = bars;
-  uint64_t* empty_bar = bars + TC_STAGES;
-  uint64_t* tmem_full_bar = bars + 2 * TC_STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * TC_STAGES + 1);
+  uint64_t* empty_bar = bars + STAGES;
+  uint64_t* tmem_full_bar = bars + 2 * STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -140,7 +141,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int n_k = max(0, min(n_k_all, k_first + k_per) - k_first);   // (the host picks splits that all get a share)
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < TC_STAGES; ++s) {
+    for (int s = 0; s < STAGES; ++s) {
       mbar_init(smem_u32(&full_bar[s]), 1);
       mbar_init(smem_u32(&empty_bar[s]), 1);
     }
@@ -160,8 +161,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (warp == 0) {
     if (lane == 0) {
       for (int i = 0; i < n_k; ++i) {
-        const int s = i % TC_STAGES;
-        if (!mbar_wait(smem_u32(&empty_bar[s]), ((i / TC_STAGES) & 1) ^ 1, abort_flag, err)) break;
+        const int s = i % STAGES;
+        if (!mbar_wait(smem_u32(&empty_bar[s]), ((i / STAGES) & 1) ^ 1, abort_flag, err)) break;
         const uint32_t bar = smem_u32(&full_bar[s]);
         mbar_expect_tx(bar, STAGE_BYTES);
         const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
@@ -175,8 +176,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       constexpr uint32_t idesc = umma_idesc(TC_BM, BN);
       bool ok = true;
       for (int i = 0; i < n_k && ok; ++i) {
-        const int s = i % TC_STAGES;
-        ok = mbar_wait(smem_u32(&full_bar[s]), (i / TC_STAGES) & 1, abort_flag, err);
+        const int s = i % STAGES;
+        ok = mbar_wait(smem_u32(&full_bar[s]), (i / STAGES) & 1, abort_flag, err);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
@@ -405,7 +406,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 // 128 x 256 tiles and two accumulator stages (1.10 to 1.16 PFLOP/s at 2048 x 8192 x 2048 against 0.88 to 0.91
 // of the other), everything else to the one-tile-per-CTA kernel with 128 x 128 tiles, two CTAs per SM (the
 // persistent kernel with narrow tiles starves on shared-memory bandwidth: 0.68 to 0.78).  Forced for comparisons.
-static int g_tc_auto = 1, g_tc_persistent = 1, g_tc_wide = 1, g_tc_narrow = 1;
+static int g_tc_auto = 1, g_tc_persistent = 1, g_tc_wide = 1, g_tc_narrow = 1, g_tc_deep = 1;
 
 // Scratch for split-K launches (set by the caller once; nothing is allocated here): without it no product is split.
 static float* g_splitk_ws = nullptr;
@@ -455,22 +456,33 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
     kern<<<grid, TC_THREADS, smem, stream>>>(ma, mb, mb2, (TOut*)out, ldo, residual, M, N, K, vec_ok, err);
     return 0;
   }
-  constexpr int smem = TC_STAGES * (TC_BM * TC_BK * 2 + NB * BN * TC_BK * 2) + 1024 + 256;
-  auto kern = gemm_tc_kernel<BN, EPI, TOut>;
-  static bool configured = false;
-  if (!configured) {
+  constexpr int STAGE_BYTES = TC_BM * TC_BK * 2 + NB * BN * TC_BK * 2;
+  constexpr int DEEP = TC_DEEP_BYTES / STAGE_BYTES;   // 6 stages of 32 KB, 8 of 24 KB
+  dim3 grid((N + BN - 1) / BN, (M + TC_BM - 1) / TC_BM);
+  const int splits = splitk_for((int)(grid.x * grid.y), (K + TC_BK - 1) / TC_BK, (size_t)NB * M * N * sizeof(float));
+  grid.z = splits;
+  g_last_launches = splits > 1 ? 2 : 1;
+  // a grid of at most one block an SM has the shared memory to itself: a deeper ring hides more of the loads' latency
+  // (a short K is a few loads behind one another: 9 of them at K 576)
+  static int n_sms = 0;
+  if (n_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const bool deep = g_tc_deep && (long long)grid.x * grid.y * grid.z <= n_sms;
+  auto go = [&](auto kern, int smem) -> int {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) {
       set_error("gemm_tc: %d bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
       return -2;
     }
-    configured = true;
-  }
-  dim3 grid((N + BN - 1) / BN, (M + TC_BM - 1) / TC_BM);
-  const int splits = splitk_for((int)(grid.x * grid.y), (K + TC_BK - 1) / TC_BK, (size_t)NB * M * N * sizeof(float));
-  grid.z = splits;
-  g_last_launches = splits > 1 ? 2 : 1;
-  kern<<<grid, TC_THREADS, smem, stream>>>(ma, mb, mb2, (TOut*)out, ldo, residual, M, N, K, vec_ok, err, splits, g_splitk_ws);
+    kern<<<grid, TC_THREADS, smem, stream>>>(ma, mb, mb2, (TOut*)out, ldo, residual, M, N, K, vec_ok, err, splits, g_splitk_ws);
+    return 0;
+  };
+  const int rc = deep ? go(gemm_tc_kernel<BN, EPI, TOut, DEEP>, DEEP * STAGE_BYTES + 1024 + 256)
+                      : go(gemm_tc_kernel<BN, EPI, TOut, TC_STAGES>, TC_STAGES * STAGE_BYTES + 1024 + 256);
+  if (rc) return rc;
   if (splits > 1) {
     const size_t plane = (size_t)M * N;
     const int blocks = (int)((plane + 255) / 256 < 1184 ? (plane + 255) / 256 : 1184);
@@ -504,8 +516,10 @@ extern "C" int edgelm_gemm_tc_splitk(float* scratch, size_t bytes, int on) {
   return 0;
 }
 
+// bit 0: 64-column tiles where they apply; bit 1: the deep ring for grids of at most one block an SM (comparisons)
 extern "C" int edgelm_gemm_tc_narrow(int on) {
-  g_tc_narrow = on;
+  g_tc_narrow = on & 1;
+  g_tc_deep = (on >> 1) & 1;
   return 0;
 }
 
