@@ -358,9 +358,14 @@ def argmax_rows(logits, out):
     _check(lib().edgelm_argmax_rows(_p(logits), logits.stride(0), logits.shape[0], logits.shape[1], _p(out), _stream()))
 
 
-def sample_topk(logits, temperature, top_k, rng_state, out, state_index=None):
+def sample_topk(logits, temperature, top_k, rng_state, out, state_index=None, scratch=None):
     """Temperature + top-k draw per row; rng_state (int64 xorshift64 states) advances by one draw.
-    Row r uses state state_index[r] when given (a sequence's slot), else state r."""
+    Row r uses state state_index[r] when given (a sequence's slot), else state r.  `scratch` (int32, a word per
+    row) lets rows with at most 1,024 kept tokens and a vocabulary of at most 49,152 take the fast kernel (the row
+    in registers, no histograms); without it every row takes the general one.  Same choices either way."""
+    if scratch is not None:
+        _i32(scratch, "scratch")
+        _need(scratch.numel() >= logits.shape[0], "sample_topk: a scratch word per row")
     _need(logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1, "sample_topk: float32 rows")
     _need(rng_state.dtype == torch.int64 and rng_state.is_contiguous(), "sample_topk: rng_state")
     if state_index is None:
@@ -369,7 +374,8 @@ def sample_topk(logits, temperature, top_k, rng_state, out, state_index=None):
         _i32(state_index, "state_index")
     _i32(out, "out")
     _check(lib().edgelm_sample_topk(_p(logits), logits.stride(0), logits.shape[0], logits.shape[1],
-                                    ctypes.c_float(temperature), int(top_k), _p(rng_state), _p(state_index), _p(out), _stream()))
+                                    ctypes.c_float(temperature), int(top_k), _p(rng_state), _p(state_index), _p(out),
+                                    _p(scratch), _stream()), launches=1 if scratch is None else 2)
 
 
 def read_error_word(err):

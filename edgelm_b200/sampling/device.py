@@ -14,6 +14,7 @@ def to_signed(u):
 class DeviceSampler:
     def __init__(self, n_slots, device):
         self.state = torch.zeros(n_slots, dtype=torch.int64, device=device)
+        self.scratch = torch.zeros(n_slots, dtype=torch.int32, device=device)  # a word per row for the sampling kernels
         self.device = device
 
     def seed(self, slots, params: SamplingParams, first_request_index=0):
@@ -29,5 +30,6 @@ class DeviceSampler:
         if params.greedy:
             ops.argmax_rows(logits, out)
         else:
-            ops.sample_topk(logits, float(params.temperature), int(params.top_k), self.state, out, state_index=seq_slots)
+            scratch = self.scratch if logits.shape[0] <= self.scratch.numel() else None
+            ops.sample_topk(logits, float(params.temperature), int(params.top_k), self.state, out, state_index=seq_slots, scratch=scratch)
         return out

@@ -333,7 +333,9 @@ def test_argmax_first_maximum(vocab):
 
 
 @pytest.mark.parametrize("vocab,temp,k,seed", [(397, 0.8, 20, 7), (256, 1.0, 40, 42), (100, 0.5, 0, 3), (64, 1.3, 1000, 9),
-                                                 (49152, 0.9, 40, 1), (5000, 2.0, -1, 12), (1000, 0.3, 2, 5)])
+                                                 (49152, 0.9, 40, 1), (5000, 2.0, -1, 12), (1000, 0.3, 2, 5),
+                                                 (49152, 0.7, 0, 2), (3001, 1.1, 1024, 4), (3001, 1.1, 1025, 4),   # ranked list up to 1,024 kept tokens, radix descent beyond
+                                                 (60000, 0.8, 50, 6)])                                           # a row too long for shared memory
 def test_sample_topk_matches_plain(vocab, temp, k, seed):
     o = ops()
     import golden_models as gm
@@ -343,13 +345,15 @@ def test_sample_topk_matches_plain(vocab, temp, k, seed):
     st = torch.tensor([s - (1 << 64) if s >= (1 << 63) else s for s in state], dtype=torch.int64, device=dev())
     samplers = [plain.Sampler(temp, k, s) for s in range(seed, seed + rows)]
     out = torch.zeros(rows, dtype=torch.int32, device=dev())
+    scratch = torch.zeros(rows, dtype=torch.int32, device=dev())
     for step in range(steps):
         if step % 2 == 0:
             x = torch.from_numpy(gm.sampler_logits(rows, vocab, step))  # coarse grid: many exact ties
         else:
             x = torch.randn(rows, vocab, generator=torch.Generator().manual_seed(step)) * 3
         xd = x.to(dev())
-        o.sample_topk(xd, temp, k, st, out)
+        # odd steps with the scratch (the fast kernel where it applies), even steps without (the general kernel)
+        o.sample_topk(xd, temp, k, st, out, scratch=scratch if step % 4 < 2 else None)
         want = [s.sample(r) for s, r in zip(samplers, x.numpy())]
         assert out.tolist() == want, (step,)
     assert [v & plain.MASK64 for v in st.tolist()] == [s.state for s in samplers]
