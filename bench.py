@@ -188,7 +188,7 @@ def main():
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "adarsh-sgh/edgelm is a C++17 CPU program with no setup.py or "
-                          "pyproject.toml: 'pip install --no-index --target baseline/_ref /root/reference' ends with 'not installable'; "
+                          "pyproject.toml: 'pip install --no-index --target baseline/_ref' of its checkout ends with 'not installable'; "
                           "it has no GPU path and no batch > 1"}))
         return 0
     if args.gpus != 1:
