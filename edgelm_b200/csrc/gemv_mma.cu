@@ -60,9 +60,25 @@ gemv_mma_kernel(const __nv_bfloat16* __restrict__ act, int lda, const float* __r
   const int ra = min(n0 + gid, N - 1), rb = min(n0 + gid + 8, N - 1);  // the two weight rows of this lane (clamped)
   const int n_kb = (K + 31) / 32;
 
-  // this warp's first K block of weights: on its way while the activations are staged
+  // Weights on their way while the activations are staged.  With one weight: the warp's whole first round of every
+  // chunk, loaded into the registers the MMAs read (ea, eb: no second copy).  With two weights a round is 64 registers
+  // held across the staging, which cost those kernels more than the loads gained (17.8 -> 21.5 us at N 8192, K 2048):
+  // there only the first K block is ahead (pa, pb).
+  constexpr bool EARLY = NW == 1;
+  uint4 ea[EARLY ? UN : 1], eb[EARLY ? UN : 1];
+  auto load_round = [&](int kb0, int kb_end) {
+#pragma unroll
+    for (int u = 0; u < (EARLY ? UN : 0); ++u) {
+      const int kb = kb0 + u * GM_WARPS;
+      const int k = kb * 32 + tig * 8;
+      const bool ok = kb < kb_end && k < K;
+      ea[u] = ok ? *reinterpret_cast<const uint4*>(W + (size_t)ra * K + k) : make_uint4(0, 0, 0, 0);
+      eb[u] = ok ? *reinterpret_cast<const uint4*>(W + (size_t)rb * K + k) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  if (EARLY) load_round(warp, (min(kc, K) + 31) / 32);
   uint4 pa[NW], pb[NW];
-  {
+  if (!EARLY) {
     const int k = warp * 32 + tig * 8;
     const bool ok = warp < n_kb && k < K;
 #pragma unroll
@@ -102,7 +118,10 @@ gemv_mma_kernel(const __nv_bfloat16* __restrict__ act, int lda, const float* __r
 
   for (int kc0 = 0; kc0 < K; kc0 += kc) {   // K in chunks whose activations fit shared memory (one chunk for the usual sizes)
     const int kn = min(kc, K - kc0);
-    if (kc0) __syncthreads();               // the previous chunk's activations are used up
+    if (kc0) {
+      if (EARLY) load_round(kc0 / 32 + warp, (kc0 + kn + 31) / 32);
+      __syncthreads();                      // the previous chunk's activations are used up
+    }
     const int kvec = kn / 8;
     if (!NORM) {
       // 16-byte asynchronous copies: all of a thread's pieces are in flight together (one load at a time, a
@@ -151,6 +170,23 @@ gemv_mma_kernel(const __nv_bfloat16* __restrict__ act, int lda, const float* __r
     __syncthreads();
 
     const int kb_begin = kc0 / 32, kb_end = (kc0 + kn + 31) / 32;
+    if constexpr (EARLY) {
+      for (int kb0 = kb_begin + warp; kb0 < kb_end; kb0 += GM_WARPS * UN) {
+        if (kb0 != kb_begin + warp) load_round(kb0, kb_end);
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+          const int kb = kb0 + u * GM_WARPS;
+          const int k = kb * 32 + tig * 8;
+          const bool ok = kb < kb_end && k < K;
+#pragma unroll
+          for (int t = 0; t < NT; ++t) {
+            const uint4 av = ok ? *reinterpret_cast<const uint4*>(As + (size_t)(t * 8 + gid) * pitch + (k - kc0)) : make_uint4(0, 0, 0, 0);
+            mma_bf16_16x8x16(acc[0][t], ea[u].x, eb[u].x, ea[u].y, eb[u].y, av.x, av.y);
+            mma_bf16_16x8x16(acc[0][t], ea[u].z, eb[u].z, ea[u].w, eb[u].w, av.z, av.w);
+          }
+        }
+      }
+    } else
     for (int kb0 = kb_begin + warp; kb0 < kb_end; kb0 += GM_WARPS * UN) {
       uint4 wa[UN][NW], wb[UN][NW];
 #pragma unroll
