@@ -15,7 +15,7 @@ void set_error(const char* fmt, ...) {
   va_end(ap);
 }
 
-static int g_pdl = 0;
+static int g_pdl = 1;   // the few-rows matrix products (bit 0) start under the tail of the kernel before them
 int pdl_enabled() { return g_pdl; }
 
 }  // namespace edgelm

@@ -50,13 +50,14 @@ class DecodeStack:
         self._records = {}   # addresses of tables and cache -> packed records on the device (kept: graphs read them)
 
     # Measured on a B200 (decode steps of SmolLM2-shaped models, contexts of 128 to 2300 tokens, device time per
-    # step, fused against the parts' own kernels): 7 MB of weights a layer: 0.78 against 0.90 to 0.97 ms at 1 sequence,
-    # 0.95 against 1.01 at 8, 1.41 against 1.30 at 16; 20 MB a layer: 1.02 against 1.12 to 1.20 at 1 sequence, 1.47
-    # against 1.30 at 8; 100 MB a layer: slower at every batch.  A phase of the fused kernel costs about as much
-    # whatever it computes (round trips through L2 and a grid barrier); the separate kernels have more blocks and
-    # more bytes in flight, which wins as soon as a phase has real work.
+    # step, fused against the parts' own kernels, whose few-rows products start under the tail of the kernel before
+    # them): 7 MB of weights a layer: 0.774 against 0.816 ms at 1 sequence, 0.826 against 0.887 at 2, 0.843 against
+    # 0.866 at 3, 0.875 against 0.853 at 4, 0.951 against 0.870 at 8; 20 MB a layer: 1.016 against 1.028 at 1 sequence,
+    # 1.086 against 1.017 at 2; 100 MB a layer: slower at every batch.  A phase of the fused kernel costs about the
+    # same whatever it computes (round trips through L2 and a grid barrier); the separate kernels have more blocks
+    # and more bytes in flight, which wins as soon as a phase has real work.
     MAX_LAYER_BYTES = 24 << 20
-    MAX_LAYER_BYTES_TIMES_SEQS = 64 << 20
+    MAX_LAYER_BYTES_TIMES_SEQS = 24 << 20
 
     def takes(self, ctx):
         if not (ctx.all_single and 1 <= ctx.n_seqs <= ops.DECODE_STACK_MAX_SEQS):
