@@ -155,6 +155,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  pdl_launch_dependents();
+  pdl_wait();   // (launched as a programmatic dependent: up to here nothing of the kernel before this one was read)
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
 
@@ -477,7 +479,12 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
       set_error("gemm_tc: %d bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
       return -2;
     }
-    kern<<<grid, TC_THREADS, smem, stream>>>(ma, mb, mb2, (TOut*)out, ldo, residual, M, N, K, vec_ok, err, splits, g_splitk_ws);
+    cudaError_t le = launch_pdl(8, kern, grid, dim3(TC_THREADS), (size_t)smem, stream, ma, mb, mb2, (TOut*)out, ldo, residual, M, N, K,
+                                vec_ok, err, splits, g_splitk_ws);
+    if (le != cudaSuccess) {
+      set_error("gemm_tc: launch failed: %s", cudaGetErrorString(le));
+      return -2;
+    }
     return 0;
   };
   const int rc = deep ? go(gemm_tc_kernel<BN, EPI, TOut, DEEP>, DEEP * STAGE_BYTES + 1024 + 256)

@@ -15,7 +15,7 @@ void set_error(const char* fmt, ...) {
   va_end(ap);
 }
 
-static int g_pdl = 1;   // the few-rows matrix products (bit 0) start under the tail of the kernel before them
+static int g_pdl = 9;   // the few-rows matrix products (bit 0) and the one-tile tcgen05 products (bit 3) start under the tail of the kernel before them
 int pdl_enabled() { return g_pdl; }
 
 }  // namespace edgelm
