@@ -5,7 +5,7 @@
 // the sequence's keys in blocks of 128 (two pages of the cache) up to the tile's last position:
 //
 //   S   = Q K^T          tcgen05.mma M128 N128 K16 x 4, accumulator in tensor memory (two S buffers)
-//   P   = exp2(S - max)  four softmax warps, a thread a row: tcgen05.ld of its row, float32 running
+//   P   = exp2(S - max)  softmax warps, two threads a row: tcgen05.ld of their halves of the row, float32
 //                        maximum and denominator, P rounded to bfloat16 into shared memory in the
 //                        128-byte-swizzled K-major layout the next MMA reads
 //   O  += P V            tcgen05.mma M128 N64 K16 x 8, accumulating in tensor memory over the blocks; V is
@@ -14,13 +14,15 @@
 //                        the running maximum has outgrown it by 2^8; then the softmax threads scale
 //                        their rows of O in place (tcgen05.ld, multiply, tcgen05.st)
 //
-// Roles: warp 0 issues the TMA loads (Q once; K and V of a block as two pages each, two stages),
-// warp 1 allocates tensor memory and issues the MMAs, warps 2-5 and 6-9 are two softmax groups.  The
+// Roles: warp 0 issues the TMA loads (Q once; K and V of a block as two pages each, four stages: with two, a
+// group's next block was only requested when its current one was done, and every block waited out a load),
+// warp 1 allocates tensor memory and issues the MMAs, warps 2-9 and 10-17 are two softmax groups.  The
 // groups take the key blocks in turn (even, odd), each with an S, a P and an O of its own and its own
-// reference maximum and denominator; group 0 merges the two at the end.  So two blocks are in
-// flight in a CTA: the tensor cores work for one group while the other computes exponentials, and an
-// SM sub-partition has two softmax warps to overlap the latencies of tcgen05.ld.  384 of 512 columns
-// of tensor memory (S, S, O, O).
+// reference maximum and denominator; group 0 merges the two at the end.  In a group two threads share a
+// row (64 keys each), so that a row's 128 scores need no more registers than a thread has without
+// spilling.  Two blocks are in flight in a CTA: the tensor cores work for one group while the other
+// computes exponentials, and an SM sub-partition has four softmax warps to overlap the latencies of
+// tcgen05.ld.  384 of 512 columns of tensor memory (S, S, O, O).
 // Every wait is bounded as in the matrix-product kernels: a wait that runs out sets ERR_WAIT_TIMEOUT,
 // raises the block's abort flag, and all roles leave; tensor memory is freed in any case.
 //
@@ -37,13 +39,15 @@ namespace edgelm {
 constexpr int AT_ROWS = 128;    // tokens of a tile = lanes of tensor memory
 constexpr int AT_KEYS = 128;    // keys of a block
 constexpr int AT_HD = 64;
-constexpr int AT_THREADS = 320; // TMA warp, MMA warp, two softmax groups of four warps
+constexpr int AT_GROUP_THREADS = 256;   // a softmax group: two threads a row, each with 64 of a block's 128 keys
+constexpr int AT_THREADS = 64 + 2 * AT_GROUP_THREADS;   // TMA warp, MMA warp, two softmax groups of eight warps
 constexpr int AT_Q_BYTES = AT_ROWS * AT_HD * 2;          // 16 KB
 constexpr int AT_KV_BYTES = AT_KEYS * AT_HD * 2;         // 16 KB: two pages
+constexpr int AT_STAGES = 4;                             // blocks of K and of V in shared memory: the loads run two blocks a group ahead
 constexpr int AT_P_BYTES = AT_ROWS * AT_KEYS * 2;        // 32 KB: two K-major tiles of 128 x 64
-constexpr int AT_SMEM = AT_Q_BYTES + 4 * AT_KV_BYTES + 2 * AT_P_BYTES + 1024 + 256;
+constexpr int AT_XCHG_BYTES = 2 * 2 * AT_ROWS * 4;   // the two threads of a row tell each other their half's maximum: [group][half][row]
+constexpr int AT_SMEM = AT_Q_BYTES + 2 * AT_STAGES * AT_KV_BYTES + 2 * AT_P_BYTES + AT_XCHG_BYTES + 1024 + 512;
 constexpr uint32_t AT_TMEM_COLS = 512;                   // S of group 0, S of group 1 (128 each), O_b of group 0, of group 1 (64 each)
-constexpr int AT_MERGE_PITCH = AT_HD + 2;                // floats a row hands over when the two groups' results are merged
 
 __device__ __forceinline__ float at_exp2(float x) {
   float y;
@@ -69,24 +73,29 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
 
 constexpr float AT_LAZY = 8.f;   // the reference maximum follows the running maximum only when that has grown by more than 2^8
 
-// The softmax of one block for one row: the row of S comes from tensor memory once and stays in registers.
-// MASKED: the block touches the diagonal (keys past `pos` do not count).  P = exp2(S scale - m_ref), rounded to
-// bfloat16, goes into the swizzled K-major tiles; returns its sum.  m_ref is the row's reference maximum: the
-// first block's maximum, replaced by a later block's only when that exceeds it by more than AT_LAZY (P then stays
-// below 2^8, far inside the range of bfloat16 and float32); `rescale` is the factor that replacement puts on
-// what was accumulated before (1 if none): softmax does not depend on the reference, only its rounding does.
+// The softmax of one block for half a row (64 of its 128 keys; the other half is the partner thread's, same lane,
+// four warps further): the scores come from tensor memory once and stay in registers; the two halves' maxima are
+// exchanged through shared memory (`mine`, `theirs`) around a barrier of the group.  MASKED: the block touches the
+// diagonal (keys past `pos` do not count).  P = exp2(S scale - m_ref), rounded to bfloat16, goes into the half's
+// swizzled K-major tile; returns its sum.  m_ref is the row's reference maximum: the first block's maximum, replaced
+// by a later block's only when that exceeds it by more than AT_LAZY (P then stays below 2^8, far inside the range
+// of bfloat16 and float32); `rescale` is the factor that replacement puts on what was accumulated before (1 if
+// none): softmax does not depend on the reference, only its rounding does.  Both threads of a row decide alike.
 template <bool MASKED>
-__device__ __forceinline__ float at_softmax_block(uint32_t s_addr, uint8_t* p_tiles, int row, int key0, int pos, float scale_log2,
-                                                  bool first, float& m_ref, float& rescale) {
-  uint32_t r[AT_KEYS];
-#pragma unroll
-  for (int c = 0; c < AT_KEYS / 32; ++c) tmem_ld32(s_addr + c * 32, r + c * 32);
+__device__ __forceinline__ float at_softmax_block(uint32_t s_addr, uint8_t* p_tile, int row, int key0, int pos, float scale_log2,
+                                                  bool first, float& m_ref, float& rescale, float* mine, const float* theirs,
+                                                  int group_barrier) {
+  uint32_t r[AT_KEYS / 2];
+  tmem_ld32(s_addr, r);
+  tmem_ld32(s_addr + 32, r + 32);
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
   float mx = -CUDART_INF_F;
 #pragma unroll
-  for (int i = 0; i < AT_KEYS; ++i)
+  for (int i = 0; i < AT_KEYS / 2; ++i)
     if (!MASKED || key0 + i <= pos) mx = fmaxf(mx, __uint_as_float(r[i]));   // (the scale is positive)
-  mx *= scale_log2;
+  *mine = mx;
+  asm volatile("bar.sync %0, %1;" ::"r"(group_barrier), "r"(AT_GROUP_THREADS) : "memory");
+  mx = fmaxf(mx, *theirs) * scale_log2;
   rescale = 1.f;
   if (first) {
     m_ref = mx;
@@ -97,7 +106,7 @@ __device__ __forceinline__ float at_softmax_block(uint32_t s_addr, uint8_t* p_ti
   const float m_use = m_ref == -CUDART_INF_F ? 0.f : m_ref;   // (a row of the tile's unused tail may see no key)
   float lsum = 0.f;
 #pragma unroll
-  for (int c = 0; c < AT_KEYS / 32; ++c) {
+  for (int c = 0; c < AT_KEYS / 64; ++c) {
     uint32_t pk[16];
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
@@ -110,10 +119,10 @@ __device__ __forceinline__ float at_softmax_block(uint32_t s_addr, uint8_t* p_ti
       lsum += p0 + p1;
       pk[i >> 1] = at_pack(p0, p1);
     }
-    uint8_t* prow = p_tiles + (c >> 1) * (AT_P_BYTES / 2) + row * 128;
+    uint8_t* prow = p_tile + row * 128;
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-      const int ch = (c & 1) * 4 + u;
+      const int ch = c * 4 + u;
       *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = make_uint4(pk[u * 4], pk[u * 4 + 1], pk[u * 4 + 2], pk[u * 4 + 3]);
     }
   }
@@ -131,18 +140,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(at_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* q_s = smem;
   uint8_t* k_s = q_s + AT_Q_BYTES;            // [2][16 KB]
-  uint8_t* v_s = k_s + 2 * AT_KV_BYTES;       // [2][16 KB]
-  uint8_t* p_s = v_s + 2 * AT_KV_BYTES;       // [2 groups][2 tiles][128 rows][128 bytes]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + 2 * AT_P_BYTES);
+  uint8_t* v_s = k_s + AT_STAGES * AT_KV_BYTES;   // [AT_STAGES][16 KB]
+  uint8_t* p_s = v_s + AT_STAGES * AT_KV_BYTES;   // [2 groups][2 tiles][128 rows][128 bytes]
+  float* xchg = reinterpret_cast<float*>(p_s + 2 * AT_P_BYTES);   // [group][half][row]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + 2 * AT_P_BYTES + AT_XCHG_BYTES);
   uint64_t* q_full = bars;
-  uint64_t* k_full = bars + 1;      // [2]
-  uint64_t* v_full = bars + 3;      // [2]
-  uint64_t* k_empty = bars + 5;     // [2]
-  uint64_t* v_empty = bars + 7;     // [2]
-  uint64_t* s_ready = bars + 9;     // [2]
-  uint64_t* p_ready = bars + 11;    // [2] 128 arrivals
-  uint64_t* o_ready = bars + 13;    // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* k_full = bars + 1;                      // [AT_STAGES]
+  uint64_t* v_full = k_full + AT_STAGES;            // [AT_STAGES]
+  uint64_t* k_empty = v_full + AT_STAGES;           // [AT_STAGES]
+  uint64_t* v_empty = k_empty + AT_STAGES;          // [AT_STAGES]
+  uint64_t* s_ready = v_empty + AT_STAGES;          // [2]
+  uint64_t* p_ready = s_ready + 2;                  // [2] one arrival per thread of the group
+  uint64_t* o_ready = p_ready + 2;                  // [2]
+  constexpr int N_BARS = 1 + 4 * AT_STAGES + 6;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + N_BARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -154,7 +165,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int n_pg = (n_keys + PAGE - 1) / PAGE;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 15; ++i) mbar_init(smem_u32(&bars[i]), (i == 11 || i == 12) ? 128u : 1u);
+    for (int i = 0; i < N_BARS; ++i) mbar_init(smem_u32(&bars[i]), (&bars[i] == &p_ready[0] || &bars[i] == &p_ready[1]) ? (uint32_t)AT_GROUP_THREADS : 1u);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -175,18 +186,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       mbar_expect_tx(smem_u32(q_full), AT_Q_BYTES);
       tma_load_2d(smem_u32(q_s), &map_q, smem_u32(q_full), head * AT_HD, tok0);
       for (int j = 0; j < n_blk; ++j) {
-        const int s = j & 1;
+        const int s = j % AT_STAGES;
+        const uint32_t par = (uint32_t)(j / AT_STAGES) & 1u;
         int p0 = pages[2 * j], p1 = 2 * j + 1 < n_pg ? pages[2 * j + 1] : p0;
         if (p0 < 0 || p0 >= n_pages || p1 < 0 || p1 >= n_pages) {
           atomicOr(err, ERR_PAGE_RANGE);
           p0 = p1 = 0;
         }
         const int y0 = (p0 * nkv + kvh) * PAGE, y1 = (p1 * nkv + kvh) * PAGE;
-        if (!mbar_wait(smem_u32(&k_empty[s]), ((j >> 1) & 1) ^ 1, abort_flag, err)) break;
+        if (!mbar_wait(smem_u32(&k_empty[s]), par ^ 1u, abort_flag, err)) break;
         mbar_expect_tx(smem_u32(&k_full[s]), AT_KV_BYTES);
         tma_load_2d(smem_u32(k_s + s * AT_KV_BYTES), &map_k, smem_u32(&k_full[s]), 0, y0);
         tma_load_2d(smem_u32(k_s + s * AT_KV_BYTES + AT_KV_BYTES / 2), &map_k, smem_u32(&k_full[s]), 0, y1);
-        if (!mbar_wait(smem_u32(&v_empty[s]), ((j >> 1) & 1) ^ 1, abort_flag, err)) break;
+        if (!mbar_wait(smem_u32(&v_empty[s]), par ^ 1u, abort_flag, err)) break;
         mbar_expect_tx(smem_u32(&v_full[s]), AT_KV_BYTES);
         tma_load_2d(smem_u32(v_s + s * AT_KV_BYTES), &map_v, smem_u32(&v_full[s]), 0, y0);
         tma_load_2d(smem_u32(v_s + s * AT_KV_BYTES + AT_KV_BYTES / 2), &map_v, smem_u32(&v_full[s]), 0, y1);
@@ -203,24 +215,24 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const uint64_t dq = umma_desc(smem_u32(q_s));
       bool ok = mbar_wait(smem_u32(q_full), 0, abort_flag, err);
       auto issue_qk = [&](int j) {   // S[j & 1] = Q K_j^T
-        const int s = j & 1;
-        if (!mbar_wait(smem_u32(&k_full[s]), (j >> 1) & 1, abort_flag, err)) return false;
+        const int s = j & 1, st = j % AT_STAGES;
+        if (!mbar_wait(smem_u32(&k_full[st]), (uint32_t)(j / AT_STAGES) & 1u, abort_flag, err)) return false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint64_t dk = umma_desc(smem_u32(k_s + s * AT_KV_BYTES));
+        const uint64_t dk = umma_desc(smem_u32(k_s + st * AT_KV_BYTES));
 #pragma unroll
         for (int k = 0; k < AT_HD / 16; ++k) umma_f16(tmem_base + (uint32_t)s * AT_KEYS, dq + 2 * k, dk + 2 * k, idesc_qk, k != 0);
         umma_commit(smem_u32(&s_ready[s]));
-        umma_commit(smem_u32(&k_empty[s]));
+        umma_commit(smem_u32(&k_empty[st]));
         return true;
       };
       if (ok) ok = issue_qk(0);
       if (ok && n_blk > 1) ok = issue_qk(1);
       for (int j = 0; j < n_blk && ok; ++j) {
-        const int s = j & 1;
+        const int s = j & 1, st = j % AT_STAGES;
         if (!(ok = mbar_wait(smem_u32(&p_ready[s]), (j >> 1) & 1, abort_flag, err))) break;
-        if (!(ok = mbar_wait(smem_u32(&v_full[s]), (j >> 1) & 1, abort_flag, err))) break;
+        if (!(ok = mbar_wait(smem_u32(&v_full[st]), (uint32_t)(j / AT_STAGES) & 1u, abort_flag, err))) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint64_t dv = umma_desc(smem_u32(v_s + s * AT_KV_BYTES));
+        const uint64_t dv = umma_desc(smem_u32(v_s + st * AT_KV_BYTES));
 #pragma unroll
         for (int k = 0; k < AT_KEYS / 16; ++k) {
           // P: two K-major tiles of 64 keys; V: 16 keys further = 16 rows of 128 bytes further
@@ -228,99 +240,103 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           umma_f16(tmem_o + (uint32_t)s * AT_HD, dp, dv + (uint64_t)(k * 16 * 128 >> 4), idesc_pv, (k != 0) || (j >= 2));   // O of the group accumulates over its blocks
         }
         umma_commit(smem_u32(&o_ready[s]));
-        umma_commit(smem_u32(&v_empty[s]));
+        umma_commit(smem_u32(&v_empty[st]));
         if (j + 2 < n_blk) ok = issue_qk(j + 2);   // (the group has read S of block j: it has written its P)
       }
     }
   } else {
-    // ---------------------------------------------------------------- softmax: two groups, a thread a row, the
-    // groups take the blocks in turn, each with a running maximum, denominator and output of its own
-    const int g = (warp - 2) >> 2, q4 = warp & 3, row = q4 * 32 + lane, pos = pos0 + row;
+    // ---------------------------------------------------------------- softmax: two groups of eight warps.  The
+    // groups take the blocks in turn, each with a reference maximum, denominator and output of its own; in a group
+    // two threads share a row (warps w and w + 4 reach the same 32 lanes of tensor memory): each has 64 of a
+    // block's 128 keys and 32 of the output's 64 dims.
+    const int sw = warp - 2, g = sw >> 3, half = (sw >> 2) & 1, q4 = warp & 3, row = q4 * 32 + lane, pos = pos0 + row;
     const uint32_t lane_off = (uint32_t)(q4 * 32) << 16;
-    const uint32_t s_addr = tmem_base + lane_off + (uint32_t)g * AT_KEYS, o_addr = tmem_o + lane_off + (uint32_t)g * AT_HD;
-    uint8_t* p_tiles = p_s + g * AT_P_BYTES;
-    float m = -CUDART_INF_F, l = 0.f;   // the row's reference maximum (log2 units) and denominator; its output lives in tensor memory
+    const uint32_t s_addr = tmem_base + lane_off + (uint32_t)g * AT_KEYS + (uint32_t)half * (AT_KEYS / 2);
+    const uint32_t o_addr = tmem_o + lane_off + (uint32_t)g * AT_HD + (uint32_t)half * (AT_HD / 2);
+    uint8_t* p_tile = p_s + g * AT_P_BYTES + half * (AT_P_BYTES / 2);
+    float* mine = xchg + (g * 2 + half) * AT_ROWS + row;
+    const float* theirs = xchg + (g * 2 + (half ^ 1)) * AT_ROWS + row;
+    const int group_barrier = 1 + g;
+    float m = -CUDART_INF_F, l = 0.f;   // the row's reference maximum (log2 units) and this half's share of the denominator
     bool ok = true;
     int u = 0;   // blocks this group has done
     for (int j = g; j < n_blk; j += 2, ++u) {
-      const int key0 = j * AT_KEYS;
+      const int key0 = j * AT_KEYS + half * (AT_KEYS / 2);
       if (!(ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&s_ready[g]), u & 1, abort_flag, err)))) break;
       // the group's block before this one has been through its P V: P and O are free (that product was issued long ago)
       if (u > 0 && !(ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&o_ready[g]), (u - 1) & 1, abort_flag, err)))) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       float rescale;
-      const float lsum = key0 + AT_KEYS - 1 > pos0 ? at_softmax_block<true>(s_addr, p_tiles, row, key0, pos, scale_log2, u == 0, m, rescale)
-                                                   : at_softmax_block<false>(s_addr, p_tiles, row, key0, pos, scale_log2, u == 0, m, rescale);
-      if (__any_sync(0xffffffffu, rescale != 1.f)) {   // rare after the first blocks: the warp's rows of O times their factors
+      const float lsum = j * AT_KEYS + AT_KEYS - 1 > pos0
+                             ? at_softmax_block<true>(s_addr, p_tile, row, key0, pos, scale_log2, u == 0, m, rescale, mine, theirs, group_barrier)
+                             : at_softmax_block<false>(s_addr, p_tile, row, key0, pos, scale_log2, u == 0, m, rescale, mine, theirs, group_barrier);
+      if (__any_sync(0xffffffffu, rescale != 1.f)) {   // rare after the first blocks: the warp's share of O times the rows' factors
+        uint32_t r[32];
+        tmem_ld32(o_addr, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-        for (int c = 0; c < AT_HD / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld32(o_addr + c * 32, r);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * rescale);
-          tmem_st32(o_addr + c * 32, r);
-        }
+        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * rescale);
+        tmem_st32(o_addr, r);
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       }
       l = fmaf(l, rescale, lsum);
-      if (j == n_blk - 1 && n_keys < key0 + AT_KEYS) {
+      if (j == n_blk - 1 && n_keys < j * AT_KEYS + AT_KEYS) {
         // value rows past the tile's last position: every weight on them is zero; make them zero too
-        if (!(ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&v_full[g]), u & 1, abort_flag, err)))) break;
-        const int first = n_keys - key0;   // 1 .. 127
-        for (int i = q4 * 32 + lane; i < (AT_KEYS - first) * 8; i += 128) {
+        if (!(ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&v_full[j % AT_STAGES]), (uint32_t)(j / AT_STAGES) & 1u, abort_flag, err)))) break;
+        const int first = n_keys - j * AT_KEYS;   // 1 .. 127
+        for (int i = (sw & 7) * 32 + lane; i < (AT_KEYS - first) * 8; i += AT_GROUP_THREADS) {
           const int r = first + (i >> 3);
-          *reinterpret_cast<uint4*>(v_s + g * AT_KV_BYTES + r * 128 + ((i & 7) << 4)) = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(v_s + (j % AT_STAGES) * AT_KV_BYTES + r * 128 + ((i & 7) << 4)) = make_uint4(0, 0, 0, 0);
         }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&p_ready[g])) : "memory");
     }
-    // ---- the group's output out of tensor memory
-    float o[AT_HD];
+    // ---- the group's output out of tensor memory: this thread's 32 dims of its row
+    float o[AT_HD / 2];
 #pragma unroll
-    for (int i = 0; i < AT_HD; ++i) o[i] = 0.f;
+    for (int i = 0; i < AT_HD / 2; ++i) o[i] = 0.f;
     if (ok && u > 0) {
       ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&o_ready[g]), (u - 1) & 1, abort_flag, err));
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (ok) {
-        uint32_t r[AT_HD];
+        uint32_t r[32];
         tmem_ld32(o_addr, r);
-        tmem_ld32(o_addr + 32, r + 32);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-        for (int i = 0; i < AT_HD; ++i) o[i] = __uint_as_float(r[i]);
+        for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(r[i]);
       }
     }
-    // ---- the two groups' results of a row are merged by group 0: group 1 hands over (m, l, o) through the P tiles
-    // (all P V products are done: both groups have read their last O_b)
-    float* hand = reinterpret_cast<float*>(p_s) + (size_t)row * AT_MERGE_PITCH;
-    asm volatile("bar.sync 1, 256;" ::: "memory");   // group 0's P tiles are no longer read either
+    // ---- a row's four threads (two groups, two halves) put their results together: every thread hands over its
+    // (m, l) and group 1 its 32 dims, through the P tiles (all P V products are done: both groups have read their O);
+    // group 0 merges and stores its own 32 dims
+    float* hand_ml = reinterpret_cast<float*>(p_s);                                  // [group][half][row][2]
+    float* hand_o = hand_ml + 2 * 2 * AT_ROWS * 2;                                   // [half][row][33] of group 1
+    asm volatile("bar.sync 3, 512;" ::: "memory");   // nobody's P tiles are read any more
+    hand_ml[((g * 2 + half) * AT_ROWS + row) * 2] = m;
+    hand_ml[((g * 2 + half) * AT_ROWS + row) * 2 + 1] = l;
     if (g == 1) {
-      hand[0] = m;
-      hand[1] = l;
 #pragma unroll
-      for (int i = 0; i < AT_HD; ++i) hand[2 + i] = o[i];
+      for (int i = 0; i < AT_HD / 2; ++i) hand_o[(half * AT_ROWS + row) * 33 + i] = o[i];
     }
-    asm volatile("bar.sync 1, 256;" ::: "memory");
+    asm volatile("bar.sync 3, 512;" ::: "memory");
     if (g == 0 && ok && row < ntok) {
-      const float m1 = hand[0], l1 = hand[1];
-      const float mm = fmaxf(m, m1);
-      const float f0 = at_exp2(m - mm), f1 = m1 == -CUDART_INF_F ? 0.f : at_exp2(m1 - mm);
-      const float inv = 1.0f / (l * f0 + l1 * f1);
-      __nv_bfloat16* dst = out + (size_t)(tok0 + row) * ldo + head * AT_HD;
+      // (the two halves of a group share m; their l add up)
+      const float m0 = m, l0 = l + hand_ml[((0 * 2 + (half ^ 1)) * AT_ROWS + row) * 2 + 1];
+      const float m1 = hand_ml[((1 * 2 + 0) * AT_ROWS + row) * 2];
+      const float l1 = hand_ml[((1 * 2 + 0) * AT_ROWS + row) * 2 + 1] + hand_ml[((1 * 2 + 1) * AT_ROWS + row) * 2 + 1];
+      const float mm = fmaxf(m0, m1);
+      const float f0 = at_exp2(m0 - mm), f1 = m1 == -CUDART_INF_F ? 0.f : at_exp2(m1 - mm);
+      const float inv = 1.0f / (l0 * f0 + l1 * f1);
+      const float* o1 = hand_o + (half * AT_ROWS + row) * 33;
+      __nv_bfloat16* dst = out + (size_t)(tok0 + row) * ldo + head * AT_HD + half * (AT_HD / 2);
 #pragma unroll
-      for (int i = 0; i < AT_HD; i += 8) {
+      for (int i = 0; i < AT_HD / 2; i += 8) {
         float v[8];
 #pragma unroll
-        for (int t = 0; t < 8; ++t) v[t] = (o[i + t] * f0 + hand[2 + i + t] * f1) * inv;
-        uint4 w;
-        w.x = at_pack(v[0], v[1]);
-        w.y = at_pack(v[2], v[3]);
-        w.z = at_pack(v[4], v[5]);
-        w.w = at_pack(v[6], v[7]);
-        *reinterpret_cast<uint4*>(dst + i) = w;
+        for (int t = 0; t < 8; ++t) v[t] = (o[i + t] * f0 + o1[i + t] * f1) * inv;
+        *reinterpret_cast<uint4*>(dst + i) = make_uint4(at_pack(v[0], v[1]), at_pack(v[2], v[3]), at_pack(v[4], v[5]), at_pack(v[6], v[7]));
       }
     }
   }
