@@ -8,21 +8,25 @@
 //   P   = exp2(S - max)  softmax warps, two threads a row: tcgen05.ld of their halves of the row, float32
 //                        maximum and denominator, P rounded to bfloat16 into shared memory in the
 //                        128-byte-swizzled K-major layout the next MMA reads
-//   O  += P V            tcgen05.mma M128 N64 K16 x 8, accumulating in tensor memory over the blocks; V is
-//                        used as it lies in the cache, [key][dim]: the MN-major B operand (rows of 128
-//                        bytes = the 64 dims of a key).  The reference maximum of a row moves only when
-//                        the running maximum has outgrown it by 2^8; then the softmax threads scale
-//                        their rows of O in place (tcgen05.ld, multiply, tcgen05.st)
+//   O  += P V            tcgen05.mma M128 N64 K16, four for each half of the block's keys, each half into
+//                        an accumulator of its own in tensor memory, over the blocks; V is used as it lies
+//                        in the cache, [key][dim]: the MN-major B operand (rows of 128 bytes = the 64 dims
+//                        of a key).  The reference maximum of a half row moves only when the running
+//                        maximum has outgrown it by 2^8; then its thread scales its row of its O in place
+//                        (tcgen05.ld, multiply, tcgen05.st)
 //
-// Roles: warp 0 issues the TMA loads (Q once; K and V of a block as two pages each, four stages: with two, a
-// group's next block was only requested when its current one was done, and every block waited out a load),
-// warp 1 allocates tensor memory and issues the MMAs, warps 2-9 and 10-17 are two softmax groups.  The
-// groups take the key blocks in turn (even, odd), each with an S, a P and an O of its own and its own
-// reference maximum and denominator; group 0 merges the two at the end.  In a group two threads share a
-// row (64 keys each), so that a row's 128 scores need no more registers than a thread has without
-// spilling.  Two blocks are in flight in a CTA: the tensor cores work for one group while the other
-// computes exponentials, and an SM sub-partition has four softmax warps to overlap the latencies of
-// tcgen05.ld.  384 of 512 columns of tensor memory (S, S, O, O).
+// Roles: warp 0 loads Q and the keys by TMA, warp 1 the values (each block as two pages, two stages; one
+// warp for both would hold the keys of the block after next behind a wait for a free value stage);
+// warp 2 allocates tensor memory and issues the Q K^T products, warp 3 the P V products (two issuers,
+// because which comes next depends on how the groups drift); warps 4-11 and 12-19 are two softmax
+// groups.  The groups take the key blocks in turn (even, odd), each with an S of its own, two P buffers
+// and its own accumulators.  In a group two threads share a row, 64 keys each, and share nothing else:
+// each has its own reference maximum, denominator and O (so no exchange between them in the loop, and a
+// row's 128 scores need no more registers than a thread has).  A thread frees its S as soon as the scores
+// are in its registers: the group's next Q K^T runs while it computes exponentials; with two P buffers
+// the next block's P can be written while the tensor cores still read this one's.  The four partial
+// results of a row (two groups, two halves) are put together through shared memory at the end.
+// All 512 columns of tensor memory (S, S, and four O of 64).
 // Every wait is bounded as in the matrix-product kernels: a wait that runs out sets ERR_WAIT_TIMEOUT,
 // raises the block's abort flag, and all roles leave; tensor memory is freed in any case.
 //
@@ -38,16 +42,24 @@ namespace edgelm {
 
 constexpr int AT_ROWS = 128;    // tokens of a tile = lanes of tensor memory
 constexpr int AT_KEYS = 128;    // keys of a block
+constexpr int AT_HALF = AT_KEYS / 2;    // keys of a thread
 constexpr int AT_HD = 64;
-constexpr int AT_GROUP_THREADS = 256;   // a softmax group: two threads a row, each with 64 of a block's 128 keys
-constexpr int AT_THREADS = 64 + 2 * AT_GROUP_THREADS;   // TMA warp, MMA warp, two softmax groups of eight warps
+constexpr int AT_GROUP_WARPS = 8;       // a softmax group: two threads a row, each with 64 of a block's 128 keys
+constexpr int AT_GROUP_THREADS = AT_GROUP_WARPS * 32;
+constexpr int AT_ROLE_WARPS = 4;        // K loads, V loads, Q K^T issue, P V issue
+constexpr int AT_THREADS = AT_ROLE_WARPS * 32 + 2 * AT_GROUP_THREADS;
 constexpr int AT_Q_BYTES = AT_ROWS * AT_HD * 2;          // 16 KB
 constexpr int AT_KV_BYTES = AT_KEYS * AT_HD * 2;         // 16 KB: two pages
-constexpr int AT_STAGES = 4;                             // blocks of K and of V in shared memory: the loads run two blocks a group ahead
-constexpr int AT_P_BYTES = AT_ROWS * AT_KEYS * 2;        // 32 KB: two K-major tiles of 128 x 64
-constexpr int AT_XCHG_BYTES = 2 * 2 * AT_ROWS * 4;   // the two threads of a row tell each other their half's maximum: [group][half][row]
-constexpr int AT_SMEM = AT_Q_BYTES + 2 * AT_STAGES * AT_KV_BYTES + 2 * AT_P_BYTES + AT_XCHG_BYTES + 1024 + 512;
-constexpr uint32_t AT_TMEM_COLS = 512;                   // S of group 0, S of group 1 (128 each), O_b of group 0, of group 1 (64 each)
+constexpr int AT_STAGES = 2;                             // blocks of K and of V in shared memory
+constexpr int AT_P_BYTES = AT_ROWS * AT_KEYS * 2;        // 32 KB: two K-major tiles of 128 x 64, one per half
+constexpr int AT_P_BUFS = 2;                             // P buffers of a group
+constexpr int AT_N_BARS = 1 + 4 * AT_STAGES + 8;
+constexpr int AT_SMEM = AT_Q_BYTES + 2 * AT_STAGES * AT_KV_BYTES + 2 * AT_P_BUFS * AT_P_BYTES + 1024 + 512;
+constexpr uint32_t AT_TMEM_COLS = 512;   // S of group 0, of group 1 (128 each); O of (group, half) at 256 + (2 group + half) 64
+// the end's exchange lies over the V stages and the P buffers: (m, l) of the four threads of a row, then their O
+constexpr int AT_HAND_PITCH = AT_HD + 1;
+static_assert(4 * AT_ROWS * 2 * 4 + 4 * AT_ROWS * AT_HAND_PITCH * 4 <= AT_STAGES * AT_KV_BYTES + 2 * AT_P_BUFS * AT_P_BYTES,
+              "the exchange does not fit");
 
 __device__ __forceinline__ float at_exp2(float x) {
   float y;
@@ -73,40 +85,39 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
 
 constexpr float AT_LAZY = 8.f;   // the reference maximum follows the running maximum only when that has grown by more than 2^8
 
-// The softmax of one block for half a row (64 of its 128 keys; the other half is the partner thread's, same lane,
-// four warps further): the scores come from tensor memory once and stay in registers; the two halves' maxima are
-// exchanged through shared memory (`mine`, `theirs`) around a barrier of the group.  MASKED: the block touches the
-// diagonal (keys past `pos` do not count).  P = exp2(S scale - m_ref), rounded to bfloat16, goes into the half's
-// swizzled K-major tile; returns its sum.  m_ref is the row's reference maximum: the first block's maximum, replaced
+// The softmax of one block for half a row (64 of its 128 keys): the scores come from tensor memory once and stay in
+// registers; `s_free` gets the warp's arrival as soon as they are there.  MASKED: the block touches the diagonal
+// (keys past `pos` do not count).  P = exp2(S scale - m_ref), rounded to bfloat16, goes into the half's swizzled
+// K-major tile; returns its sum.  m_ref is the half row's reference maximum: the first block's maximum, replaced
 // by a later block's only when that exceeds it by more than AT_LAZY (P then stays below 2^8, far inside the range
 // of bfloat16 and float32); `rescale` is the factor that replacement puts on what was accumulated before (1 if
-// none): softmax does not depend on the reference, only its rounding does.  Both threads of a row decide alike.
+// none): softmax does not depend on the reference, only its rounding does.
 template <bool MASKED>
-__device__ __forceinline__ float at_softmax_block(uint32_t s_addr, uint8_t* p_tile, int row, int key0, int pos, float scale_log2,
-                                                  bool first, float& m_ref, float& rescale, float* mine, const float* theirs,
-                                                  int group_barrier) {
-  uint32_t r[AT_KEYS / 2];
+__device__ __forceinline__ float at_softmax_block(uint32_t s_addr, uint32_t s_free, uint8_t* p_tile, int row, int key0, int pos,
+                                                  float scale_log2, bool first, float& m_ref, float& rescale) {
+  uint32_t r[AT_HALF];
   tmem_ld32(s_addr, r);
   tmem_ld32(s_addr + 32, r + 32);
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s_free) : "memory");
   float mx = -CUDART_INF_F;
 #pragma unroll
-  for (int i = 0; i < AT_KEYS / 2; ++i)
+  for (int i = 0; i < AT_HALF; ++i)
     if (!MASKED || key0 + i <= pos) mx = fmaxf(mx, __uint_as_float(r[i]));   // (the scale is positive)
-  *mine = mx;
-  asm volatile("bar.sync %0, %1;" ::"r"(group_barrier), "r"(AT_GROUP_THREADS) : "memory");
-  mx = fmaxf(mx, *theirs) * scale_log2;
+  mx *= scale_log2;
   rescale = 1.f;
   if (first) {
     m_ref = mx;
   } else if (mx > m_ref + AT_LAZY) {
-    rescale = at_exp2(m_ref - mx);   // (0 if the row has seen no key so far)
+    rescale = at_exp2(m_ref - mx);   // (0 if the half row has seen no key so far)
     m_ref = mx;
   }
-  const float m_use = m_ref == -CUDART_INF_F ? 0.f : m_ref;   // (a row of the tile's unused tail may see no key)
+  const float m_use = m_ref == -CUDART_INF_F ? 0.f : m_ref;   // (a half row may have seen no key yet)
   float lsum = 0.f;
 #pragma unroll
-  for (int c = 0; c < AT_KEYS / 64; ++c) {
+  for (int c = 0; c < AT_HALF / 32; ++c) {
     uint32_t pk[16];
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
@@ -139,21 +150,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   extern __shared__ uint8_t at_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(at_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* q_s = smem;
-  uint8_t* k_s = q_s + AT_Q_BYTES;            // [2][16 KB]
+  uint8_t* k_s = q_s + AT_Q_BYTES;                // [AT_STAGES][16 KB]
   uint8_t* v_s = k_s + AT_STAGES * AT_KV_BYTES;   // [AT_STAGES][16 KB]
-  uint8_t* p_s = v_s + AT_STAGES * AT_KV_BYTES;   // [2 groups][2 tiles][128 rows][128 bytes]
-  float* xchg = reinterpret_cast<float*>(p_s + 2 * AT_P_BYTES);   // [group][half][row]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + 2 * AT_P_BYTES + AT_XCHG_BYTES);
+  uint8_t* p_s = v_s + AT_STAGES * AT_KV_BYTES;   // [2 groups][AT_P_BUFS][2 halves][128 rows][128 bytes]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + 2 * AT_P_BUFS * AT_P_BYTES);
   uint64_t* q_full = bars;
   uint64_t* k_full = bars + 1;                      // [AT_STAGES]
   uint64_t* v_full = k_full + AT_STAGES;            // [AT_STAGES]
   uint64_t* k_empty = v_full + AT_STAGES;           // [AT_STAGES]
   uint64_t* v_empty = k_empty + AT_STAGES;          // [AT_STAGES]
-  uint64_t* s_ready = v_empty + AT_STAGES;          // [2]
-  uint64_t* p_ready = s_ready + 2;                  // [2] one arrival per thread of the group
-  uint64_t* o_ready = p_ready + 2;                  // [2]
-  constexpr int N_BARS = 1 + 4 * AT_STAGES + 6;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + N_BARS);
+  uint64_t* s_ready = v_empty + AT_STAGES;          // [2] the group's scores are in tensor memory
+  uint64_t* s_free = s_ready + 2;                   // [2] ... and in the group's registers: one arrival per warp
+  uint64_t* p_ready = s_free + 2;                   // [2] the group's P is in shared memory: one arrival per warp
+  uint64_t* o_ready = p_ready + 2;                  // [2] the group's P V is done
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + AT_N_BARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -165,11 +175,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int n_pg = (n_keys + PAGE - 1) / PAGE;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < N_BARS; ++i) mbar_init(smem_u32(&bars[i]), (&bars[i] == &p_ready[0] || &bars[i] == &p_ready[1]) ? (uint32_t)AT_GROUP_THREADS : 1u);
+    for (int i = 0; i < AT_N_BARS; ++i) {
+      const bool by_warps = &bars[i] >= s_free && &bars[i] < o_ready;
+      mbar_init(smem_u32(&bars[i]), by_warps ? (uint32_t)AT_GROUP_WARPS : 1u);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {
+  if (warp == 2) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(AT_TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -177,14 +190,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_o = tmem_base + 2 * AT_KEYS;   // O_b of group g at + g * AT_HD
+  const uint32_t tmem_o = tmem_base + 2 * AT_KEYS;   // O of (group g, half h) at + (2 g + h) * AT_HD
 
-  if (warp == 0) {
-    // ---------------------------------------------------------------- TMA producer
+  if (warp < 2) {
+    // ---------------------------------------------------------------- TMA producers: warp 0 Q and K, warp 1 V
     if (lane == 0) {
       const int32_t* pages = page_table + (size_t)seq_slot[seq] * table_stride;
-      mbar_expect_tx(smem_u32(q_full), AT_Q_BYTES);
-      tma_load_2d(smem_u32(q_s), &map_q, smem_u32(q_full), head * AT_HD, tok0);
+      const CUtensorMap* map = warp == 0 ? &map_k : &map_v;
+      uint8_t* dst = warp == 0 ? k_s : v_s;
+      uint64_t* full = warp == 0 ? k_full : v_full;
+      uint64_t* empty = warp == 0 ? k_empty : v_empty;
+      if (warp == 0) {
+        mbar_expect_tx(smem_u32(q_full), AT_Q_BYTES);
+        tma_load_2d(smem_u32(q_s), &map_q, smem_u32(q_full), head * AT_HD, tok0);
+      }
       for (int j = 0; j < n_blk; ++j) {
         const int s = j % AT_STAGES;
         const uint32_t par = (uint32_t)(j / AT_STAGES) & 1u;
@@ -194,89 +213,93 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           p0 = p1 = 0;
         }
         const int y0 = (p0 * nkv + kvh) * PAGE, y1 = (p1 * nkv + kvh) * PAGE;
-        if (!mbar_wait(smem_u32(&k_empty[s]), par ^ 1u, abort_flag, err)) break;
-        mbar_expect_tx(smem_u32(&k_full[s]), AT_KV_BYTES);
-        tma_load_2d(smem_u32(k_s + s * AT_KV_BYTES), &map_k, smem_u32(&k_full[s]), 0, y0);
-        tma_load_2d(smem_u32(k_s + s * AT_KV_BYTES + AT_KV_BYTES / 2), &map_k, smem_u32(&k_full[s]), 0, y1);
-        if (!mbar_wait(smem_u32(&v_empty[s]), par ^ 1u, abort_flag, err)) break;
-        mbar_expect_tx(smem_u32(&v_full[s]), AT_KV_BYTES);
-        tma_load_2d(smem_u32(v_s + s * AT_KV_BYTES), &map_v, smem_u32(&v_full[s]), 0, y0);
-        tma_load_2d(smem_u32(v_s + s * AT_KV_BYTES + AT_KV_BYTES / 2), &map_v, smem_u32(&v_full[s]), 0, y1);
+        if (!mbar_wait(smem_u32(&empty[s]), par ^ 1u, abort_flag, err)) break;
+        mbar_expect_tx(smem_u32(&full[s]), AT_KV_BYTES);
+        tma_load_2d(smem_u32(dst + s * AT_KV_BYTES), map, smem_u32(&full[s]), 0, y0);
+        tma_load_2d(smem_u32(dst + s * AT_KV_BYTES + AT_KV_BYTES / 2), map, smem_u32(&full[s]), 0, y1);
       }
     }
-  } else if (warp == 1) {
-    // ---------------------------------------------------------------- MMA issuer
-    // Block j belongs to softmax group j & 1 and uses that group's S, P and O_b.  Order: the scores of blocks 0
-    // and 1, then for every block its P V as soon as its P is there, followed by the scores of block j + 2 into
-    // the S buffer that the group has just finished reading.
+  } else if (warp == 2) {
+    // ---------------------------------------------------------------- Q K^T issuer.  Block j belongs to softmax group
+    // j & 1 and goes into that group's S as soon as the group has the scores of block j - 2 in its registers.
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc(AT_ROWS, AT_KEYS);
-      constexpr uint32_t idesc_pv = umma_idesc(AT_ROWS, AT_HD) | (1u << 16);   // B (the values) is MN-major
       const uint64_t dq = umma_desc(smem_u32(q_s));
       bool ok = mbar_wait(smem_u32(q_full), 0, abort_flag, err);
-      auto issue_qk = [&](int j) {   // S[j & 1] = Q K_j^T
-        const int s = j & 1, st = j % AT_STAGES;
-        if (!mbar_wait(smem_u32(&k_full[st]), (uint32_t)(j / AT_STAGES) & 1u, abort_flag, err)) return false;
+      for (int j = 0; j < n_blk && ok; ++j) {
+        const int g = j & 1, st = j % AT_STAGES;
+        if (j >= 2 && !(ok = mbar_wait(smem_u32(&s_free[g]), (uint32_t)((j >> 1) - 1) & 1u, abort_flag, err))) break;
+        if (!(ok = mbar_wait(smem_u32(&k_full[st]), (uint32_t)(j / AT_STAGES) & 1u, abort_flag, err))) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint64_t dk = umma_desc(smem_u32(k_s + st * AT_KV_BYTES));
 #pragma unroll
-        for (int k = 0; k < AT_HD / 16; ++k) umma_f16(tmem_base + (uint32_t)s * AT_KEYS, dq + 2 * k, dk + 2 * k, idesc_qk, k != 0);
-        umma_commit(smem_u32(&s_ready[s]));
+        for (int k = 0; k < AT_HD / 16; ++k) umma_f16(tmem_base + (uint32_t)g * AT_KEYS, dq + 2 * k, dk + 2 * k, idesc_qk, k != 0);
+        umma_commit(smem_u32(&s_ready[g]));
         umma_commit(smem_u32(&k_empty[st]));
-        return true;
-      };
-      if (ok) ok = issue_qk(0);
-      if (ok && n_blk > 1) ok = issue_qk(1);
+      }
+    }
+  } else if (warp == 3) {
+    // ---------------------------------------------------------------- P V issuer: a block's two halves (64 keys each)
+    // into the two accumulators of its group, which add up over the group's blocks.
+    if (lane == 0) {
+      constexpr uint32_t idesc_pv = umma_idesc(AT_ROWS, AT_HD) | (1u << 16);   // B (the values) is MN-major
+      bool ok = true;
       for (int j = 0; j < n_blk && ok; ++j) {
-        const int s = j & 1, st = j % AT_STAGES;
-        if (!(ok = mbar_wait(smem_u32(&p_ready[s]), (j >> 1) & 1, abort_flag, err))) break;
+        const int g = j & 1, u = j >> 1, st = j % AT_STAGES;
+        if (!(ok = mbar_wait(smem_u32(&p_ready[g]), (uint32_t)u & 1u, abort_flag, err))) break;
         if (!(ok = mbar_wait(smem_u32(&v_full[st]), (uint32_t)(j / AT_STAGES) & 1u, abort_flag, err))) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint64_t dv = umma_desc(smem_u32(v_s + st * AT_KV_BYTES));
+        const uint8_t* p_buf = p_s + (g * AT_P_BUFS + (u % AT_P_BUFS)) * AT_P_BYTES;
 #pragma unroll
-        for (int k = 0; k < AT_KEYS / 16; ++k) {
-          // P: two K-major tiles of 64 keys; V: 16 keys further = 16 rows of 128 bytes further
-          const uint64_t dp = umma_desc(smem_u32(p_s + s * AT_P_BYTES + (k >> 2) * (AT_P_BYTES / 2))) + 2 * (k & 3);
-          umma_f16(tmem_o + (uint32_t)s * AT_HD, dp, dv + (uint64_t)(k * 16 * 128 >> 4), idesc_pv, (k != 0) || (j >= 2));   // O of the group accumulates over its blocks
+        for (int h = 0; h < 2; ++h) {
+          const uint64_t dp = umma_desc(smem_u32(p_buf + h * (AT_P_BYTES / 2)));
+#pragma unroll
+          for (int k = 0; k < AT_HALF / 16; ++k) {
+            // V: 16 keys further = 16 rows of 128 bytes further
+            umma_f16(tmem_o + (uint32_t)(2 * g + h) * AT_HD, dp + 2 * k, dv + (uint64_t)((h * AT_HALF + k * 16) * 128 >> 4), idesc_pv,
+                     (k != 0) || (u > 0));
+          }
         }
-        umma_commit(smem_u32(&o_ready[s]));
+        umma_commit(smem_u32(&o_ready[g]));
         umma_commit(smem_u32(&v_empty[st]));
-        if (j + 2 < n_blk) ok = issue_qk(j + 2);   // (the group has read S of block j: it has written its P)
       }
     }
   } else {
     // ---------------------------------------------------------------- softmax: two groups of eight warps.  The
-    // groups take the blocks in turn, each with a reference maximum, denominator and output of its own; in a group
-    // two threads share a row (warps w and w + 4 reach the same 32 lanes of tensor memory): each has 64 of a
-    // block's 128 keys and 32 of the output's 64 dims.
-    const int sw = warp - 2, g = sw >> 3, half = (sw >> 2) & 1, q4 = warp & 3, row = q4 * 32 + lane, pos = pos0 + row;
+    // groups take the blocks in turn; in a group two threads share a row (warps w and w + 4 reach the same 32
+    // lanes of tensor memory): each has 64 of a block's 128 keys, and a reference maximum, a denominator and an
+    // accumulator of its own.
+    const int sw = warp - AT_ROLE_WARPS, g = sw >> 3, half = (sw >> 2) & 1, q4 = warp & 3, row = q4 * 32 + lane, pos = pos0 + row;
     const uint32_t lane_off = (uint32_t)(q4 * 32) << 16;
-    const uint32_t s_addr = tmem_base + lane_off + (uint32_t)g * AT_KEYS + (uint32_t)half * (AT_KEYS / 2);
-    const uint32_t o_addr = tmem_o + lane_off + (uint32_t)g * AT_HD + (uint32_t)half * (AT_HD / 2);
-    uint8_t* p_tile = p_s + g * AT_P_BYTES + half * (AT_P_BYTES / 2);
-    float* mine = xchg + (g * 2 + half) * AT_ROWS + row;
-    const float* theirs = xchg + (g * 2 + (half ^ 1)) * AT_ROWS + row;
-    const int group_barrier = 1 + g;
-    float m = -CUDART_INF_F, l = 0.f;   // the row's reference maximum (log2 units) and this half's share of the denominator
+    const uint32_t s_addr = tmem_base + lane_off + (uint32_t)g * AT_KEYS + (uint32_t)half * AT_HALF;
+    const uint32_t o_addr = tmem_o + lane_off + (uint32_t)(2 * g + half) * AT_HD;
+    float m = -CUDART_INF_F, l = 0.f;   // the half row's reference maximum (log2 units) and denominator
     bool ok = true;
     int u = 0;   // blocks this group has done
     for (int j = g; j < n_blk; j += 2, ++u) {
-      const int key0 = j * AT_KEYS + half * (AT_KEYS / 2);
-      if (!(ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&s_ready[g]), u & 1, abort_flag, err)))) break;
-      // the group's block before this one has been through its P V: P and O are free (that product was issued long ago)
-      if (u > 0 && !(ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&o_ready[g]), (u - 1) & 1, abort_flag, err)))) break;
+      const int key0 = j * AT_KEYS + half * AT_HALF;
+      uint8_t* p_tile = p_s + (g * AT_P_BUFS + (u % AT_P_BUFS)) * AT_P_BYTES + half * (AT_P_BYTES / 2);   // (its last reader, the P V
+      if (!(ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&s_ready[g]), u & 1, abort_flag, err)))) break;   //  of block u - 2, was waited for in block u - 1)
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       float rescale;
       const float lsum = j * AT_KEYS + AT_KEYS - 1 > pos0
-                             ? at_softmax_block<true>(s_addr, p_tile, row, key0, pos, scale_log2, u == 0, m, rescale, mine, theirs, group_barrier)
-                             : at_softmax_block<false>(s_addr, p_tile, row, key0, pos, scale_log2, u == 0, m, rescale, mine, theirs, group_barrier);
-      if (__any_sync(0xffffffffu, rescale != 1.f)) {   // rare after the first blocks: the warp's share of O times the rows' factors
-        uint32_t r[32];
-        tmem_ld32(o_addr, r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                             ? at_softmax_block<true>(s_addr, smem_u32(&s_free[g]), p_tile, row, key0, pos, scale_log2, u == 0, m, rescale)
+                             : at_softmax_block<false>(s_addr, smem_u32(&s_free[g]), p_tile, row, key0, pos, scale_log2, u == 0, m, rescale);
+      // the group's block before this one has been through its P V: its accumulators may be scaled, and its P buffer
+      // is free for the next block
+      if (u > 0 && !(ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&o_ready[g]), (u - 1) & 1, abort_flag, err)))) break;
+      if (__any_sync(0xffffffffu, rescale != 1.f)) {   // rare after the first blocks
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * rescale);
-        tmem_st32(o_addr, r);
+        for (int c = 0; c < AT_HD / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(o_addr + c * 32, r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * rescale);
+          tmem_st32(o_addr + c * 32, r);
+        }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       }
       l = fmaf(l, rescale, lsum);
@@ -291,58 +314,68 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&p_ready[g])) : "memory");
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&p_ready[g])) : "memory");
     }
-    // ---- the group's output out of tensor memory: this thread's 32 dims of its row
-    float o[AT_HD / 2];
+    // ---- the thread's accumulator out of tensor memory: the 64 dims of its half row
+    float o[AT_HD];
 #pragma unroll
-    for (int i = 0; i < AT_HD / 2; ++i) o[i] = 0.f;
+    for (int i = 0; i < AT_HD; ++i) o[i] = 0.f;
     if (ok && u > 0) {
       ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&o_ready[g]), (u - 1) & 1, abort_flag, err));
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (ok) {
-        uint32_t r[32];
-        tmem_ld32(o_addr, r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(r[i]);
+        for (int c = 0; c < AT_HD / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(o_addr + c * 32, r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[c * 32 + i] = __uint_as_float(r[i]);
+        }
       }
     }
-    // ---- a row's four threads (two groups, two halves) put their results together: every thread hands over its
-    // (m, l) and group 1 its 32 dims, through the P tiles (all P V products are done: both groups have read their O);
-    // group 0 merges and stores its own 32 dims
-    float* hand_ml = reinterpret_cast<float*>(p_s);                                  // [group][half][row][2]
-    float* hand_o = hand_ml + 2 * 2 * AT_ROWS * 2;                                   // [half][row][33] of group 1
-    asm volatile("bar.sync 3, 512;" ::: "memory");   // nobody's P tiles are read any more
-    hand_ml[((g * 2 + half) * AT_ROWS + row) * 2] = m;
-    hand_ml[((g * 2 + half) * AT_ROWS + row) * 2 + 1] = l;
-    if (g == 1) {
+    // ---- a row's four threads (two groups, two halves) put their results together through shared memory (all
+    // products are done and every loaded block has been used: both groups have waited for their last P V): each
+    // hands over its (m, l) and its 64 dims, then merges and stores 16 dims of the row
+    const int q = g * 2 + half;
+    float* hand_ml = reinterpret_cast<float*>(v_s);                  // [4][row][2]
+    float* hand_o = hand_ml + 4 * AT_ROWS * 2;                       // [4][row][AT_HAND_PITCH]
+    asm volatile("bar.sync 1, %0;" ::"n"(2 * AT_GROUP_THREADS) : "memory");   // nobody's tiles are read any more
+    hand_ml[(q * AT_ROWS + row) * 2] = m;
+    hand_ml[(q * AT_ROWS + row) * 2 + 1] = l;
 #pragma unroll
-      for (int i = 0; i < AT_HD / 2; ++i) hand_o[(half * AT_ROWS + row) * 33 + i] = o[i];
-    }
-    asm volatile("bar.sync 3, 512;" ::: "memory");
-    if (g == 0 && ok && row < ntok) {
-      // (the two halves of a group share m; their l add up)
-      const float m0 = m, l0 = l + hand_ml[((0 * 2 + (half ^ 1)) * AT_ROWS + row) * 2 + 1];
-      const float m1 = hand_ml[((1 * 2 + 0) * AT_ROWS + row) * 2];
-      const float l1 = hand_ml[((1 * 2 + 0) * AT_ROWS + row) * 2 + 1] + hand_ml[((1 * 2 + 1) * AT_ROWS + row) * 2 + 1];
-      const float mm = fmaxf(m0, m1);
-      const float f0 = at_exp2(m0 - mm), f1 = m1 == -CUDART_INF_F ? 0.f : at_exp2(m1 - mm);
-      const float inv = 1.0f / (l0 * f0 + l1 * f1);
-      const float* o1 = hand_o + (half * AT_ROWS + row) * 33;
-      __nv_bfloat16* dst = out + (size_t)(tok0 + row) * ldo + head * AT_HD + half * (AT_HD / 2);
+    for (int i = 0; i < AT_HD; ++i) hand_o[(q * AT_ROWS + row) * AT_HAND_PITCH + i] = o[i];
+    asm volatile("bar.sync 1, %0;" ::"n"(2 * AT_GROUP_THREADS) : "memory");
+    if (ok && row < ntok) {
+      float mq[4], mm = -CUDART_INF_F, den = 0.f;
 #pragma unroll
-      for (int i = 0; i < AT_HD / 2; i += 8) {
-        float v[8];
+      for (int t = 0; t < 4; ++t) mm = fmaxf(mm, mq[t] = hand_ml[(t * AT_ROWS + row) * 2]);
 #pragma unroll
-        for (int t = 0; t < 8; ++t) v[t] = (o[i + t] * f0 + o1[i + t] * f1) * inv;
-        *reinterpret_cast<uint4*>(dst + i) = make_uint4(at_pack(v[0], v[1]), at_pack(v[2], v[3]), at_pack(v[4], v[5]), at_pack(v[6], v[7]));
+      for (int t = 0; t < 4; ++t) {
+        mq[t] = mq[t] == -CUDART_INF_F ? 0.f : at_exp2(mq[t] - mm);   // (a thread may have seen no key; the row has seen key 0)
+        den = fmaf(hand_ml[(t * AT_ROWS + row) * 2 + 1], mq[t], den);
       }
+      const float inv = 1.0f / den;
+      float v[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = 0.f;
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float* src = hand_o + (t * AT_ROWS + row) * AT_HAND_PITCH + q * 16;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = fmaf(src[i], mq[t], v[i]);
+      }
+      __nv_bfloat16* dst = out + (size_t)(tok0 + row) * ldo + head * AT_HD + q * 16;
+#pragma unroll
+      for (int i = 0; i < 16; i += 8)
+        *reinterpret_cast<uint4*>(dst + i) = make_uint4(at_pack(v[i] * inv, v[i + 1] * inv), at_pack(v[i + 2] * inv, v[i + 3] * inv),
+                                                        at_pack(v[i + 4] * inv, v[i + 5] * inv), at_pack(v[i + 6] * inv, v[i + 7] * inv));
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 1) {
+  if (warp == 2) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(AT_TMEM_COLS) : "memory");
   }
