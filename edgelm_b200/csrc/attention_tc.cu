@@ -66,6 +66,55 @@ __device__ __forceinline__ float at_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// two float32 in a 64-bit register pair, and the packed instructions on them
+__device__ __forceinline__ uint64_t at_pair(float lo, float hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+  return d;
+}
+__device__ __forceinline__ void at_unpair(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t at_fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t at_add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float at_max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// A bounded wait that lets the hardware park the warp (a time hint on try_wait) and looks at the abort flag and the
+// clock only now and then: the roles of this kernel wait often and long, and their polling would take issue slots
+// from the exponentials.
+__device__ __forceinline__ bool at_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err) {
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+#pragma unroll 1
+    for (int i = 0; i < 8; ++i) {
+      uint32_t ok;
+      asm volatile(
+          "{\n\t.reg .pred p;\n\t"
+          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+          "selp.u32 %0, 1, 0, p;\n\t}"
+          : "=r"(ok)
+          : "r"(bar), "r"(parity), "r"(20000u)
+          : "memory");
+      if (ok) return true;
+    }
+    if (*abort_flag) return false;
+    if (clock64() - t0 > TC_WAIT_CYCLES) {
+      *abort_flag = 1;
+      atomicOr(err, ERR_WAIT_TIMEOUT);
+      return false;
+    }
+  }
+}
 __device__ __forceinline__ uint32_t at_pack(float a, float b) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<const uint32_t*>(&v);
@@ -102,11 +151,18 @@ __device__ __forceinline__ float at_softmax_block(uint32_t s_addr, uint32_t s_fr
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncwarp();
   if ((threadIdx.x & 31) == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s_free) : "memory");
-  float mx = -CUDART_INF_F;
+  if (MASKED) {
 #pragma unroll
-  for (int i = 0; i < AT_HALF; ++i)
-    if (!MASKED || key0 + i <= pos) mx = fmaxf(mx, __uint_as_float(r[i]));   // (the scale is positive)
-  mx *= scale_log2;
+    for (int i = 0; i < AT_HALF; ++i)
+      if (key0 + i > pos) r[i] = __float_as_uint(-CUDART_INF_F);   // exp2 makes a zero of it
+  }
+  float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F;
+#pragma unroll
+  for (int i = 0; i < AT_HALF; i += 4) {
+    mx0 = at_max3(mx0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+    mx1 = at_max3(mx1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+  }
+  const float mx = fmaxf(mx0, mx1) * scale_log2;   // (the scale is positive)
   rescale = 1.f;
   if (first) {
     m_ref = mx;
@@ -115,20 +171,22 @@ __device__ __forceinline__ float at_softmax_block(uint32_t s_addr, uint32_t s_fr
     m_ref = mx;
   }
   const float m_use = m_ref == -CUDART_INF_F ? 0.f : m_ref;   // (a half row may have seen no key yet)
-  float lsum = 0.f;
+  const uint64_t scale2 = at_pair(scale_log2, scale_log2), minus_m2 = at_pair(-m_use, -m_use);
+  uint64_t sum_a = at_pair(0.f, 0.f), sum_b = sum_a;
 #pragma unroll
   for (int c = 0; c < AT_HALF / 32; ++c) {
     uint32_t pk[16];
 #pragma unroll
-    for (int i = 0; i < 32; i += 2) {
-      float p0 = at_exp2(fmaf(__uint_as_float(r[c * 32 + i]), scale_log2, -m_use));
-      float p1 = at_exp2(fmaf(__uint_as_float(r[c * 32 + i + 1]), scale_log2, -m_use));
-      if (MASKED) {
-        if (key0 + c * 32 + i > pos) p0 = 0.f;
-        if (key0 + c * 32 + i + 1 > pos) p1 = 0.f;
-      }
-      lsum += p0 + p1;
-      pk[i >> 1] = at_pack(p0, p1);
+    for (int i = 0; i < 32; i += 4) {
+      const uint32_t* x = r + c * 32 + i;
+      float a0, a1, b0, b1;
+      at_unpair(at_fma2(at_pair(__uint_as_float(x[0]), __uint_as_float(x[1])), scale2, minus_m2), a0, a1);
+      at_unpair(at_fma2(at_pair(__uint_as_float(x[2]), __uint_as_float(x[3])), scale2, minus_m2), b0, b1);
+      a0 = at_exp2(a0), a1 = at_exp2(a1), b0 = at_exp2(b0), b1 = at_exp2(b1);
+      sum_a = at_add2(sum_a, at_pair(a0, a1));
+      sum_b = at_add2(sum_b, at_pair(b0, b1));
+      pk[i >> 1] = at_pack(a0, a1);
+      pk[(i >> 1) + 1] = at_pack(b0, b1);
     }
     uint8_t* prow = p_tile + row * 128;
 #pragma unroll
@@ -137,6 +195,10 @@ __device__ __forceinline__ float at_softmax_block(uint32_t s_addr, uint32_t s_fr
       *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = make_uint4(pk[u * 4], pk[u * 4 + 1], pk[u * 4 + 2], pk[u * 4 + 3]);
     }
   }
+  float s0, s1, s2, s3;
+  at_unpair(sum_a, s0, s1);
+  at_unpair(sum_b, s2, s3);
+  const float lsum = (s0 + s1) + (s2 + s3);
   return lsum;
 }
 
@@ -213,7 +275,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           p0 = p1 = 0;
         }
         const int y0 = (p0 * nkv + kvh) * PAGE, y1 = (p1 * nkv + kvh) * PAGE;
-        if (!mbar_wait(smem_u32(&empty[s]), par ^ 1u, abort_flag, err)) break;
+        if (!at_wait(smem_u32(&empty[s]), par ^ 1u, abort_flag, err)) break;
         mbar_expect_tx(smem_u32(&full[s]), AT_KV_BYTES);
         tma_load_2d(smem_u32(dst + s * AT_KV_BYTES), map, smem_u32(&full[s]), 0, y0);
         tma_load_2d(smem_u32(dst + s * AT_KV_BYTES + AT_KV_BYTES / 2), map, smem_u32(&full[s]), 0, y1);
@@ -225,11 +287,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc(AT_ROWS, AT_KEYS);
       const uint64_t dq = umma_desc(smem_u32(q_s));
-      bool ok = mbar_wait(smem_u32(q_full), 0, abort_flag, err);
+      bool ok = at_wait(smem_u32(q_full), 0, abort_flag, err);
       for (int j = 0; j < n_blk && ok; ++j) {
         const int g = j & 1, st = j % AT_STAGES;
-        if (j >= 2 && !(ok = mbar_wait(smem_u32(&s_free[g]), (uint32_t)((j >> 1) - 1) & 1u, abort_flag, err))) break;
-        if (!(ok = mbar_wait(smem_u32(&k_full[st]), (uint32_t)(j / AT_STAGES) & 1u, abort_flag, err))) break;
+        if (j >= 2 && !(ok = at_wait(smem_u32(&s_free[g]), (uint32_t)((j >> 1) - 1) & 1u, abort_flag, err))) break;
+        if (!(ok = at_wait(smem_u32(&k_full[st]), (uint32_t)(j / AT_STAGES) & 1u, abort_flag, err))) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint64_t dk = umma_desc(smem_u32(k_s + st * AT_KV_BYTES));
 #pragma unroll
@@ -246,8 +308,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       bool ok = true;
       for (int j = 0; j < n_blk && ok; ++j) {
         const int g = j & 1, u = j >> 1, st = j % AT_STAGES;
-        if (!(ok = mbar_wait(smem_u32(&p_ready[g]), (uint32_t)u & 1u, abort_flag, err))) break;
-        if (!(ok = mbar_wait(smem_u32(&v_full[st]), (uint32_t)(j / AT_STAGES) & 1u, abort_flag, err))) break;
+        if (!(ok = at_wait(smem_u32(&p_ready[g]), (uint32_t)u & 1u, abort_flag, err))) break;
+        if (!(ok = at_wait(smem_u32(&v_full[st]), (uint32_t)(j / AT_STAGES) & 1u, abort_flag, err))) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint64_t dv = umma_desc(smem_u32(v_s + st * AT_KV_BYTES));
         const uint8_t* p_buf = p_s + (g * AT_P_BUFS + (u % AT_P_BUFS)) * AT_P_BYTES;
@@ -280,7 +342,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     for (int j = g; j < n_blk; j += 2, ++u) {
       const int key0 = j * AT_KEYS + half * AT_HALF;
       uint8_t* p_tile = p_s + (g * AT_P_BUFS + (u % AT_P_BUFS)) * AT_P_BYTES + half * (AT_P_BYTES / 2);   // (its last reader, the P V
-      if (!(ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&s_ready[g]), u & 1, abort_flag, err)))) break;   //  of block u - 2, was waited for in block u - 1)
+      if (!(ok = __all_sync(0xffffffffu, at_wait(smem_u32(&s_ready[g]), u & 1, abort_flag, err)))) break;   //  of block u - 2, was waited for in block u - 1)
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       float rescale;
       const float lsum = j * AT_KEYS + AT_KEYS - 1 > pos0
@@ -288,7 +350,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                              : at_softmax_block<false>(s_addr, smem_u32(&s_free[g]), p_tile, row, key0, pos, scale_log2, u == 0, m, rescale);
       // the group's block before this one has been through its P V: its accumulators may be scaled, and its P buffer
       // is free for the next block
-      if (u > 0 && !(ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&o_ready[g]), (u - 1) & 1, abort_flag, err)))) break;
+      if (u > 0 && !(ok = __all_sync(0xffffffffu, at_wait(smem_u32(&o_ready[g]), (u - 1) & 1, abort_flag, err)))) break;
       if (__any_sync(0xffffffffu, rescale != 1.f)) {   // rare after the first blocks
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
@@ -305,7 +367,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       l = fmaf(l, rescale, lsum);
       if (j == n_blk - 1 && n_keys < j * AT_KEYS + AT_KEYS) {
         // value rows past the tile's last position: every weight on them is zero; make them zero too
-        if (!(ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&v_full[j % AT_STAGES]), (uint32_t)(j / AT_STAGES) & 1u, abort_flag, err)))) break;
+        if (!(ok = __all_sync(0xffffffffu, at_wait(smem_u32(&v_full[j % AT_STAGES]), (uint32_t)(j / AT_STAGES) & 1u, abort_flag, err)))) break;
         const int first = n_keys - j * AT_KEYS;   // 1 .. 127
         for (int i = (sw & 7) * 32 + lane; i < (AT_KEYS - first) * 8; i += AT_GROUP_THREADS) {
           const int r = first + (i >> 3);
@@ -322,7 +384,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
     for (int i = 0; i < AT_HD; ++i) o[i] = 0.f;
     if (ok && u > 0) {
-      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&o_ready[g]), (u - 1) & 1, abort_flag, err));
+      ok = __all_sync(0xffffffffu, at_wait(smem_u32(&o_ready[g]), (u - 1) & 1, abort_flag, err));
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (ok) {
 #pragma unroll
