@@ -50,16 +50,17 @@ constexpr int AT_ROLE_WARPS = 4;        // K loads, V loads, Q K^T issue, P V is
 constexpr int AT_THREADS = AT_ROLE_WARPS * 32 + 2 * AT_GROUP_THREADS;
 constexpr int AT_Q_BYTES = AT_ROWS * AT_HD * 2;          // 16 KB
 constexpr int AT_KV_BYTES = AT_KEYS * AT_HD * 2;         // 16 KB: two pages
-constexpr int AT_STAGES = 2;                             // blocks of K and of V in shared memory
+constexpr int AT_STAGES = 2;                             // blocks of K in shared memory: a group's blocks use one of them
+constexpr int AT_V_STAGES = 3;                           // blocks of V (with two, V came late: a stage is free only when the
+                                                         // block two before has been through its P V, one and a half blocks later)
 constexpr int AT_P_BYTES = AT_ROWS * AT_KEYS * 2;        // 32 KB: two K-major tiles of 128 x 64, one per half
 constexpr int AT_P_BUFS = 2;                             // P buffers of a group
-constexpr int AT_N_BARS = 1 + 4 * AT_STAGES + 8;
-constexpr int AT_SMEM = AT_Q_BYTES + 2 * AT_STAGES * AT_KV_BYTES + 2 * AT_P_BUFS * AT_P_BYTES + 1024 + 512;
+constexpr int AT_N_BARS = 1 + 2 * AT_STAGES + 2 * AT_V_STAGES + 12;
+constexpr int AT_SMEM = AT_Q_BYTES + (AT_STAGES + AT_V_STAGES) * AT_KV_BYTES + 2 * AT_P_BUFS * AT_P_BYTES + 1024 + 512;
+static_assert(AT_SMEM <= 227 * 1024, "shared memory");
 constexpr uint32_t AT_TMEM_COLS = 512;   // S of group 0, of group 1 (128 each); O of (group, half) at 256 + (2 group + half) 64
-// the end's exchange lies over the V stages and the P buffers: (m, l) of the four threads of a row, then their O
-constexpr int AT_HAND_PITCH = AT_HD + 1;
-static_assert(4 * AT_ROWS * 2 * 4 + 4 * AT_ROWS * AT_HAND_PITCH * 4 <= AT_STAGES * AT_KV_BYTES + 2 * AT_P_BUFS * AT_P_BYTES,
-              "the exchange does not fit");
+constexpr int AT_TRACE_BLOCKS = 64;   // blocks of a group that a trace has room for
+static_assert(AT_STAGES == 2, "a group's blocks use one K stage (the end's exchange lies there)");
 
 __device__ __forceinline__ float at_exp2(float x) {
   float y;
@@ -130,6 +131,14 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
         "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
         "r"(r[30]), "r"(r[31])
       : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
 }
 
 constexpr float AT_LAZY = 8.f;   // the reference maximum follows the running maximum only when that has grown by more than 2^8
@@ -208,27 +217,37 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const int32_t* __restrict__ page_table, int table_stride, int n_pages,
                        const int32_t* __restrict__ seq_slot, const int32_t* __restrict__ tile_seq,
                        const int32_t* __restrict__ tile_tok0, const int32_t* __restrict__ tile_ntok,
-                       const int32_t* __restrict__ tile_pos0, int n_tiles, int nh, int nkv, float scale_log2, int* err) {
+                       const int32_t* __restrict__ tile_pos0, int n_tiles, int nh, int nkv, float scale_log2, int* err,
+                       long long* trace) {
   extern __shared__ uint8_t at_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(at_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* q_s = smem;
   uint8_t* k_s = q_s + AT_Q_BYTES;                // [AT_STAGES][16 KB]
-  uint8_t* v_s = k_s + AT_STAGES * AT_KV_BYTES;   // [AT_STAGES][16 KB]
-  uint8_t* p_s = v_s + AT_STAGES * AT_KV_BYTES;   // [2 groups][AT_P_BUFS][2 halves][128 rows][128 bytes]
+  uint8_t* v_s = k_s + AT_STAGES * AT_KV_BYTES;   // [AT_V_STAGES][16 KB]
+  uint8_t* p_s = v_s + AT_V_STAGES * AT_KV_BYTES;   // [2 groups][AT_P_BUFS][2 halves][128 rows][128 bytes]
   uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + 2 * AT_P_BUFS * AT_P_BYTES);
   uint64_t* q_full = bars;
   uint64_t* k_full = bars + 1;                      // [AT_STAGES]
-  uint64_t* v_full = k_full + AT_STAGES;            // [AT_STAGES]
-  uint64_t* k_empty = v_full + AT_STAGES;           // [AT_STAGES]
-  uint64_t* v_empty = k_empty + AT_STAGES;          // [AT_STAGES]
-  uint64_t* s_ready = v_empty + AT_STAGES;          // [2] the group's scores are in tensor memory
+  uint64_t* v_full = k_full + AT_STAGES;            // [AT_V_STAGES]
+  uint64_t* k_empty = v_full + AT_V_STAGES;         // [AT_STAGES]
+  uint64_t* v_empty = k_empty + AT_STAGES;          // [AT_V_STAGES]
+  uint64_t* s_ready = v_empty + AT_V_STAGES;         // [2] the group's scores are in tensor memory
   uint64_t* s_free = s_ready + 2;                   // [2] ... and in the group's registers: one arrival per warp
-  uint64_t* p_ready = s_free + 2;                   // [2] the group's P is in shared memory: one arrival per warp
-  uint64_t* o_ready = p_ready + 2;                  // [2] the group's P V is done
+  // The next two come in pairs, for a group's even and odd blocks, so that a waiter may fall a block behind.
+  uint64_t* p_ready = s_free + 2;                   // [2][2] the group's P is in shared memory: one arrival per warp
+  uint64_t* o_ready = p_ready + 4;                  // [2][2] the group's P V is done
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + AT_N_BARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // `trace` (may be null): clock stamps of the grid's first block.  [group][block][8] from one warp of each softmax
+  // group; after those, eight of the block as a whole (thread AT_ROLE_WARPS * 32: entry, tensor memory there, the
+  // kernel before this one done, the key blocks done, accumulator read, row stored, block done)
+  const bool tracing = trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
+  auto block_stamp = [&](int i) {
+    if (tracing && threadIdx.x == AT_ROLE_WARPS * 32) trace[2 * AT_TRACE_BLOCKS * 8 + i] = clock64();
+  };
+  block_stamp(0);
   const int tile = n_tiles - 1 - (int)blockIdx.x;   // late tiles (long rows of keys) first
   const int head = blockIdx.y, kvh = head / (nh / nkv);
   const int seq = tile_seq[tile], tok0 = tile_tok0[tile], ntok = tile_ntok[tile], pos0 = tile_pos0[tile];
@@ -252,7 +271,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
+  block_stamp(1);
+  pdl_launch_dependents();
+  pdl_wait();   // (launched as a programmatic dependent: up to here only the step's tables were read)
   const uint32_t tmem_o = tmem_base + 2 * AT_KEYS;   // O of (group g, half h) at + (2 g + h) * AT_HD
+  block_stamp(2);
 
   if (warp < 2) {
     // ---------------------------------------------------------------- TMA producers: warp 0 Q and K, warp 1 V
@@ -266,9 +289,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         mbar_expect_tx(smem_u32(q_full), AT_Q_BYTES);
         tma_load_2d(smem_u32(q_s), &map_q, smem_u32(q_full), head * AT_HD, tok0);
       }
+      const int n_stages = warp == 0 ? AT_STAGES : AT_V_STAGES;
       for (int j = 0; j < n_blk; ++j) {
-        const int s = j % AT_STAGES;
-        const uint32_t par = (uint32_t)(j / AT_STAGES) & 1u;
+        const int s = j % n_stages;
+        const uint32_t par = (uint32_t)(j / n_stages) & 1u;
         int p0 = pages[2 * j], p1 = 2 * j + 1 < n_pg ? pages[2 * j + 1] : p0;
         if (p0 < 0 || p0 >= n_pages || p1 < 0 || p1 >= n_pages) {
           atomicOr(err, ERR_PAGE_RANGE);
@@ -284,48 +308,57 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   } else if (warp == 2) {
     // ---------------------------------------------------------------- Q K^T issuer.  Block j belongs to softmax group
     // j & 1 and goes into that group's S as soon as the group has the scores of block j - 2 in its registers.
-    if (lane == 0) {
-      constexpr uint32_t idesc_qk = umma_idesc(AT_ROWS, AT_KEYS);
-      const uint64_t dq = umma_desc(smem_u32(q_s));
-      bool ok = at_wait(smem_u32(q_full), 0, abort_flag, err);
-      for (int j = 0; j < n_blk && ok; ++j) {
-        const int g = j & 1, st = j % AT_STAGES;
-        if (j >= 2 && !(ok = at_wait(smem_u32(&s_free[g]), (uint32_t)((j >> 1) - 1) & 1u, abort_flag, err))) break;
-        if (!(ok = at_wait(smem_u32(&k_full[st]), (uint32_t)(j / AT_STAGES) & 1u, abort_flag, err))) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint64_t dk = umma_desc(smem_u32(k_s + st * AT_KV_BYTES));
+    // The whole warp walks the loop and waits; one elected lane issues.  (With the loop inside `if (lane == 0)` the
+    // descriptors are computed in a divergent region, out of reach of the uniform datapath that the instruction
+    // takes them from, and an issue took some 120 clocks.)
+    constexpr uint32_t idesc_qk = umma_idesc(AT_ROWS, AT_KEYS);
+    const uint64_t dq = umma_desc(smem_u32(q_s));
+    bool ok = __all_sync(0xffffffffu, at_wait(smem_u32(q_full), 0, abort_flag, err));
+    for (int j = 0; j < n_blk && ok; ++j) {
+      const int g = j & 1, st = j % AT_STAGES;
+      if (j >= 2 && !(ok = __all_sync(0xffffffffu, at_wait(smem_u32(&s_free[g]), (uint32_t)((j >> 1) - 1) & 1u, abort_flag, err)))) break;
+      if (!(ok = __all_sync(0xffffffffu, at_wait(smem_u32(&k_full[st]), (uint32_t)(j / AT_STAGES) & 1u, abort_flag, err)))) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint64_t dk = umma_desc(smem_u32(k_s + st * AT_KV_BYTES));
+      const uint32_t d_s = tmem_base + (uint32_t)g * AT_KEYS, bar_s = smem_u32(&s_ready[g]), bar_k = smem_u32(&k_empty[st]);
+      if (elect_one()) {
 #pragma unroll
-        for (int k = 0; k < AT_HD / 16; ++k) umma_f16(tmem_base + (uint32_t)g * AT_KEYS, dq + 2 * k, dk + 2 * k, idesc_qk, k != 0);
-        umma_commit(smem_u32(&s_ready[g]));
-        umma_commit(smem_u32(&k_empty[st]));
+        for (int k = 0; k < AT_HD / 16; ++k) umma_f16(d_s, dq + 2 * k, dk + 2 * k, idesc_qk, k != 0);
+        umma_commit(bar_s);
+        umma_commit(bar_k);
       }
+      __syncwarp();
     }
   } else if (warp == 3) {
     // ---------------------------------------------------------------- P V issuer: a block's two halves (64 keys each)
     // into the two accumulators of its group, which add up over the group's blocks.
-    if (lane == 0) {
-      constexpr uint32_t idesc_pv = umma_idesc(AT_ROWS, AT_HD) | (1u << 16);   // B (the values) is MN-major
-      bool ok = true;
-      for (int j = 0; j < n_blk && ok; ++j) {
-        const int g = j & 1, u = j >> 1, st = j % AT_STAGES;
-        if (!(ok = at_wait(smem_u32(&p_ready[g]), (uint32_t)u & 1u, abort_flag, err))) break;
-        if (!(ok = at_wait(smem_u32(&v_full[st]), (uint32_t)(j / AT_STAGES) & 1u, abort_flag, err))) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint64_t dv = umma_desc(smem_u32(v_s + st * AT_KV_BYTES));
-        const uint8_t* p_buf = p_s + (g * AT_P_BUFS + (u % AT_P_BUFS)) * AT_P_BYTES;
+    constexpr uint32_t idesc_pv = umma_idesc(AT_ROWS, AT_HD) | (1u << 16);   // B (the values) is MN-major
+    bool ok = true;
+    for (int j = 0; j < n_blk && ok; ++j) {
+      const int g = j & 1, u = j >> 1, st = j % AT_V_STAGES;
+      if (!(ok = __all_sync(0xffffffffu, at_wait(smem_u32(&p_ready[2 * g + (u & 1)]), (uint32_t)(u >> 1) & 1u, abort_flag, err)))) break;
+      if (!(ok = __all_sync(0xffffffffu, at_wait(smem_u32(&v_full[st]), (uint32_t)(j / AT_V_STAGES) & 1u, abort_flag, err)))) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (tracing && lane == 0 && u < AT_TRACE_BLOCKS) trace[(g * AT_TRACE_BLOCKS + u) * 8 + 6] = clock64();   // (the issuer's view: P and V seen,
+      const uint64_t dv = umma_desc(smem_u32(v_s + st * AT_KV_BYTES));
+      const uint64_t dp = umma_desc(smem_u32(p_s + (g * AT_P_BUFS + (u % AT_P_BUFS)) * AT_P_BYTES));
+      const uint32_t d_o = tmem_o + (uint32_t)(2 * g) * AT_HD, bar_o = smem_u32(&o_ready[2 * g + (u & 1)]), bar_v = smem_u32(&v_empty[st]);
+      const uint32_t acc = u > 0;
+      if (elect_one()) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          const uint64_t dp = umma_desc(smem_u32(p_buf + h * (AT_P_BYTES / 2)));
 #pragma unroll
           for (int k = 0; k < AT_HALF / 16; ++k) {
-            // V: 16 keys further = 16 rows of 128 bytes further
-            umma_f16(tmem_o + (uint32_t)(2 * g + h) * AT_HD, dp + 2 * k, dv + (uint64_t)((h * AT_HALF + k * 16) * 128 >> 4), idesc_pv,
-                     (k != 0) || (u > 0));
+            // P: the half's tile, 16 keys = 32 bytes further a step; V: 16 keys = 16 rows of 128 bytes further
+            umma_f16(d_o + (uint32_t)h * AT_HD, dp + (uint64_t)(h * (AT_P_BYTES / 2) >> 4) + 2 * k,
+                     dv + (uint64_t)((h * AT_HALF + k * 16) * 128 >> 4), idesc_pv, k != 0 ? 1u : acc);
           }
         }
-        umma_commit(smem_u32(&o_ready[g]));
-        umma_commit(smem_u32(&v_empty[st]));
+        umma_commit(bar_o);
+        umma_commit(bar_v);
       }
+      __syncwarp();
+      if (tracing && lane == 0 && u < AT_TRACE_BLOCKS) trace[(g * AT_TRACE_BLOCKS + u) * 8 + 7] = clock64();   //  product issued)
     }
   } else {
     // ---------------------------------------------------------------- softmax: two groups of eight warps.  The
@@ -337,20 +370,30 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t s_addr = tmem_base + lane_off + (uint32_t)g * AT_KEYS + (uint32_t)half * AT_HALF;
     const uint32_t o_addr = tmem_o + lane_off + (uint32_t)(2 * g + half) * AT_HD;
     float m = -CUDART_INF_F, l = 0.f;   // the half row's reference maximum (log2 units) and denominator
+    const bool stamps = tracing && lane == 0 && (sw & 7) == 0;
+    auto stamp = [&](int u, int i) {
+      if (stamps && u < AT_TRACE_BLOCKS) trace[(g * AT_TRACE_BLOCKS + u) * 8 + i] = clock64();
+    };
     bool ok = true;
     int u = 0;   // blocks this group has done
     for (int j = g; j < n_blk; j += 2, ++u) {
       const int key0 = j * AT_KEYS + half * AT_HALF;
-      uint8_t* p_tile = p_s + (g * AT_P_BUFS + (u % AT_P_BUFS)) * AT_P_BYTES + half * (AT_P_BYTES / 2);   // (its last reader, the P V
-      if (!(ok = __all_sync(0xffffffffu, at_wait(smem_u32(&s_ready[g]), u & 1, abort_flag, err)))) break;   //  of block u - 2, was waited for in block u - 1)
+      uint8_t* p_tile = p_s + (g * AT_P_BUFS + (u % AT_P_BUFS)) * AT_P_BYTES + half * (AT_P_BYTES / 2);
+      stamp(u, 0);
+      if (!(ok = __all_sync(0xffffffffu, at_wait(smem_u32(&s_ready[g]), u & 1, abort_flag, err)))) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      stamp(u, 1);
       float rescale;
       const float lsum = j * AT_KEYS + AT_KEYS - 1 > pos0
                              ? at_softmax_block<true>(s_addr, smem_u32(&s_free[g]), p_tile, row, key0, pos, scale_log2, u == 0, m, rescale)
                              : at_softmax_block<false>(s_addr, smem_u32(&s_free[g]), p_tile, row, key0, pos, scale_log2, u == 0, m, rescale);
-      // the group's block before this one has been through its P V: its accumulators may be scaled, and its P buffer
-      // is free for the next block
-      if (u > 0 && !(ok = __all_sync(0xffffffffu, at_wait(smem_u32(&o_ready[g]), (u - 1) & 1, abort_flag, err)))) break;
+      stamp(u, 2);
+      // The group's block before this one has been through its P V: its accumulators may be scaled, and the P buffer
+      // it read is free for the block after this one.  (The P V of the block before last would do for the buffer,
+      // and the scaling is rare; but without this wait the two groups fall into step, are at their exponentials
+      // together and leave the special-function units idle together: measured a quarter slower.)
+      if (u > 0 && !(ok = __all_sync(0xffffffffu, at_wait(smem_u32(&o_ready[2 * g + ((u - 1) & 1)]), (uint32_t)((u - 1) >> 1) & 1u, abort_flag, err)))) break;
+      stamp(u, 3);
       if (__any_sync(0xffffffffu, rescale != 1.f)) {   // rare after the first blocks
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
@@ -364,79 +407,82 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       }
+      stamp(u, 4);
       l = fmaf(l, rescale, lsum);
       if (j == n_blk - 1 && n_keys < j * AT_KEYS + AT_KEYS) {
         // value rows past the tile's last position: every weight on them is zero; make them zero too
-        if (!(ok = __all_sync(0xffffffffu, at_wait(smem_u32(&v_full[j % AT_STAGES]), (uint32_t)(j / AT_STAGES) & 1u, abort_flag, err)))) break;
+        if (!(ok = __all_sync(0xffffffffu, at_wait(smem_u32(&v_full[j % AT_V_STAGES]), (uint32_t)(j / AT_V_STAGES) & 1u, abort_flag, err)))) break;
         const int first = n_keys - j * AT_KEYS;   // 1 .. 127
         for (int i = (sw & 7) * 32 + lane; i < (AT_KEYS - first) * 8; i += AT_GROUP_THREADS) {
           const int r = first + (i >> 3);
-          *reinterpret_cast<uint4*>(v_s + (j % AT_STAGES) * AT_KV_BYTES + r * 128 + ((i & 7) << 4)) = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(v_s + (j % AT_V_STAGES) * AT_KV_BYTES + r * 128 + ((i & 7) << 4)) = make_uint4(0, 0, 0, 0);
         }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&p_ready[g])) : "memory");
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&p_ready[2 * g + (u & 1)])) : "memory");
+      stamp(u, 5);
     }
-    // ---- the thread's accumulator out of tensor memory: the 64 dims of its half row
-    float o[AT_HD];
+    block_stamp(3);
+    // ---- a row's four threads (two groups, two halves) put their results together.  All four reach the same lanes
+    // of tensor memory, so each reads its 16 dims of the row from all four accumulators; only (m, l) go through
+    // shared memory (over this group's K stage: its last Q K^T is long done).
+    if (ok && u > 0)
+      ok = __all_sync(0xffffffffu, at_wait(smem_u32(&o_ready[2 * g + ((u - 1) & 1)]), (uint32_t)((u - 1) >> 1) & 1u, abort_flag, err));
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    const int q = g * 2 + half;
+    float* hand_ml = reinterpret_cast<float*>(k_s + g * AT_KV_BYTES);   // [half][row][2]
+    hand_ml[(half * AT_ROWS + row) * 2] = m;
+    hand_ml[(half * AT_ROWS + row) * 2 + 1] = l;
+    block_stamp(4);
+    asm volatile("bar.sync 1, %0;" ::"n"(2 * AT_GROUP_THREADS) : "memory");   // both groups' last P V are done
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok && !*abort_flag) {
+      float f[4], mm = -CUDART_INF_F, den = 0.f;
 #pragma unroll
-    for (int i = 0; i < AT_HD; ++i) o[i] = 0.f;
-    if (ok && u > 0) {
-      ok = __all_sync(0xffffffffu, at_wait(smem_u32(&o_ready[g]), (u - 1) & 1, abort_flag, err));
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (ok) {
+      for (int t = 0; t < 4; ++t) {
+        const float* ml = reinterpret_cast<const float*>(k_s + (t >> 1) * AT_KV_BYTES) + ((t & 1) * AT_ROWS + row) * 2;
+        mm = fmaxf(mm, f[t] = ml[0]);
+      }
 #pragma unroll
-        for (int c = 0; c < AT_HD / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld32(o_addr + c * 32, r);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      for (int t = 0; t < 4; ++t) {
+        const float* ml = reinterpret_cast<const float*>(k_s + (t >> 1) * AT_KV_BYTES) + ((t & 1) * AT_ROWS + row) * 2;
+        f[t] = f[t] == -CUDART_INF_F ? 0.f : at_exp2(f[t] - mm);   // (a thread may have seen no key; the row has seen key 0)
+        den = fmaf(ml[1], f[t], den);
+      }
+      uint32_t r[4][16];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[c * 32 + i] = __uint_as_float(r[i]);
+      for (int t = 0; t < 4; ++t) {
+        if (t < 2 || n_blk > 1) {   // (with one block, group 1's accumulators were never written)
+          tmem_ld16(tmem_o + lane_off + (uint32_t)(t * AT_HD + q * 16), r[t]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) r[t][i] = 0u;
         }
       }
-    }
-    // ---- a row's four threads (two groups, two halves) put their results together through shared memory (all
-    // products are done and every loaded block has been used: both groups have waited for their last P V): each
-    // hands over its (m, l) and its 64 dims, then merges and stores 16 dims of the row
-    const int q = g * 2 + half;
-    float* hand_ml = reinterpret_cast<float*>(v_s);                  // [4][row][2]
-    float* hand_o = hand_ml + 4 * AT_ROWS * 2;                       // [4][row][AT_HAND_PITCH]
-    asm volatile("bar.sync 1, %0;" ::"n"(2 * AT_GROUP_THREADS) : "memory");   // nobody's tiles are read any more
-    hand_ml[(q * AT_ROWS + row) * 2] = m;
-    hand_ml[(q * AT_ROWS + row) * 2 + 1] = l;
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      if (row < ntok) {
+        const float inv = 1.0f / den;
+        float v[16];
 #pragma unroll
-    for (int i = 0; i < AT_HD; ++i) hand_o[(q * AT_ROWS + row) * AT_HAND_PITCH + i] = o[i];
-    asm volatile("bar.sync 1, %0;" ::"n"(2 * AT_GROUP_THREADS) : "memory");
-    if (ok && row < ntok) {
-      float mq[4], mm = -CUDART_INF_F, den = 0.f;
+        for (int i = 0; i < 16; ++i) {
+          v[i] = __uint_as_float(r[0][i]) * f[0];
 #pragma unroll
-      for (int t = 0; t < 4; ++t) mm = fmaxf(mm, mq[t] = hand_ml[(t * AT_ROWS + row) * 2]);
+          for (int t = 1; t < 4; ++t) v[i] = fmaf(__uint_as_float(r[t][i]), f[t], v[i]);
+          v[i] *= inv;
+        }
+        __nv_bfloat16* dst = out + (size_t)(tok0 + row) * ldo + head * AT_HD + q * 16;
 #pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        mq[t] = mq[t] == -CUDART_INF_F ? 0.f : at_exp2(mq[t] - mm);   // (a thread may have seen no key; the row has seen key 0)
-        den = fmaf(hand_ml[(t * AT_ROWS + row) * 2 + 1], mq[t], den);
+        for (int i = 0; i < 16; i += 8)
+          *reinterpret_cast<uint4*>(dst + i) = make_uint4(at_pack(v[i], v[i + 1]), at_pack(v[i + 2], v[i + 3]), at_pack(v[i + 4], v[i + 5]), at_pack(v[i + 6], v[i + 7]));
       }
-      const float inv = 1.0f / den;
-      float v[16];
-#pragma unroll
-      for (int i = 0; i < 16; ++i) v[i] = 0.f;
-#pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        const float* src = hand_o + (t * AT_ROWS + row) * AT_HAND_PITCH + q * 16;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) v[i] = fmaf(src[i], mq[t], v[i]);
-      }
-      __nv_bfloat16* dst = out + (size_t)(tok0 + row) * ldo + head * AT_HD + q * 16;
-#pragma unroll
-      for (int i = 0; i < 16; i += 8)
-        *reinterpret_cast<uint4*>(dst + i) = make_uint4(at_pack(v[i] * inv, v[i + 1] * inv), at_pack(v[i + 2] * inv, v[i + 3] * inv),
-                                                        at_pack(v[i + 4] * inv, v[i + 5] * inv), at_pack(v[i + 6] * inv, v[i + 7] * inv));
     }
   }
+  block_stamp(5);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  block_stamp(6);
   if (warp == 2) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(AT_TMEM_COLS) : "memory");
@@ -446,6 +492,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 }  // namespace edgelm
 
 using namespace edgelm;
+
+static long long* g_at_trace = nullptr;
+// A device buffer of 2 x 64 x 8 + 8 clock stamps that the next launches fill (one softmax warp of each group of the
+// grid's first block: before and after the wait for the scores, after the exponentials, after the wait for the
+// last P V, after a rescaling, after the arrival; then eight of the block as a whole), or null to stop.
+extern "C" void edgelm_attn_prefill_tc_trace(void* buffer) { g_at_trace = (long long*)buffer; }
 
 // 1 if the tcgen05 prefill attention takes this head size (bfloat16 is implied), else 0.
 extern "C" int edgelm_attn_prefill_tc_takes(int hd) { return hd == AT_HD ? 1 : 0; }
@@ -475,9 +527,9 @@ extern "C" int edgelm_attn_prefill_tc(const void* qkv, int ldq, int n_tokens, vo
     configured = true;
   }
   const float scale_log2 = scale * 1.4426950408889634f;
-  attn_prefill_tc_kernel<<<dim3(n_tiles, nh), AT_THREADS, AT_SMEM, stream>>>(
+  launch_pdl(16, attn_prefill_tc_kernel, dim3(n_tiles, nh), dim3(AT_THREADS), (size_t)AT_SMEM, stream,
       mq, mk, mv, (__nv_bfloat16*)out, ldo, page_table, table_stride, n_pages, seq_slot, tile_seq, tile_tok0, tile_ntok,
-      tile_pos0, n_tiles, nh, nkv, scale_log2, err);
+      tile_pos0, n_tiles, nh, nkv, scale_log2, err, g_at_trace);
   EL_LAUNCH_CHECK("attn_prefill_tc");
   return 0;
 }

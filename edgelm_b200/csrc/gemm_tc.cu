@@ -160,40 +160,50 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
 
+  // The two role warps walk their loops whole and wait as warps; one elected lane of each issues.  (With the loop
+  // inside `if (lane == 0)` the descriptors and coordinates are computed in a divergent region, out of reach of the
+  // uniform datapath that the instructions take them from: an MMA then took some 120 clocks to issue, twice what a
+  // 128 x 128 x 16 one runs.)
   if (warp == 0) {
-    if (lane == 0) {
-      for (int i = 0; i < n_k; ++i) {
-        const int s = i % STAGES;
-        if (!mbar_wait(smem_u32(&empty_bar[s]), ((i / STAGES) & 1) ^ 1, abort_flag, err)) break;
-        const uint32_t bar = smem_u32(&full_bar[s]);
+    const bool leader = elect_one();
+    for (int i = 0; i < n_k; ++i) {
+      const int s = i % STAGES;
+      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&empty_bar[s]), ((i / STAGES) & 1) ^ 1, abort_flag, err))) break;
+      const uint32_t bar = smem_u32(&full_bar[s]);
+      const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+      const int x = (k_first + i) * TC_BK;
+      if (leader) {
         mbar_expect_tx(bar, STAGE_BYTES);
-        const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
-        tma_load_2d(sa, &map_a, bar, (k_first + i) * TC_BK, m0);
-        tma_load_2d(sa + A_BYTES, &map_b, bar, (k_first + i) * TC_BK, n0);
-        if (NB == 2) tma_load_2d(sa + A_BYTES + B_BYTES, &map_b2, bar, (k_first + i) * TC_BK, n0);
+        tma_load_2d(sa, &map_a, bar, x, m0);
+        tma_load_2d(sa + A_BYTES, &map_b, bar, x, n0);
+        if (NB == 2) tma_load_2d(sa + A_BYTES + B_BYTES, &map_b2, bar, x, n0);
       }
+      __syncwarp();
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc(TC_BM, BN);
-      bool ok = true;
-      for (int i = 0; i < n_k && ok; ++i) {
-        const int s = i % STAGES;
-        ok = mbar_wait(smem_u32(&full_bar[s]), (i / STAGES) & 1, abort_flag, err);
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
-        const uint64_t da = umma_desc(sa), db = umma_desc(sa + A_BYTES), db2 = umma_desc(sa + A_BYTES + B_BYTES);
+    constexpr uint32_t idesc = umma_idesc(TC_BM, BN);
+    const bool leader = elect_one();
+    bool ok = true;
+    for (int i = 0; i < n_k && ok; ++i) {
+      const int s = i % STAGES;
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&full_bar[s]), (i / STAGES) & 1, abort_flag, err));
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+      const uint64_t da = umma_desc(sa), db = umma_desc(sa + A_BYTES), db2 = umma_desc(sa + A_BYTES + B_BYTES);
+      const uint32_t bar_e = smem_u32(&empty_bar[s]);
+      if (leader) {
 #pragma unroll
         for (int k = 0; k < TC_BK / 16; ++k) {  // 16 bfloat16 = 32 bytes = 2 descriptor address units per step
           const uint32_t acc = (i | k) != 0;
           umma_f16(tmem_base, da + 2 * k, db + 2 * k, idesc, acc);
           if (NB == 2) umma_f16(tmem_base + BN, da + 2 * k, db2 + 2 * k, idesc, acc);
         }
-        umma_commit(smem_u32(&empty_bar[s]));  // arrives when these MMAs have read the stage
+        umma_commit(bar_e);  // arrives when these MMAs have read the stage
       }
-      if (ok) umma_commit(smem_u32(tmem_full_bar));
+      __syncwarp();
     }
+    if (ok && leader) umma_commit(smem_u32(tmem_full_bar));
   } else {
     const int q = warp & 3;  // a warp reads the 32 lanes of tensor memory that its index modulo 4 selects
     ResidualAhead ra[2];
@@ -322,53 +332,59 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
 
+  // (the role warps walk their loops whole, one elected lane issues: see the one-tile kernel)
   if (warp == 0) {
-    if (lane == 0) {
-      int it = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * BN;
-        for (int i = 0; i < n_k; ++i, ++it) {
-          const int s = it % TCP_STAGES;
-          ok = mbar_wait(smem_u32(&empty_bar[s]), ((it / TCP_STAGES) & 1) ^ 1, abort_flag, err);
-          if (!ok) break;
-          const uint32_t bar = smem_u32(&full_bar[s]);
+    const bool leader = elect_one();
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * BN;
+      for (int i = 0; i < n_k; ++i, ++it) {
+        const int s = it % TCP_STAGES;
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&empty_bar[s]), ((it / TCP_STAGES) & 1) ^ 1, abort_flag, err));
+        if (!ok) break;
+        const uint32_t bar = smem_u32(&full_bar[s]);
+        const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+        if (leader) {
           mbar_expect_tx(bar, STAGE_BYTES);
-          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
           tma_load_2d(sa, &map_a, bar, i * TC_BK, m0);
           tma_load_2d(sa + A_BYTES, &map_b, bar, i * TC_BK, n0);
           if (NB == 2) tma_load_2d(sa + A_BYTES + B_BYTES, &map_b2, bar, i * TC_BK, n0);
         }
+        __syncwarp();
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc(TC_BM, BN);
-      int it = 0, ti = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++ti) {
-        const int as = ti & 1;
-        ok = mbar_wait(smem_u32(&tmem_empty_bar[as]), ((ti >> 1) & 1) ^ 1, abort_flag, err);  // the epilogue has drained this stage
+    constexpr uint32_t idesc = umma_idesc(TC_BM, BN);
+    const bool leader = elect_one();
+    int it = 0, ti = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++ti) {
+      const int as = ti & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&tmem_empty_bar[as]), ((ti >> 1) & 1) ^ 1, abort_flag, err));  // the epilogue has drained this stage
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t acc_addr = tmem_base + (uint32_t)as * ACC_COLS;
+      for (int i = 0; i < n_k; ++i, ++it) {
+        const int s = it % TCP_STAGES;
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&full_bar[s]), (it / TCP_STAGES) & 1, abort_flag, err));
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t acc_addr = tmem_base + (uint32_t)as * ACC_COLS;
-        for (int i = 0; i < n_k; ++i, ++it) {
-          const int s = it % TCP_STAGES;
-          ok = mbar_wait(smem_u32(&full_bar[s]), (it / TCP_STAGES) & 1, abort_flag, err);
-          if (!ok) break;
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
-          const uint64_t da = umma_desc(sa), db = umma_desc(sa + A_BYTES), db2 = umma_desc(sa + A_BYTES + B_BYTES);
+        const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+        const uint64_t da = umma_desc(sa), db = umma_desc(sa + A_BYTES), db2 = umma_desc(sa + A_BYTES + B_BYTES);
+        const uint32_t bar_e = smem_u32(&empty_bar[s]);
+        if (leader) {
 #pragma unroll
           for (int k = 0; k < TC_BK / 16; ++k) {
             const uint32_t acc = (i | k) != 0;
             umma_f16(acc_addr, da + 2 * k, db + 2 * k, idesc, acc);
             if (NB == 2) umma_f16(acc_addr + BN, da + 2 * k, db2 + 2 * k, idesc, acc);
           }
-          umma_commit(smem_u32(&empty_bar[s]));
+          umma_commit(bar_e);
         }
-        if (ok) umma_commit(smem_u32(&tmem_full_bar[as]));
+        __syncwarp();
       }
+      if (ok && leader) umma_commit(smem_u32(&tmem_full_bar[as]));
     }
   } else {
     const int q = warp & 3;

@@ -309,6 +309,20 @@ def attn_prefill_tc(qkv, out, kcache, vcache, page_table, seq_slot, tile_seq, ti
                                         _p(err), _stream()))
 
 
+ATTN_PREFILL_TC_TRACE_SHAPE = (2 * 64 + 1, 8)
+
+
+def attn_prefill_tc_trace(buffer):
+    """The next launches of the tcgen05 prefill attention stamp the clock of one softmax warp per group of the
+    grid's first block into `buffer` (int64, ATTN_PREFILL_TC_TRACE_SHAPE: [group * 64 + block][before / after the
+    wait for the scores, after the exponentials, after the wait for the last P V, after a rescaling, after the
+    arrival], and a last row for the block as a whole: entry, tensor memory there, the kernel before done, key
+    blocks done, accumulator read, row stored, block done); None stops it."""
+    if buffer is not None:
+        _need(buffer.dtype == torch.int64 and buffer.is_contiguous() and tuple(buffer.shape) == ATTN_PREFILL_TC_TRACE_SHAPE, "attn_prefill_tc_trace: buffer")
+    lib().edgelm_attn_prefill_tc_trace(_p(buffer))
+
+
 def attn_decode(qkv, out, kcache, vcache, page_table, seq_slot, seq_pos, n_seqs, nh, nkv, hd, scale, n_splits=1,
                 part_o=None, part_ml=None):
     """Attention of one new token per sequence over the paged cache, pages dealt to `n_splits` blocks."""

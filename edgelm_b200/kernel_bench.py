@@ -35,6 +35,7 @@ def main(argv=None):
     ap.add_argument("--only", default=None, help="run only the kernels whose name contains this")
     ap.add_argument("--splits", type=int, default=0, help="decode: blocks per (sequence, kv head) of the attention")
     ap.add_argument("--no-fuse-norm", action="store_true", help="decode: the projections read a normalised input instead of computing the norm")
+    ap.add_argument("--trace", action="store_true", help="prefill: clock stamps inside the tcgen05 attention kernel")
     ap.add_argument("--plain", action="store_true", help="eager launches, no graph and no timing (for profilers)")
     args = ap.parse_args(argv)
 
@@ -124,6 +125,31 @@ def main(argv=None):
         }
         if not o.attn_prefill_tc_takes(bf, hd):
             del cases["attn_prefill_tc"]
+        elif args.trace:
+            # one launch with clock stamps of a softmax warp per group, in the block with the most keys
+            stamps = torch.zeros(o.ATTN_PREFILL_TC_TRACE_SHAPE, dtype=torch.int64, device=d)
+            cases["attn_prefill_tc"](0)
+            o.attn_prefill_tc_trace(stamps)
+            cases["attn_prefill_tc"](0)
+            o.attn_prefill_tc_trace(None)
+            torch.cuda.synchronize()
+            whole = stamps[-1].cpu()
+            st = stamps[:-1].view(2, 64, 8).cpu()
+            print("block: " + ", ".join(f"{nm} {(whole[i + 1] - whole[i]).item()}" for i, nm in enumerate(
+                ["prologue", "wait for the kernel before", "key blocks", "accumulator", "merge and store", "last barrier"])))
+            names = ["wait S", "scores to P", "wait P V", "(gap)", "rescale", "arrive"]
+            for grp in range(2):
+                n = int((st[grp, :, 0] > 0).sum())
+                if n < 4:
+                    continue
+                body = st[grp, 2:n]   # steady state: without the first blocks
+                per = (body[-1, 0] - body[0, 0]).item() / max(1, len(body) - 1)
+                parts = [(body[:, i + 1] - body[:, i]).float().mean().item() for i in range(5)]
+                print(f"group {grp}: {n} blocks, {per:.0f} clocks a block: " + ", ".join(f"{nm} {v:.0f}" for nm, v in zip(names, parts)))
+                print(f"         issuer: P seen {(body[:, 6] - body[:, 5]).float().mean().item():.0f} clocks after the arrival, product issued {(body[:, 7] - body[:, 6]).float().mean().item():.0f} later;"
+                      f" last block: arrival {(st[grp, n - 1, 5] - st[0, 0, 0]).item()}, seen {(st[grp, n - 1, 6] - st[0, 0, 0]).item()}, issued {(st[grp, n - 1, 7] - st[0, 0, 0]).item()}")
+                print(f"         first stamp to last {(st[grp, n - 1, 5] - st[grp, 0, 0]).item()} clocks; starts of the blocks: "
+                      + " ".join(str((st[grp, i, 0] - st[0, 0, 0]).item()) for i in range(min(n, 10))))
         print(f"prefill: {args.preset}, {T} tokens, {L} layers of weights")
     for name, fn in cases.items():
         if args.only and args.only not in name:
