@@ -15,17 +15,24 @@
 //                        maximum has outgrown it by 2^8; then its thread scales its row of its O in place
 //                        (tcgen05.ld, multiply, tcgen05.st)
 //
-// Roles: warp 0 loads Q and the keys by TMA, warp 1 the values (each block as two pages, two stages; one
-// warp for both would hold the keys of the block after next behind a wait for a free value stage);
-// warp 2 allocates tensor memory and issues the Q K^T products, warp 3 the P V products (two issuers,
-// because which comes next depends on how the groups drift); warps 4-11 and 12-19 are two softmax
-// groups.  The groups take the key blocks in turn (even, odd), each with an S of its own, two P buffers
-// and its own accumulators.  In a group two threads share a row, 64 keys each, and share nothing else:
-// each has its own reference maximum, denominator and O (so no exchange between them in the loop, and a
-// row's 128 scores need no more registers than a thread has).  A thread frees its S as soon as the scores
-// are in its registers: the group's next Q K^T runs while it computes exponentials; with two P buffers
-// the next block's P can be written while the tensor cores still read this one's.  The four partial
-// results of a row (two groups, two halves) are put together through shared memory at the end.
+// Roles: warp 0 loads Q and the keys by TMA (two stages), warp 1 the values (three; each block as two
+// pages; one warp for both would hold the keys of the block after next behind a wait for a free value
+// stage); warp 2 allocates tensor memory and issues the Q K^T products, warp 3 the P V products (two
+// issuers, because which comes next depends on how the groups drift); warps 4-11 and 12-19 are two
+// softmax groups.  The groups take the key blocks in turn (even, odd), each with an S of its own, two P
+// buffers and its own accumulators.  In a group two threads share a row, 64 keys each, and share nothing
+// else: each has its own reference maximum, denominator and O (so no exchange between them in the loop,
+// and a row's 128 scores need no more registers than a thread has).  A thread frees its S as soon as the
+// scores are in its registers: the group's next Q K^T runs while it computes exponentials; with two P
+// buffers the next block's P can be written while the tensor cores still read this one's.  The four
+// partial results of a row (two groups, two halves) are put together at the end: all four threads reach
+// the same lanes of tensor memory, so each reads its 16 dims of the row from all four accumulators.
+// What limits the kernel is the special-function unit (an exp2 per score, 16 a clock per SM: 1,024
+// clocks a block); the second group starts half a block behind the first so that one group is at its
+// exponentials while the other waits, loads and stores.  (Tried and slower: turns at the exponentials,
+// strictly one group at a time, 3,050 clocks for a pair of blocks against 2,650; one group of 16 warps,
+// four threads a row, each holding the scores of two blocks in registers, 4,200: a block's waits and
+// fences then stand against 32 exponentials a thread instead of 64.)
 // All 512 columns of tensor memory (S, S, and four O of 64).
 // Every wait is bounded as in the matrix-product kernels: a wait that runs out sets ERR_WAIT_TIMEOUT,
 // raises the block's abort flag, and all roles leave; tensor memory is freed in any case.
@@ -59,6 +66,7 @@ constexpr int AT_N_BARS = 1 + 2 * AT_STAGES + 2 * AT_V_STAGES + 12;
 constexpr int AT_SMEM = AT_Q_BYTES + (AT_STAGES + AT_V_STAGES) * AT_KV_BYTES + 2 * AT_P_BUFS * AT_P_BYTES + 1024 + 512;
 static_assert(AT_SMEM <= 227 * 1024, "shared memory");
 constexpr uint32_t AT_TMEM_COLS = 512;   // S of group 0, of group 1 (128 each); O of (group, half) at 256 + (2 group + half) 64
+constexpr int AT_STAGGER_CLOCKS = 1300;   // half of what a group takes for a block
 constexpr int AT_TRACE_BLOCKS = 64;   // blocks of a group that a trace has room for
 static_assert(AT_STAGES == 2, "a group's blocks use one K stage (the end's exchange lies there)");
 
@@ -318,6 +326,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const int g = j & 1, st = j % AT_STAGES;
       if (j >= 2 && !(ok = __all_sync(0xffffffffu, at_wait(smem_u32(&s_free[g]), (uint32_t)((j >> 1) - 1) & 1u, abort_flag, err)))) break;
       if (!(ok = __all_sync(0xffffffffu, at_wait(smem_u32(&k_full[st]), (uint32_t)(j / AT_STAGES) & 1u, abort_flag, err)))) break;
+      if (j == 1 && n_blk >= 4) {
+        // The second group starts half a block's time behind the first.  Nothing else sets the groups' offset, and it
+        // stays where it starts: in step, both groups are at their exponentials together and leave the special-function
+        // units idle together afterwards (3,100 to 3,400 clocks for a pair of blocks against 2,650 half a block apart).
+        const long long t0 = clock64();
+        while (clock64() - t0 < AT_STAGGER_CLOCKS) {}
+      }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint64_t dk = umma_desc(smem_u32(k_s + st * AT_KV_BYTES));
       const uint32_t d_s = tmem_base + (uint32_t)g * AT_KEYS, bar_s = smem_u32(&s_ready[g]), bar_k = smem_u32(&k_empty[st]);
