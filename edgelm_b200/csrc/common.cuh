@@ -82,8 +82,8 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // Bit mask of the kernel families launched as programmatic dependent launches (1: few-rows matrix
-// products, 2: decode attention, 4: unused, 8: one-tile tcgen05 matrix products, 16: tcgen05 prefill attention); 0: ordinary
-// launches everywhere.
+// products, 2: decode attention, 4: unused, 8: one-tile tcgen05 matrix products, 16: tcgen05 prefill attention, 32: RMSNorm,
+// the vectorised rotation and cache append, the persistent tcgen05 matrix products); 0: ordinary launches everywhere.
 int pdl_enabled();
 
 template <typename... KArgs, typename... Args>

@@ -2,6 +2,7 @@
 //
 // The residual stream is float32 in both precisions; `T` below is the storage type of
 // weights, of normalised activations and of the cache (float or bfloat16).
+#include "attention_tile_mma.cuh"
 #include "common.cuh"
 
 namespace edgelm {
@@ -46,6 +47,8 @@ template <typename TOut, bool VEC>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, TOut* __restrict__ y,
                                const int32_t* __restrict__ rows_idx, int dim, float eps) {
   __shared__ float red[33];
+  pdl_launch_dependents();
+  pdl_wait();   // (launched as a programmatic dependent: the rows are the kernel before this one's)
   const int r = blockIdx.x;
   const float* xr = x + (size_t)(rows_idx ? rows_idx[r] : r) * dim;
   float ss = 0.f;
@@ -127,6 +130,51 @@ __global__ void rope_kv_append_kernel(T* __restrict__ qkv, const int32_t* __rest
   }
 }
 
+// The same for bfloat16 with head sizes that are multiples of 16, eight elements (16 bytes) at a time: a work item is
+// eight rotation pairs of a query or key head (elements j .. j + 7 and their partners half a head further), or eight
+// elements of a value head; a block takes `tokens_per_block` tokens.  Same arithmetic as the kernel above and as
+// the rotation fused into the decode attention (dm_rotate8).
+__global__ void rope_kv_append_vec_kernel(__nv_bfloat16* __restrict__ qkv, const int32_t* __restrict__ tok_pos,
+                                          const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ seq_slot,
+                                          const int32_t* __restrict__ page_table, int table_stride, int n_pages,
+                                          const float* __restrict__ cos_t, const float* __restrict__ sin_t, int max_pos,
+                                          __nv_bfloat16* __restrict__ kcache, __nv_bfloat16* __restrict__ vcache, int nh, int nkv,
+                                          int hd, int n_tokens, int tokens_per_block, int* __restrict__ err) {
+  pdl_launch_dependents();
+  pdl_wait();   // (launched as a programmatic dependent: the projections are the kernel before this one's)
+  const int half = hd >> 1, per_head = half >> 3;
+  const int rot_items = (nh + nkv) * per_head, items = rot_items + nkv * (hd >> 3);
+  for (int w = threadIdx.x; w < tokens_per_block * items; w += blockDim.x) {
+    const int tl = w / items, it = w - tl * items, t = blockIdx.x * tokens_per_block + tl;
+    if (t >= n_tokens) break;
+    const int pos = tok_pos[t];
+    if (pos < 0 || pos >= max_pos) {
+      if (it == 0) atomicOr(err, ERR_POSITION_RANGE);
+      continue;
+    }
+    const int page = page_table[(size_t)seq_slot[tok_seq[t]] * table_stride + pos / PAGE];
+    if (page < 0 || page >= n_pages) {
+      if (it == 0) atomicOr(err, ERR_PAGE_RANGE);
+      continue;
+    }
+    const int in_page = pos % PAGE;
+    __nv_bfloat16* row = qkv + (size_t)t * (nh + 2 * nkv) * hd;
+    if (it < rot_items) {
+      const int h = it / per_head, j = (it - h * per_head) << 3;   // heads 0 .. nh - 1: queries; then the keys
+      __nv_bfloat16* src = row + h * hd + j;
+      uint4 lo = *reinterpret_cast<const uint4*>(src), hi = *reinterpret_cast<const uint4*>(src + half);
+      dm_rotate8(lo, hi, cos_t + (size_t)pos * half, sin_t + (size_t)pos * half, j);
+      __nv_bfloat16* dst = h < nh ? src : kcache + (((size_t)page * nkv + (h - nh)) * PAGE + in_page) * hd + j;
+      *reinterpret_cast<uint4*>(dst) = lo;
+      *reinterpret_cast<uint4*>(dst + half) = hi;
+    } else {
+      const int e = (it - rot_items) << 3, h = e / hd, j = e - h * hd;
+      *reinterpret_cast<uint4*>(vcache + (((size_t)page * nkv + h) * PAGE + in_page) * hd + j) =
+          *reinterpret_cast<const uint4*>(row + (size_t)(nh + nkv) * hd + e);
+    }
+  }
+}
+
 }  // namespace edgelm
 
 using namespace edgelm;
@@ -153,11 +201,11 @@ extern "C" int edgelm_rmsnorm(const float* x, const float* w, void* y, int out_d
   const int threads = dim >= 1024 ? 256 : 128;
   const bool vec = dim % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)y % 16 == 0;
   if (out_dtype == DT_F32) {
-    if (vec) rmsnorm_kernel<float, true><<<rows, threads, 0, stream>>>(x, w, (float*)y, rows_idx, dim, eps);
-    else rmsnorm_kernel<float, false><<<rows, threads, 0, stream>>>(x, w, (float*)y, rows_idx, dim, eps);
+    if (vec) launch_pdl(32, rmsnorm_kernel<float, true>, dim3(rows), dim3(threads), (size_t)0, stream, x, w, (float*)y, rows_idx, dim, eps);
+    else launch_pdl(32, rmsnorm_kernel<float, false>, dim3(rows), dim3(threads), (size_t)0, stream, x, w, (float*)y, rows_idx, dim, eps);
   } else if (out_dtype == DT_BF16) {
-    if (vec) rmsnorm_kernel<__nv_bfloat16, true><<<rows, threads, 0, stream>>>(x, w, (__nv_bfloat16*)y, rows_idx, dim, eps);
-    else rmsnorm_kernel<__nv_bfloat16, false><<<rows, threads, 0, stream>>>(x, w, (__nv_bfloat16*)y, rows_idx, dim, eps);
+    if (vec) launch_pdl(32, rmsnorm_kernel<__nv_bfloat16, true>, dim3(rows), dim3(threads), (size_t)0, stream, x, w, (__nv_bfloat16*)y, rows_idx, dim, eps);
+    else launch_pdl(32, rmsnorm_kernel<__nv_bfloat16, false>, dim3(rows), dim3(threads), (size_t)0, stream, x, w, (__nv_bfloat16*)y, rows_idx, dim, eps);
   } else
     EL_REFUSE(false, "rmsnorm: unknown dtype code %d", out_dtype);
   EL_LAUNCH_CHECK("rmsnorm");
@@ -176,7 +224,14 @@ extern "C" int edgelm_rope_kv_append(void* qkv, int dtype, const int32_t* tok_po
     rope_kv_append_kernel<float><<<n_tokens, threads, 0, stream>>>((float*)qkv, tok_pos, tok_seq, seq_slot, page_table,
                                                                     table_stride, n_pages, cos_t, sin_t, max_pos,
                                                                     (float*)kcache, (float*)vcache, nh, nkv, hd, err);
-  else if (dtype == DT_BF16)
+  else if (dtype == DT_BF16 && hd % 16 == 0 && (uintptr_t)qkv % 16 == 0 && (uintptr_t)kcache % 16 == 0 && (uintptr_t)vcache % 16 == 0 &&
+           (uintptr_t)cos_t % 16 == 0 && (uintptr_t)sin_t % 16 == 0) {
+    const int items = (nh + nkv) * (hd / 16) + nkv * (hd / 8);
+    const int per_block = items >= 256 ? 1 : 256 / items;
+    launch_pdl(32, rope_kv_append_vec_kernel, dim3((n_tokens + per_block - 1) / per_block), dim3(256), (size_t)0, stream,
+               (__nv_bfloat16*)qkv, tok_pos, tok_seq, seq_slot, page_table, table_stride, n_pages, cos_t, sin_t, max_pos,
+               (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, nh, nkv, hd, n_tokens, per_block, err);
+  } else if (dtype == DT_BF16)
     rope_kv_append_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
         (__nv_bfloat16*)qkv, tok_pos, tok_seq, seq_slot, page_table, table_stride, n_pages, cos_t, sin_t, max_pos,
         (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, nh, nkv, hd, err);

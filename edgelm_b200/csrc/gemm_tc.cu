@@ -329,6 +329,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  pdl_launch_dependents();   // (after the allocation: a dependent that allocates too then finds every block of this grid served)
+  pdl_wait();                // (launched as a programmatic dependent: up to here nothing of the kernel before this one was read)
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
 
@@ -471,7 +473,12 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
     const int tiles = ((N + BN - 1) / BN) * ((M + TC_BM - 1) / TC_BM);
     const int grid = tiles < n_sms ? tiles : n_sms;
     g_last_launches = 1;
-    kern<<<grid, TC_THREADS, smem, stream>>>(ma, mb, mb2, (TOut*)out, ldo, residual, M, N, K, vec_ok, err);
+    cudaError_t le = launch_pdl(32, kern, dim3(grid), dim3(TC_THREADS), (size_t)smem, stream, ma, mb, mb2, (TOut*)out, ldo, residual, M, N, K,
+                                vec_ok, err);
+    if (le != cudaSuccess) {
+      set_error("gemm_tc: launch failed: %s", cudaGetErrorString(le));
+      return -2;
+    }
     return 0;
   }
   constexpr int STAGE_BYTES = TC_BM * TC_BK * 2 + NB * BN * TC_BK * 2;

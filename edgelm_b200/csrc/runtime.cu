@@ -15,8 +15,8 @@ void set_error(const char* fmt, ...) {
   va_end(ap);
 }
 
-static int g_pdl = 25;   // the few-rows matrix products (bit 0), the one-tile tcgen05 products (bit 3) and the tcgen05 prefill
-                         // attention (bit 4) start under the tail of the kernel before them
+static int g_pdl = 57;   // the few-rows matrix products (bit 0), the tcgen05 products (bits 3 and 5), the tcgen05 prefill attention
+                         // (bit 4), RMSNorm and the rotation (bit 5) start under the tail of the kernel before them
 int pdl_enabled() { return g_pdl; }
 
 }  // namespace edgelm
