@@ -56,8 +56,9 @@ class Attention(Part):
         return KVNeed(self.nkv, self.hd)
 
     # Steps whose longest sequence brings fewer new tokens than this stay on the mma.sync kernel (tiles of 64 rows):
-    # measured at 9 heads of 64, 512 new tokens: 10.7 us against 12.1 us on tcgen05; at 2,048: 44.6 against 28.5 us.
-    TC_PREFILL_MIN_TOKENS = 768
+    # measured at 9 heads of 64 (32 heads): 128 new tokens 4.6 (5.0) us against 5.7 (5.8) us on tcgen05, 256 tokens
+    # 7.0 (7.4) against 6.4 (6.7), 2,048 tokens 44.6 (104.5) against 17.6 (50.1).
+    TC_PREFILL_MIN_TOKENS = 256
 
     def tile_sizes(self):
         sizes = ()
