@@ -628,6 +628,13 @@ int launch_prefill(const void* q, int ldq, void* out, int ldo, const void* kc, c
 // the affected rows are then NaN, which no caller can overlook).
 static int* g_attn_err = nullptr;
 static int g_decode_cuda_cores = 0;  // 1: decode attention on the CUDA-core kernel even where the tensor-core one applies
+// 1: up to 8 splits of the tensor-core decode attention are launched as one thread-block cluster whose first block folds
+// them out of the others' shared memory.  Off: the kernel alone is as fast either way (8.8 us at 8 sequences of 1,500
+// keys, 9 / 3 heads; 19.1 against 20.6 us at 64), but whole decode steps are slower with it (135M sizes, 16 sequences:
+// 1.22 against 1.17 ms; 1.7B sizes, 8 sequences: 2.33 against 2.00 ms): a cluster waits for room in one GPC while the
+// blocks of the kernels around it come and go.
+static int g_decode_cluster = 0;
+static int g_decode_last_launches = 1;
 
 // Keys per tile: the largest power of two up to 64 whose K rows fit DEC_TILE_BYTES.
 static int decode_tile_keys(int hd, size_t elem) {
@@ -644,7 +651,7 @@ int launch_decode(const void* q, int ldq, void* out, int ldo, const void* kc, co
   constexpr int NP = NC <= 2 ? 1 : NC / 2;  // pairs of dims per lane: ceil(hd / 64)
   dim3 grid(n_seqs, nkv, n_splits);
   cudaError_t le = cudaSuccess;
-  bool on_mma = false;
+  bool on_mma = false, folded = false;
   if constexpr (sizeof(T) == 2) {
     // bfloat16 with a head size the MMAs tile (32, 64, 96, 128): the tensor-core kernel, whatever the number of
     // query heads a kv head (with one, 15 of the 16 rows are zero, but the kernel is bound by the cache's bytes:
@@ -654,12 +661,38 @@ int launch_decode(const void* q, int ldq, void* out, int ldo, const void* kc, co
     if ((hd == 32 || hd == 64 || hd == 96 || hd == 128) && counters == nullptr && !g_decode_cuda_cores && aligned) {
       on_mma = true;
       const size_t smem = decode_mma_head_bytes(hd) + (size_t)DEC_WARPS * 2 * PAGE * (hd + 8) * 2;
+      // The splits of a (sequence, kv head) as one thread-block cluster whose first block folds them out of the others'
+      // shared memory: no partial results in global memory and no second kernel.  Up to 8 splits (the portable cluster
+      // size), one pass of query heads.
+      folded = g_decode_cluster && n_splits > 1 && n_splits <= 8 && nh / nkv <= DM_ROWS;
       auto go = [&](auto kern) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
-        return launch_pdl(2, kern, grid, dim3(DEC_WARPS * 32), smem, stream, (const __nv_bfloat16*)q, ldq, (__nv_bfloat16*)out, ldo,
-                          (__nv_bfloat16*)const_cast<void*>(kc), (__nv_bfloat16*)const_cast<void*>(vc), page_table, table_stride,
-                          seq_slot, seq_pos, nh, nkv, scale, n_splits, part_o, part_ml, g_attn_err, cos_t, sin_t, max_pos);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(DEC_WARPS * 32);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        int n_attr = 0;
+        if (pdl_enabled() & 2) {
+          attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+          attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+          ++n_attr;
+        }
+        if (folded) {
+          attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+          attr[n_attr].val.clusterDim.x = 1;
+          attr[n_attr].val.clusterDim.y = 1;
+          attr[n_attr].val.clusterDim.z = (unsigned)n_splits;
+          ++n_attr;
+        }
+        cfg.attrs = attr;
+        cfg.numAttrs = n_attr;
+        return cudaLaunchKernelEx(&cfg, kern, (const __nv_bfloat16*)q, ldq, (__nv_bfloat16*)out, ldo,
+                                  (__nv_bfloat16*)const_cast<void*>(kc), (__nv_bfloat16*)const_cast<void*>(vc), page_table, table_stride,
+                                  seq_slot, seq_pos, nh, nkv, scale, n_splits, part_o, part_ml, g_attn_err, cos_t, sin_t, max_pos,
+                                  folded ? 1 : 0);
       };
       switch (hd / 16) {
         case 2: le = go(attn_decode_mma_kernel<2>); break;
@@ -683,7 +716,8 @@ int launch_decode(const void* q, int ldq, void* out, int ldo, const void* kc, co
                     (T*)const_cast<void*>(kc), (T*)const_cast<void*>(vc), page_table, table_stride, seq_slot, seq_pos,
                     nh, nkv, hd, scale, n_splits, tk, part_o, part_ml, g_attn_err, cos_t, sin_t, max_pos, counters);
   }
-  if (le == cudaSuccess && n_splits > 1 && counters == nullptr) {
+  g_decode_last_launches = n_splits > 1 && counters == nullptr && !folded ? 2 : 1;
+  if (le == cudaSuccess && n_splits > 1 && counters == nullptr && !folded) {
     dim3 cgrid(n_seqs, nh);
     le = launch_pdl(2, attn_decode_combine_kernel<T>, cgrid, dim3(64), 0, stream, (const float*)part_o, (const float*)part_ml,
                     (T*)out, ldo, nh, hd, n_splits);
@@ -747,6 +781,15 @@ extern "C" int edgelm_attn_decode_on_cuda_cores(int on) {
   g_decode_cuda_cores = on ? 1 : 0;
   return 0;
 }
+
+// 1: up to 8 splits of the tensor-core decode attention are one thread-block cluster that folds them itself;
+// 0 (default): the combine kernel folds them always.
+extern "C" int edgelm_attn_decode_cluster(int on) {
+  g_decode_cluster = on ? 1 : 0;
+  return 0;
+}
+// Kernels that the last decode attention call of this process launched (1, or 2 with the combine kernel).
+extern "C" int edgelm_attn_decode_last_launches() { return g_decode_last_launches; }
 
 // The device error word (one int32) that decode attention ORs ERR_WAIT_TIMEOUT into; null: none.
 extern "C" int edgelm_attn_set_error_word(int* err) {

@@ -48,6 +48,8 @@ def lib():
                     loaded.edgelm_gemm_tc_persistent(int(os.environ["EDGELM_GEMM_TC_PERSISTENT"]))
                 if os.environ.get("EDGELM_GEMM_TC_NARROW") is not None:
                     loaded.edgelm_gemm_tc_narrow(int(os.environ["EDGELM_GEMM_TC_NARROW"]))
+                if os.environ.get("EDGELM_DECODE_CLUSTER") is not None:
+                    loaded.edgelm_attn_decode_cluster(int(os.environ["EDGELM_DECODE_CLUSTER"]))
                 if os.environ.get("EDGELM_PDL") is not None:
                     loaded.edgelm_set_pdl(int(os.environ["EDGELM_PDL"]))
                 _lib = loaded
@@ -323,6 +325,12 @@ def attn_prefill_tc_trace(buffer):
     lib().edgelm_attn_prefill_tc_trace(_p(buffer))
 
 
+def attn_decode_cluster(on):
+    """Whether up to 8 splits of the tensor-core decode attention fold themselves as a thread-block cluster, or leave
+    it to the combine kernel (the default: whole steps are faster that way)."""
+    lib().edgelm_attn_decode_cluster(int(bool(on)))
+
+
 def attn_decode(qkv, out, kcache, vcache, page_table, seq_slot, seq_pos, n_seqs, nh, nkv, hd, scale, n_splits=1,
                 part_o=None, part_ml=None):
     """Attention of one new token per sequence over the paged cache, pages dealt to `n_splits` blocks."""
@@ -335,7 +343,8 @@ def attn_decode(qkv, out, kcache, vcache, page_table, seq_slot, seq_pos, n_seqs,
     _check(lib().edgelm_attn_decode(_p(qkv), qkv.stride(0), _p(out), out.stride(0), _p(kcache), _p(vcache), _dt(qkv),
                                     _p(page_table), page_table.stride(0), _p(seq_slot), _p(seq_pos), n_seqs, nh, nkv, hd,
                                     ctypes.c_float(scale), n_splits, _p(part_o), _p(part_ml), _stream()),
-           launches=2 if n_splits > 1 else 1)
+           launches=0)
+    count_launches(lib().edgelm_attn_decode_last_launches())
 
 
 def attn_decode_rope(qkv, out, kcache, vcache, page_table, seq_slot, seq_pos, cos, sin, n_seqs, nh, nkv, hd, scale,
@@ -357,7 +366,8 @@ def attn_decode_rope(qkv, out, kcache, vcache, page_table, seq_slot, seq_pos, co
                                          _p(page_table), page_table.stride(0), _p(seq_slot), _p(seq_pos), _p(cos), _p(sin),
                                          cos.shape[0], n_seqs, nh, nkv, hd, ctypes.c_float(scale), n_splits, _p(part_o),
                                          _p(part_ml), _p(counters), _stream()),
-           launches=2 if (n_splits > 1 and counters is None) else 1)
+           launches=0)
+    count_launches(lib().edgelm_attn_decode_last_launches())
 
 
 def attn_set_error_word(err):

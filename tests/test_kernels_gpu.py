@@ -236,6 +236,37 @@ def test_attn_decode(dtype, nh, nkv, hd, n_splits):
         assert rel_err(out[s:s + 1], want) < (1e-5 if dtype == torch.float32 else 1e-2), (s, n)
 
 
+@pytest.mark.parametrize("nh,nkv,hd", [(9, 3, 64), (32, 32, 64), (6, 1, 96)])
+@pytest.mark.parametrize("n_splits", [3, 8])
+def test_attn_decode_splits_folded_in_a_cluster(nh, nkv, hd, n_splits):
+    """The optional form in which the splits of a (sequence, kv head) are one thread-block cluster: no partial
+    results in global memory (the buffers stay as they were) and the same output as with the combine kernel."""
+    o = ops()
+    lengths = [1, 64, 65, 700, 128, 37]
+    case = PagedCase(o, torch.bfloat16, lengths, nkv, hd, seed=nh + hd + n_splits)
+    B = len(lengths)
+    qkv = rnd((B, (nh + 2 * nkv) * hd), torch.bfloat16, 21)
+    seq_pos = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=dev())
+    outs = []
+    for cluster in (False, True):
+        out = torch.zeros(B, nh * hd, dtype=torch.bfloat16, device=dev())
+        part_o = torch.full((B * nh * n_splits * hd,), float("nan"), device=dev())
+        part_ml = torch.full((B * nh * n_splits * 2,), float("nan"), device=dev())
+        o.attn_decode_cluster(cluster)
+        try:
+            o.attn_decode(qkv, out, case.kcache, case.vcache, case.table, case.seq_slot, seq_pos, B, nh, nkv, hd,
+                          1.0 / math.sqrt(hd), n_splits, part_o, part_ml)
+            torch.cuda.synchronize()
+        finally:
+            o.attn_decode_cluster(False)
+        assert bool(torch.isnan(part_o).all()) == cluster
+        outs.append(out)
+    for s, n in enumerate(lengths):
+        want = attention_rows(qkv[s:s + 1, :nh * hd].float().cpu(), case.k[s], case.v[s], n - 1, nh, nkv, hd)
+        assert rel_err(outs[1][s:s + 1], want) < 1e-2, (s, n)
+    assert torch.equal(outs[0], outs[1])   # same arithmetic in the same order
+
+
 def test_attention_far_key_stands_out():
     """One early key among hundreds is made to dominate: the output must be its value."""
     o = ops()
