@@ -575,8 +575,10 @@ extern "C" int edgelm_gemm_tc(const void* a, int lda, const void* w, const void*
   // wide tiles (128 x 256, or 2 x 128 for SwiGLU) when the output is wide enough to fill the device with
   // them: twice the multiply-adds per byte that comes through shared memory
   const long long wide_tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((N + (epilogue == TC_EPI_SWIGLU ? 127 : 255)) / (epilogue == TC_EPI_SWIGLU ? 128 : 256));
-  const bool wide = g_tc_auto ? (wide_tiles >= 120 && N >= 1024 && K >= 1024 && epilogue != TC_EPI_RESIDUAL) : (g_tc_wide && wide_tiles >= 120 && N >= 1024);
-  const bool persistent = g_tc_auto ? wide : g_tc_persistent != 0;
+  const bool wide = g_tc_auto ? (wide_tiles >= 120 && N >= 1024 && K >= 1024) : (g_tc_wide && wide_tiles >= 120 && N >= 1024);
+  // (with a residual the wide tiles go one to a block: measured at 2,048 rows, N 2048: K 8192 65.9 -> 60.0 us, K 2048
+  // 25.3 -> 24.0 us; persistent 69.0 and 31.3 us)
+  const bool persistent = g_tc_auto ? (wide && epilogue != TC_EPI_RESIDUAL) : g_tc_persistent != 0;
   // tiles of 64 columns for a single weight when 128-column tiles would not fill one wave of SMs and there are
   // several row tiles to share a weight tile in L2 (measured at 2,048 rows: N 576, K 576: 11.6 -> 8.8 us; N 576,
   // K 1536: 16.1 -> 13.5 us; with 256 tiles of 128 columns and K 8192 the narrow tiles lose: 68 -> 107 us)
