@@ -116,6 +116,23 @@ __device__ __forceinline__ void hist_add(unsigned int* hist, bool take, uint32_t
   if (take && (threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&hist[bucket], (unsigned int)__popc(peers));
 }
 
+// The same for 64-bit amounts (at most 2^40 each): the lanes of a warp that share a bucket add their amounts up first
+// (two 32-bit warp reductions of the low and the high 20 bits) and one of them adds the sum.  Integer adds: the
+// histogram does not depend on the grouping.  Whole warps call it.
+__device__ __forceinline__ void whist_add(unsigned long long* whist, bool take, uint32_t bucket, unsigned long long amount) {
+  const int lane = threadIdx.x & 31;
+  unsigned int todo = __ballot_sync(0xffffffffu, take);
+  while (todo) {
+    const int leader = __ffs(todo) - 1;
+    const uint32_t b = __shfl_sync(0xffffffffu, bucket, leader);
+    const bool mine = take && bucket == b;
+    const unsigned int lo = __reduce_add_sync(0xffffffffu, mine ? (unsigned int)(amount & 0xfffffull) : 0u);
+    const unsigned int hi = __reduce_add_sync(0xffffffffu, mine ? (unsigned int)(amount >> 20) : 0u);
+    if (lane == leader) atomicAdd(&whist[b], (unsigned long long)lo + ((unsigned long long)hi << 20));
+    todo &= ~__ballot_sync(0xffffffffu, mine);
+  }
+}
+
 // Index of the n-th (0-based) element, in index order, whose key equals `key`; vocab if fewer.  A thread counts the
 // matches of its own run of consecutive elements (an odd run length keeps the reads off each other's banks), the
 // counts are scanned over the block, and the thread whose run holds the n-th match walks it again.
@@ -212,7 +229,8 @@ sample_topk_kernel(const float* __restrict__ logits, int ld, int vocab, float te
   // ---- the k-th largest key: radix select, most significant byte first
   uint32_t prefix = 0;            // the decided high bits of the k-th largest key
   unsigned int remaining = k;     // its rank (1-based, descending) among keys that share those bits
-  for (int shift = 24; shift >= 0; shift -= 8) {
+  const bool keep_all = k >= (unsigned int)vocab;   // (top_k 0: nothing to select; every key is at or above 0)
+  for (int shift = 24; shift >= 0 && !keep_all; shift -= 8) {
     for (int i = threadIdx.x; i < 256; i += ST) sh.hist[i] = 0;
     __syncthreads();
     const uint32_t mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
@@ -240,7 +258,7 @@ sample_topk_kernel(const float* __restrict__ logits, int ld, int vocab, float te
   }
   const uint32_t kth = prefix;            // key of the k-th largest logit
   // of the tokens whose key equals kth, the first `remaining` by index are kept
-  const int tie_end = nth_equal_index(src, vocab, kth, remaining - 1, sh) + 1;  // keep equal keys with index < tie_end
+  const int tie_end = keep_all ? vocab : nth_equal_index(src, vocab, kth, remaining - 1, sh) + 1;  // keep equal keys with index < tie_end
 
   if (k <= (unsigned int)SK_LIST) {
     // ---- few kept tokens: list them, rank them in the order of the walk (key descending, index ascending), add up
@@ -310,11 +328,13 @@ sample_topk_kernel(const float* __restrict__ logits, int ld, int vocab, float te
     for (int i = threadIdx.x; i < 256; i += ST) sh.whist[i] = 0;
     __syncthreads();
     const uint32_t mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
-    for (int i = threadIdx.x; i < vocab; i += ST) {
-      const float v = src[i];
+    for (int base = 0; base < vocab; base += ST) {   // (whole warps, for the votes inside whist_add)
+      const int i = base + threadIdx.x;
+      const float v = i < vocab ? src[i] : 0.f;
       const uint32_t key = order_key(v);
-      const bool kept = key > kth || (key == kth && i < tie_end);
-      if (kept && (key & mask) == dprefix) atomicAdd(&sh.whist[(key >> shift) & 255u], fixed_p(v, lmax, temperature));
+      const bool kept = i < vocab && (key > kth || (key == kth && i < tie_end));
+      const bool take = kept && (key & mask) == dprefix;
+      whist_add(sh.whist, take, (key >> shift) & 255u, take ? fixed_p(v, lmax, temperature) : 0ull);
     }
     __syncthreads();
     if (threadIdx.x == 0) {
