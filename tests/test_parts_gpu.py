@@ -239,6 +239,160 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
     eng.cache.check()
 
 
+# ----------------------------------------------------------------------------- a toy feed-forward with routing, a toy position encoding
+def _register_toy_routed():
+    """A feed-forward that sends every token to one of a few small experts (the router's first maximum) and scales
+    the expert's output by the router's softmax weight, and a rotary encoding whose positions are divided by a
+    factor.  Torch ops and the package's own rotation kernel; toys to show the interfaces."""
+    from edgelm_b200.config import register_architecture
+    from edgelm_b200.config.base import LayerSpec, ModelPlan, PartSpec, ScheduleEntry
+    from edgelm_b200.csrc import ops
+    from edgelm_b200.parts import Part, register_ffn, register_positions
+    from edgelm_b200.parts.registry import FEED_FORWARDS
+
+    if "toy_top1_experts" in FEED_FORWARDS:
+        return
+
+    @register_ffn("toy_top1_experts")
+    class ToyRoutedFeedForward(Part):
+        def __init__(self, spec, env):
+            self.dim, self.inner, self.n_experts = spec["dim"], spec["inner"], spec["experts"]
+
+        def weight_shapes(self, prefix):
+            shapes = {prefix + "router.weight": (self.n_experts, self.dim)}
+            for e in range(self.n_experts):
+                shapes[prefix + f"experts.{e}.in.weight"] = (self.inner, self.dim)
+                shapes[prefix + f"experts.{e}.out.weight"] = (self.dim, self.inner)
+            return shapes
+
+        def load(self, tensors, prefix, device):
+            f = lambda name: tensors[prefix + name].to(device=device, dtype=torch.float32)
+            self.router = f("router.weight")
+            self.w_in = [f(f"experts.{e}.in.weight") for e in range(self.n_experts)]
+            self.w_out = [f(f"experts.{e}.out.weight") for e in range(self.n_experts)]
+
+        def forward(self, ctx, h, x):
+            hf = h.float()
+            logits = hf @ self.router.T                       # float32 router logits
+            chosen = logits.argmax(dim=1)
+            weight = torch.softmax(logits, dim=1).gather(1, chosen[:, None])
+            for e in range(self.n_experts):
+                y = torch.nn.functional.silu(hf @ self.w_in[e].T) @ self.w_out[e].T
+                x += torch.where((chosen == e)[:, None], y * weight, torch.zeros_like(y))
+
+    @register_positions("toy_interpolated_rope")
+    class InterpolatedRotaryPositions(Part):
+        def __init__(self, spec, env):
+            self.head_dim, self.theta, self.factor = spec["head_dim"], float(spec["theta"]), float(spec["factor"])
+            self.max_positions = spec["max_positions"]
+            self.cos = self.sin = None
+
+        def load(self, tensors, prefix, device):
+            i = torch.arange(0, self.head_dim, 2, dtype=torch.float64)
+            inv = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -(i / self.head_dim))
+            ang = (torch.arange(self.max_positions, dtype=torch.float64) / self.factor)[:, None] * inv[None, :]
+            self.cos = torch.cos(ang).to(torch.float32).to(device).contiguous()
+            self.sin = torch.sin(ang).to(torch.float32).to(device).contiguous()
+
+        def rotation_tables(self):
+            return self.cos, self.sin
+
+        def encode_and_append(self, ctx, qkv, cache, n_heads, n_kv_heads):
+            ops.rope_kv_append(qkv, ctx.tok_pos, ctx.tok_seq, ctx.seq_index, ctx.page_table(cache.group), self.cos, self.sin,
+                               cache.k, cache.v, n_heads, n_kv_heads, self.head_dim, ctx.err)
+
+    @register_architecture("ToyRoutedForCausalLM", model_type="toy_routed")
+    class ToyRoutedConfig:
+        def __init__(self, d):
+            self.d = d
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d)
+
+        def plan(self):
+            d = self.d
+            D, V = d["width"], d["vocab_size"]
+            norm = lambda name: PartSpec("rmsnorm", {"dim": D, "eps": d["eps"], "name": name})
+
+            def att(positions):
+                return PartSpec("attention", {"hidden_size": D, "num_heads": 3, "num_kv_heads": 1, "head_dim": 16, "positions": positions,
+                                              "names": {"q": "q.weight", "k": "k.weight", "v": "v.weight", "o": "o.weight"}})
+            squeezed = PartSpec("toy_interpolated_rope", {"head_dim": 16, "theta": 1000.0, "factor": d["factor"], "max_positions": 128})
+            rope = PartSpec("rope", {"head_dim": 16, "theta": 1000.0, "max_positions": 128})
+            routed = PartSpec("toy_top1_experts", {"dim": D, "inner": d["inner"], "experts": d["experts"]})
+            dense = PartSpec("swiglu", {"hidden_size": D, "intermediate_size": d["inner"],
+                                        "names": {"gate": "g.weight", "up": "u.weight", "down": "d.weight"}})
+            # two layers with different position encodings and different feed-forwards
+            layers = (LayerSpec("l0.", "prenorm", att(squeezed), norm("n1.weight"), routed, norm("n2.weight")),
+                      LayerSpec("l1.", "prenorm", att(rope), norm("n1.weight"), dense, norm("n2.weight")))
+            return ModelPlan(hidden_size=D, vocab_size=V, max_positions=128,
+                             embedding=PartSpec("embedding", {"vocab_size": V, "dim": D, "name": "emb.weight"}),
+                             layers=layers, schedule=(ScheduleEntry(0), ScheduleEntry(1)), final_norm=norm("final.weight"),
+                             head=PartSpec("lm_head", {"vocab_size": V, "dim": D, "tied_to": "emb.weight", "name": "head.weight"}))
+
+
+def _toy_routed_plain(W, d, tokens):
+    """The toy model in plain NumPy: whole sequence, no cache."""
+    n = len(tokens)
+
+    def att(x, p, positions):
+        h = plain.rmsnorm(x, W[p + "n1.weight"], d["eps"])
+        q = plain.rope(h @ W[p + "q.weight"].T, positions, 3, 16, 1000.0)
+        k = plain.rope(h @ W[p + "k.weight"].T, positions, 1, 16, 1000.0)
+        return x + plain.attention(q, k, h @ W[p + "v.weight"].T, 3, 1, 16) @ W[p + "o.weight"].T
+
+    x = plain.embed(W["emb.weight"], tokens)
+    x = att(x, "l0.", np.arange(n) / d["factor"])
+    h = plain.rmsnorm(x, W["l0.n2.weight"], d["eps"])
+    logits = h @ W["l0.router.weight"].T
+    out = x.copy()
+    for t in range(n):
+        e = int(np.argmax(logits[t]))
+        p = np.exp(logits[t] - logits[t].max())
+        y = plain.silu(h[t] @ W[f"l0.experts.{e}.in.weight"].T) @ W[f"l0.experts.{e}.out.weight"].T
+        out[t] += y * np.float32(p[e] / p.sum())
+    x = att(out, "l1.", np.arange(n))
+    h = plain.rmsnorm(x, W["l1.n2.weight"], d["eps"])
+    x = x + plain.swiglu_mlp(h, W["l1.g.weight"], W["l1.u.weight"], W["l1.d.weight"])
+    return plain.rmsnorm(x, W["final.weight"], d["eps"]) @ W["emb.weight"].T
+
+
+def test_toy_routed_feed_forward_and_position_encoding_register_build_and_step(tmp_path):
+    _register_toy_routed()
+    from edgelm_b200.config import read_config
+    from edgelm_b200.engine.engine import Engine, load_model
+    from edgelm_b200.engine.model import expected_weights
+    from edgelm_b200.weights import random_tensors, read_dir, write_file
+    d = {"architectures": ["ToyRoutedForCausalLM"], "vocab_size": 47, "width": 24, "inner": 40, "experts": 3, "eps": 1e-6, "factor": 2.5}
+    folder = tmp_path / "toy_routed"
+    folder.mkdir()
+    (folder / "config.json").write_text(json.dumps(d))
+    exp = expected_weights(read_config(str(folder)).plan())
+    assert exp["l0.router.weight"] == (3, 24) and exp["l0.experts.2.out.weight"] == (24, 40) and "l1.router.weight" not in exp
+    tensors = random_tensors(exp, seed=3, sigma=0.2, dtype=torch.float32)
+    tensors["l0.router.weight"] = tensors["l0.router.weight"] * 6.0   # clear choices: no token sits on the fence between two experts
+    write_file(str(folder / "model.safetensors"), tensors)
+    model = load_model(str(folder), "float32")
+    assert type(model.layers[0].mixer.positions).__name__ == "InterpolatedRotaryPositions"
+    assert type(model.layers[1].mixer.positions).__name__ == "RotaryPositions"
+    eng = Engine(model, max_tokens=512)
+    W = {k: v.float().numpy() for k, v in read_dir(str(folder)).items()}
+    reqs = [[int(v) for v in np.random.default_rng(10 + i).integers(0, 47, size=n)] for i, n in enumerate([26, 5, 90, 41])]
+    used = set()
+    for r in reqs:
+        want = _toy_routed_plain(W, d, r)
+        assert H.rel_err(H.run_whole(eng, r), want) < 5e-5
+        assert H.rel_err(H.run_tail_one_by_one(eng, r, 12), want) < 5e-5
+        h = plain.rmsnorm(plain.embed(W["emb.weight"], r), W["l0.n1.weight"], d["eps"])
+        used |= set(np.argmax(h @ W["l0.router.weight"].T, axis=1).tolist())
+    assert len(used) > 1   # (a rough check on the first norm's output that the router does not send everything one way)
+    got = H.run_batches(eng, reqs, batch_size=3, decode_tail=6)
+    for r, g in zip(reqs, got):
+        assert H.rel_err(g, _toy_routed_plain(W, d, r)) < 5e-5
+    eng.cache.check()
+
+
 def test_cli_commands(tmp_path, capsys):
     from edgelm_b200.cli import main
     d = H.make_model_dir(tmp_path, "tiny_a")
