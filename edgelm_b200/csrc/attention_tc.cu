@@ -58,8 +58,8 @@ constexpr int AT_THREADS = AT_ROLE_WARPS * 32 + 2 * AT_GROUP_THREADS;
 constexpr int AT_Q_BYTES = AT_ROWS * AT_HD * 2;          // 16 KB
 constexpr int AT_KV_BYTES = AT_KEYS * AT_HD * 2;         // 16 KB: two pages
 constexpr int AT_STAGES = 2;                             // blocks of K in shared memory: a group's blocks use one of them
-constexpr int AT_V_STAGES = 3;                           // blocks of V (with two, V came late: a stage is free only when the
-                                                         // block two before has been through its P V, one and a half blocks later)
+constexpr int AT_V_STAGES = 3;                           // blocks of V (a stage is free only when the block that used it has been
+                                                         // through its P V; measured no faster than two with the cache in L2)
 constexpr int AT_P_BYTES = AT_ROWS * AT_KEYS * 2;        // 32 KB: two K-major tiles of 128 x 64, one per half
 constexpr int AT_P_BUFS = 2;                             // P buffers of a group
 constexpr int AT_N_BARS = 1 + 2 * AT_STAGES + 2 * AT_V_STAGES + 12;
