@@ -18,6 +18,9 @@
 //   * epilogues: store (bfloat16 or float32), += residual (float32), SwiGLU of two weights.
 // K must be a multiple of 8 with 16-byte aligned rows; M <= 16.  Launched as a programmatic dependent
 // launch: the first weight loads are issued before the wait for the previous kernel.
+// A launch can be told the weights that the step reads next (`edgelm_gemv_mma_prefetch_next`): its blocks then ask
+// the L2 cache for a slice of them each (cp.async.bulk.prefetch.L2) once their own first loads are out, so that the
+// next product's transfer from memory runs under this one's waits, staging and epilogue instead of after them.
 #include "common.cuh"
 
 namespace edgelm {
@@ -37,6 +40,21 @@ __device__ __forceinline__ void mma_bf16_16x8x16(float* c, uint32_t a0, uint32_t
 
 __device__ __forceinline__ float gm_silu(float z) { return z / (1.0f + expf(-z)); }
 
+// This block's share of `bytes` at `p` (16-byte aligned, a multiple of 16 bytes) into the L2 cache; one thread calls it.
+__device__ __forceinline__ void gm_prefetch_slice(const uint8_t* p, unsigned long long bytes) {
+  if (p == nullptr || bytes == 0) return;
+  const unsigned long long per = ((bytes + gridDim.x - 1) / gridDim.x + 127ull) & ~127ull;
+  unsigned long long off = (unsigned long long)blockIdx.x * per;
+  if (off >= bytes) return;
+  unsigned long long left = (bytes - off < per ? bytes - off : per) & ~15ull;
+  while (left) {
+    const unsigned int n = left < 16384ull ? (unsigned int)left : 16384u;
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p + off), "r"(n) : "memory");
+    off += n;
+    left -= n;
+  }
+}
+
 // NT: 8-row tiles of the batch (1: M <= 8, 2: M <= 16).  NORM: activations = RMSNorm(x).
 // MAXW: the most warps a block is launched with.  UN: K blocks whose weight loads a warp has in flight together
 // (4, or 8 for long rows of a single weight: 64 registers of weights either way).
@@ -46,7 +64,8 @@ gemv_mma_kernel(const __nv_bfloat16* __restrict__ act, int lda, const float* __r
                 const float* __restrict__ norm_w, float eps, const __nv_bfloat16* __restrict__ W,
                 const __nv_bfloat16* __restrict__ W2, TOut* out, int ldo, const float* residual, int M, int N, int K,
                 int pitch /* bfloat16 elements per activation row in shared memory */,
-                int kc /* columns of the activations staged at a time: a multiple of 32 */) {
+                int kc /* columns of the activations staged at a time: a multiple of 32 */,
+                const uint8_t* next0, unsigned long long next0_bytes, const uint8_t* next1, unsigned long long next1_bytes) {
   constexpr int NW = EPI == GM_SWIGLU ? 2 : 1;
   constexpr int ROWS = 8 * NT;
   const int GM_WARPS = blockDim.x >> 5;  // the block's warps share the K blocks
@@ -89,6 +108,10 @@ gemv_mma_kernel(const __nv_bfloat16* __restrict__ act, int lda, const float* __r
     }
   }
 
+  if (threadIdx.x == 0) {   // (weights: nothing on the stream writes them)
+    gm_prefetch_slice(next0, next0_bytes);
+    gm_prefetch_slice(next1, next1_bytes);
+  }
   pdl_launch_dependents();
   pdl_wait();  // from here on: activations that the kernel before this one wrote
   // ---- activations into shared memory (rows >= M are zero)
@@ -260,6 +283,13 @@ gemv_mma_kernel(const __nv_bfloat16* __restrict__ act, int lda, const float* __r
   }
 }
 
+// What the next launch from this thread prefetches (set by edgelm_gemv_mma_prefetch_next, cleared by the launch).
+struct NextWeights {
+  const uint8_t* p;
+  unsigned long long bytes;
+};
+static thread_local NextWeights g_next[2] = {{nullptr, 0}, {nullptr, 0}};
+
 // Activation row pitch in shared memory: K rounded up so that pitch * 2 bytes = 64 (mod 128); then
 // the fragment reads of a quarter-warp (two rows, four 16-byte chunks each) hit distinct banks.
 static int act_pitch(int K) {
@@ -300,7 +330,7 @@ static int launch_gemv_mma(const void* act, int lda, const float* x, const float
     }
     cudaError_t le = launch_pdl(1, kern, dim3((N + GM_COLS - 1) / GM_COLS), dim3(GM_WARPS * 32), smem, stream,
                                 (const __nv_bfloat16*)act, lda, x, norm_w, eps, (const __nv_bfloat16*)W, (const __nv_bfloat16*)W2,
-                                (TOut*)out, ldo, residual, M, N, K, pitch, kc);
+                                (TOut*)out, ldo, residual, M, N, K, pitch, kc, g_next[0].p, g_next[0].bytes, g_next[1].p, g_next[1].bytes);
     if (le != cudaSuccess) {
       set_error("gemv_mma: launch failed: %s", cudaGetErrorString(le));
       return -2;
@@ -355,7 +385,18 @@ extern "C" int edgelm_gemv_mma(const void* act, int lda, const float* norm_w, fl
   else if (epilogue == GM_SWIGLU && out_dtype == DT_BF16) EL_GM(GM_SWIGLU, __nv_bfloat16);
   else EL_REFUSE(false, "gemv_mma: unsupported epilogue %d with output dtype %d", epilogue, out_dtype);
 #undef EL_GM
+  g_next[0] = g_next[1] = NextWeights{nullptr, 0};
   if (rc) return rc;
   EL_LAUNCH_CHECK("gemv_mma");
+  return 0;
+}
+
+// Up to two regions of weights that the step reads after the next few-rows product launched from this thread: that
+// launch prefetches them into L2.  Null or 0 bytes: none.  Pointers 16-byte aligned (refused otherwise); the bytes
+// are rounded down to whole 16.
+extern "C" int edgelm_gemv_mma_prefetch_next(const void* p0, unsigned long long bytes0, const void* p1, unsigned long long bytes1) {
+  EL_REFUSE((uintptr_t)p0 % 16 == 0 && (uintptr_t)p1 % 16 == 0, "gemv_mma_prefetch_next: regions must be 16-byte aligned");
+  g_next[0] = NextWeights{(const uint8_t*)p0, p0 ? bytes0 : 0};
+  g_next[1] = NextWeights{(const uint8_t*)p1, p1 ? bytes1 : 0};
   return 0;
 }

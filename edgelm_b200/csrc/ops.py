@@ -183,9 +183,10 @@ def gemv_mma_takes(a, w, w2=None, normed=False):
     return bool(lib().edgelm_gemv_mma_takes(_p(a), a.stride(0), _p(w), _p(w2), a.shape[0], a.shape[1], 1 if normed else 0))
 
 
-def gemv_mma(a, w, out, epilogue=EPI_STORE, w2=None, residual=None, norm_weight=None, eps=0.0):
+def gemv_mma(a, w, out, epilogue=EPI_STORE, w2=None, residual=None, norm_weight=None, eps=0.0, prefetch=()):
     """out = act @ w.T (+ epilogue) for at most 16 rows on mma.sync tensor cores; act = a, or
-    RMSNorm(a) * norm_weight rounded to bfloat16 when norm_weight is given."""
+    RMSNorm(a) * norm_weight rounded to bfloat16 when norm_weight is given.  `prefetch`: up to two
+    contiguous tensors (the weights the step reads next) that the kernel's blocks ask the L2 cache for."""
     M, K = a.shape
     N = w.shape[0]
     _need(w.shape[1] == K and out.shape == (M, N), f"gemv_mma: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
@@ -197,6 +198,10 @@ def gemv_mma(a, w, out, epilogue=EPI_STORE, w2=None, residual=None, norm_weight=
         _need(a.dtype == torch.bfloat16 and a.stride(1) == 1, "gemv_mma: activation dtype")
     if residual is not None:
         _need(residual.dtype == torch.float32 and residual.shape == out.shape and residual.stride() == out.stride(), "gemv_mma: residual layout")
+    if prefetch:
+        _need(len(prefetch) <= 2 and all(t.is_contiguous() for t in prefetch), "gemv_mma: prefetch takes up to two contiguous tensors")
+        regions = [(_p(t), ctypes.c_ulonglong(t.numel() * t.element_size())) for t in prefetch] + [(ctypes.c_void_p(0), ctypes.c_ulonglong(0))]
+        _check(lib().edgelm_gemv_mma_prefetch_next(regions[0][0], regions[0][1], regions[1][0], regions[1][1]), launches=0)
     _check(lib().edgelm_gemv_mma(_p(a), a.stride(0), _p(norm_weight), ctypes.c_float(eps), _p(w), _p(w2), _p(out), out.stride(0),
                                  _p(residual), M, N, K, _dt(out), epilogue, _stream()))
 

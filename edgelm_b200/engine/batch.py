@@ -39,13 +39,16 @@ def make_tiles(seq_ntok, seq_pos0, tile_tokens):
 
 
 class StepContext:
-    """What parts see of a step.  Built by the engine; parts read, never write."""
+    """What parts see of a step.  Built by the engine; parts read it.  The one thing written on the way is
+    `weights_after` (by the model's loop and the block arrangement): the weight tensors that the step reads
+    once the running part is done."""
 
     def __init__(self, ws, err, device, n_sms, profiler=None):
         self.ws, self.err, self.device, self.n_sms = ws, err, device, n_sms
         self.prof = profiler or NULL_PROFILER
         self.n_tokens = self.n_seqs = 0
         self.all_single = False
+        self.weights_after = ()
         self.token_ids = self.tok_pos = self.tok_seq = self.seq_index = self.seq_pos = self.want_rows = None
         self.seq_slots = None          # real slot of each sequence (int32 device tensor): state groups, sampler streams
         self._tables = {}              # cache group id -> device page-table rows [n_seqs, stride]

@@ -133,7 +133,10 @@ class DecoderModel:
             for i in indices:
                 e = self.schedule[i]
                 entry = cache.entries[e.reads_cache_of if e.reads_cache_of is not None else i]
+                nxt = self.schedule[i + 1].layer if i + 1 < len(self.schedule) else None
+                ctx.weights_after = self.layers[nxt].first_weights() if nxt is not None else ()
                 self.layers[e.layer].forward(ctx, x, entry)
+        ctx.weights_after = ()
         if R:
             with ws.frame():
                 xn = ws.alloc((R, self.plan.hidden_size), self.dtype)

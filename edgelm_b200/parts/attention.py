@@ -45,6 +45,9 @@ class Attention(Part):
         self.w_o = as_matrix(tensors[prefix + n["o"]], self.dtype, device)
         self.positions.load(tensors, prefix, device)
 
+    def first_weights(self):
+        return (self.w_qkv,)
+
     def decode_fusion(self):
         if not hasattr(self.positions, "rotation_tables"):
             return None
@@ -108,7 +111,7 @@ class Attention(Part):
                 ops.attn_decode_rope(qkv, a, cache.k, cache.v, table, ctx.seq_index, ctx.seq_pos, tables[0], tables[1],
                                      ctx.n_seqs, self.nh, self.nkv, self.hd, self.scale, splits, part_o, part_ml, counters)
             with ctx.prof("o_proj_residual"):
-                linear.matmul(ctx, a, self.w_o, x, epilogue=linear.EPI_RESIDUAL, residual=x)
+                linear.matmul(ctx, a, self.w_o, x, epilogue=linear.EPI_RESIDUAL, residual=x, prefetch=ctx.weights_after)
             return
         with ctx.prof("rope_kv_append"):
             self.positions.encode_and_append(ctx, qkv, cache, self.nh, self.nkv)
@@ -138,4 +141,4 @@ class Attention(Part):
                 ops.attn_prefill(qkv, a, cache.k, cache.v, table, ctx.seq_index, tiles.seq, tiles.tok0, tiles.ntok,
                                  tiles.pos0, tiles.count, self.tile_tokens, self.nh, self.nkv, self.hd, self.scale)
         with ctx.prof("o_proj_residual"):
-            linear.matmul(ctx, a, self.w_o, x, epilogue=linear.EPI_RESIDUAL, residual=x)
+            linear.matmul(ctx, a, self.w_o, x, epilogue=linear.EPI_RESIDUAL, residual=x, prefetch=ctx.weights_after)

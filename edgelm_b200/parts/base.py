@@ -66,6 +66,11 @@ class Part:
         The engine's fusion pass reads these once the weights are loaded; a part never sees the fused kernel."""
         return None
 
+    def first_weights(self):
+        """The weight tensors that this part's `forward` reads first (at most two): whoever runs before it may
+        start them on their way into the L2 cache.  Default: none."""
+        return ()
+
     def tile_sizes(self):
         """Sizes of attention tiles (`ctx.tiles(n)`) this part will ask for: the engine lays them out
         with the step's metadata, which is what lets a whole step be replayed from a CUDA graph."""

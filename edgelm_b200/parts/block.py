@@ -61,8 +61,17 @@ class PreNormBlock(Part):
             norm.forward(ctx, x, h)
         return h
 
+    def first_weights(self):
+        return self.mixer.first_weights()
+
     def forward(self, ctx, x, cache):
+        # `ctx.weights_after`: what the step reads once the running part is done (a part's last product may start
+        # it on its way into L2): after the mixer the feed-forward's first weights, after that whatever the caller
+        # named as coming after this layer
+        after_layer = ctx.weights_after
+        ctx.weights_after = self.ffn.first_weights()
         with ctx.ws.frame():
             self.mixer.forward(ctx, self._normed(ctx, x, self.mixer_norm, self.mixer), x, cache)
+        ctx.weights_after = after_layer
         with ctx.ws.frame():
             self.ffn.forward(ctx, self._normed(ctx, x, self.ffn_norm, self.ffn), x)

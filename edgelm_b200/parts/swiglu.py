@@ -35,9 +35,12 @@ class SwiGLU(Part):
     def workspace_bytes(self, n_tokens, n_seqs):
         return nbytes((n_tokens, self.inter), self.dtype) + nbytes((n_tokens, self.hidden), self.dtype)
 
+    def first_weights(self):
+        return (self.w_gate, self.w_up)
+
     def forward(self, ctx, h, x):
         mid = ctx.ws.alloc((h.shape[0], self.inter), self.dtype)
         with ctx.prof("gate_up_swiglu"):
-            linear.matmul(ctx, h, self.w_gate, mid, epilogue=linear.EPI_SWIGLU, w2=self.w_up)
+            linear.matmul(ctx, h, self.w_gate, mid, epilogue=linear.EPI_SWIGLU, w2=self.w_up, prefetch=(self.w_down,))
         with ctx.prof("down_proj_residual"):
-            linear.matmul(ctx, mid, self.w_down, x, epilogue=linear.EPI_RESIDUAL, residual=x)
+            linear.matmul(ctx, mid, self.w_down, x, epilogue=linear.EPI_RESIDUAL, residual=x, prefetch=ctx.weights_after)
