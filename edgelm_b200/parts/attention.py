@@ -93,7 +93,7 @@ class Attention(Part):
         ws = ctx.ws
         qkv = ws.alloc((T, (self.nh + 2 * self.nkv) * self.hd), self.dtype)
         with ctx.prof("qkv_proj"):
-            linear.matmul(ctx, h, self.w_qkv, qkv)
+            linear.matmul(ctx, h, self.w_qkv, qkv, prefetch=(self.w_o,))
         a = ws.alloc((T, self.nh * self.hd), self.dtype)
         table = ctx.page_table(cache.group)
         tables = self.positions.rotation_tables() if hasattr(self.positions, "rotation_tables") else None
