@@ -569,6 +569,32 @@ def test_gemv_mma_row_independent_of_batch_and_refusals():
         o.gemv_mma(rnd((17, 96), torch.bfloat16, 1), w, torch.zeros(17, 50, device=dev()))
 
 
+def test_gemv_mma_prefetch_of_the_next_weights_changes_no_result():
+    """The hint that starts other tensors on their way into L2: odd sizes (not a multiple of the blocks' slices),
+    one and two regions, more blocks than 16-byte pieces; the product is the same bit for bit and the regions are
+    untouched.  Misaligned regions are refused."""
+    o = ops()
+    a = rnd((5, 576), torch.bfloat16, 79)
+    w = rnd((960, 576), torch.bfloat16, 80, 0.2)
+    want = torch.empty(5, 960, device=dev())
+    o.gemv_mma(a, w, want)
+    big = rnd((1536, 577 * 8), torch.bfloat16, 81)        # 14 MB, rows of an odd number of 16-byte pieces
+    small = rnd((3, 8), torch.bfloat16, 82)               # 48 bytes: fewer pieces than blocks
+    big0, small0 = big.clone(), small.clone()
+    for regions in ((big,), (small,), (big, small), (small, big)):
+        got = torch.full((5, 960), float("nan"), device=dev())
+        o.gemv_mma(a, w, got, prefetch=regions)
+        assert torch.equal(got, want)
+    got = torch.full((5, 960), float("nan"), device=dev())
+    o.gemv_mma(a, w, got)                                  # (the hint is used up by the launch after it)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want) and torch.equal(big, big0) and torch.equal(small, small0)
+    with pytest.raises(o.KernelError, match="16-byte aligned"):
+        o.gemv_mma(a, w, got, prefetch=(big.view(-1)[4:4 + 1024],))
+    o.gemv_mma(a, w, got)
+    assert torch.equal(got, want)
+
+
 # ----------------------------------------------------------------------------- prefill attention on mma.sync (bfloat16)
 @pytest.mark.parametrize("groups", [0, 1, 2, 4])
 @pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 32), (9, 3, 64), (3, 1, 96), (4, 4, 128), (8, 1, 64)])
