@@ -45,6 +45,15 @@ class Attention(Part):
         self.w_o = as_matrix(tensors[prefix + n["o"]], self.dtype, device)
         self.positions.load(tensors, prefix, device)
 
+    def _decode_resident(self):
+        """Blocks of the tensor-core decode attention kernel that an SM holds (its shared memory: the staged
+        queries and four warps' key and value tiles of 64 padded rows), or None where that kernel does not run."""
+        if self.dtype != torch.bfloat16 or self.hd not in (32, 64, 96, 128):
+            return None
+        head = (16 * (self.hd + 8) * 2 + 2 * self.hd * 2 + 4 * 8 + 127) // 128 * 128
+        block = head + 4 * 2 * 64 * (self.hd + 8) * 2
+        return max(1, (227 * 1024) // (block + 1024))
+
     def first_weights(self):
         return (self.w_qkv,)
 
@@ -83,8 +92,9 @@ class Attention(Part):
         qkv = nbytes((n_tokens, (self.nh + 2 * self.nkv) * self.hd), self.dtype)
         out = nbytes((n_tokens, self.nh * self.hd), self.dtype)
         h = nbytes((n_tokens, self.hidden), self.dtype)  # the normalised input, when it is written out
-        # split partials of decoding: sequences x heads x splits cells, and splits <= 2 SMs / (sequences x kv heads) + 1
-        cells = self.group * (2 * 256 + n_seqs * self.nkv)
+        # split partials of decoding: sequences x heads x splits cells; (sequences x kv heads) x splits is at most
+        # 2 SMs + (sequences x kv heads), or three waves of resident blocks (`decode_splits`); up to 256 SMs
+        cells = self.group * max(2 * 256 + n_seqs * self.nkv, 3 * 256 * (self._decode_resident() or 0))
         part = nbytes((cells * self.hd,), torch.float32) + nbytes((cells * 2,), torch.float32)
         return qkv + out + h + part
 
@@ -99,7 +109,7 @@ class Attention(Part):
         tables = self.positions.rotation_tables() if hasattr(self.positions, "rotation_tables") else None
         if ctx.all_single and tables is not None:
             # one token per sequence: rotation, append and attention in one kernel
-            splits = ctx.decode_splits(self.nkv)
+            splits = ctx.decode_splits(self.nkv, self._decode_resident())
             part_o = part_ml = None
             if splits > 1:
                 part_o = ws.alloc((ctx.n_seqs * self.nh * splits * self.hd,), torch.float32)
@@ -116,7 +126,7 @@ class Attention(Part):
         with ctx.prof("rope_kv_append"):
             self.positions.encode_and_append(ctx, qkv, cache, self.nh, self.nkv)
         if ctx.all_single:
-            splits = ctx.decode_splits(self.nkv)
+            splits = ctx.decode_splits(self.nkv, self._decode_resident())
             part_o = part_ml = None
             if splits > 1:
                 part_o = ws.alloc((ctx.n_seqs * self.nh * splits * self.hd,), torch.float32)
