@@ -283,12 +283,189 @@ gemv_mma_kernel(const __nv_bfloat16* __restrict__ act, int lda, const float* __r
   }
 }
 
+// The same product for outputs so wide that every SM would get several blocks of 16 columns one after the other
+// (the vocabulary, the projections of a wide model): a fixed number of blocks, 16 warps' worth an SM, each of which
+// stages the activations once and walks the groups of 16 columns blockIdx.x, blockIdx.x + gridDim.x, ...; the first
+// weights of a block's next group are on their way while the warps' partial tiles of this one are added up and
+// stored.  (One block a group: 384 to 3,072 blocks came in one and a half to seven waves, each block staged all
+// activations again, and nothing streamed while a block staged, reduced and stored.)  All of K in one chunk of
+// activations; no norm prologue, no residual epilogue (none of the wide products has them).
+template <int EPI, typename TOut, int NT, int MAXW, int UN>
+__global__ void __launch_bounds__(MAXW * 32, GM_MAX_WARPS / MAXW)
+gemv_mma_walk_kernel(const __nv_bfloat16* __restrict__ act, int lda, const __nv_bfloat16* __restrict__ W,
+                     const __nv_bfloat16* __restrict__ W2, TOut* out, int ldo, int M, int N, int K,
+                     int pitch /* bfloat16 elements per activation row in shared memory */, int n_groups,
+                     const uint8_t* next0, unsigned long long next0_bytes, const uint8_t* next1, unsigned long long next1_bytes) {
+  constexpr int NW = EPI == GM_SWIGLU ? 2 : 1;
+  constexpr int ROWS = 8 * NT;
+  const int GM_WARPS = blockDim.x >> 5;
+  extern __shared__ __align__(16) uint8_t gm_smem[];
+  __nv_bfloat16* As = reinterpret_cast<__nv_bfloat16*>(gm_smem);                       // [ROWS][pitch]
+  float* red = reinterpret_cast<float*>(gm_smem + (size_t)ROWS * pitch * 2);           // [2][GM_WARPS][NW][NT][32][4]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int gid = lane >> 2, tig = lane & 3;
+  const int n_kb = (K + 31) / 32;
+  int grp = blockIdx.x;
+  int ra = min(grp * GM_COLS + gid, N - 1), rb = min(grp * GM_COLS + gid + 8, N - 1);  // the two weight rows of this lane (clamped)
+
+  constexpr bool EARLY = NW == 1;   // (as in the kernel above: a whole round ahead with one weight, a K block with two)
+  uint4 ea[EARLY ? UN : 1], eb[EARLY ? UN : 1];
+  auto load_round = [&](int kb0) {
+#pragma unroll
+    for (int u = 0; u < (EARLY ? UN : 0); ++u) {
+      const int kb = kb0 + u * GM_WARPS;
+      const int k = kb * 32 + tig * 8;
+      const bool ok = kb < n_kb && k < K;
+      ea[u] = ok ? *reinterpret_cast<const uint4*>(W + (size_t)ra * K + k) : make_uint4(0, 0, 0, 0);
+      eb[u] = ok ? *reinterpret_cast<const uint4*>(W + (size_t)rb * K + k) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  uint4 pa[NW], pb[NW];
+  auto load_first = [&]() {
+    const int k = warp * 32 + tig * 8;
+    const bool ok = warp < n_kb && k < K;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) {
+      const __nv_bfloat16* Wp = w == 0 ? W : W2;
+      pa[w] = ok ? *reinterpret_cast<const uint4*>(Wp + (size_t)ra * K + k) : make_uint4(0, 0, 0, 0);
+      pb[w] = ok ? *reinterpret_cast<const uint4*>(Wp + (size_t)rb * K + k) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  if (EARLY) load_round(warp);
+  else load_first();
+  if (threadIdx.x == 0) {
+    gm_prefetch_slice(next0, next0_bytes);
+    gm_prefetch_slice(next1, next1_bytes);
+  }
+  pdl_launch_dependents();
+  pdl_wait();  // from here on: activations that the kernel before this one wrote
+  // ---- activations into shared memory, once (rows >= M are zero)
+  {
+    const int kvec = K / 8;
+    for (int i = threadIdx.x; i < ROWS * kvec; i += blockDim.x) {
+      const int r = i / kvec, k = (i - r * kvec) * 8;
+      __nv_bfloat16* dst = As + (size_t)r * pitch + k;
+      if (r < M)
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(act + (size_t)r * lda + k) : "memory");
+      else
+        *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+  }
+  __syncthreads();
+
+  for (int it = 0; grp < n_groups; ++it) {
+    float acc[NW][NT][4];
+#pragma unroll
+    for (int w = 0; w < NW; ++w)
+#pragma unroll
+      for (int t = 0; t < NT; ++t)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[w][t][j] = 0.f;
+    if constexpr (EARLY) {
+      for (int kb0 = warp; kb0 < n_kb; kb0 += GM_WARPS * UN) {
+        if (kb0 != warp) load_round(kb0);
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+          const int kb = kb0 + u * GM_WARPS;
+          const int k = kb * 32 + tig * 8;
+          const bool ok = kb < n_kb && k < K;
+#pragma unroll
+          for (int t = 0; t < NT; ++t) {
+            const uint4 av = ok ? *reinterpret_cast<const uint4*>(As + (size_t)(t * 8 + gid) * pitch + k) : make_uint4(0, 0, 0, 0);
+            mma_bf16_16x8x16(acc[0][t], ea[u].x, eb[u].x, ea[u].y, eb[u].y, av.x, av.y);
+            mma_bf16_16x8x16(acc[0][t], ea[u].z, eb[u].z, ea[u].w, eb[u].w, av.z, av.w);
+          }
+        }
+      }
+    } else {
+      for (int kb0 = warp; kb0 < n_kb; kb0 += GM_WARPS * UN) {
+        uint4 wa[UN][NW], wb[UN][NW];
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+          const int kb = kb0 + u * GM_WARPS;
+          const int k = kb * 32 + tig * 8;
+          const bool ok = kb < n_kb && k < K;
+#pragma unroll
+          for (int w = 0; w < NW; ++w) {
+            if (u == 0 && kb0 == warp) {
+              wa[u][w] = pa[w];
+              wb[u][w] = pb[w];
+            } else {
+              const __nv_bfloat16* Wp = w == 0 ? W : W2;
+              wa[u][w] = ok ? *reinterpret_cast<const uint4*>(Wp + (size_t)ra * K + k) : make_uint4(0, 0, 0, 0);
+              wb[u][w] = ok ? *reinterpret_cast<const uint4*>(Wp + (size_t)rb * K + k) : make_uint4(0, 0, 0, 0);
+            }
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+          const int kb = kb0 + u * GM_WARPS;
+          const int k = kb * 32 + tig * 8;
+          const bool ok = kb < n_kb && k < K;
+#pragma unroll
+          for (int t = 0; t < NT; ++t) {
+            const uint4 av = ok ? *reinterpret_cast<const uint4*>(As + (size_t)(t * 8 + gid) * pitch + k) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int w = 0; w < NW; ++w) {
+              mma_bf16_16x8x16(acc[w][t], wa[u][w].x, wb[u][w].x, wa[u][w].y, wb[u][w].y, av.x, av.y);
+              mma_bf16_16x8x16(acc[w][t], wa[u][w].z, wb[u][w].z, wa[u][w].w, wb[u][w].w, av.z, av.w);
+            }
+          }
+        }
+      }
+    }
+    // ---- the next group's first weights set out; then the warps' partial tiles are added (in the order of the
+    // warps) and stored by warp 0, out of the half of `red` that belongs to this turn
+    const int n0 = grp * GM_COLS;
+    grp += gridDim.x;
+    if (grp < n_groups) {
+      ra = min(grp * GM_COLS + gid, N - 1), rb = min(grp * GM_COLS + gid + 8, N - 1);
+      if (EARLY) load_round(warp);
+      else load_first();
+    }
+    float* turn = red + (size_t)(it & 1) * GM_WARPS * NW * NT * 128;
+    float* mine = turn + (size_t)warp * NW * NT * 128;
+#pragma unroll
+    for (int w = 0; w < NW; ++w)
+#pragma unroll
+      for (int t = 0; t < NT; ++t)
+        *reinterpret_cast<float4*>(mine + ((w * NT + t) * 32 + lane) * 4) = make_float4(acc[w][t][0], acc[w][t][1], acc[w][t][2], acc[w][t][3]);
+    __syncthreads();
+    if (warp != 0) continue;
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      float s[NW][4];
+#pragma unroll
+      for (int w = 0; w < NW; ++w) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s[w][j] = 0.f;
+        for (int ww = 0; ww < GM_WARPS; ++ww) {
+          const float4 p = *reinterpret_cast<const float4*>(turn + (((size_t)ww * NW + w) * NT + t) * 128 + lane * 4);
+          s[w][0] += p.x; s[w][1] += p.y; s[w][2] += p.z; s[w][3] += p.w;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int n = n0 + gid + (j >> 1) * 8;
+        const int m = t * 8 + tig * 2 + (j & 1);
+        if (n < N && m < M) {
+          const size_t idx = (size_t)m * ldo + n;
+          if (EPI == GM_STORE) out[idx] = from_f32<TOut>(s[0][j]);
+          if (EPI == GM_SWIGLU) out[idx] = from_f32<TOut>(gm_silu(s[0][j]) * s[NW - 1][j]);
+        }
+      }
+    }
+  }
+}
+
 // What the next launch from this thread prefetches (set by edgelm_gemv_mma_prefetch_next, cleared by the launch).
 struct NextWeights {
   const uint8_t* p;
   unsigned long long bytes;
 };
 static thread_local NextWeights g_next[2] = {{nullptr, 0}, {nullptr, 0}};
+static int g_walk = 1;   // 0: wide outputs also go to the kernel of one block a column group (comparisons)
 
 // Activation row pitch in shared memory: K rounded up so that pitch * 2 bytes = 64 (mod 128); then
 // the fragment reads of a quarter-warp (two rows, four 16-byte chunks each) hit distinct banks.
@@ -318,6 +495,52 @@ static int launch_gemv_mma(const void* act, int lda, const float* x, const float
     while (GM_WARPS < GM_MAX_WARPS && GM_WARPS * 2 <= (n_kb + 1) / 2) GM_WARPS *= 2;
   } else if (blocks < 8 * 148) {
     while (GM_WARPS < GM_MAX_WARPS && n_kb > GM_WARPS * un) GM_WARPS *= 2;
+  }
+  if constexpr (!NORM && EPI != GM_RESIDUAL) {
+    // outputs of at least two blocks of 16 columns for every SM, all of K in one chunk: the walking kernel, 16 warps'
+    // worth of blocks an SM, a block's warps as many as it takes to have all of K in flight in one round
+    // (measured at 8 rows: N 6144, K 2048: 8.6 -> 7.4 us; N 2 x 8192, K 2048: 16.5 -> 15.5; N 49152, K 2048: 41.0 -> 34.3;
+    // a short K loses a little, N 49152, K 576: 10.5 -> 11.0 us, and keeps the other kernel)
+    if (g_walk && blocks >= 2 * 148 && K <= GM_K_CHUNK && K >= 1024) {
+      int ww = 4;
+      while (ww < GM_MAX_WARPS && ww * un < n_kb) ww *= 2;
+      static int n_sms = 0;
+      if (n_sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
+        if (n_sms <= 0) n_sms = 148;
+      }
+      const int grid = blocks < n_sms * (GM_MAX_WARPS / ww) ? blocks : n_sms * (GM_MAX_WARPS / ww);
+      const size_t wsmem = (size_t)8 * NT * pitch * 2 + (size_t)2 * ww * NW * NT * 128 * 4;
+      auto walk = [&](auto kern) -> int {
+        if (wsmem > 48 * 1024) {
+          cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)wsmem);
+          if (e != cudaSuccess) {
+            set_error("gemv_mma: %zu bytes of shared memory refused (K = %d): %s", wsmem, K, cudaGetErrorString(e));
+            return -2;
+          }
+        }
+        cudaError_t le = launch_pdl(1, kern, dim3(grid), dim3(ww * 32), wsmem, stream, (const __nv_bfloat16*)act, lda,
+                                    (const __nv_bfloat16*)W, (const __nv_bfloat16*)W2, (TOut*)out, ldo, M, N, K, pitch, blocks,
+                                    g_next[0].p, g_next[0].bytes, g_next[1].p, g_next[1].bytes);
+        if (le != cudaSuccess) {
+          set_error("gemv_mma: launch failed: %s", cudaGetErrorString(le));
+          return -2;
+        }
+        return 0;
+      };
+      if constexpr (NW == 1) {
+        if (deep) {
+          if (ww <= 4) return walk(gemv_mma_walk_kernel<EPI, TOut, NT, 4, 8>);
+          if (ww <= 8) return walk(gemv_mma_walk_kernel<EPI, TOut, NT, 8, 8>);
+          return walk(gemv_mma_walk_kernel<EPI, TOut, NT, 16, 8>);
+        }
+      }
+      if (ww <= 4) return walk(gemv_mma_walk_kernel<EPI, TOut, NT, 4, 4>);
+      if (ww <= 8) return walk(gemv_mma_walk_kernel<EPI, TOut, NT, 8, 4>);
+      return walk(gemv_mma_walk_kernel<EPI, TOut, NT, 16, 4>);
+    }
   }
   const size_t smem = (size_t)8 * NT * pitch * 2 + (size_t)GM_WARPS * NW * NT * 128 * 4 + 8 * NT * 4;
   auto go = [&](auto kern) -> int {
@@ -388,6 +611,12 @@ extern "C" int edgelm_gemv_mma(const void* act, int lda, const float* norm_w, fl
   g_next[0] = g_next[1] = NextWeights{nullptr, 0};
   if (rc) return rc;
   EL_LAUNCH_CHECK("gemv_mma");
+  return 0;
+}
+
+// 1 (default): wide outputs (at least 296 groups of 16 columns, K from 1,024 to 4,096) go to the walking kernel; 0: never.
+extern "C" int edgelm_gemv_mma_walk(int on) {
+  g_walk = on ? 1 : 0;
   return 0;
 }
 

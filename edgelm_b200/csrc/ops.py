@@ -48,6 +48,8 @@ def lib():
                     loaded.edgelm_gemm_tc_persistent(int(os.environ["EDGELM_GEMM_TC_PERSISTENT"]))
                 if os.environ.get("EDGELM_GEMM_TC_NARROW") is not None:
                     loaded.edgelm_gemm_tc_narrow(int(os.environ["EDGELM_GEMM_TC_NARROW"]))
+                if os.environ.get("EDGELM_GEMV_WALK") is not None:
+                    loaded.edgelm_gemv_mma_walk(int(os.environ["EDGELM_GEMV_WALK"]))
                 if os.environ.get("EDGELM_DECODE_CLUSTER") is not None:
                     loaded.edgelm_attn_decode_cluster(int(os.environ["EDGELM_DECODE_CLUSTER"]))
                 if os.environ.get("EDGELM_PDL") is not None:
@@ -204,6 +206,12 @@ def gemv_mma(a, w, out, epilogue=EPI_STORE, w2=None, residual=None, norm_weight=
         _check(lib().edgelm_gemv_mma_prefetch_next(regions[0][0], regions[0][1], regions[1][0], regions[1][1]), launches=0)
     _check(lib().edgelm_gemv_mma(_p(a), a.stride(0), _p(norm_weight), ctypes.c_float(eps), _p(w), _p(w2), _p(out), out.stride(0),
                                  _p(residual), M, N, K, _dt(out), epilogue, _stream()))
+
+
+def gemv_mma_walk(on):
+    """Whether few-rows products with wide outputs (at least 296 groups of 16 columns, K up to 4,096) run on the
+    kernel whose blocks walk several column groups (default) or on the one of a block per group."""
+    lib().edgelm_gemv_mma_walk(int(bool(on)))
 
 
 def gemm_tc_takes(a, w, out, w2=None):

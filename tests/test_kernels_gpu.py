@@ -569,6 +569,36 @@ def test_gemv_mma_row_independent_of_batch_and_refusals():
         o.gemv_mma(rnd((17, 96), torch.bfloat16, 1), w, torch.zeros(17, 50, device=dev()))
 
 
+@pytest.mark.parametrize("M,N,K", [(8, 6144, 2048), (3, 4744, 1032), (16, 8192, 2048), (1, 49152, 1024), (12, 5000, 4096), (5, 4736, 576)])
+def test_gemv_mma_wide_outputs_on_the_walking_kernel(M, N, K):
+    """Outputs wide enough for the kernel whose blocks walk several groups of 16 columns: a ragged last group, one and
+    two tiles of rows, one and several rounds of K, K that is no multiple of 32; against float64 and against the kernel
+    of one block a group."""
+    o = ops()
+    a = rnd((M, K), torch.bfloat16, 83)
+    w = rnd((N, K), torch.bfloat16, 84, 0.2)
+    w2 = rnd((N, K), torch.bfloat16, 85, 0.2)
+    want = a.double().cpu() @ w.double().cpu().T
+    u = a.double().cpu() @ w2.double().cpu().T
+    got = {}
+    for walk in (True, False):
+        o.gemv_mma_walk(walk)
+        try:
+            out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev())
+            o.gemv_mma(a, w, out)
+            out32 = torch.full((M, N), float("nan"), dtype=torch.float32, device=dev())
+            o.gemv_mma(a, w, out32, prefetch=(w2,))
+            sw = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev())
+            o.gemv_mma(a, w, sw, epilogue=o.EPI_SWIGLU, w2=w2)
+            torch.cuda.synchronize()
+        finally:
+            o.gemv_mma_walk(True)
+        assert rel_err(out, want) < 1.6e-2 and rel_err(out32, want) < 2e-5
+        assert rel_err(sw, want / (1 + torch.exp(-want)) * u) < 1.6e-2
+        got[walk] = (out32, sw)
+    assert rel_err(got[True][0], got[False][0].double().cpu()) < 1e-5   # (the warps may share K differently: last bits)
+
+
 def test_gemv_mma_prefetch_of_the_next_weights_changes_no_result():
     """The hint that starts other tensors on their way into L2: odd sizes (not a multiple of the blocks' slices),
     one and two regions, more blocks than 16-byte pieces; the product is the same bit for bit and the regions are
