@@ -136,7 +136,7 @@ def main(argv=None):
             whole = stamps[-1].cpu()
             st = stamps[:-1].view(2, 64, 8).cpu()
             print("block: " + ", ".join(f"{nm} {(whole[i + 1] - whole[i]).item()}" for i, nm in enumerate(
-                ["prologue", "wait for the kernel before", "key blocks", "accumulator", "merge and store", "last barrier"])))
+                ["prologue", "wait for the kernel before", "key blocks", "last product and (m, l)", "merge and store", "last barrier"])))
             names = ["wait S", "scores to P", "wait P V", "(gap)", "rescale", "arrive"]
             for grp in range(2):
                 n = int((st[grp, :, 0] > 0).sum())
