@@ -166,6 +166,34 @@ class SequenceCache:
         self.length[slot] = 0
         self.slots.give(slot)
 
+    def footprint(self, length):
+        """Tokens of room, in whole pages, that one sequence of `length` tokens takes from the fullest key/value
+        group; 0 for a model whose mixers keep states of fixed size only (such a model is bound by slots alone)."""
+        return max((pages_for(length) * PAGE for _ in self.kv_groups), default=0)
+
+    @property
+    def capacity_tokens(self):
+        """Tokens of room for live sequences, each counted by `footprint`; None: no bound but the slots."""
+        return self.n_pages * PAGE if self.kv_groups else None
+
+    def storage_bytes(self):
+        total = 0
+        for g in self.groups:
+            for t in (getattr(g, "k", None), getattr(g, "v", None), getattr(g, "state", None)):
+                if t is not None:
+                    total += t.numel() * t.element_size()
+        return total
+
+    def describe(self):
+        """Lines for people: slots, and each group's storage as the group accounts for it."""
+        lines = [f"{self.n_slots} slots, {self.storage_bytes() / 1e6:.2f} MB"]
+        for g in self.kv_groups:
+            lines.append(f"  keys/values of {g.n_entries} layer run(s): {g.need.n_kv_heads} heads of {g.need.head_dim}, {self.n_pages} pages "
+                         f"of {PAGE} tokens, {g.bytes_per_token(torch.empty(0, dtype=self.dtype).element_size())} B a token")
+        for g in self.state_groups:
+            lines.append(f"  fixed-size state of {g.n_entries} layer run(s): float32 {list(g.need.shape)} a sequence")
+        return lines
+
     def tokens_held(self):
         """Tokens of room that live sequences hold, in whole pages."""
         return max((int(g.n_held.sum()) * PAGE for g in self.kv_groups), default=0)

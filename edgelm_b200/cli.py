@@ -58,18 +58,15 @@ def _engine(args, model, slots=None, profile=False):
 
 
 def _describe(model, engine):
-    cfg = model.config
-    lines = [
-        f"model   : {type(cfg).__name__} {str(model.dtype).replace('torch.', '')} weights, {model.weight_bytes() / 1e6:.1f} MB, "
-        f"vocab {cfg.vocab_size}, dim {cfg.hidden_size}, {cfg.num_hidden_layers} layers, "
-        f"{cfg.num_attention_heads}/{cfg.num_key_value_heads} heads of {cfg.head_dim}, ffn {cfg.intermediate_size}",
-        f"schedule: {len(model.schedule)} layer runs over {len(model.layers)} layers; parts "
-        f"{model.layers[0].mixer.kind} + {model.layers[0].ffn.kind}, block {model.plan.layers[0].block}",
-        f"kv cache: {engine.cache.n_pages} pages of 64 tokens in {len(engine.cache.kv_groups)} group(s), "
-        f"{engine.cache.bytes_per_token()} B per token, {engine.cache.n_pages * 64 * engine.cache.bytes_per_token() / 1e6:.2f} MB; "
-        f"{engine.cache.n_slots} slots",
-        f"arena   : {engine.ws.capacity / 1e6:.2f} MB for steps of up to {engine.max_step_tokens} tokens",
-    ]
+    """What `info` and `run --verbose` print: the model as its parts describe themselves (no architecture's
+    configuration fields are read here), the cache as it accounts for itself, the step's workspace."""
+    desc = model.describe()
+    lines = [f"model   : {type(model.config).__name__ if getattr(model, 'config', None) is not None else 'plan'}, {desc[0]}"]
+    lines += [f"          {l.strip()}" for l in desc[1:]]
+    lines += [f"cache   : {l}" for l in engine.cache.describe()]
+    peak = f", {100.0 * engine.ws.peak / engine.ws.capacity:.0f} % used so far" if engine.ws.peak else ""
+    lines.append(f"arena   : {engine.ws.capacity / 1e6:.2f} MB for steps of up to {engine.max_step_tokens} tokens and "
+                 f"{engine.max_step_seqs} sequences{peak}")
     return "\n".join(lines)
 
 
@@ -145,8 +142,7 @@ def cmd_bench(args):
         row = {"dtype": str(model.dtype).replace("torch.", ""), "batch": b, "prompt": P, "gen": G,
                "prefill_tok_s": round(statistics.median(pre), 2), "ttft_ms": round(statistics.median(ttft), 2),
                "decode_tok_s": round(statistics.median(dec), 2), "weights_mb": round(model.weight_bytes() / 1e6, 2),
-               "arena_mb": round(engine.ws.capacity / 1e6, 3),
-               "kv_mb": round(engine.cache.n_pages * 64 * engine.cache.bytes_per_token() / 1e6, 2)}
+               "arena_mb": round(engine.ws.capacity / 1e6, 3), "cache_mb": round(engine.cache.storage_bytes() / 1e6, 2)}
         if args.json:
             print(json.dumps(row))
         else:
@@ -165,7 +161,7 @@ def cmd_info(args):
         for i, e in enumerate(model.schedule):
             layer = model.layers[e.layer]
             reads = f" (reads the cache of run {e.reads_cache_of})" if e.reads_cache_of is not None else ""
-            print(f"  {i + 1:3d} {model.plan.layers[e.layer].block:<8} {layer.prefix}: norm -> {layer.mixer.kind} -> norm -> {layer.ffn.kind}{reads}")
+            print(f"  {i + 1:3d} {getattr(layer, 'prefix', '')} {layer.describe()}{reads}")
         print(f"  {len(model.schedule) + 1:3d} final norm + {model.head.kind}")
     return 0
 

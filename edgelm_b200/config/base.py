@@ -74,6 +74,19 @@ class ModelPlan:
     stop_token_ids: Tuple[int, ...] = ()
     bos_token_id: Optional[int] = None
 
+    def first_runs(self, n):
+        """The same plan cut to its first `n` schedule entries (and the layers they name): a shallower model of the
+        same layer sizes, for runs where the full depth costs too much memory or time."""
+        import dataclasses
+        n = int(n)
+        if not 1 <= n <= len(self.schedule):
+            raise ConfigError(f"a plan of {len(self.schedule)} layer runs cannot be cut to {n}")
+        schedule = self.schedule[:n]
+        used = sorted({e.layer for e in schedule})
+        renumber = {old: new for new, old in enumerate(used)}
+        return dataclasses.replace(self, layers=tuple(self.layers[i] for i in used),
+                                   schedule=tuple(ScheduleEntry(renumber[e.layer], e.reads_cache_of) for e in schedule)).validate()
+
     def validate(self):
         if not self.layers or not self.schedule:
             raise ConfigError("a model needs at least one layer and one schedule entry")

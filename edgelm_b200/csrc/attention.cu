@@ -244,7 +244,7 @@ attn_decode_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ld
                    const int32_t* __restrict__ page_table, int table_stride, const int32_t* __restrict__ seq_slot,
                    const int32_t* __restrict__ seq_pos, int nh, int nkv, int hd, float scale, int n_splits, int tk,
                    float* __restrict__ part_o, float* __restrict__ part_ml, int* err,
-                   const float* __restrict__ cos_t, const float* __restrict__ sin_t, int max_pos, int* counters) {
+                   const float* __restrict__ cos_t, const float* __restrict__ sin_t, int max_pos) {
   // cos_t given: q, k, v are the raw projections of the new token; this kernel rotates q and k at
   // the token's position (float32, half-split pairing, rounded to T as the stand-alone kernel
   // stores them) and the block that owns the token's page appends k and v to the cache.
@@ -529,53 +529,6 @@ attn_decode_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ld
       }
     }
   }
-  // ---- with a counter per (sequence, kv head): the block that finishes last folds the splits itself,
-  // in the order of the splits, which saves the second kernel; it leaves the counter at zero again
-  if (n_splits > 1 && counters != nullptr) {
-    __shared__ int is_last;
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) is_last = atomicAdd(&counters[seq * nkv + kvh], 1) == n_splits - 1;
-    __syncthreads();
-    if (is_last) {
-      __threadfence();
-      // weights of the splits per head in shared memory first (a warp per head, lanes over splits), then
-      // every thread folds its output elements with one independent load per split
-      float* wts = Ps;                                     // [heads of a chunk][n_splits], at most 1024 floats
-      float* linv = Wp;                                    // [heads of a chunk]
-      const int chunk = max(1, min(g, (DEC_WARPS * RW * 64) / n_splits));
-      for (int hc = 0; hc < g; hc += chunk) {
-        const int nhead = min(chunk, g - hc);
-        __syncthreads();
-        for (int hi = warp; hi < nhead; hi += DEC_WARPS) {
-          const size_t base = ((size_t)seq * nh + kvh * g + hc + hi) * n_splits;
-          float mx = -CUDART_INF_F;
-          for (int sp = lane; sp < n_splits; sp += 32) mx = fmaxf(mx, __ldcg(part_ml + (base + sp) * 2));
-          mx = warp_max(mx);
-          float lsum = 0.f;
-          for (int sp = lane; sp < n_splits; sp += 32) {
-            const float ms = __ldcg(part_ml + (base + sp) * 2);
-            const float f = ms == -CUDART_INF_F ? 0.f : expf(ms - mx);  // a split that held no page weighs nothing
-            wts[hi * n_splits + sp] = f;
-            lsum = fmaf(__ldcg(part_ml + (base + sp) * 2 + 1), f, lsum);
-          }
-          lsum = warp_sum(lsum);
-          if (lane == 0) linv[hi] = 1.0f / lsum;
-        }
-        __syncthreads();
-        for (int i = threadIdx.x; i < nhead * hd; i += blockDim.x) {
-          const int hi = i / hd, d = i - hi * hd;
-          const int head = kvh * g + hc + hi;
-          const size_t base = ((size_t)seq * nh + head) * n_splits;
-          float o = 0.f;
-#pragma unroll 4
-          for (int sp = 0; sp < n_splits; ++sp) o = fmaf(__ldcg(part_o + (base + sp) * hd + d), wts[hi * n_splits + sp], o);
-          out[(size_t)seq * ldo + head * hd + d] = from_f32<T>(o * linv[hi]);
-        }
-      }
-      if (threadIdx.x == 0) counters[seq * nkv + kvh] = 0;
-    }
-  }
 }
 
 }  // namespace edgelm
@@ -624,16 +577,10 @@ int launch_prefill(const void* q, int ldq, void* out, int ldo, const void* kc, c
   return 0;
 }
 
-// Device error word that decode attention reports a copy that never arrived to (may stay null:
-// the affected rows are then NaN, which no caller can overlook).
+// Device error word that decode attention reports a copy that never arrived to when its caller names none (the
+// entry point without allocations); may stay null: the affected rows are then NaN, which no caller can overlook.
 static int* g_attn_err = nullptr;
 static int g_decode_cuda_cores = 0;  // 1: decode attention on the CUDA-core kernel even where the tensor-core one applies
-// 1: up to 8 splits of the tensor-core decode attention are launched as one thread-block cluster whose first block folds
-// them out of the others' shared memory.  Off: the kernel alone is as fast either way (8.8 us at 8 sequences of 1,500
-// keys, 9 / 3 heads; 19.1 against 20.6 us at 64), but whole decode steps are slower with it (135M sizes, 16 sequences:
-// 1.22 against 1.17 ms; 1.7B sizes, 8 sequences: 2.33 against 2.00 ms): a cluster waits for room in one GPC while the
-// blocks of the kernels around it come and go.
-static int g_decode_cluster = 0;
 static int g_decode_last_launches = 1;
 
 // Keys per tile: the largest power of two up to 64 whose K rows fit DEC_TILE_BYTES.
@@ -646,25 +593,21 @@ static int decode_tile_keys(int hd, size_t elem) {
 template <typename T, int NC>
 int launch_decode(const void* q, int ldq, void* out, int ldo, const void* kc, const void* vc, const int32_t* page_table,
                   int table_stride, const int32_t* seq_slot, const int32_t* seq_pos, int n_seqs, int nh, int nkv, int hd,
-                  float scale, int n_splits, float* part_o, float* part_ml, cudaStream_t stream,
-                  const float* cos_t = nullptr, const float* sin_t = nullptr, int max_pos = 0, int* counters = nullptr) {
+                  float scale, int n_splits, float* part_o, float* part_ml, int* err, cudaStream_t stream,
+                  const float* cos_t = nullptr, const float* sin_t = nullptr, int max_pos = 0) {
   constexpr int NP = NC <= 2 ? 1 : NC / 2;  // pairs of dims per lane: ceil(hd / 64)
   dim3 grid(n_seqs, nkv, n_splits);
   cudaError_t le = cudaSuccess;
-  bool on_mma = false, folded = false;
+  bool on_mma = false;
+  if (err == nullptr) err = g_attn_err;
   if constexpr (sizeof(T) == 2) {
     // bfloat16 with a head size the MMAs tile (32, 64, 96, 128): the tensor-core kernel, whatever the number of
     // query heads a kv head (with one, 15 of the 16 rows are zero, but the kernel is bound by the cache's bytes:
-    // measured at 32/32 heads, 1,500 keys, batch 64: 136 us against the CUDA-core kernel's 210 us).  It folds the
-    // splits with the combine kernel only (no counters).
+    // measured at 32/32 heads, 1,500 keys, batch 64: 136 us against the CUDA-core kernel's 210 us).
     const bool aligned = ldq % 8 == 0 && (uintptr_t)q % 16 == 0;   // it reads the query rows 16 bytes at a time
-    if ((hd == 32 || hd == 64 || hd == 96 || hd == 128) && counters == nullptr && !g_decode_cuda_cores && aligned) {
+    if ((hd == 32 || hd == 64 || hd == 96 || hd == 128) && !g_decode_cuda_cores && aligned) {
       on_mma = true;
       const size_t smem = decode_mma_head_bytes(hd) + (size_t)DEC_WARPS * 2 * PAGE * (hd + 8) * 2;
-      // The splits of a (sequence, kv head) as one thread-block cluster whose first block folds them out of the others'
-      // shared memory: no partial results in global memory and no second kernel.  Up to 8 splits (the portable cluster
-      // size), one pass of query heads.
-      folded = g_decode_cluster && n_splits > 1 && n_splits <= 8 && nh / nkv <= DM_ROWS;
       auto go = [&](auto kern) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
@@ -673,26 +616,18 @@ int launch_decode(const void* q, int ldq, void* out, int ldo, const void* kc, co
         cfg.blockDim = dim3(DEC_WARPS * 32);
         cfg.dynamicSmemBytes = smem;
         cfg.stream = stream;
-        cudaLaunchAttribute attr[2];
+        cudaLaunchAttribute attr[1];
         int n_attr = 0;
         if (pdl_enabled() & 2) {
           attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
           attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
           ++n_attr;
         }
-        if (folded) {
-          attr[n_attr].id = cudaLaunchAttributeClusterDimension;
-          attr[n_attr].val.clusterDim.x = 1;
-          attr[n_attr].val.clusterDim.y = 1;
-          attr[n_attr].val.clusterDim.z = (unsigned)n_splits;
-          ++n_attr;
-        }
         cfg.attrs = attr;
         cfg.numAttrs = n_attr;
         return cudaLaunchKernelEx(&cfg, kern, (const __nv_bfloat16*)q, ldq, (__nv_bfloat16*)out, ldo,
                                   (__nv_bfloat16*)const_cast<void*>(kc), (__nv_bfloat16*)const_cast<void*>(vc), page_table, table_stride,
-                                  seq_slot, seq_pos, nh, nkv, scale, n_splits, part_o, part_ml, g_attn_err, cos_t, sin_t, max_pos,
-                                  folded ? 1 : 0);
+                                  seq_slot, seq_pos, nh, nkv, scale, n_splits, part_o, part_ml, err, cos_t, sin_t, max_pos);
       };
       switch (hd / 16) {
         case 2: le = go(attn_decode_mma_kernel<2>); break;
@@ -714,10 +649,10 @@ int launch_decode(const void* q, int ldq, void* out, int ldo, const void* kc, co
     // both kernels are programmatic dependent launches when that is switched on
     le = launch_pdl(2, kern, grid, dim3(DEC_WARPS * 32), smem, stream, (const T*)q, ldq, (T*)out, ldo,
                     (T*)const_cast<void*>(kc), (T*)const_cast<void*>(vc), page_table, table_stride, seq_slot, seq_pos,
-                    nh, nkv, hd, scale, n_splits, tk, part_o, part_ml, g_attn_err, cos_t, sin_t, max_pos, counters);
+                    nh, nkv, hd, scale, n_splits, tk, part_o, part_ml, err, cos_t, sin_t, max_pos);
   }
-  g_decode_last_launches = n_splits > 1 && counters == nullptr && !folded ? 2 : 1;
-  if (le == cudaSuccess && n_splits > 1 && counters == nullptr && !folded) {
+  g_decode_last_launches = n_splits > 1 ? 2 : 1;
+  if (le == cudaSuccess && n_splits > 1) {
     dim3 cgrid(n_seqs, nh);
     le = launch_pdl(2, attn_decode_combine_kernel<T>, cgrid, dim3(64), 0, stream, (const float*)part_o, (const float*)part_ml,
                     (T*)out, ldo, nh, hd, n_splits);
@@ -782,16 +717,10 @@ extern "C" int edgelm_attn_decode_on_cuda_cores(int on) {
   return 0;
 }
 
-// 1: up to 8 splits of the tensor-core decode attention are one thread-block cluster that folds them itself;
-// 0 (default): the combine kernel folds them always.
-extern "C" int edgelm_attn_decode_cluster(int on) {
-  g_decode_cluster = on ? 1 : 0;
-  return 0;
-}
 // Kernels that the last decode attention call of this process launched (1, or 2 with the combine kernel).
 extern "C" int edgelm_attn_decode_last_launches() { return g_decode_last_launches; }
 
-// The device error word (one int32) that decode attention ORs ERR_WAIT_TIMEOUT into; null: none.
+// The device error word (one int32) that decode attention ORs ERR_WAIT_TIMEOUT into when a call names none; null: none.
 extern "C" int edgelm_attn_set_error_word(int* err) {
   g_attn_err = err;
   return 0;
@@ -801,13 +730,13 @@ extern "C" int edgelm_attn_set_error_word(int* err) {
 extern "C" int edgelm_attn_decode(const void* q, int ldq, void* out, int ldo, const void* kcache, const void* vcache,
                                   int dtype, const int32_t* page_table, int table_stride, const int32_t* seq_slot,
                                   const int32_t* seq_pos, int n_seqs, int nh, int nkv, int hd, float scale, int n_splits,
-                                  float* part_o, float* part_ml, cudaStream_t stream) {
+                                  float* part_o, float* part_ml, int* err, cudaStream_t stream) {
   if (n_seqs == 0) return 0;
   if (check_heads("attn_decode", nh, nkv, hd)) return -1;
   EL_REFUSE(n_splits >= 1 && n_splits <= 65535 && nkv <= 65535, "attn_decode: bad split count %d", n_splits);
   EL_REFUSE(n_splits == 1 || (part_o && part_ml), "attn_decode: %d splits need the scratch buffers", n_splits);
   EL_ATT_DISPATCH(launch_decode, q, ldq, out, ldo, kcache, vcache, page_table, table_stride, seq_slot, seq_pos, n_seqs, nh,
-                  nkv, hd, scale, n_splits, part_o, part_ml, stream);
+                  nkv, hd, scale, n_splits, part_o, part_ml, err, stream);
   EL_LAUNCH_CHECK("attn_decode");
   return 0;
 }
@@ -820,16 +749,14 @@ extern "C" int edgelm_attn_decode_rope(const void* qkv, int ldq, void* out, int 
                                        const int32_t* page_table, int table_stride, const int32_t* seq_slot,
                                        const int32_t* seq_pos, const float* cos_t, const float* sin_t, int max_pos,
                                        int n_seqs, int nh, int nkv, int hd, float scale, int n_splits, float* part_o,
-                                       float* part_ml, int* counters, cudaStream_t stream) {
-  // counters: n_seqs * nkv int32 that are zero between calls (the kernel leaves them so); with them the
-  // splits are folded by the last block of the main kernel, without them by a second kernel.
+                                       float* part_ml, int* err, cudaStream_t stream) {
   if (n_seqs == 0) return 0;
   if (check_heads("attn_decode_rope", nh, nkv, hd)) return -1;
   EL_REFUSE(n_splits >= 1 && n_splits <= 65535 && nkv <= 65535, "attn_decode_rope: bad split count %d", n_splits);
   EL_REFUSE(n_splits == 1 || (part_o && part_ml), "attn_decode_rope: %d splits need the scratch buffers", n_splits);
   EL_REFUSE(cos_t && sin_t && max_pos > 0, "attn_decode_rope: needs the position table");
   EL_ATT_DISPATCH(launch_decode, qkv, ldq, out, ldo, kcache, vcache, page_table, table_stride, seq_slot, seq_pos, n_seqs, nh,
-                  nkv, hd, scale, n_splits, part_o, part_ml, stream, cos_t, sin_t, max_pos, counters);
+                  nkv, hd, scale, n_splits, part_o, part_ml, err, stream, cos_t, sin_t, max_pos);
   EL_LAUNCH_CHECK("attn_decode_rope");
   return 0;
 }
@@ -892,7 +819,7 @@ extern "C" int edgelm_attn_decode_noalloc(const void* q, int ldq, void* out, int
     part_ml = base + cells * hd;   // [cells][2]
   }
   EL_ATT_DISPATCH(launch_decode, q, ldq, out, ldo, kcache, vcache, page_table, table_stride, seq_slot, seq_pos, n_seqs, nh,
-                  nkv, hd, scale, n_splits, part_o, part_ml, stream);
+                  nkv, hd, scale, n_splits, part_o, part_ml, (int*)nullptr, stream);
   EL_LAUNCH_CHECK("attn_decode_noalloc");
   return 0;
 }

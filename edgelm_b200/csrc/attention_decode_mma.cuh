@@ -30,7 +30,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat
                        __nv_bfloat16* kcache, __nv_bfloat16* vcache, const int32_t* __restrict__ page_table,
                        int table_stride, const int32_t* __restrict__ seq_slot, const int32_t* __restrict__ seq_pos, int nh,
                        int nkv, float scale, int n_splits, float* __restrict__ part_o, float* __restrict__ part_ml, int* err,
-                       const float* __restrict__ cos_t, const float* __restrict__ sin_t, int max_pos, int cluster_fold) {
+                       const float* __restrict__ cos_t, const float* __restrict__ sin_t, int max_pos) {
   using T = __nv_bfloat16;
   constexpr int HD = HDT * 16;
   constexpr int PITCH = HD + 8;          // elements per padded row
@@ -212,15 +212,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat
         L = CUDART_NAN_F;
       }
       const int head = kvh * g + h0 + r;
-      if (cluster_fold) {   // (one pass: the launch sees to it) into the first warp's value tile, for the cluster's first block
-        float* mine = reinterpret_cast<float*>(dm_raw + decode_mma_head_bytes(HD) + (size_t)TILE * 2) + r * WS;
-        mine[d] = o0;
-        mine[d + 1] = o1;
-        if (d == 0) {
-          mine[HD] = M;
-          mine[HD + 1] = L;
-        }
-      } else if (n_splits == 1) {
+      if (n_splits == 1) {
         const float inv = 1.0f / L;
         *reinterpret_cast<__nv_bfloat162*>(out + (size_t)seq * ldo + head * HD + d) = __floats2bfloat162_rn(o0 * inv, o1 * inv);
       } else {
@@ -232,40 +224,6 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat
           part_ml[pi * 2 + 1] = L;
         }
       }
-    }
-    if (cluster_fold) {
-      // The splits of a (sequence, kv head) are one thread-block cluster: the first block folds them, in the order of
-      // the splits, out of the others' shared memory, and no second kernel is needed.  Same arithmetic as the combine
-      // kernel.  Every block stays until the first has read.
-      asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-      asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-      if (split == 0) {
-        const uint32_t mine = dec_smem_u32(dm_raw + decode_mma_head_bytes(HD) + (size_t)TILE * 2);
-        auto remote = [&](int s, int index) {
-          uint32_t addr;
-          float v;
-          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(mine + (uint32_t)index * 4u), "r"(s));
-          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
-          return v;
-        };
-        for (int i = threadIdx.x; i < rows * (HD / 2); i += blockDim.x) {
-          const int r = i / (HD / 2), d = (i - r * (HD / 2)) * 2;
-          float M = -CUDART_INF_F;
-          for (int s = 0; s < n_splits; ++s) M = fmaxf(M, remote(s, r * WS + HD));
-          float L = 0.f, o0 = 0.f, o1 = 0.f;
-          for (int s = 0; s < n_splits; ++s) {
-            const float ms = remote(s, r * WS + HD);
-            if (ms == -CUDART_INF_F) continue;   // a split that held no page
-            const float f = expf(ms - M);
-            L = fmaf(remote(s, r * WS + HD + 1), f, L);
-            o0 = fmaf(remote(s, r * WS + d), f, o0);
-            o1 = fmaf(remote(s, r * WS + d + 1), f, o1);
-          }
-          *reinterpret_cast<__nv_bfloat162*>(out + (size_t)seq * ldo + (kvh * g + h0 + r) * HD + d) = __floats2bfloat162_rn(o0 / L, o1 / L);
-        }
-      }
-      asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-      asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
   }
 }

@@ -433,6 +433,9 @@ static float* g_splitk_ws = nullptr;
 static size_t g_splitk_bytes = 0;
 static int g_splitk_on = 1;
 static int g_last_launches = 1;   // kernels the last edgelm_gemm_tc call launched (2 when it split K)
+// Which kernel the last edgelm_gemm_tc call took: tile columns | persistent << 12 | deep ring << 13 | K splits << 16.
+// Tests read it so that a product meant for one kernel cannot pass on another.
+static int g_last_kernel = 0;
 
 // Splits of K for a product of `tiles` one-tile blocks and `n_k` K blocks of 64: none unless the tiles would leave
 // more than half of the SMs idle and K is at least 1,024 (below that the second kernel costs more than the idle
@@ -473,6 +476,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
     const int tiles = ((N + BN - 1) / BN) * ((M + TC_BM - 1) / TC_BM);
     const int grid = tiles < n_sms ? tiles : n_sms;
     g_last_launches = 1;
+    g_last_kernel = BN | (1 << 12) | (1 << 16);
     cudaError_t le = launch_pdl(32, kern, dim3(grid), dim3(TC_THREADS), (size_t)smem, stream, ma, mb, mb2, (TOut*)out, ldo, residual, M, N, K,
                                 vec_ok, err);
     if (le != cudaSuccess) {
@@ -496,6 +500,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
     cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
   }
   const bool deep = g_tc_deep && (long long)grid.x * grid.y * grid.z <= n_sms;
+  g_last_kernel = BN | ((deep ? 1 : 0) << 13) | (splits << 16);
   auto go = [&](auto kern, int smem) -> int {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) {
@@ -554,6 +559,7 @@ extern "C" int edgelm_gemm_tc_narrow(int on) {
 }
 
 extern "C" int edgelm_gemm_tc_last_launches() { return g_last_launches; }
+extern "C" int edgelm_gemm_tc_last_kernel() { return g_last_kernel; }
 
 // 1 if the tensor-core kernel takes these operands (alignment and pitch rules of TMA), else 0.
 extern "C" int edgelm_gemm_tc_takes(const void* a, int lda, const void* w, const void* w2, int K) {

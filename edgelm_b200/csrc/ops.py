@@ -42,16 +42,6 @@ def lib():
                 except OSError as e:  # pragma: no cover
                     raise KernelError(f"edgelm_b200: cannot load the kernel library {path}: {e}") from e
                 loaded.edgelm_last_error.restype = ctypes.c_char_p
-                if os.environ.get("EDGELM_DECODE_CUDA_CORES") is not None:
-                    loaded.edgelm_attn_decode_on_cuda_cores(int(os.environ["EDGELM_DECODE_CUDA_CORES"]))
-                if os.environ.get("EDGELM_GEMM_TC_PERSISTENT") is not None:
-                    loaded.edgelm_gemm_tc_persistent(int(os.environ["EDGELM_GEMM_TC_PERSISTENT"]))
-                if os.environ.get("EDGELM_GEMM_TC_NARROW") is not None:
-                    loaded.edgelm_gemm_tc_narrow(int(os.environ["EDGELM_GEMM_TC_NARROW"]))
-                if os.environ.get("EDGELM_GEMV_WALK") is not None:
-                    loaded.edgelm_gemv_mma_walk(int(os.environ["EDGELM_GEMV_WALK"]))
-                if os.environ.get("EDGELM_DECODE_CLUSTER") is not None:
-                    loaded.edgelm_attn_decode_cluster(int(os.environ["EDGELM_DECODE_CLUSTER"]))
                 if os.environ.get("EDGELM_PDL") is not None:
                     loaded.edgelm_set_pdl(int(os.environ["EDGELM_PDL"]))
                 _lib = loaded
@@ -231,9 +221,8 @@ def _splitk_ready():
     global _splitk_scratch
     if _splitk_scratch is None and not torch.cuda.is_current_stream_capturing():
         _splitk_scratch = torch.empty(SPLITK_SCRATCH_BYTES // 4, dtype=torch.float32, device="cuda")
-        on = int(os.environ.get("EDGELM_GEMM_TC_SPLITK", "1"))
         lib().edgelm_gemm_tc_splitk.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int]
-        lib().edgelm_gemm_tc_splitk(_p(_splitk_scratch), SPLITK_SCRATCH_BYTES, on)
+        lib().edgelm_gemm_tc_splitk(_p(_splitk_scratch), SPLITK_SCRATCH_BYTES, 1)
 
 
 def gemm_tc(a, w, out, err, epilogue=EPI_STORE, w2=None, residual=None):
@@ -251,6 +240,12 @@ def gemm_tc(a, w, out, err, epilogue=EPI_STORE, w2=None, residual=None):
     _check(lib().edgelm_gemm_tc(_p(a), a.stride(0), _p(w), _p(w2), _p(out), out.stride(0), _p(residual), M, N, K, _dt(out),
                                 epilogue, _p(err), _stream()), launches=0)
     count_launches(lib().edgelm_gemm_tc_last_launches())
+
+
+def gemm_tc_last_kernel():
+    """Which kernel the last `gemm_tc` call took: {"tile_columns", "persistent", "deep_ring", "k_splits"}."""
+    v = int(lib().edgelm_gemm_tc_last_kernel())
+    return {"tile_columns": v & 0xFFF, "persistent": bool(v >> 12 & 1), "deep_ring": bool(v >> 13 & 1), "k_splits": v >> 16}
 
 
 def rope_kv_append(qkv, tok_pos, tok_seq, seq_slot, page_table, cos, sin, kcache, vcache, nh, nkv, hd, err):
@@ -338,15 +333,10 @@ def attn_prefill_tc_trace(buffer):
     lib().edgelm_attn_prefill_tc_trace(_p(buffer))
 
 
-def attn_decode_cluster(on):
-    """Whether up to 8 splits of the tensor-core decode attention fold themselves as a thread-block cluster, or leave
-    it to the combine kernel (the default: whole steps are faster that way)."""
-    lib().edgelm_attn_decode_cluster(int(bool(on)))
-
-
 def attn_decode(qkv, out, kcache, vcache, page_table, seq_slot, seq_pos, n_seqs, nh, nkv, hd, scale, n_splits=1,
-                part_o=None, part_ml=None):
-    """Attention of one new token per sequence over the paged cache, pages dealt to `n_splits` blocks."""
+                part_o=None, part_ml=None, err=None):
+    """Attention of one new token per sequence over the paged cache, pages dealt to `n_splits` blocks.
+    `err`: the device error word that a copy which never arrives is reported to."""
     _need(qkv.dtype == out.dtype == kcache.dtype and qkv.stride(1) == 1 and out.stride(1) == 1, "attn_decode: layout")
     for t, n in ((page_table, "page_table"), (seq_slot, "seq_slot"), (seq_pos, "seq_pos")):
         _i32(t, n)
@@ -355,13 +345,13 @@ def attn_decode(qkv, out, kcache, vcache, page_table, seq_slot, seq_pos, n_seqs,
         _need(part_ml is not None and part_ml.dtype == torch.float32 and part_ml.numel() >= n_seqs * nh * n_splits * 2, "attn_decode: part_ml too small")
     _check(lib().edgelm_attn_decode(_p(qkv), qkv.stride(0), _p(out), out.stride(0), _p(kcache), _p(vcache), _dt(qkv),
                                     _p(page_table), page_table.stride(0), _p(seq_slot), _p(seq_pos), n_seqs, nh, nkv, hd,
-                                    ctypes.c_float(scale), n_splits, _p(part_o), _p(part_ml), _stream()),
+                                    ctypes.c_float(scale), n_splits, _p(part_o), _p(part_ml), _p(err), _stream()),
            launches=0)
     count_launches(lib().edgelm_attn_decode_last_launches())
 
 
 def attn_decode_rope(qkv, out, kcache, vcache, page_table, seq_slot, seq_pos, cos, sin, n_seqs, nh, nkv, hd, scale,
-                     n_splits=1, part_o=None, part_ml=None, counters=None):
+                     n_splits=1, part_o=None, part_ml=None, err=None):
     """Decode attention with RoPE and the cache append fused in: `qkv` holds the raw projections of one
     new token per sequence; the rotated keys and the values are written into the cache pages."""
     _need(qkv.dtype == out.dtype == kcache.dtype and qkv.stride(1) == 1 and out.stride(1) == 1, "attn_decode_rope: layout")
@@ -369,22 +359,20 @@ def attn_decode_rope(qkv, out, kcache, vcache, page_table, seq_slot, seq_pos, co
     _need(cos.dtype == torch.float32 and cos.shape[1] == hd // 2 and cos.is_contiguous() and sin.shape == cos.shape and sin.is_contiguous(), "attn_decode_rope: table layout")
     for t, n in ((page_table, "page_table"), (seq_slot, "seq_slot"), (seq_pos, "seq_pos")):
         _i32(t, n)
-    if counters is not None:
-        _i32(counters, "counters")
-        _need(counters.numel() >= n_seqs * nkv, "attn_decode_rope: one counter per sequence and kv head")
     if n_splits > 1:
         _need(part_o is not None and part_o.dtype == torch.float32 and part_o.numel() >= n_seqs * nh * n_splits * hd, "attn_decode_rope: part_o too small")
         _need(part_ml is not None and part_ml.dtype == torch.float32 and part_ml.numel() >= n_seqs * nh * n_splits * 2, "attn_decode_rope: part_ml too small")
     _check(lib().edgelm_attn_decode_rope(_p(qkv), qkv.stride(0), _p(out), out.stride(0), _p(kcache), _p(vcache), _dt(qkv),
                                          _p(page_table), page_table.stride(0), _p(seq_slot), _p(seq_pos), _p(cos), _p(sin),
                                          cos.shape[0], n_seqs, nh, nkv, hd, ctypes.c_float(scale), n_splits, _p(part_o),
-                                         _p(part_ml), _p(counters), _stream()),
+                                         _p(part_ml), _p(err), _stream()),
            launches=0)
     count_launches(lib().edgelm_attn_decode_last_launches())
 
 
 def attn_set_error_word(err):
-    """The device int32 that decode attention reports a copy that never arrived to (bit 8)."""
+    """The device int32 that decode attention calls which name no error word of their own (the entry point that
+    allocates nothing) report a copy that never arrived to (bit 8)."""
     _check(lib().edgelm_attn_set_error_word(_p(err)), launches=0)
 
 

@@ -55,14 +55,6 @@ class StepContext:
         self._tiles = {}
         self._seq_ntok = self._seq_pos0 = None
         self._fixed_splits = None
-        self._counters = None
-
-    def zero_counters(self, n):
-        """At least `n` int32 counters that are zero whenever a kernel starts: kernels that use them for a
-        "last block folds" hand-over leave them at zero again.  Shared by all layers of a step."""
-        if self._counters is None or self._counters.numel() < n:
-            self._counters = torch.zeros(max(n, 1024), dtype=torch.int32, device=self.device)
-        return self._counters
 
     def page_table(self, group):
         """Device page-table rows [n_seqs, pages] of a key/value cache group, one row per sequence of the batch."""

@@ -71,8 +71,12 @@ class Engine:
         self.n_sms = props.multi_processor_count
         ws_bytes = model.workspace_bytes(self.max_step_tokens, self.max_step_seqs, self.max_step_tokens)
         self.ws = Workspace(ws_bytes, self.device)
+        # the device error word: kernels OR a bit into it for bad input (a token id, a position, a page) and for a
+        # bounded wait that ran out; every call that hands results to the host reads it with them
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
-        ops.attn_set_error_word(self.err)
+        self._err_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._err_copied = torch.cuda.Event()
+        self._err_pending = False
         self.buffers = BatchBuffers(self.max_step_tokens, self.max_step_seqs, self.cache.kv_groups, self.max_step_tokens,
                                     self.device, tile_sizes=model.tile_sizes())
         self.profiler = Profiler() if profile else None
@@ -99,13 +103,23 @@ class Engine:
         """The sequences are finished: what they hold is given back."""
         for s in slots:
             self.cache.close(s)
+        self._raise_pending()
 
     def length(self, slot):
         return int(self.cache.length[slot])
 
     @property
     def capacity_tokens(self):
-        return self.cache.n_pages * 64
+        """Room for live sequences in tokens as the cache counts them (`footprint`); None: the slots are the only bound."""
+        return self.cache.capacity_tokens
+
+    @property
+    def max_seqs(self):
+        return self.cache.n_slots
+
+    def footprint(self, length):
+        """Tokens of the cache's room that one sequence of `length` tokens takes."""
+        return self.cache.footprint(length)
 
     @property
     def max_positions(self):
@@ -134,7 +148,10 @@ class Engine:
                     raise EngineError(f"slot {e.slot} wants logits at place {w} of {n} tokens")
 
     def step(self, entries: List[StepEntry]):
-        """Run the entries' tokens; return float32 logits [total wanted, vocab] on the device."""
+        """Run the entries' tokens; return float32 logits [total wanted, vocab] on the device.  The step is not
+        waited for; what its kernels report to the error word is read, without a wait of its own, by the next call
+        to the engine (or at once by `check_device_errors`), which raises `ops.KernelError`."""
+        self._raise_pending()
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         self._validate(entries)
         for e in entries:  # room for every token before anything runs
@@ -171,6 +188,9 @@ class Engine:
         if order != list(range(n_want)):  # a cut sequence with unsorted wants: put the rows where they belong
             dest = torch.tensor(order, dtype=torch.int64, device=self.device)
             logits = torch.empty_like(logits).index_copy_(0, dest, logits)
+        self._err_host.copy_(self.err, non_blocking=True)
+        self._err_copied.record()
+        self._err_pending = True
         return logits
 
     def _run_pieces(self, pieces, logits, row0, row_of, order):
@@ -225,8 +245,10 @@ class Engine:
             if len(self._step_graphs) >= self.STEP_GRAPH_LIMIT:
                 self._step_graphs.pop(next(iter(self._step_graphs)))
             buf = torch.empty((n_want, self.plan.vocab_size), dtype=torch.float32, device=self.device)
+            states = self._save_states(ctx)
             self.model.forward(ctx, self.cache, buf)   # once eagerly: kernel attributes are set outside the capture
             torch.cuda.synchronize()
+            self._restore_states(ctx, states)
             graph = torch.cuda.CUDAGraph()
             before = ops.LAUNCHES
             with torch.cuda.graph(graph):
@@ -241,13 +263,41 @@ class Engine:
             out.copy_(g["logits"])
         return True
 
+    def _save_states(self, ctx):
+        """Copies of the batch's rows of every fixed-size state group: a step that is run once eagerly and then
+        replayed from its fresh capture must advance such a state once, not twice."""
+        if not self.cache.state_groups:
+            return None
+        idx = ctx.seq_slots.to(torch.int64)
+        return idx, [g.state.index_select(1, idx) for g in self.cache.state_groups]
+
+    def _restore_states(self, ctx, saved):
+        if saved is not None:
+            idx, rows = saved
+            for g, r in zip(self.cache.state_groups, rows):
+                g.state.index_copy_(1, idx, r)
+
     def check_device_errors(self):
-        """Raise if a kernel flagged bad input since the last check (synchronises)."""
-        try:
-            ops.read_error_word(self.err)
-        except ops.KernelError:
+        """Raise if a kernel flagged bad input or a wait that ran out since the last check (synchronises)."""
+        self._err_pending = False
+        self._flagged(int(self.err.item()))
+
+    def _flagged(self, word):
+        """`word`: the error word as the host read it.  Non-zero: the word and whatever a kernel that gave up left
+        behind (the fused decode kernel's barrier words) are put right again, the captured graphs stay valid, and
+        the call raises; the logits and tokens of the steps since the last reading are not to be used."""
+        if word:
+            self.err.zero_()
             self.model.reset_after_device_error()
-            raise
+            what = [m for b, m in ops.ERR_BITS.items() if word & b]
+            raise ops.KernelError("a kernel reported: " + "; ".join(what or [f"error word {word:#x}"]))
+
+    def _raise_pending(self):
+        """Read the error word that the last `step` copied out, once that copy has landed."""
+        if self._err_pending:
+            self._err_pending = False
+            self._err_copied.synchronize()
+            self._flagged(int(self._err_host[0]))
 
     # ------------------------------------------------------------------ sampled steps (generation)
     def prefill_sampled(self, slots, prompts, params):
@@ -257,7 +307,9 @@ class Engine:
         tokens = torch.empty(len(slots), dtype=torch.int32, device=self.device)
         self.sampler.sample(logits, params, self.ctx.seq_slots if len(slots) == self.ctx.n_seqs else
                             torch.tensor(slots, dtype=torch.int32, device=self.device), tokens)
-        return tokens.tolist()
+        out = tokens.tolist()
+        self.check_device_errors()
+        return out
 
     def decode_sampled(self, slots, last_tokens, params):
         """One token per sequence, sampled on the device; from a CUDA graph when enabled.
@@ -267,15 +319,20 @@ class Engine:
             logits = self.step([StepEntry(s, [t], [0]) for s, t in zip(slots, last_tokens)])
             tokens = torch.empty(B, dtype=torch.int32, device=self.device)
             self.sampler.sample(logits, params, self.ctx.seq_slots, tokens)
-            return tokens.tolist()
+            out = tokens.tolist()
+            self.check_device_errors()
+            return out
         g = self.decode_launch(slots, last_tokens, params)
         g["host"].copy_(g["tokens"], non_blocking=True)
+        self._err_host.copy_(self.err, non_blocking=True)   # the error word comes with the tokens: one wait for both
         torch.cuda.current_stream().synchronize()
+        self._flagged(int(self._err_host[0]))
         return g["host"].tolist()
 
     def decode_launch(self, slots, last_tokens, params):
         """Issue one decode step (metadata copy + graph replay) without waiting for it; the
         sampled tokens land in the returned record's device tensor `tokens`."""
+        self._raise_pending()
         B = len(slots)
         vocab = self.plan.vocab_size
         for s, t in zip(slots, last_tokens):
@@ -307,13 +364,16 @@ class Engine:
         tokens = torch.empty(B, dtype=torch.int32, device=self.device)
         host = torch.empty(B, dtype=torch.int32).pin_memory()
         ops.lib()  # library loaded and kernels' attributes set before capture
-        # one eager run first: it sets kernel attributes (shared-memory sizes) outside of the capture.
-        # It writes the same cache rows and advances no state but the sampler's, which is restored.
+        # one eager run first: it sets kernel attributes (shared-memory sizes) outside of the capture.  It writes
+        # the same cache rows as the replay that follows; what it advances (the sampler's streams, the fixed-size
+        # states of mixers that keep one) is put back.
         saved = self.sampler.state.clone()
+        states = self._save_states(ctx)
         self.model.forward(ctx, self.cache, logits)
         self.sampler.sample(logits, params, ctx.seq_slots, tokens)
         torch.cuda.synchronize()
         self.sampler.state.copy_(saved)
+        self._restore_states(ctx, states)
         graph = torch.cuda.CUDAGraph()
         before = ops.LAUNCHES
         with torch.cuda.graph(graph):

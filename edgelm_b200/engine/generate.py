@@ -52,20 +52,24 @@ def round_up_page(n):
     return (int(n) + PAGE - 1) // PAGE * PAGE
 
 
-def plan_batches(prompt_lens: Sequence[int], max_new_tokens: int, max_batch: int, capacity_tokens: int,
-                 max_positions: int) -> List[List[int]]:
+def plan_batches(prompt_lens: Sequence[int], max_new_tokens: int, max_batch: int, capacity_tokens: Optional[int],
+                 max_positions: int, footprint=round_up_page) -> List[List[int]]:
     """Requests, in order, into batches: at most `max_batch` sequences, and room in the cache for
-    every sequence at its longest (prompt + max_new_tokens - 1 tokens are ever written, rounded
-    up to whole pages).  A request that cannot fit even alone is refused here, before anything runs."""
+    every sequence at its longest (prompt + max_new_tokens - 1 tokens are ever written).  How much
+    room a sequence of some length takes is the cache's own account (`footprint`; by default whole
+    pages of 64 tokens), and so is the room there is (`capacity_tokens`; None: no bound but the
+    number of sequences).  A request that cannot fit even alone is refused here, before anything runs."""
     if max_batch < 1:
         raise GenerationError("max_batch must be at least 1")
+    if capacity_tokens is None:
+        capacity_tokens = float("inf")
     batches, cur, cur_tokens = [], [], 0
     for i, n in enumerate(prompt_lens):
         if n < 1:
             raise GenerationError(f"request {i} has an empty prompt")
         if n + max_new_tokens > max_positions:
             raise GenerationError(f"request {i}: prompt of {n} tokens + {max_new_tokens} new tokens exceeds the context of {max_positions}")
-        need = round_up_page(n + max(max_new_tokens - 1, 0))
+        need = footprint(n + max(max_new_tokens - 1, 0))
         if need > capacity_tokens:
             raise GenerationError(f"request {i} needs room for {need} tokens; the cache holds {capacity_tokens}")
         if cur and (len(cur) == max_batch or cur_tokens + need > capacity_tokens):
@@ -105,8 +109,9 @@ class GenerationLoop:
             for g in results:
                 g.finish_reason = "length"
             return results
-        batches = plan_batches([len(p) for p in prompts], self.max_new_tokens, self.max_batch,
-                               self.backend.capacity_tokens, self.backend.max_positions)
+        be = self.backend
+        batches = plan_batches([len(p) for p in prompts], self.max_new_tokens, min(self.max_batch, getattr(be, "max_seqs", self.max_batch)),
+                               be.capacity_tokens, be.max_positions, getattr(be, "footprint", round_up_page))
         for batch in batches:
             self._run_batch(batch, prompts, results)
         return results

@@ -99,6 +99,34 @@ class DecoderModel:
         head = nbytes((n_want, d), self.dtype)
         return x + max(layers, head) + 4096
 
+    def flops(self, n_tokens, attended, n_logit_rows):
+        """Floating-point operations of one step, added up from the parts in schedule order: `n_tokens` new tokens,
+        `attended` (query, key) pairs scored per attention layer, logits for `n_logit_rows` rows."""
+        layers = sum(self.layers[e.layer].flops(n_tokens, attended) for e in self.schedule)
+        return layers + self.head.flops(n_logit_rows)
+
+    def sizes(self):
+        """The model's sizes under plain names, from the parts themselves: the width, the vocabulary, the number of
+        layer runs, and the sizes of the first layer's parts (`layer_kinds` says how many distinct layers there are)."""
+        out = {"layers": len(self.schedule), "hidden": self.plan.hidden_size}
+        out.update(self.layers[0].sizes())
+        out.update(self.head.sizes())
+        out["layer_kinds"] = len({l.describe() for l in self.layers})
+        return out
+
+    def describe(self):
+        """Lines for people: what the model is made of, from the parts' own descriptions."""
+        kinds = {}
+        for e in self.schedule:
+            d = self.layers[e.layer].describe()
+            kinds[d] = kinds.get(d, 0) + 1
+        lines = [f"{str(self.dtype).replace('torch.', '')} weights, {self.weight_bytes() / 1e6:.1f} MB; width {self.plan.hidden_size}, "
+                 f"{len(self.schedule)} layer runs over {len(self.layers)} layers, up to {self.plan.max_positions} positions",
+                 f"  {self.embedding.describe()}"]
+        lines += [f"  {n} x {d}" for d, n in kinds.items()]
+        lines += [f"  {self.final_norm.describe()} -> {self.head.describe()}"]
+        return lines
+
     def weight_bytes(self):
         """Bytes of every distinct device tensor the parts hold (a tied head counts once)."""
         seen, total = set(), 0

@@ -9,6 +9,7 @@ import math
 
 import torch
 
+from ..config.base import ConfigError
 from ..csrc import ops
 from . import linear
 from .base import KVNeed, Part, as_matrix, nbytes
@@ -23,6 +24,10 @@ class Attention(Part):
     def __init__(self, spec, env):
         self.hidden = spec["hidden_size"]
         self.nh, self.nkv, self.hd = spec["num_heads"], spec["num_kv_heads"], spec["head_dim"]
+        if self.nh <= 0 or self.nkv <= 0 or self.nh % self.nkv:
+            raise ConfigError(f"attention: {self.nh} query heads are not a multiple of {self.nkv} key/value heads")
+        if not (16 <= self.hd <= 256 and self.hd % 16 == 0):
+            raise ConfigError(f"attention: head_dim {self.hd} is not taken by the attention kernels (16 to 256 in steps of 16)")
         self.names = dict(spec["names"])
         self.dtype = env.dtype
         self.positions = env.build_shared("positions", spec["positions"])
@@ -32,6 +37,13 @@ class Attention(Part):
         self.w_qkv = self.w_o = None
         self._mma = None  # whether the mma.sync prefill kernel takes this head size (asked once a device is there)
         self._tc = None   # whether the tcgen05 prefill kernel does
+
+    def sizes(self):
+        return {"heads": self.nh, "kv_heads": self.nkv, "head_dim": self.hd, **self.positions.sizes()}
+
+    def flops(self, n_tokens, attended):
+        proj = 2.0 * n_tokens * self.hidden * (2 * self.nh + 2 * self.nkv) * self.hd    # q, k, v and the output projection
+        return proj + 4.0 * attended * self.nh * self.hd                                # scores and weighted values
 
     def weight_shapes(self, prefix):
         n = self.names
@@ -114,12 +126,9 @@ class Attention(Part):
             if splits > 1:
                 part_o = ws.alloc((ctx.n_seqs * self.nh * splits * self.hd,), torch.float32)
                 part_ml = ws.alloc((ctx.n_seqs * self.nh * splits * 2,), torch.float32)
-            # the splits are folded by a second small kernel: measured faster than handing the fold to the last
-            # block of the main kernel through `ctx.zero_counters` (1.11 ms against 1.17 ms per step at batch 8)
-            counters = None
             with ctx.prof("attn_decode"):
                 ops.attn_decode_rope(qkv, a, cache.k, cache.v, table, ctx.seq_index, ctx.seq_pos, tables[0], tables[1],
-                                     ctx.n_seqs, self.nh, self.nkv, self.hd, self.scale, splits, part_o, part_ml, counters)
+                                     ctx.n_seqs, self.nh, self.nkv, self.hd, self.scale, splits, part_o, part_ml, err=ctx.err)
             with ctx.prof("o_proj_residual"):
                 linear.matmul(ctx, a, self.w_o, x, epilogue=linear.EPI_RESIDUAL, residual=x, prefetch=ctx.weights_after)
             return
@@ -133,7 +142,7 @@ class Attention(Part):
                 part_ml = ws.alloc((ctx.n_seqs * self.nh * splits * 2,), torch.float32)
             with ctx.prof("attn_decode"):
                 ops.attn_decode(qkv, a, cache.k, cache.v, table, ctx.seq_index, ctx.seq_pos, ctx.n_seqs, self.nh, self.nkv,
-                                self.hd, self.scale, splits, part_o, part_ml)
+                                self.hd, self.scale, splits, part_o, part_ml, err=ctx.err)
         elif self._tc_prefill() and max(ctx.seq_lengths) >= self.TC_PREFILL_MIN_TOKENS:
             tiles = ctx.tiles(ops.TC_PREFILL_TILE)
             with ctx.prof("attn_prefill"):

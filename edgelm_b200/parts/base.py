@@ -7,6 +7,14 @@ Every part, whatever its role, answers four questions:
   workspace_bytes(n_tokens, n_seqs) -> int        scratch it takes from the step's workspace
   cache_need() -> KVNeed | StateNeed | None       what it keeps per sequence between steps (mixers)
 
+two about itself, which the command line and the benchmark add up instead of reading any
+architecture's configuration fields:
+
+  sizes() -> {name: value}                        its sizes and constants under plain names
+  flops(n_tokens, attended) -> float              floating-point operations of a step of `n_tokens` tokens in which
+                                                  `attended` (query, key) pairs are scored (matrix products count 2 per
+                                                  multiply-add; norms, rotations and activations are left out)
+
 and has one `forward`, whose signature depends on the role:
 
   embedding   forward(ctx, x)                     x[T, D] float32 <- rows of the table for ctx.token_ids
@@ -59,6 +67,17 @@ class Part:
 
     def cache_need(self):
         return None
+
+    def sizes(self):
+        return {}
+
+    def flops(self, n_tokens, attended):
+        return 0.0
+
+    def describe(self):
+        """One line: the kind and the sizes."""
+        inner = ", ".join(f"{k} {v}" for k, v in self.sizes().items())
+        return f"{self.kind}({inner})"
 
     def decode_fusion(self):
         """What a fused decode kernel needs to know to do this part's work itself: a dict with a "kind" and the

@@ -30,6 +30,18 @@ class PreNormBlock(Part):
     def cache_need(self):
         return self.mixer.cache_need()
 
+    def sizes(self):
+        out = {}
+        for p in (self.mixer, self.ffn, self.mixer_norm):
+            out.update(p.sizes())
+        return out
+
+    def flops(self, n_tokens, attended):
+        return sum(p.flops(n_tokens, attended) for p in self.parts)
+
+    def describe(self):
+        return f"{self.kind}: {self.mixer_norm.describe()} -> {self.mixer.describe()}; {self.ffn_norm.describe()} -> {self.ffn.describe()}"
+
     def tile_sizes(self):
         return tuple(self.mixer.tile_sizes())
 

@@ -12,6 +12,9 @@ class Embedding(Part):
         self.dtype = env.dtype
         self.table = None
 
+    def sizes(self):
+        return {"vocab": self.vocab_size, "hidden": self.dim}
+
     def weight_shapes(self, prefix=""):
         return {self.name: (self.vocab_size, self.dim)}
 

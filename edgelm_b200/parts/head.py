@@ -14,6 +14,12 @@ class LMHead(Part):
         self.dtype = env.dtype
         self.weight = None
 
+    def sizes(self):
+        return {"vocab": self.vocab_size, "tied": bool(self.tied_to)}
+
+    def flops(self, n_rows, attended=0):
+        return 2.0 * n_rows * self.dim * self.vocab_size
+
     def weight_shapes(self, prefix=""):
         return {} if self.tied_to else {self.name: (self.vocab_size, self.dim)}
 

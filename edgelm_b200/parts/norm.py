@@ -14,6 +14,9 @@ class RMSNorm(Part):
         self.dim, self.eps, self.name = spec["dim"], float(spec["eps"]), spec["name"]
         self.weight = None
 
+    def sizes(self):
+        return {"rms_norm_eps": self.eps}
+
     def weight_shapes(self, prefix):
         return {prefix + self.name: (self.dim,)}
 

@@ -20,6 +20,9 @@ class RotaryPositions(Part):
         self.head_dim, self.theta, self.max_positions = spec["head_dim"], float(spec["theta"]), spec["max_positions"]
         self.cos = self.sin = None
 
+    def sizes(self):
+        return {"rope_theta": self.theta}
+
     def load(self, tensors, prefix, device):
         if self.cos is not None and self.cos.device == torch.device(device):
             return

@@ -18,6 +18,12 @@ class SwiGLU(Part):
         self.dtype = env.dtype
         self.w_gate = self.w_up = self.w_down = None
 
+    def sizes(self):
+        return {"intermediate": self.inter}
+
+    def flops(self, n_tokens, attended):
+        return 6.0 * n_tokens * self.hidden * self.inter
+
     def weight_shapes(self, prefix):
         n = self.names
         return {prefix + n["gate"]: (self.inter, self.hidden), prefix + n["up"]: (self.inter, self.hidden),

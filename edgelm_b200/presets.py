@@ -28,18 +28,18 @@ def preset_config(name):
 
 def random_model(config, seed=0, sigma=0.02, dtype="bfloat16", device="cuda:0", layers=None):
     """A DecoderModel of `config` with random weights made on the device (matrices N(0, sigma),
-    norm weights 1 + N(0, sigma)); `layers` keeps only the first so many layers."""
-    import dataclasses
-
+    norm weights 1 + N(0, sigma)); `layers` keeps only the plan's first so many layer runs (the configuration
+    object stays whole: it is the plan that is cut)."""
     import torch
 
     from .engine.engine import DTYPES
     from .engine.model import DecoderModel
     from .weights import random_tensors
-    if layers is not None and layers != config.num_hidden_layers:
-        config = dataclasses.replace(config, num_hidden_layers=int(layers))
+    plan = config.plan()
+    if layers is not None and int(layers) != len(plan.schedule):
+        plan = plan.first_runs(layers)
     torch_dtype = DTYPES[dtype] if isinstance(dtype, str) else dtype
-    model = DecoderModel(config.plan(), torch_dtype)
+    model = DecoderModel(plan, torch_dtype)
     tensors = random_tensors(model.expected_weights(), seed, sigma, torch_dtype, device=device)
     model.load(tensors, device)
     model.config = config

@@ -2,8 +2,10 @@
 
 The model says which tensors it wants (`expected`: name -> shape).  `check` compares that with
 the tensors found and raises ONE error that lists everything wrong at once: missing names,
-unexpected names, and wrong shapes.  `keep_dtype` is the storage policy: 16-bit floats are kept
-as bfloat16, a tensor stored in 32 bits stays in 32 bits, 64-bit floats become float32, and
+unexpected names, and wrong shapes.  `keep_dtype` is the storage policy: bfloat16 stays bfloat16,
+a tensor stored in 32 bits stays in 32 bits, float16 stays as stored (it has more mantissa bits
+than bfloat16: a float32 engine widens it exactly, as adarsh-sgh/edgelm's exporter does,
+tools/export.py:35, and a bfloat16 engine rounds it once), 64-bit floats become float32, and
 integer tables become int32.  What precision a part computes in is the part's decision, taken
 when it receives its tensors.
 """
@@ -14,10 +16,8 @@ from .errors import WeightsError
 
 
 def keep_dtype(t):
-    if t.dtype == torch.bfloat16 or t.dtype == torch.float32 or t.dtype == torch.int32:
+    if t.dtype in (torch.bfloat16, torch.float16, torch.float32, torch.int32):
         return t
-    if t.dtype == torch.float16:
-        return t.to(torch.bfloat16)
     if t.dtype == torch.float64:
         return t.to(torch.float32)
     if t.dtype in (torch.int64, torch.int16, torch.int8, torch.uint8, torch.bool):

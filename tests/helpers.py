@@ -91,11 +91,12 @@ def run_tail_one_by_one(engine, tokens, tail=32):
     return np.concatenate(parts, axis=0)
 
 
-def run_batches(engine, requests, batch_size, decode_tail):
+def run_batches(engine, requests, batch_size, decode_tail, prompt_rows=None):
     """Batches of unequal lengths, one after another.  In each batch all requests start together:
     step 0 brings each request's first len - decode_tail tokens (at least 1), then every step
     brings one token per request still running; shorter requests end earlier and give back what
-    they hold.  Returns per request its logits at every position."""
+    they hold.  Returns per request its logits at every position (with `prompt_rows`: at the last
+    so many positions of its first step, then at every later position)."""
     from edgelm_b200.engine.engine import StepEntry
     out = [None] * len(requests)
     for b0 in range(0, len(requests), batch_size):
@@ -105,14 +106,15 @@ def run_batches(engine, requests, batch_size, decode_tail):
         entries = []
         for i in idxs:
             n0 = max(1, len(requests[i]) - decode_tail)
-            entries.append(StepEntry(slots[i], requests[i][:n0], list(range(n0))))
+            want = list(range(n0)) if prompt_rows is None else list(range(max(0, n0 - prompt_rows), n0))
+            entries.append(StepEntry(slots[i], requests[i][:n0], want))
             fed[i] = n0
         lg = engine.step(entries).cpu().numpy()
         rows = {i: [] for i in idxs}
         r = 0
-        for i in idxs:
-            rows[i].append(lg[r:r + fed[i]])
-            r += fed[i]
+        for e, i in zip(entries, idxs):
+            rows[i].append(lg[r:r + len(e.want)])
+            r += len(e.want)
         live = list(idxs)
         while live:
             for i in [i for i in live if fed[i] == len(requests[i])]:
@@ -128,3 +130,27 @@ def run_batches(engine, requests, batch_size, decode_tail):
             out[i] = np.concatenate(rows[i], axis=0)
         engine.cache.check()
     return out
+
+
+def make_preset_dir(tmp, preset, layers, seed=0, sigma=0.02):
+    """A model folder with a built-in shape's layer sizes (width, heads, head size, feed-forward width,
+    vocabulary, theta, eps, tied head: all untouched) cut to `layers` layers, random weights N(0, sigma)
+    in a bfloat16 file: small enough for the plain implementation to follow on the CPU."""
+    import dataclasses
+
+    from edgelm_b200 import write_model_dir
+    from edgelm_b200.presets import preset_config
+    cfg = dataclasses.replace(preset_config(preset), num_hidden_layers=int(layers))
+    return write_model_dir(str(tmp / f"{preset}_{layers}L"), cfg, seed, sigma=sigma, dtype="bfloat16")
+
+
+def decisive_agreement(got, want, gap=0.15):
+    """Share of rows of `got` whose argmax is `want`'s, among the rows where `want` is decisive (its two
+    largest logits at least `gap` apart), and the number of such rows."""
+    want = np.asarray(want)
+    top2 = np.partition(want, -2, axis=-1)[:, -2:]
+    decisive = (top2[:, 1] - top2[:, 0]) >= gap
+    if not decisive.any():
+        return 1.0, 0
+    same = np.asarray(got).argmax(-1)[decisive] == want.argmax(-1)[decisive]
+    return float(same.mean()), int(decisive.sum())

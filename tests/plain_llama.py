@@ -186,13 +186,21 @@ def lm_head(cfg, W, x):
     return (xn @ head.T).astype(f32)
 
 
-def forward(cfg, W, tokens):
-    """Logits [len(tokens), vocab] for every position of one whole sequence."""
+def forward(cfg, W, tokens, rows=None):
+    """Logits [len(tokens), vocab] for every position of one whole sequence, or [len(rows), vocab] for
+    the positions `rows` (edgelm's LAST_ROWS idea, tools/elm.py:154-156: the layers run on every position,
+    the head only where logits are wanted; with a large vocabulary the head is most of the work)."""
+    x = hidden(cfg, W, tokens)
+    return lm_head(cfg, W, x if rows is None else x[np.asarray(rows, dtype=np.int64)])
+
+
+def hidden(cfg, W, tokens):
+    """The residual stream [len(tokens), dim] after the last layer, before the final norm."""
     W = {k: np.asarray(v, dtype=f32) for k, v in W.items()}
     x = embed(W["model.embed_tokens.weight"], tokens)
     for l in range(cfg["n_layers"]):
         x = decoder_layer(cfg, W, l, x)
-    return lm_head(cfg, W, x)
+    return x
 
 
 # ----------------------------------------------------------------------------- sampling

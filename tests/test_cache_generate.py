@@ -231,3 +231,32 @@ def test_decode_splits_rule():
     assert splits(8, 32, 1) == 2                                                    # one block an SM: nothing fills a wave twice over
     ctx._fixed_splits = 5
     assert splits(8, 32, 3) == 5
+
+
+def test_capacity_is_the_caches_own_account():
+    """Room is counted by the cache: whole pages for key/value groups, nothing for a model whose mixers keep
+    fixed-size states only, which is then bound by its slots alone."""
+    kv = make_cache(max_tokens=640)
+    assert kv.capacity_tokens == 640 and kv.footprint(1) == 64 and kv.footprint(65) == 128 and kv.footprint(0) == 0
+    st = SequenceCache([StateNeed((4, 8)), StateNeed((4, 8))], 640, 4096, device=None, max_seqs=3)
+    assert st.capacity_tokens is None and st.footprint(5000) == 0 and st.n_slots == 3
+    a = st.open()
+    st.reserve(a, 3000)          # no pages to run out of
+    st.advance(a, 3000)
+    st.check()
+    assert plan_batches([900, 900, 900, 900], 100, 3, st.capacity_tokens, 4096, st.footprint) == [[0, 1, 2], [3]]
+    assert plan_batches([100, 100, 100], 29, 8, kv.capacity_tokens, 256, kv.footprint) == [[0, 1, 2]]
+    assert plan_batches([100] * 6, 29, 8, kv.capacity_tokens, 256, kv.footprint) == [[0, 1, 2, 3, 4], [5]]
+
+
+def test_the_loop_asks_the_backend_for_its_account():
+    class StateOnly(ScriptedBackend):
+        max_seqs = 2
+
+        def footprint(self, length):
+            return 0
+    be = StateOnly({0: [5] * 9, 1: [6] * 9, 2: [7] * 9}, capacity_tokens=None)
+    loop = GenerationLoop(be, max_new_tokens=3, max_batch=8)
+    out = loop.run([[0] * 500, [1] * 700, [2] * 900])
+    assert [g.tokens for g in out] == [[5] * 3, [6] * 3, [7] * 3]
+    assert be.max_live == 2      # the backend's slots, not the caller's max_batch, bound a batch

@@ -146,7 +146,8 @@ def test_untied_model_needs_its_head(tmp_path):
 
 
 def test_kept_dtypes():
-    assert keep_dtype(torch.zeros(2, dtype=torch.float16)).dtype == torch.bfloat16
+    half = torch.tensor([1.0009765625, 0.333251953125], dtype=torch.float16)   # 10 mantissa bits: bfloat16 would lose some
+    assert keep_dtype(half).dtype == torch.float16 and torch.equal(keep_dtype(half), half)
     assert keep_dtype(torch.zeros(2, dtype=torch.bfloat16)).dtype == torch.bfloat16
     assert keep_dtype(torch.zeros(2, dtype=torch.float32)).dtype == torch.float32
     assert keep_dtype(torch.zeros(2, dtype=torch.float64)).dtype == torch.float32

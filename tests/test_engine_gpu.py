@@ -291,3 +291,76 @@ def test_context_overflow_and_bad_input(model_dirs):
         eng.step([StepEntry(held[0], [1], [0])])
     eng.close(held)
     eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_generation_reads_the_device_error_word(model_dirs, oracles, dtype):
+    """What a kernel reports (here: set from the host, no kernel is made to give up) ends generation with an
+    error instead of tokens sampled from bad logits: in the prompt step, in a captured decode step, in `step`,
+    and through the entry point; afterwards the engine works again."""
+    import edgelm_b200
+    from edgelm_b200.csrc import ops
+    from edgelm_b200.engine.engine import StepEntry
+    from edgelm_b200.sampling import SamplingParams
+    name = "tiny_d"
+    eng = edgelm_b200.load_engine(model_dirs[name], dtype=dtype, ctx=256, slots=4)
+    params = SamplingParams()
+    prompts = [H.tokens_for(name, n, 400 + i) for i, n in enumerate([9, 40])]
+    slots = eng.open(2)
+    eng.err.fill_(8)
+    with pytest.raises(ops.KernelError, match="wait ran out"):
+        eng.prefill_sampled(slots, prompts, params)
+    assert int(eng.err.item()) == 0
+    eng.close(slots)
+    slots = eng.open(2)
+    toks = eng.prefill_sampled(slots, prompts, params)
+    toks = eng.decode_sampled(slots, toks, params)          # captures the decode graph
+    eng.err.fill_(4)
+    with pytest.raises(ops.KernelError, match="page"):
+        eng.decode_sampled(slots, toks, params)
+    eng.close(slots)
+    slot = eng.open(1)[0]
+    eng.err.fill_(1)
+    eng.step([StepEntry(slot, prompts[0], [0])])            # not waited for: the next call reports it
+    with pytest.raises(ops.KernelError, match="vocabulary"):
+        eng.step([StepEntry(slot, [3], [0])])
+    eng.close([slot])
+    eng.err.fill_(2)
+    with pytest.raises(ops.KernelError, match="position"):
+        edgelm_b200.generate(None, prompts, n=4, engine=eng, slots=2, stop=[], ignore_eos=True)
+    eng.cache.check()
+    assert eng.cache.slots.available() == eng.cache.n_slots   # the loop gave its slots back on the way out
+    got = edgelm_b200.generate(None, prompts, n=6, engine=eng, slots=2, stop=[], ignore_eos=True)
+    if dtype == "float32":
+        o = oracles[name]
+        assert got == [plain.generate(o.cfg, o.W, p, 6, stop_ids=[], ignore_eos=True) for p in prompts]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_prompt_steps_replayed_from_a_graph(model_dirs, oracles, dtype):
+    """A prompt step whose shape comes back is captured at its second appearance and replayed from then on: other
+    tokens, other slots and pages, the same shape.  Every run is compared with the plain implementation."""
+    name = "tiny_b"
+    eng = edgelm_b200_engine(model_dirs[name], dtype)
+    from edgelm_b200.engine.engine import StepEntry
+    lens = (70, 33)
+    for rep in range(4):
+        reqs = [H.tokens_for(name, n, 500 + 10 * rep + i) for i, n in enumerate(lens)]
+        filler = eng.open(rep)              # other slots, hence other pages, each time
+        for f in filler:
+            eng.step([StepEntry(f, [1] * (64 * rep + 1), [])])
+        slots = eng.open(2)
+        lg = eng.step([StepEntry(s, r, list(range(len(r)))) for s, r in zip(slots, reqs)]).cpu().numpy()
+        assert (((70, 33), 103) in eng._step_graphs) == (rep >= 1), rep
+        r0 = 0
+        for r in reqs:
+            assert H.rel_err(lg[r0:r0 + len(r)], oracles[name].logits(r)) < H.TOL[dtype], (rep,)
+            r0 += len(r)
+        eng.close(slots + filler)
+    eng.check_device_errors()
+    eng.cache.check()
+
+
+def edgelm_b200_engine(model_dir, dtype):
+    from edgelm_b200.engine.engine import Engine
+    return Engine.from_dir(model_dir, dtype=dtype, max_tokens=1024)

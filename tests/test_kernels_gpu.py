@@ -236,37 +236,6 @@ def test_attn_decode(dtype, nh, nkv, hd, n_splits):
         assert rel_err(out[s:s + 1], want) < (1e-5 if dtype == torch.float32 else 1e-2), (s, n)
 
 
-@pytest.mark.parametrize("nh,nkv,hd", [(9, 3, 64), (32, 32, 64), (6, 1, 96)])
-@pytest.mark.parametrize("n_splits", [3, 8])
-def test_attn_decode_splits_folded_in_a_cluster(nh, nkv, hd, n_splits):
-    """The optional form in which the splits of a (sequence, kv head) are one thread-block cluster: no partial
-    results in global memory (the buffers stay as they were) and the same output as with the combine kernel."""
-    o = ops()
-    lengths = [1, 64, 65, 700, 128, 37]
-    case = PagedCase(o, torch.bfloat16, lengths, nkv, hd, seed=nh + hd + n_splits)
-    B = len(lengths)
-    qkv = rnd((B, (nh + 2 * nkv) * hd), torch.bfloat16, 21)
-    seq_pos = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=dev())
-    outs = []
-    for cluster in (False, True):
-        out = torch.zeros(B, nh * hd, dtype=torch.bfloat16, device=dev())
-        part_o = torch.full((B * nh * n_splits * hd,), float("nan"), device=dev())
-        part_ml = torch.full((B * nh * n_splits * 2,), float("nan"), device=dev())
-        o.attn_decode_cluster(cluster)
-        try:
-            o.attn_decode(qkv, out, case.kcache, case.vcache, case.table, case.seq_slot, seq_pos, B, nh, nkv, hd,
-                          1.0 / math.sqrt(hd), n_splits, part_o, part_ml)
-            torch.cuda.synchronize()
-        finally:
-            o.attn_decode_cluster(False)
-        assert bool(torch.isnan(part_o).all()) == cluster
-        outs.append(out)
-    for s, n in enumerate(lengths):
-        want = attention_rows(qkv[s:s + 1, :nh * hd].float().cpu(), case.k[s], case.v[s], n - 1, nh, nkv, hd)
-        assert rel_err(outs[1][s:s + 1], want) < 1e-2, (s, n)
-    assert torch.equal(outs[0], outs[1])   # same arithmetic in the same order
-
-
 def test_attention_far_key_stands_out():
     """One early key among hundreds is made to dominate: the output must be its value."""
     o = ops()
@@ -392,7 +361,7 @@ def test_sample_topk_matches_plain(vocab, temp, k, seed):
 
 # ----------------------------------------------------------------------------- GEMM (tcgen05 tensor cores)
 TC_SHAPES = [(128, 128, 64), (17, 64, 72), (129, 192, 576), (300, 100, 200), (256, 960, 576), (2048, 576, 1536),
-             (64, 397, 96), (130, 49, 8), (1000, 130, 136), (2048, 2048, 256), (1920, 2050, 200),  # the last two: 128 x 256 tiles
+             (64, 397, 96), (130, 49, 8), (1000, 130, 136), (2048, 2048, 256), (1920, 2050, 200),
              (64, 2048, 8192), (64, 576, 1536), (100, 397, 1032), (129, 200, 4096)]  # few tiles and long K: split-K
 
 
@@ -436,6 +405,89 @@ def test_gemm_tc_swiglu(M, N, K):
     o.gemm_tc(a, wg, out, err, epilogue=o.EPI_SWIGLU, w2=wu)
     assert int(err.item()) == 0
     assert rel_err(out, want) < 1.6e-2
+
+
+# Products that the dispatch gives to the 128 x 256 tiles (128 x 2 x 128 for SwiGLU): at least 120 of them, N and K
+# at least 1,024.  Without a residual they run on the persistent kernel (a block walks several tiles, two accumulator
+# stages), with one as one wide tile a block.  Ragged M, N and K tails, a last wave that is not full, and a row count
+# whose last tile holds one row.  Every case asserts which kernel ran.
+TC_WIDE = [(2048, 6144, 2048), (1985, 2050, 1032), (3000, 1544, 1096), (2049, 4096, 1024)]
+TC_WIDE_RESIDUAL = [(2048, 2048, 8192), (1920, 2050, 1032), (1985, 3080, 1096)]
+TC_WIDE_SWIGLU = [(2048, 8192, 2048), (1100, 2050, 1096), (1985, 1536, 1032)]
+
+
+def _products(a, w):
+    """Float64 product on the device (the CPU would take seconds at these sizes)."""
+    return (a.double() @ w.double().T).cpu()
+
+
+@pytest.mark.parametrize("M,N,K", TC_WIDE)
+def test_gemm_tc_wide_persistent_store(M, N, K):
+    o = ops()
+    a = rnd((M, K), torch.bfloat16, 150)
+    w = rnd((N, K), torch.bfloat16, 151, 0.2)
+    err = torch.zeros(1, dtype=torch.int32, device=dev())
+    want = _products(a, w)
+    for dt, tol_ in ((torch.bfloat16, 1.6e-2), (torch.float32, 2e-5)):
+        out = torch.full((M, N), float("nan"), dtype=dt, device=dev())
+        o.gemm_tc(a, w, out, err)
+        k = o.gemm_tc_last_kernel()
+        assert k["tile_columns"] == 256 and k["persistent"], k
+        assert int(err.item()) == 0
+        assert rel_err(out, want) < tol_
+        # every element, not only the largest: a tile written to the wrong place shows as an error of order 1
+        assert (out.double().cpu() - want).abs().max() < (0.3 if dt == torch.bfloat16 else 2e-3)
+
+
+@pytest.mark.parametrize("M,N,K", TC_WIDE_RESIDUAL)
+def test_gemm_tc_wide_residual(M, N, K):
+    o = ops()
+    a = rnd((M, K), torch.bfloat16, 152)
+    w = rnd((N, K), torch.bfloat16, 153, 0.2)
+    err = torch.zeros(1, dtype=torch.int32, device=dev())
+    res = rnd((M, N), torch.float32, 154)
+    want = res.double().cpu() + _products(a, w)
+    o.gemm_tc(a, w, res, err, epilogue=o.EPI_RESIDUAL, residual=res)
+    k = o.gemm_tc_last_kernel()
+    assert k["tile_columns"] == 256 and not k["persistent"] and k["k_splits"] == 1, k
+    assert int(err.item()) == 0
+    assert rel_err(res, want) < 2e-5
+
+
+@pytest.mark.parametrize("M,N,K", TC_WIDE_SWIGLU)
+def test_gemm_tc_wide_persistent_swiglu(M, N, K):
+    o = ops()
+    a = rnd((M, K), torch.bfloat16, 155, 0.5)
+    wg = rnd((N, K), torch.bfloat16, 156, 0.1)
+    wu = rnd((N, K), torch.bfloat16, 157, 0.1)
+    err = torch.zeros(1, dtype=torch.int32, device=dev())
+    g, u = _products(a, wg), _products(a, wu)
+    want = g / (1 + torch.exp(-g)) * u
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev())
+    o.gemm_tc(a, wg, out, err, epilogue=o.EPI_SWIGLU, w2=wu)
+    k = o.gemm_tc_last_kernel()
+    assert k["tile_columns"] == 128 and k["persistent"], k
+    assert int(err.item()) == 0
+    assert rel_err(out, want) < 1.6e-2
+
+
+def test_gemm_tc_dispatch_names_its_kernel():
+    """The other branches of the dispatch, each on a product that should reach it."""
+    o = ops()
+    err = torch.zeros(1, dtype=torch.int32, device=dev())
+    for (M, N, K), want in (((2048, 576, 576), dict(tile_columns=64, persistent=False, k_splits=1)),
+                            ((2048, 2048, 256), dict(tile_columns=128, persistent=False, k_splits=1)),
+                            ((256, 960, 576), dict(tile_columns=64, persistent=False)),
+                            ((64, 2048, 8192), dict(tile_columns=128, persistent=False))):
+        a = rnd((M, K), torch.bfloat16, 158)
+        w = rnd((N, K), torch.bfloat16, 159, 0.2)
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=dev())
+        o.gemm_tc(a, w, out, err)
+        k = o.gemm_tc_last_kernel()
+        assert all(k[key] == v for key, v in want.items()), ((M, N, K), k)
+        assert rel_err(out, _products(a, w)) < 1.6e-2
+    k = o.gemm_tc_last_kernel()
+    assert k["k_splits"] > 1, k   # 64 rows, N 2048, K 8192: sixteen tiles, split over K
 
 
 def test_gemm_tc_strided_rows_and_refusals():
@@ -774,16 +826,16 @@ def test_attn_decode_rope_equals_separate_kernels(dtype, nh, nkv, hd, n_splits):
                        1.0 / math.sqrt(hd), n_splits, po, pm)
     assert int(err.item()) == 0
     assert rel_err(got, want) < (1e-6 if dtype == torch.float32 else 4e-3)
-    # with counters the last block folds the splits itself (sums in another fixed order); the counters are zero again
-    c = PagedCase(o, dtype, lengths, nkv, hd, seed=nh + hd)
-    counters = torch.zeros(B * nkv, dtype=torch.int32, device=dev())
-    for _ in range(2):
-        got2 = torch.full_like(want, float("nan"))
-        po, pm = mk()
-        o.attn_decode_rope(raw.clone(), got2, c.kcache, c.vcache, c.table, c.seq_slot, seq_pos, cos_t, sin_t, B, nh, nkv, hd,
-                           1.0 / math.sqrt(hd), n_splits, po, pm, counters)
-        assert rel_err(got2, got) < (1e-6 if dtype == torch.float32 else 4e-3)
-        assert int(counters.abs().sum()) == 0
+    # and against the plain implementation: rotate the new token's q and k, put k and v at the end, attend
+    for s, n in enumerate(lengths):
+        row = raw[s].float().cpu().numpy()
+        vh = row[(nh + nkv) * hd:].reshape(1, nkv, hd)
+        qr = torch.from_numpy(plain.rope(row[None, :nh * hd], [n - 1], nh, hd, 5000.0)).to(dtype).float()
+        kr = torch.from_numpy(plain.rope(row[None, nh * hd:(nh + nkv) * hd], [n - 1], nkv, hd, 5000.0)).to(dtype).float().reshape(1, nkv, hd)
+        keys = torch.cat([a.k[s][:n - 1], kr], dim=0)
+        vals = torch.cat([a.v[s][:n - 1], torch.from_numpy(vh).to(dtype).float()], dim=0)
+        ref = attention_rows(qr, keys, vals, n - 1, nh, nkv, hd)
+        assert rel_err(got[s:s + 1], ref) < (1e-5 if dtype == torch.float32 else 1.2e-2), (s, n)
     for s, n in enumerate(lengths):   # the appended rows are the same, nothing else changed
         for cache_a, cache_b in ((a.kcache, b.kcache), (a.vcache, b.vcache)):
             page = int(a.table[int(a.seq_slot[s]), (n - 1) // o.PAGE])
