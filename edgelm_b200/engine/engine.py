@@ -15,6 +15,7 @@ in (one copy) and the sampled tokens out (one copy).
 from dataclasses import dataclass
 from typing import List, Sequence
 
+import numpy as np
 import torch
 
 from ..cache import SequenceCache
@@ -137,12 +138,16 @@ class Engine:
             if e.slot in seen:
                 raise EngineError(f"slot {e.slot} appears twice in one step")
             seen.add(e.slot)
-            n = len(e.tokens)
+            ids = np.asarray(e.tokens, dtype=np.int64)     # one pass in NumPy: a prompt of thousands of ids is checked in microseconds
+            n = ids.size
             if n == 0:
                 raise EngineError(f"slot {e.slot} brings no token")
-            for t in e.tokens:
-                if not 0 <= int(t) < vocab:
-                    raise EngineError(f"token id {t} is outside the vocabulary of {vocab}")
+            if ids.ndim != 1:
+                raise EngineError(f"slot {e.slot}: tokens must be a flat list of ids")
+            lo, hi = int(ids.min()), int(ids.max())
+            if lo < 0 or hi >= vocab:
+                raise EngineError(f"token id {lo if lo < 0 else hi} is outside the vocabulary of {vocab}")
+            e.tokens = ids
             for w in e.want:
                 if not 0 <= int(w) < n:
                     raise EngineError(f"slot {e.slot} wants logits at place {w} of {n} tokens")
@@ -152,7 +157,7 @@ class Engine:
         waited for; what its kernels report to the error word is read, without a wait of its own, by the next call
         to the engine (or at once by `check_device_errors`), which raises `ops.KernelError`."""
         self._raise_pending()
-        entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        entries = [StepEntry(e.slot, e.tokens, e.want) if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         self._validate(entries)
         for e in entries:  # room for every token before anything runs
             self.cache.reserve(e.slot, len(e.tokens))
@@ -197,7 +202,7 @@ class Engine:
         token_ids, slots, ntok, pos0, want_rows = [], [], [], [], []
         t0 = 0
         for e, start, take in pieces:
-            token_ids.extend(int(t) for t in e.tokens[start:start + take])
+            token_ids.append(e.tokens[start:start + take])
             slots.append(e.slot)
             ntok.append(take)
             pos0.append(int(self.cache.length[e.slot]))
@@ -206,7 +211,7 @@ class Engine:
                     want_rows.append(t0 + int(w) - start)
                     order.append(row_of[(id(e), int(w))].pop(0))
             t0 += take
-        ctx = self.buffers.fill(self.ctx, token_ids, slots, ntok, pos0, want_rows, self.cache)
+        ctx = self.buffers.fill(self.ctx, np.concatenate(token_ids), slots, ntok, pos0, want_rows, self.cache)
         self.h2d_bytes_last = self.buffers.last_bytes
         out = logits[row0:row0 + len(want_rows)]
         if self.profiler is not None:
