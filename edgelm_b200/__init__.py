@@ -8,11 +8,28 @@ manner: a `Session` that prefills and decodes one sequence and hands out logits
 (include/edgelm/runtime.hpp:28-49), sampling options named as its `run` command names them
 (src/main.cpp:74-86), and `generate` for whole batches of requests.
 """
+import importlib
+import os
+
 from .config import ConfigError, LlamaConfig, read_config, register_architecture, registered_architectures
 from .sampling import SamplingParams
 from .weights import WeightsError, write_model_dir
 
 __version__ = "0.1.0"
+
+
+def load_plugins(names=None):
+    """Import modules that register parts or architectures of their own, so that every program of the package (the
+    command line, bin/trace_run, bench.py) knows them without a change to the package's files.  `names`: a list of
+    "module" or "module:function" (the function is called once the module is imported); by default the
+    comma-separated list in the environment variable EDGELM_B200_PLUGINS."""
+    if names is None:
+        names = [n.strip() for n in os.environ.get("EDGELM_B200_PLUGINS", "").split(",") if n.strip()]
+    for name in names:
+        module, _, fn = name.partition(":")
+        m = importlib.import_module(module)
+        if fn:
+            getattr(m, fn)()
 
 
 def load_engine(model, dtype="bfloat16", ctx=1024, slots=8, max_tokens=None, batch=8192, profile=False, device="cuda:0",
@@ -78,5 +95,7 @@ class Session:
         self.slot = self.engine.open(1)[0]
 
 
-__all__ = ["ConfigError", "LlamaConfig", "read_config", "register_architecture", "registered_architectures",
+load_plugins()
+
+__all__ = ["load_plugins", "ConfigError", "LlamaConfig", "read_config", "register_architecture", "registered_architectures",
            "SamplingParams", "WeightsError", "write_model_dir", "load_engine", "generate", "Session"]

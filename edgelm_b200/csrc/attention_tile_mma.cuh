@@ -31,10 +31,7 @@ __device__ __forceinline__ uint32_t dm_smem_u32(const void* p) { return (uint32_
 // Rotary encoding of eight dims d .. d + 7 of a head row's first half (`lo`) with their partners in the second
 // half (`hi`): (a, b) -> (a cos - b sin, b cos + a sin) in float32, rounded to bfloat16.  cos_row / sin_row: the
 // position's row of the tables [head_dim / 2], 16-byte aligned at d.
-__device__ __forceinline__ void dm_rotate8(uint4& lo, uint4& hi, const float* cos_row, const float* sin_row, int d) {
-  const float4 c0 = *reinterpret_cast<const float4*>(cos_row + d), c1 = *reinterpret_cast<const float4*>(cos_row + d + 4);
-  const float4 s0 = *reinterpret_cast<const float4*>(sin_row + d), s1 = *reinterpret_cast<const float4*>(sin_row + d + 4);
-  const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w}, sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+__device__ __forceinline__ void dm_rotate8_vals(uint4& lo, uint4& hi, const float* cs, const float* sn) {   // cs, sn: 8 values each
   const __nv_bfloat16* pl = reinterpret_cast<const __nv_bfloat16*>(&lo);
   const __nv_bfloat16* ph = reinterpret_cast<const __nv_bfloat16*>(&hi);
   __nv_bfloat16 ol[8], oh[8];
@@ -46,6 +43,12 @@ __device__ __forceinline__ void dm_rotate8(uint4& lo, uint4& hi, const float* co
   }
   lo = *reinterpret_cast<const uint4*>(ol);
   hi = *reinterpret_cast<const uint4*>(oh);
+}
+__device__ __forceinline__ void dm_rotate8(uint4& lo, uint4& hi, const float* cos_row, const float* sin_row, int d) {
+  const float4 c0 = *reinterpret_cast<const float4*>(cos_row + d), c1 = *reinterpret_cast<const float4*>(cos_row + d + 4);
+  const float4 s0 = *reinterpret_cast<const float4*>(sin_row + d), s1 = *reinterpret_cast<const float4*>(sin_row + d + 4);
+  const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w}, sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+  dm_rotate8_vals(lo, hi, cs, sn);
 }
 
 constexpr int DM_ROWS = 16;       // query heads of a kv head served in one pass (rows of the A operand)

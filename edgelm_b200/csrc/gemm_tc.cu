@@ -18,11 +18,28 @@
 // Every wait on an mbarrier is bounded (about a second of SM clock): when it runs out the kernel
 // sets ERR_WAIT_TIMEOUT in the error word, raises a block-wide abort flag that ends the other
 // roles' waits, frees its tensor memory and returns.
+#include "attention_tile_mma.cuh"   // dm_rotate8: the rotation, as the separate kernels and the decode attention do it
 #include "tc_common.cuh"
 
 namespace edgelm {
 
-enum : int { TC_EPI_STORE = 0, TC_EPI_RESIDUAL = 1, TC_EPI_SWIGLU = 2 };
+enum : int { TC_EPI_STORE = 0, TC_EPI_RESIDUAL = 1, TC_EPI_SWIGLU = 2, TC_EPI_ROPE = 3 };
+
+// What the epilogue of the stacked q, k, v projection of a prompt step needs to finish the job of three kernels
+// (TC_EPI_ROPE): each token's position, its sequence's row of the page table, the rotation table, the cache.
+// Query heads are rotated and stored to `out`; key heads are rotated and written into their cache page, value heads
+// written there as they are; the k and v columns of `out` are not written (attention reads the cache).
+struct RopeAppend {
+  const int32_t* tok_pos;
+  const int32_t* tok_seq;
+  const int32_t* seq_slot;
+  const int32_t* page_table;
+  const float* cos_t;
+  const float* sin_t;
+  __nv_bfloat16* kcache;
+  __nv_bfloat16* vcache;
+  int table_stride, n_pages, max_pos, nh, nkv, hd;
+};
 
 constexpr int TC_BM = 128;   // rows of `a` per tile = lanes of tensor memory
 constexpr int TC_STAGES = 3;   // ring stages of the one-tile kernel when several blocks share an SM (48 KB stages: 144 KB)
@@ -108,11 +125,108 @@ __device__ __forceinline__ void epilogue_piece(const uint32_t* r, const uint32_t
   }
 }
 
+// What a row of the rotation epilogue needs besides the sums, fetched while the sums are still being made: the token's
+// position, its page (tiles that hold key or value heads), and, at head size 64, the position's row of the rotation
+// table in registers (the same for every head of the tile).
+struct RopeRow {
+  int pos;    // -1: the row takes no part (beyond M, or a position or page out of range, which is reported)
+  int page;
+  bool have_table;
+  float c[32], s[32];
+};
+__device__ __forceinline__ void rope_row_fetch(RopeRow& rr, const RopeAppend& ra, int row, int M, bool with_page, int* err) {
+  rr.pos = rr.page = -1;
+  rr.have_table = false;
+  if (row >= M) return;
+  const int pos = ra.tok_pos[row];
+  if (pos < 0 || pos >= ra.max_pos) {
+    atomicOr(err, ERR_POSITION_RANGE);
+    return;
+  }
+  if (with_page) {
+    const int page = ra.page_table[(size_t)ra.seq_slot[ra.tok_seq[row]] * ra.table_stride + pos / PAGE];
+    if (page < 0 || page >= ra.n_pages) {
+      atomicOr(err, ERR_PAGE_RANGE);
+      return;
+    }
+    rr.page = page;
+  }
+  rr.pos = pos;
+  if (ra.hd == 64) {
+    const float4* c = reinterpret_cast<const float4*>(ra.cos_t + (size_t)pos * 32);
+    const float4* sn = reinterpret_cast<const float4*>(ra.sin_t + (size_t)pos * 32);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float4 cv = c[i], sv = sn[i];
+      rr.c[4 * i] = cv.x; rr.c[4 * i + 1] = cv.y; rr.c[4 * i + 2] = cv.z; rr.c[4 * i + 3] = cv.w;
+      rr.s[4 * i] = sv.x; rr.s[4 * i + 1] = sv.y; rr.s[4 * i + 2] = sv.z; rr.s[4 * i + 3] = sv.w;
+    }
+    rr.have_table = true;
+  }
+}
+
+// 32 columns of a head's first half (`lo`, the head's dims d0 .. d0 + 31) and their partners in its second half (`hi`)
+// of one token's row.  The sums are rounded to bfloat16 first and rotated then, eight pairs at a time with the
+// arithmetic of the separate rotation kernel: a token's cache rows are the same bits whichever way they were made.
+__device__ __forceinline__ void epilogue_rope_piece(const uint32_t* lo, const uint32_t* hi, const RopeAppend& ra, const RopeRow& rr,
+                                                    __nv_bfloat16* out, int ldo, int row, int head, int d0) {
+  if (rr.pos < 0) return;
+  const int half = ra.hd >> 1;
+  __nv_bfloat16* dst;
+  if (head < ra.nh) {
+    dst = out + (size_t)row * ldo + (size_t)head * ra.hd;
+  } else {
+    const bool is_k = head < ra.nh + ra.nkv;
+    const int kvh = is_k ? head - ra.nh : head - ra.nh - ra.nkv;
+    dst = (is_k ? ra.kcache : ra.vcache) + (((size_t)rr.page * ra.nkv + kvh) * PAGE + rr.pos % PAGE) * ra.hd;
+  }
+  const bool rotate = head < ra.nh + ra.nkv;
+  const float* c = ra.cos_t + (size_t)rr.pos * half;
+  const float* sn = ra.sin_t + (size_t)rr.pos * half;
+#pragma unroll
+  for (int j0 = 0; j0 < 32; j0 += 8) {
+    uint4 a, b;
+    a.x = dm_pack(__uint_as_float(lo[j0]), __uint_as_float(lo[j0 + 1]));
+    a.y = dm_pack(__uint_as_float(lo[j0 + 2]), __uint_as_float(lo[j0 + 3]));
+    a.z = dm_pack(__uint_as_float(lo[j0 + 4]), __uint_as_float(lo[j0 + 5]));
+    a.w = dm_pack(__uint_as_float(lo[j0 + 6]), __uint_as_float(lo[j0 + 7]));
+    b.x = dm_pack(__uint_as_float(hi[j0]), __uint_as_float(hi[j0 + 1]));
+    b.y = dm_pack(__uint_as_float(hi[j0 + 2]), __uint_as_float(hi[j0 + 3]));
+    b.z = dm_pack(__uint_as_float(hi[j0 + 4]), __uint_as_float(hi[j0 + 5]));
+    b.w = dm_pack(__uint_as_float(hi[j0 + 6]), __uint_as_float(hi[j0 + 7]));
+    if (rotate) {
+      if (rr.have_table) dm_rotate8_vals(a, b, rr.c + j0, rr.s + j0);   // (head size 64: d0 is 0)
+      else dm_rotate8(a, b, c, sn, d0 + j0);
+    }
+    *reinterpret_cast<uint4*>(dst + d0 + j0) = a;
+    *reinterpret_cast<uint4*>(dst + half + d0 + j0) = b;
+  }
+}
+
+// All heads of a tile of BN columns (a multiple of the head size) for the rows of one epilogue warp.
+template <int BN>
+__device__ __forceinline__ void epilogue_rope_tile(uint32_t taddr, const RopeAppend& ra, const RopeRow& rr, __nv_bfloat16* out,
+                                                   int ldo, int row, int n0, int N) {
+  const int hd = ra.hd, half = hd >> 1;
+#pragma unroll 1
+  for (int h0 = 0; h0 < BN; h0 += hd) {
+    if (n0 + h0 >= N) break;   // uniform over the block
+#pragma unroll 1
+    for (int d0 = 0; d0 < half; d0 += 32) {
+      uint32_t lo[32], hi[32];
+      tmem_ld32(taddr + (uint32_t)(h0 + d0), lo);
+      tmem_ld32(taddr + (uint32_t)(h0 + half + d0), hi);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      epilogue_rope_piece(lo, hi, ra, rr, out, ldo, row, (n0 + h0) / hd, d0);
+    }
+  }
+}
+
 template <int BN, int EPI, typename TOut, int STAGES>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_b2, TOut* out, int ldo, const float* residual,
-               int M, int N, int K, int vec_ok, int* err, int k_splits, float* partial) {
+               int M, int N, int K, int vec_ok, int* err, int k_splits, float* partial, const RopeAppend rope) {
   // k_splits > 1: block z of the grid accumulates its share of K only and leaves the raw sums in
   // `partial` [split][weight][M][N] (float32); splitk_reduce_kernel adds the splits in their order and
   // applies the epilogue.  For products of few tiles and long K (decoding 17 to 128 sequences), which
@@ -209,9 +323,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     ResidualAhead ra[2];
     ra[0].have = ra[1].have = false;
     if (EPI == TC_EPI_RESIDUAL && k_splits == 1) fetch_residual(ra[0], residual, ldo, m0 + q * 32 + lane, n0, M, N, vec_ok);  // while the MMAs run
+    RopeRow rr;
+    if constexpr (EPI == TC_EPI_ROPE) rope_row_fetch(rr, rope, m0 + q * 32 + lane, M, n0 + BN > rope.nh * rope.hd, err);   // likewise
     const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(tmem_full_bar), 0, abort_flag, err));  // one decision per warp
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ok) {
+    if (ok && EPI == TC_EPI_ROPE) {
+      if constexpr (EPI == TC_EPI_ROPE)
+        epilogue_rope_tile<BN>(tmem_base + ((uint32_t)(q * 32) << 16), rope, rr, out, ldo, m0 + q * 32 + lane, n0, N);
+    } else if (ok) {
 #pragma unroll
       for (int c0 = 0; c0 < BN; c0 += 32) {
         if (n0 + c0 >= N) break;  // uniform over the block
@@ -287,7 +406,7 @@ template <int BN, int EPI, typename TOut>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                           const __grid_constant__ CUtensorMap map_b2, TOut* out, int ldo, const float* residual,
-                          int M, int N, int K, int vec_ok, int* err) {
+                          int M, int N, int K, int vec_ok, int* err, const RopeAppend rope) {
   constexpr int NB = EPI == TC_EPI_SWIGLU ? 2 : 1;
   constexpr int A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
   constexpr int STAGE_BYTES = A_BYTES + NB * B_BYTES;
@@ -394,18 +513,24 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++ti) {
       const int as = ti & 1;
       const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * BN;
+      RopeRow rr;
+      if constexpr (EPI == TC_EPI_ROPE) rope_row_fetch(rr, rope, m0 + q * 32 + lane, M, n0 + BN > rope.nh * rope.hd, err);   // while the MMAs run
       const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&tmem_full_bar[as]), (ti >> 1) & 1, abort_flag, err));
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (!ok) break;
       const uint32_t acc_addr = tmem_base + (uint32_t)as * ACC_COLS + ((uint32_t)(q * 32) << 16);
+      if constexpr (EPI == TC_EPI_ROPE) {
+        epilogue_rope_tile<BN>(acc_addr, rope, rr, out, ldo, m0 + q * 32 + lane, n0, N);
+      } else {
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        if (n0 + c0 >= N) break;
-        uint32_t r[32], r2[32];
-        tmem_ld32(acc_addr + (uint32_t)c0, r);
-        if (NB == 2) tmem_ld32(acc_addr + (uint32_t)c0 + BN, r2);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        epilogue_piece<EPI, TOut>(r, r2, out, ldo, residual, m0 + q * 32 + lane, n0 + c0, M, N, vec_ok);
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          if (n0 + c0 >= N) break;
+          uint32_t r[32], r2[32];
+          tmem_ld32(acc_addr + (uint32_t)c0, r);
+          if (NB == 2) tmem_ld32(acc_addr + (uint32_t)c0 + BN, r2);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          epilogue_piece<EPI, TOut>(r, r2, out, ldo, residual, m0 + q * 32 + lane, n0 + c0, M, N, vec_ok);
+        }
       }
       // this warp's rows of the stage are in registers or stored: hand the stage back to the MMA warp
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -454,7 +579,8 @@ static int splitk_for(int tiles, int n_k, size_t bytes_per_split) {
 
 template <int BN, int EPI, typename TOut>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, void* out, int ldo,
-                     const float* residual, int M, int N, int K, int vec_ok, int* err, cudaStream_t stream, bool persistent) {
+                     const float* residual, int M, int N, int K, int vec_ok, int* err, cudaStream_t stream, bool persistent,
+                     const RopeAppend& rope) {
   constexpr int NB = EPI == TC_EPI_SWIGLU ? 2 : 1;
   if (persistent) {
     constexpr int smem = TCP_STAGES * (TC_BM * TC_BK * 2 + NB * BN * TC_BK * 2) + 1024 + 256;
@@ -478,7 +604,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
     g_last_launches = 1;
     g_last_kernel = BN | (1 << 12) | (1 << 16);
     cudaError_t le = launch_pdl(32, kern, dim3(grid), dim3(TC_THREADS), (size_t)smem, stream, ma, mb, mb2, (TOut*)out, ldo, residual, M, N, K,
-                                vec_ok, err);
+                                vec_ok, err, rope);
     if (le != cudaSuccess) {
       set_error("gemm_tc: launch failed: %s", cudaGetErrorString(le));
       return -2;
@@ -488,7 +614,8 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
   constexpr int STAGE_BYTES = TC_BM * TC_BK * 2 + NB * BN * TC_BK * 2;
   constexpr int DEEP = TC_DEEP_BYTES / STAGE_BYTES;   // 6 stages of 32 KB, 8 of 24 KB
   dim3 grid((N + BN - 1) / BN, (M + TC_BM - 1) / TC_BM);
-  const int splits = splitk_for((int)(grid.x * grid.y), (K + TC_BK - 1) / TC_BK, (size_t)NB * M * N * sizeof(float));
+  // (the rotation epilogue is not one the reduce kernel of split products knows: such a product stays whole)
+  const int splits = EPI == TC_EPI_ROPE ? 1 : splitk_for((int)(grid.x * grid.y), (K + TC_BK - 1) / TC_BK, (size_t)NB * M * N * sizeof(float));
   grid.z = splits;
   g_last_launches = splits > 1 ? 2 : 1;
   // a grid of at most one block an SM has the shared memory to itself: a deeper ring hides more of the loads' latency
@@ -508,7 +635,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
       return -2;
     }
     cudaError_t le = launch_pdl(8, kern, grid, dim3(TC_THREADS), (size_t)smem, stream, ma, mb, mb2, (TOut*)out, ldo, residual, M, N, K,
-                                vec_ok, err, splits, g_splitk_ws);
+                                vec_ok, err, splits, g_splitk_ws, rope);
     if (le != cudaSuccess) {
       set_error("gemm_tc: launch failed: %s", cudaGetErrorString(le));
       return -2;
@@ -518,7 +645,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
   const int rc = deep ? go(gemm_tc_kernel<BN, EPI, TOut, DEEP>, DEEP * STAGE_BYTES + 1024 + 256)
                       : go(gemm_tc_kernel<BN, EPI, TOut, TC_STAGES>, TC_STAGES * STAGE_BYTES + 1024 + 256);
   if (rc) return rc;
-  if (splits > 1) {
+  if (EPI != TC_EPI_ROPE && splits > 1) {
     const size_t plane = (size_t)M * N;
     const int blocks = (int)((plane + 255) / 256 < 1184 ? (plane + 255) / 256 : 1184);
     splitk_reduce_kernel<EPI, TOut><<<blocks, 256, 0, stream>>>(g_splitk_ws, splits, (TOut*)out, ldo, residual, M, N);
@@ -568,9 +695,8 @@ extern "C" int edgelm_gemm_tc_takes(const void* a, int lda, const void* w, const
   return ok ? 1 : 0;
 }
 
-extern "C" int edgelm_gemm_tc(const void* a, int lda, const void* w, const void* w2, void* out, int ldo,
-                              const float* residual, int M, int N, int K, int out_dtype, int epilogue, int* err,
-                              cudaStream_t stream) {
+static int gemm_tc_run(const void* a, int lda, const void* w, const void* w2, void* out, int ldo, const float* residual,
+                       int M, int N, int K, int out_dtype, int epilogue, int* err, cudaStream_t stream, const RopeAppend& rope) {
   if (M == 0) return 0;
   EL_REFUSE(M > 0 && N > 0 && K > 0 && lda >= K && ldo >= N, "gemm_tc: bad sizes M=%d N=%d K=%d lda=%d ldo=%d", M, N, K, lda, ldo);
   EL_REFUSE(edgelm_gemm_tc_takes(a, lda, w, w2, K), "gemm_tc: K=%d and lda=%d must be multiples of 8 and the operands 16-byte aligned", K, lda);
@@ -589,7 +715,8 @@ extern "C" int edgelm_gemm_tc(const void* a, int lda, const void* w, const void*
   // several row tiles to share a weight tile in L2 (measured at 2,048 rows: N 576, K 576: 11.6 -> 8.8 us; N 576,
   // K 1536: 16.1 -> 13.5 us; with 256 tiles of 128 columns and K 8192 the narrow tiles lose: 68 -> 107 us)
   const long long tiles128 = (long long)((M + TC_BM - 1) / TC_BM) * ((N + 127) / 128);
-  const bool narrow = !wide && epilogue != TC_EPI_SWIGLU && g_tc_narrow && tiles128 < 148 && M > TC_BM;
+  const bool narrow = !wide && epilogue != TC_EPI_SWIGLU && g_tc_narrow && tiles128 < 148 && M > TC_BM &&
+                      (epilogue != TC_EPI_ROPE || rope.hd == 64);   // (a tile holds whole heads)
   const int bn = epilogue == TC_EPI_SWIGLU ? (wide ? 128 : 64) : (wide ? 256 : (narrow ? 64 : 128));
   CUtensorMap ma, mb, mb2;
   if (tensor_map(a, M, K, lda, TC_BM, &ma)) return -1;
@@ -602,32 +729,72 @@ extern "C" int edgelm_gemm_tc(const void* a, int lda, const void* w, const void*
   int rc = 0;
   if (wide) {
     if (epilogue == TC_EPI_STORE && out_dtype == DT_BF16)
-      rc = launch_tc<256, TC_EPI_STORE, __nv_bfloat16>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent);
+      rc = launch_tc<256, TC_EPI_STORE, __nv_bfloat16>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent, rope);
     else if (epilogue == TC_EPI_STORE && out_dtype == DT_F32)
-      rc = launch_tc<256, TC_EPI_STORE, float>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent);
+      rc = launch_tc<256, TC_EPI_STORE, float>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent, rope);
     else if (epilogue == TC_EPI_RESIDUAL)
-      rc = launch_tc<256, TC_EPI_RESIDUAL, float>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent);
+      rc = launch_tc<256, TC_EPI_RESIDUAL, float>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent, rope);
     else if (epilogue == TC_EPI_SWIGLU && out_dtype == DT_BF16)
-      rc = launch_tc<128, TC_EPI_SWIGLU, __nv_bfloat16>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent);
+      rc = launch_tc<128, TC_EPI_SWIGLU, __nv_bfloat16>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent, rope);
+    else if (epilogue == TC_EPI_ROPE && out_dtype == DT_BF16)
+      rc = launch_tc<256, TC_EPI_ROPE, __nv_bfloat16>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent, rope);
     else
       EL_REFUSE(false, "gemm_tc: unsupported epilogue %d with output dtype %d", epilogue, out_dtype);
-  } else if (narrow && epilogue == TC_EPI_STORE && out_dtype == DT_BF16)
-    rc = launch_tc<64, TC_EPI_STORE, __nv_bfloat16>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent);
+  } else if (narrow && epilogue == TC_EPI_ROPE && out_dtype == DT_BF16)
+    rc = launch_tc<64, TC_EPI_ROPE, __nv_bfloat16>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent, rope);
+  else if (epilogue == TC_EPI_ROPE && out_dtype == DT_BF16)
+    rc = launch_tc<128, TC_EPI_ROPE, __nv_bfloat16>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent, rope);
+  else if (narrow && epilogue == TC_EPI_STORE && out_dtype == DT_BF16)
+    rc = launch_tc<64, TC_EPI_STORE, __nv_bfloat16>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent, rope);
   else if (narrow && epilogue == TC_EPI_STORE && out_dtype == DT_F32)
-    rc = launch_tc<64, TC_EPI_STORE, float>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent);
+    rc = launch_tc<64, TC_EPI_STORE, float>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent, rope);
   else if (narrow && epilogue == TC_EPI_RESIDUAL)
-    rc = launch_tc<64, TC_EPI_RESIDUAL, float>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent);
+    rc = launch_tc<64, TC_EPI_RESIDUAL, float>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent, rope);
   else if (epilogue == TC_EPI_STORE && out_dtype == DT_BF16)
-    rc = launch_tc<128, TC_EPI_STORE, __nv_bfloat16>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent);
+    rc = launch_tc<128, TC_EPI_STORE, __nv_bfloat16>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent, rope);
   else if (epilogue == TC_EPI_STORE && out_dtype == DT_F32)
-    rc = launch_tc<128, TC_EPI_STORE, float>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent);
+    rc = launch_tc<128, TC_EPI_STORE, float>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent, rope);
   else if (epilogue == TC_EPI_RESIDUAL)
-    rc = launch_tc<128, TC_EPI_RESIDUAL, float>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent);
+    rc = launch_tc<128, TC_EPI_RESIDUAL, float>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent, rope);
   else if (epilogue == TC_EPI_SWIGLU && out_dtype == DT_BF16)
-    rc = launch_tc<64, TC_EPI_SWIGLU, __nv_bfloat16>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent);
+    rc = launch_tc<64, TC_EPI_SWIGLU, __nv_bfloat16>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent, rope);
   else
     EL_REFUSE(false, "gemm_tc: unsupported epilogue %d with output dtype %d", epilogue, out_dtype);
   if (rc) return rc;
   EL_LAUNCH_CHECK("gemm_tc");
   return 0;
+}
+
+extern "C" int edgelm_gemm_tc(const void* a, int lda, const void* w, const void* w2, void* out, int ldo,
+                              const float* residual, int M, int N, int K, int out_dtype, int epilogue, int* err,
+                              cudaStream_t stream) {
+  EL_REFUSE(epilogue >= TC_EPI_STORE && epilogue <= TC_EPI_SWIGLU, "gemm_tc: unknown epilogue %d", epilogue);
+  return gemm_tc_run(a, lda, w, w2, out, ldo, residual, M, N, K, out_dtype, epilogue, err, stream, RopeAppend{});
+}
+
+// 1 if the stacked q, k, v projection of a prompt step can rotate and append in its epilogue: bfloat16, head size 64
+// or 128, and the alignments that its 16-byte stores and table reads need.
+extern "C" int edgelm_gemm_tc_rope_takes(const void* a, int lda, const void* w, const void* qkv, int ldo, int K, int hd,
+                                         const void* kcache, const void* vcache, const void* cos_t, const void* sin_t) {
+  const bool ok = edgelm_gemm_tc_takes(a, lda, w, nullptr, K) && (hd == 64 || hd == 128) && (uintptr_t)qkv % 16 == 0 && ldo % 8 == 0 &&
+                  (uintptr_t)kcache % 16 == 0 && (uintptr_t)vcache % 16 == 0 && (uintptr_t)cos_t % 16 == 0 && (uintptr_t)sin_t % 16 == 0;
+  return ok ? 1 : 0;
+}
+
+// qkv[:, :nh * hd] = rotate(a . W^T) for the query heads; the rotated keys and the values go into the cache pages of
+// each token's sequence and position (and nowhere else).  W [(nh + 2 nkv) hd, K] is the three weights stacked.
+extern "C" int edgelm_gemm_tc_rope(const void* a, int lda, const void* w, void* qkv, int ldo, int M, int K,
+                                   const int32_t* tok_pos, const int32_t* tok_seq, const int32_t* seq_slot,
+                                   const int32_t* page_table, int table_stride, int n_pages, const float* cos_t,
+                                   const float* sin_t, int max_pos, void* kcache, void* vcache, int nh, int nkv, int hd,
+                                   int* err, cudaStream_t stream) {
+  EL_REFUSE(nh > 0 && nkv > 0 && table_stride > 0 && n_pages > 0 && max_pos > 0, "gemm_tc_rope: bad sizes");
+  EL_REFUSE(edgelm_gemm_tc_rope_takes(a, lda, w, qkv, ldo, K, hd, kcache, vcache, cos_t, sin_t),
+            "gemm_tc_rope: head size %d (takes 64 and 128), or an operand that is not 16-byte aligned", hd);
+  RopeAppend ra;
+  ra.tok_pos = tok_pos; ra.tok_seq = tok_seq; ra.seq_slot = seq_slot; ra.page_table = page_table;
+  ra.cos_t = cos_t; ra.sin_t = sin_t;
+  ra.kcache = static_cast<__nv_bfloat16*>(kcache); ra.vcache = static_cast<__nv_bfloat16*>(vcache);
+  ra.table_stride = table_stride; ra.n_pages = n_pages; ra.max_pos = max_pos; ra.nh = nh; ra.nkv = nkv; ra.hd = hd;
+  return gemm_tc_run(a, lda, w, nullptr, qkv, ldo, nullptr, M, (nh + 2 * nkv) * hd, K, DT_BF16, TC_EPI_ROPE, err, stream, ra);
 }

@@ -242,6 +242,35 @@ def gemm_tc(a, w, out, err, epilogue=EPI_STORE, w2=None, residual=None):
     count_launches(lib().edgelm_gemm_tc_last_launches())
 
 
+def gemm_tc_rope_takes(a, w, qkv, kcache, vcache, cos, sin, hd):
+    """Whether the stacked q, k, v projection can rotate and append in its epilogue (`gemm_tc_rope`)."""
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or qkv.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16:
+        return False
+    if a.stride(1) != 1 or qkv.stride(1) != 1 or not w.is_contiguous() or not (kcache.is_contiguous() and vcache.is_contiguous()):
+        return False
+    return bool(lib().edgelm_gemm_tc_rope_takes(_p(a), a.stride(0), _p(w), _p(qkv), qkv.stride(0), a.shape[1], int(hd),
+                                                _p(kcache), _p(vcache), _p(cos), _p(sin)))
+
+
+def gemm_tc_rope(a, w, qkv, tok_pos, tok_seq, seq_slot, page_table, cos, sin, kcache, vcache, nh, nkv, hd, err):
+    """The stacked q, k, v projection of a prompt step with rotation and cache append in its epilogue:
+    qkv[:, :nh hd] = rotated query heads of a @ w.T; the rotated keys and the values go to each token's place in the
+    cache pages.  The k and v columns of `qkv` are left as they were."""
+    _splitk_ready()
+    M, K = a.shape
+    _need(w.shape == ((nh + 2 * nkv) * hd, K) and qkv.shape == (M, (nh + 2 * nkv) * hd), "gemm_tc_rope: shapes")
+    _need(gemm_tc_rope_takes(a, w, qkv, kcache, vcache, cos, sin, hd), "gemm_tc_rope: these operands are not taken (bfloat16, head size 64 or 128, aligned)")
+    _need(kcache.shape[1:] == (nkv, PAGE, hd) and vcache.shape == kcache.shape, "gemm_tc_rope: cache layout")
+    _need(cos.dtype == torch.float32 and cos.shape[1] == hd // 2 and cos.is_contiguous() and sin.shape == cos.shape and sin.is_contiguous(), "gemm_tc_rope: table layout")
+    for t, n in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (seq_slot, "seq_slot"), (page_table, "page_table")):
+        _i32(t, n)
+    _need(tok_pos.numel() == M and tok_seq.numel() == M, "gemm_tc_rope: one position and one sequence index per token")
+    _check(lib().edgelm_gemm_tc_rope(_p(a), a.stride(0), _p(w), _p(qkv), qkv.stride(0), M, K, _p(tok_pos), _p(tok_seq), _p(seq_slot),
+                                     _p(page_table), page_table.stride(0), kcache.shape[0], _p(cos), _p(sin), cos.shape[0],
+                                     _p(kcache), _p(vcache), nh, nkv, hd, _p(err), _stream()), launches=0)
+    count_launches(lib().edgelm_gemm_tc_last_launches())
+
+
 def gemm_tc_last_kernel():
     """Which kernel the last `gemm_tc` call took: {"tile_columns", "persistent", "deep_ring", "k_splits"}."""
     v = int(lib().edgelm_gemm_tc_last_kernel())

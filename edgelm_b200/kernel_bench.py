@@ -116,6 +116,7 @@ def main(argv=None):
         cases = {
             "rmsnorm": lambda l: o.rmsnorm(x, nw, 1e-5, h),
             "qkv_proj": lambda l: o.gemm_tc(h, wq[l], qkv, err),
+            "qkv_proj_rope_append": lambda l: o.gemm_tc_rope(h, wq[l], qkv, tokpos, tokseq, seq, table, cos, sin, kc[l], vc[l], nh, nkv, hd, err),
             "rope_kv_append": lambda l: o.rope_kv_append(qkv, tokpos, tokseq, seq, table, cos, sin, kc[l], vc[l], nh, nkv, hd, err),
             "attn_prefill": lambda l: o.attn_prefill_mma(qkv, att, kc[l], vc[l], table, seq, t_seq, t_tok0, t_ntok, t_pos0, nt, nh, nkv, hd, scale, max_keys=T),
             "attn_prefill_tc": lambda l: o.attn_prefill_tc(qkv, att, kc[l], vc[l], table, seq, u_seq, u_tok0, u_ntok, u_pos0, nt2, nh, nkv, hd, scale, err),
@@ -123,6 +124,9 @@ def main(argv=None):
             "gate_up_swiglu": lambda l: o.gemm_tc(h, wg[l], mid, err, epilogue=o.EPI_SWIGLU, w2=wu[l]),
             "down_proj_residual": lambda l: o.gemm_tc(mid, wd[l], x, err, epilogue=o.EPI_RESIDUAL, residual=x),
         }
+        flops["qkv_proj_rope_append"] = flops["qkv_proj"]
+        if not o.gemm_tc_rope_takes(h, wq[0], qkv, kc[0], vc[0], cos, sin, hd):
+            del cases["qkv_proj_rope_append"]
         if not o.attn_prefill_tc_takes(bf, hd):
             del cases["attn_prefill_tc"]
         elif args.trace:

@@ -114,11 +114,17 @@ class Attention(Part):
         T = h.shape[0]
         ws = ctx.ws
         qkv = ws.alloc((T, (self.nh + 2 * self.nkv) * self.hd), self.dtype)
-        with ctx.prof("qkv_proj"):
-            linear.matmul(ctx, h, self.w_qkv, qkv, prefetch=(self.w_o,))
         a = ws.alloc((T, self.nh * self.hd), self.dtype)
         table = ctx.page_table(cache.group)
         tables = self.positions.rotation_tables() if hasattr(self.positions, "rotation_tables") else None
+        encoded = False
+        if not ctx.all_single and hasattr(self.positions, "project_encode_append"):
+            # a prompt step: the position encoding may know a kernel that projects, encodes and appends in one
+            with ctx.prof("qkv_proj_rope_append"):
+                encoded = self.positions.project_encode_append(ctx, h, self.w_qkv, qkv, cache, self.nh, self.nkv)
+        if not encoded:
+            with ctx.prof("qkv_proj"):
+                linear.matmul(ctx, h, self.w_qkv, qkv, prefetch=(self.w_o,))
         if ctx.all_single and tables is not None:
             # one token per sequence: rotation, append and attention in one kernel
             splits = ctx.decode_splits(self.nkv, self._decode_resident())
@@ -132,8 +138,9 @@ class Attention(Part):
             with ctx.prof("o_proj_residual"):
                 linear.matmul(ctx, a, self.w_o, x, epilogue=linear.EPI_RESIDUAL, residual=x, prefetch=ctx.weights_after)
             return
-        with ctx.prof("rope_kv_append"):
-            self.positions.encode_and_append(ctx, qkv, cache, self.nh, self.nkv)
+        if not encoded:
+            with ctx.prof("rope_kv_append"):
+                self.positions.encode_and_append(ctx, qkv, cache, self.nh, self.nkv)
         if ctx.all_single:
             splits = ctx.decode_splits(self.nkv, self._decode_resident())
             part_o = part_ml = None

@@ -37,6 +37,22 @@ class RotaryPositions(Part):
         by itself asks for these instead of calling encode_and_append."""
         return self.cos, self.sin
 
+    def project_encode_append(self, ctx, h, w_qkv, qkv, cache, n_heads, n_kv_heads):
+        """The stacked projection, the rotation and the append as ONE kernel, where that kernel exists: a prompt step
+        in bfloat16 with a head size the tensor-core product's epilogue rotates (its threads hold a head's two halves
+        after reading the accumulator).  True if done: `qkv` then holds the rotated queries (its key and value
+        columns are not written; attention reads the cache).  False: the caller runs the product and then
+        `encode_and_append`.  (adarsh-sgh/edgelm fuses the rotation into its attention op, src/passes.cpp:115-135.)"""
+        from . import linear
+        if h.shape[0] <= linear.FEW_ROWS or qkv.dtype != torch.bfloat16 or self.head_dim not in (64, 128):
+            return False
+        h = linear.as_tensor(h)
+        if not ops.gemm_tc_rope_takes(h, w_qkv, qkv, cache.k, cache.v, self.cos, self.sin, self.head_dim):
+            return False
+        ops.gemm_tc_rope(h, w_qkv, qkv, ctx.tok_pos, ctx.tok_seq, ctx.seq_index, ctx.page_table(cache.group), self.cos, self.sin,
+                         cache.k, cache.v, n_heads, n_kv_heads, self.head_dim, ctx.err)
+        return True
+
     def encode_and_append(self, ctx, qkv, cache, n_heads, n_kv_heads):
         """Rotate the query and key heads of qkv[T, (nh + 2 nkv) hd] in place at each token's
         position; write the rotated keys and the values into the cache entry's pages."""

@@ -795,6 +795,84 @@ def test_attn_prefill_tc_far_key_and_diagonal():
     assert rel_err(out[:, hd:], case.v[0][p0:p0 + n, 0]) < 5e-2
 
 
+# ----------------------------------------------------------------------------- q, k, v projection with RoPE and append in its epilogue
+@pytest.mark.parametrize("nh,nkv,hd,K,lens,kernel", [
+    (9, 3, 64, 576, [(0, 300)], dict(tile_columns=64)),                                   # one head a tile
+    (15, 5, 64, 960, [(0, 1500), (64, 1), (100, 447), (63, 100)], dict(tile_columns=128)),     # continued prompts, 2,048 tokens
+    (32, 32, 64, 2048, [(0, 2048), (10, 37)], dict(tile_columns=256, persistent=True)),   # the persistent kernel, ragged last tile
+    (4, 2, 128, 256, [(0, 130), (5, 70)], dict(tile_columns=128)),                        # head size 128: a head is a whole tile
+    (6, 1, 128, 1096, [(0, 3100), (3, 900)], dict(tile_columns=256, persistent=True)),
+])
+def test_gemm_tc_rope_append_epilogue(nh, nkv, hd, K, lens, kernel):
+    """Against the plain implementation (product, rotation of q and k at each token's position, k and v at their
+    places in the pages), and bit for bit against the separate kernels (product, then rotate + append)."""
+    o = ops()
+    seqs = lens
+    T = sum(n for _, n in seqs)
+    width = (nh + 2 * nkv) * hd
+    theta, max_pos = 30000.0, max(p + n for p, n in seqs) + 5
+    cos, sin = plain.rope_angles(np.arange(max_pos), hd, theta)
+    cos_t, sin_t = torch.from_numpy(cos).to(dev()), torch.from_numpy(sin).to(dev())
+    a = rnd((T, K), torch.bfloat16, 170, 0.5)
+    w = rnd((width, K), torch.bfloat16, 171, 0.1)
+    lengths = [p + n for p, n in seqs]
+    ca = PagedCase(o, torch.bfloat16, lengths, nkv, hd, seed=nh + K)
+    cb = PagedCase(o, torch.bfloat16, lengths, nkv, hd, seed=nh + K)
+    tok_pos = torch.tensor([p + i for p, n in seqs for i in range(n)], dtype=torch.int32, device=dev())
+    tok_seq = torch.tensor([s for s, (p, n) in enumerate(seqs) for _ in range(n)], dtype=torch.int32, device=dev())
+    err = torch.zeros(1, dtype=torch.int32, device=dev())
+    # separate kernels
+    q1 = torch.empty(T, width, dtype=torch.bfloat16, device=dev())
+    o.gemm_tc(a, w, q1, err)
+    o.rope_kv_append(q1, tok_pos, tok_seq, ca.seq_slot, ca.table, cos_t, sin_t, ca.kcache, ca.vcache, nh, nkv, hd, err)
+    # one kernel
+    q2 = torch.full((T, width), 7.0, dtype=torch.bfloat16, device=dev())
+    assert o.gemm_tc_rope_takes(a, w, q2, cb.kcache, cb.vcache, cos_t, sin_t, hd)
+    o.gemm_tc_rope(a, w, q2, tok_pos, tok_seq, cb.seq_slot, cb.table, cos_t, sin_t, cb.kcache, cb.vcache, nh, nkv, hd, err)
+    k = o.gemm_tc_last_kernel()
+    assert all(k[key] == v for key, v in kernel.items()) and k["k_splits"] == 1, k
+    assert int(err.item()) == 0
+    assert torch.equal(q2[:, :nh * hd], q1[:, :nh * hd])
+    assert bool((q2[:, nh * hd:] == 7.0).all())                     # the k and v columns are not written
+    same = lambda x, y: bool(((x == y) | (torch.isnan(x) & torch.isnan(y))).all())
+    assert same(cb.kcache, ca.kcache) and same(cb.vcache, ca.vcache)  # every row of every page, written or not
+    # the plain implementation
+    y = (a.double() @ w.double().T).float().cpu().to(torch.bfloat16).float().numpy()
+    pos = tok_pos.cpu().numpy()
+    qr = plain.rope(y[:, :nh * hd], pos, nh, hd, theta)
+    kr = plain.rope(y[:, nh * hd:(nh + nkv) * hd], pos, nkv, hd, theta).reshape(T, nkv, hd)
+    vr = y[:, (nh + nkv) * hd:].reshape(T, nkv, hd)
+    assert rel_err(q2[:, :nh * hd], torch.from_numpy(qr)) < 1.6e-2
+    t0 = 0
+    for s, (p0, n) in enumerate(seqs):
+        slot = int(cb.seq_slot[s])
+        for t in (0, n // 2, n - 1):
+            page = int(cb.table[slot, (p0 + t) // o.PAGE])
+            assert rel_err(cb.kcache[page, :, (p0 + t) % o.PAGE], torch.from_numpy(kr[t0 + t])) < 1.6e-2
+            assert rel_err(cb.vcache[page, :, (p0 + t) % o.PAGE], torch.from_numpy(vr[t0 + t])) < 1.6e-2
+        t0 += n
+
+
+def test_gemm_tc_rope_reports_bad_positions_and_pages():
+    o = ops()
+    nh, nkv, hd, K, T = 2, 1, 64, 64, 40
+    cos, sin = plain.rope_angles(np.arange(64), hd, 1e4)
+    cos_t, sin_t = torch.from_numpy(cos).to(dev()), torch.from_numpy(sin).to(dev())
+    a, w = rnd((T, K), torch.bfloat16, 1), rnd(((nh + 2 * nkv) * hd, K), torch.bfloat16, 2)
+    case = PagedCase(o, torch.bfloat16, [64], nkv, hd, seed=3)
+    qkv = torch.zeros(T, (nh + 2 * nkv) * hd, dtype=torch.bfloat16, device=dev())
+    tok_seq = torch.zeros(T, dtype=torch.int32, device=dev())
+    for bad, bit in ((torch.arange(30, 30 + T), 2), (torch.arange(0, T), 4)):
+        err = torch.zeros(1, dtype=torch.int32, device=dev())
+        table = case.table.clone()
+        if bit == 4:
+            table[:] = -1
+        o.gemm_tc_rope(a, w, qkv, bad.to(torch.int32).to(dev()), tok_seq, case.seq_slot, table, cos_t, sin_t, case.kcache, case.vcache,
+                       nh, nkv, hd, err)
+        assert int(err.item()) == bit
+    assert not o.gemm_tc_rope_takes(a, w, qkv, case.kcache, case.vcache, cos_t, sin_t, 32)
+
+
 # ----------------------------------------------------------------------------- decode attention with RoPE and append fused
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (9, 3, 64), (3, 1, 32), (12, 2, 128), (2, 2, 48)])

@@ -142,12 +142,18 @@ def _register_toy():
             slots = ctx.seq_slots.long()
             t0 = 0
             for i, n in enumerate(ctx.seq_lengths):
-                s = state[slots[i]]
+                s = state.index_select(0, slots[i:i + 1])[0]     # (indexing by a device tensor: nothing is read on the host)
                 for t in range(t0, t0 + n):
                     s = self.decay * s + h[t].float()
                     x[t] += s @ self.w.T
-                state[slots[i]] = s
+                state.index_copy_(0, slots[i:i + 1], s[None])
                 t0 += n
+
+    @register_mixer("toy_decay_state_replayable")
+    class ToyStateMixerReplayable(ToyStateMixer):
+        # Nothing in `forward` reads device data on the host (the slots are indexed as device tensors, the loops run
+        # over the step's shape, which a captured graph is keyed by): steps through it may be replayed from a graph.
+        graph_safe = True
 
     @register_architecture("ToyStateForCausalLM", model_type="toy_state")
     class ToyConfig:
@@ -162,7 +168,8 @@ def _register_toy():
             d = self.d
             D, V = d["width"], d["vocab_size"]
             norm = lambda name: PartSpec("rmsnorm", {"dim": D, "eps": d["eps"], "name": name})
-            toy = PartSpec("toy_decay_state", {"dim": D, "decay": d["decay"], "name": "mix.weight"})
+            toy = PartSpec("toy_decay_state_replayable" if d.get("replayable") else "toy_decay_state",
+                           {"dim": D, "decay": d["decay"], "name": "mix.weight"})
             att = PartSpec("attention", {"hidden_size": D, "num_heads": 2, "num_kv_heads": 1, "head_dim": 16,
                                          "positions": PartSpec("rope", {"head_dim": 16, "theta": 1000.0, "max_positions": 128}),
                                          "names": {"q": "q.weight", "k": "k.weight", "v": "v.weight", "o": "o.weight"}})
@@ -237,6 +244,91 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
     for r, g in zip(reqs, got):
         assert H.rel_err(g, _toy_plain(W, d, r)) < 5e-5
     eng.cache.check()
+
+
+def _toy_folder(tmp_path, name="toy", **extra):
+    from edgelm_b200.config import read_config
+    from edgelm_b200.engine.model import expected_weights
+    from edgelm_b200.weights import random_tensors, read_dir, write_file
+    d = {"architectures": ["ToyStateForCausalLM"], "vocab_size": 53, "width": 40, "inner": 56, "eps": 1e-5, "decay": 0.8, **extra}
+    folder = tmp_path / name
+    folder.mkdir()
+    (folder / "config.json").write_text(json.dumps(d))
+    exp = expected_weights(read_config(str(folder)).plan())
+    write_file(str(folder / "model.safetensors"), random_tensors(exp, seed=9, sigma=0.15, dtype=torch.float32))
+    W = {k: v.float().numpy() for k, v in read_dir(str(folder)).items()}
+    return d, str(folder), W
+
+
+def _toy_greedy(W, d, prompt, n):
+    seq, out = list(prompt), []
+    for _ in range(n):
+        out.append(int(np.argmax(_toy_plain(W, d, seq)[-1])))
+        seq.append(out[-1])
+    return out
+
+
+def test_a_state_mixer_that_allows_graphs_advances_its_state_once(tmp_path):
+    """Decode steps of a model whose mixer keeps a fixed-size state are captured like any other (one eager run, then
+    the capture, then the replay, all in the step that meets a batch size first): the state must move once in that
+    step.  Greedy generation through the entry point against the plain toy model."""
+    _register_toy()
+    import edgelm_b200
+    d, folder, W = _toy_folder(tmp_path, replayable=True)
+    eng = edgelm_b200.load_engine(folder, dtype="float32", ctx=128, slots=3)
+    assert eng.use_graphs and eng.cache.state_groups
+    prompts = [[5, 17, 3, 44], [9], [int(v) for v in np.random.default_rng(1).integers(0, 53, size=40)]]
+    got = edgelm_b200.generate(None, prompts, n=10, engine=eng, slots=3, stop=[], ignore_eos=True)
+    assert eng._graphs, "the decode steps were not captured"
+    assert got == [_toy_greedy(W, d, p, 10) for p in prompts]
+    # a prompt step whose shape comes back is captured too (at its second appearance), on the state of fresh slots
+    from edgelm_b200.engine.engine import StepEntry
+    long = [[int(v) for v in np.random.default_rng(10 + i).integers(0, 53, size=50)] for i in range(3)]
+    for r in long:
+        slot = eng.open(1)[0]
+        lg = eng.step([StepEntry(slot, r, list(range(50)))]).cpu().numpy()
+        lg2 = eng.step([StepEntry(slot, [7], [0])]).cpu().numpy()
+        eng.close([slot])
+        assert H.rel_err(np.concatenate([lg, lg2]), _toy_plain(W, d, r + [7])) < 5e-5
+    assert ((50,), 50) in eng._step_graphs
+
+
+def test_a_toy_architecture_through_every_program(tmp_path, capsys):
+    """run, info, bench and logits of the command line, and bin/trace_run as its own process, on the folder of an
+    architecture that only this test file knows: none of them reads an architecture's configuration fields."""
+    import os
+    import subprocess
+    import sys
+    _register_toy()
+    from edgelm_b200.cli import main
+    d, folder, W = _toy_folder(tmp_path)
+    assert main(["info", "-m", folder, "--ops", "--dtype", "f32"]) == 0
+    out = capsys.readouterr().out
+    assert "ToyConfig" in out and "toy_decay_state(" in out and "fixed-size state of 2 layer run(s)" in out and "keys/values of 1 layer run(s)" in out
+    toks = [int(v) for v in np.random.default_rng(5).integers(0, 53, size=14)]
+    path = str(tmp_path / "lg.f32")
+    assert main(["logits", "-m", folder, "--dtype", "f32", "--tokens", ",".join(map(str, toks)), "--prefill", "6", "--out", path]) == 0
+    assert H.rel_err(np.fromfile(path, dtype="<f4").reshape(14, -1), _toy_plain(W, d, toks)) < 5e-5
+    capsys.readouterr()
+    assert main(["run", "-m", folder, "--dtype", "f32", "-p", "5,17,3;9", "-n", "5", "--ignore-eos", "--verbose"]) == 0
+    out = capsys.readouterr().out
+    assert "5,17,3 => " + ",".join(map(str, _toy_greedy(W, d, [5, 17, 3], 5))) in out and "9 => " + ",".join(map(str, _toy_greedy(W, d, [9], 5))) in out
+    assert main(["bench", "-m", folder, "--dtype", "f32", "--prompt-len", "12", "--gen", "3", "--reps", "1", "--batch-sizes", "2", "--json"]) == 0
+    row = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert row["batch"] == 2 and row["decode_tok_s"] > 0
+    # the replay program in a process of its own learns the architecture from a plugin named in the environment
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, EDGELM_B200_PLUGINS="test_parts_gpu:_register_toy",
+               PYTHONPATH=os.pathsep.join([os.path.dirname(os.path.abspath(__file__)), root, os.environ.get("PYTHONPATH", "")]))
+    outdir = tmp_path / "replay"
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": toks[:9], "want": list(range(9))}], "end": []}]
+    steps += [{"step": i + 1, "entries": [{"id": "a", "tokens": [t], "want": [0]}], "end": ["a"] if i == 4 else []} for i, t in enumerate(toks[9:])]
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folder, "--dtype", "float32", "--out", str(outdir),
+                        "--max-tokens", "64"], input="\n".join(json.dumps(s) for s in steps) + "\n", text=True, capture_output=True, env=env, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(6)]
+    got = np.concatenate([np.fromfile(outdir / f"{i}.f32", dtype="<f4").reshape(-1, 53) for i in range(6)])
+    assert H.rel_err(got, _toy_plain(W, d, toks)) < 5e-5
 
 
 # ----------------------------------------------------------------------------- a toy feed-forward with routing, a toy position encoding
@@ -399,7 +491,7 @@ def test_cli_commands(tmp_path, capsys):
     o = H.Oracle(d)
     assert main(["info", "-m", d, "--ops", "--dtype", "f32"]) == 0
     out = capsys.readouterr().out
-    assert "kv cache" in out and "attention" in out and "swiglu" in out
+    assert "cache   :" in out and "keys/values of 2 layer run(s)" in out and "attention(heads 4, kv_heads 2, head_dim 16" in out and "swiglu(intermediate 128)" in out
     toks = H.tokens_for("tiny_a", 12, 400)
     path = str(tmp_path / "lg.f32")
     assert main(["logits", "-m", d, "--dtype", "f32", "--tokens", ",".join(map(str, toks)), "--prefill", "5", "--out", path]) == 0
