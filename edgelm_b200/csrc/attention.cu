@@ -34,7 +34,8 @@ attn_prefill_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int l
                     const T* __restrict__ vcache, const int32_t* __restrict__ page_table, int table_stride,
                     const int32_t* __restrict__ seq_slot, const int32_t* __restrict__ tile_seq,
                     const int32_t* __restrict__ tile_tok0, const int32_t* __restrict__ tile_ntok,
-                    const int32_t* __restrict__ tile_pos0, int nh, int nkv, int hd, float scale) {
+                    const int32_t* __restrict__ tile_pos0, int nh, int nkv, int hd, float scale, int window) {
+  // window > 0: a token at position p sees the keys p - window + 1 .. p only (0: every key up to p)
   extern __shared__ float smem[];
   const int ks = hd + 1;                       // padded key row: lanes read different rows
   float* Ks = smem;                            // [PAGE][hd + 1]
@@ -63,13 +64,14 @@ attn_prefill_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int l
   }
 
   float m[RW], l[RW], acc[RW][NC];
-  int limit[RW];
+  int limit[RW], first[RW];
 #pragma unroll
   for (int r = 0; r < RW; ++r) {
     m[r] = -CUDART_INF_F;
     l[r] = 0.f;
     const int rr = row_base + warp * RW + r;
     limit[r] = rr < rows_total ? pos0 + rr / g : -1;  // last key this row may see; -1: no row
+    first[r] = window > 0 ? max(0, limit[r] - window + 1) : 0;   // first key it may see
 #pragma unroll
     for (int c = 0; c < NC; ++c) acc[r][c] = 0.f;
   }
@@ -78,7 +80,9 @@ attn_prefill_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int l
   for (int r = 0; r < RW; ++r) warp_limit = max(warp_limit, limit[r]);
 
   const int n_tiles = (nkeys_block + PAGE - 1) / PAGE;
-  for (int kt = 0; kt < n_tiles; ++kt) {
+  // pages before the first key of the block's first row are seen by none of its rows (and may no longer be held)
+  const int kt_begin = window > 0 ? max(0, pos0 + row_base / g - window + 1) / PAGE : 0;
+  for (int kt = kt_begin; kt < n_tiles; ++kt) {
     const int page = pages[kt];
     const T* kp = kcache + ((size_t)page * nkv + kvh) * PAGE * hd;
     const T* vp = vcache + ((size_t)page * nkv + kvh) * PAGE * hd;
@@ -109,8 +113,8 @@ attn_prefill_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int l
     float corr[RW];
 #pragma unroll
     for (int r = 0; r < RW; ++r) {
-      const float a = j0 <= limit[r] ? s0[r] * scale : -CUDART_INF_F;
-      const float b = j1 <= limit[r] ? s1[r] * scale : -CUDART_INF_F;
+      const float a = j0 <= limit[r] && j0 >= first[r] ? s0[r] * scale : -CUDART_INF_F;
+      const float b = j1 <= limit[r] && j1 >= first[r] ? s1[r] * scale : -CUDART_INF_F;
       const float mx = fmaxf(m[r], warp_max(fmaxf(a, b)));
       float p0 = 0.f, p1 = 0.f;
       corr[r] = 1.f;
@@ -244,7 +248,8 @@ attn_decode_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ld
                    const int32_t* __restrict__ page_table, int table_stride, const int32_t* __restrict__ seq_slot,
                    const int32_t* __restrict__ seq_pos, int nh, int nkv, int hd, float scale, int n_splits, int tk,
                    float* __restrict__ part_o, float* __restrict__ part_ml, int* err,
-                   const float* __restrict__ cos_t, const float* __restrict__ sin_t, int max_pos) {
+                   const float* __restrict__ cos_t, const float* __restrict__ sin_t, int max_pos, int window) {
+  // window > 0: the token sees the last `window` keys only (its own included); the pages before them are not touched.
   // cos_t given: q, k, v are the raw projections of the new token; this kernel rotates q and k at
   // the token's position (float32, half-split pairing, rounded to T as the stand-alone kernel
   // stores them) and the block that owns the token's page appends k and v to the cache.
@@ -267,9 +272,11 @@ attn_decode_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ld
   const int g = nh / nkv;
   const int nkeys = seq_pos[seq] + 1;      // the new token's own key is the last one
   const int32_t* pages = page_table + (size_t)seq_slot[seq] * table_stride;
-  const int n_pages = (nkeys + PAGE - 1) / PAGE;
+  const int first_key = window > 0 ? max(0, nkeys - window) : 0;
+  const int page0 = first_key / PAGE;                       // the first page that holds a key the token sees
+  const int n_pages = (nkeys + PAGE - 1) / PAGE - page0;
   const int per_split = (n_pages + n_splits - 1) / n_splits;
-  const int p_begin = split * per_split, p_end = min(n_pages, p_begin + per_split);
+  const int p_begin = page0 + split * per_split, p_end = min(page0 + n_pages, p_begin + per_split);
   const int tiles_per_page = PAGE / tk;
   const int n_tiles = max(0, p_end - p_begin) * tiles_per_page;
   const int cpr = hd / VEC;                // 16-byte chunks per key row
@@ -290,7 +297,7 @@ attn_decode_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ld
   const int half = hd >> 1;
   const bool fused = cos_t != nullptr;
   const int tpos = min(pos, max_pos - 1);
-  const bool owner = fused && (pos / PAGE) / per_split == split;   // this block's pages include the new token's
+  const bool owner = fused && (pos / PAGE - page0) / per_split == split;   // this block's pages include the new token's
   if (fused && pos >= max_pos && threadIdx.x == 0 && err) atomicOr(err, ERR_POSITION_RANGE);
   auto rotated = [&](const T* row, int d) {   // element d of the rotated head `row`
     const int j = d < half ? d : d - half;
@@ -328,8 +335,11 @@ attn_decode_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ld
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dec_smem_u32(Vt)), "l"(vcache + src), "r"(bytes), "r"(bar) : "memory");
   };
+  // a tile takes part if it holds a key of the sequence that the token sees (tiles ascend; the first ones of the
+  // window's first page may lie before the window)
+  auto tile_key0 = [&](int t) { return (p_begin + t / tiles_per_page) * PAGE + (t - (t / tiles_per_page) * tiles_per_page) * tk; };
   bool pre_issued = false;
-  if (warp < n_tiles && (p_begin * PAGE + warp * tk) < nkeys) {   // the first tile is on its way while the queries are staged
+  if (warp < n_tiles && tile_key0(warp) < nkeys && tile_key0(warp) + tk > first_key) {   // the first tile is on its way while the queries are staged
     if (lane == 0) issue_tile(warp);
     pre_issued = true;
   }
@@ -355,6 +365,7 @@ attn_decode_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ld
       const int pg = p_begin + t / tiles_per_page, sub = t - (t / tiles_per_page) * tiles_per_page;
       const int key0 = pg * PAGE + sub * tk;
       if (key0 >= nkeys) break;            // later tiles of the last page hold no key (tiles ascend)
+      if (key0 + tk <= first_key) continue;   // wholly before the window
       const int valid = min(tk, nkeys - key0);
       if (pre_issued) pre_issued = false;   // this tile's copies were started before the queries were staged
       else if (lane == 0) issue_tile(t);
@@ -411,9 +422,9 @@ attn_decode_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ld
 #pragma unroll
       for (int r = 0; r < RW; ++r) {
         if (r < rows) {
-          const float a = lane < valid ? s[0][r] * scale : -CUDART_INF_F;
-          const float b = lane + 32 < valid ? s[1][r] * scale : -CUDART_INF_F;
-          const float mx = fmaxf(m[r], warp_max(fmaxf(a, b)));  // finite: valid >= 1
+          const float a = lane < valid && key0 + lane >= first_key ? s[0][r] * scale : -CUDART_INF_F;
+          const float b = lane + 32 < valid && key0 + lane + 32 >= first_key ? s[1][r] * scale : -CUDART_INF_F;
+          const float mx = fmaxf(m[r], warp_max(fmaxf(a, b)));  // finite: the tile holds a key that the token sees
           const float corr = expf(m[r] - mx);
           const float p0 = expf(a - mx), p1 = expf(b - mx);
           l[r] = l[r] * corr + warp_sum(p0 + p1);
@@ -561,7 +572,7 @@ template <typename T, int NC>
 int launch_prefill(const void* q, int ldq, void* out, int ldo, const void* kc, const void* vc, const int32_t* page_table,
                    int table_stride, const int32_t* seq_slot, const int32_t* tile_seq, const int32_t* tile_tok0,
                    const int32_t* tile_ntok, const int32_t* tile_pos0, int n_tiles, int max_tile_tokens, int nh, int nkv,
-                   int hd, float scale, cudaStream_t stream) {
+                   int hd, float scale, int window, cudaStream_t stream) {
   const int g = nh / nkv;
   const size_t smem = sizeof(float) * ((size_t)PAGE * (hd + 1) + (size_t)PAGE * hd + (size_t)ATT_ROWS * hd + (size_t)ATT_ROWS * PAGE);
   auto kern = attn_prefill_kernel<T, NC>;
@@ -573,7 +584,7 @@ int launch_prefill(const void* q, int ldq, void* out, int ldo, const void* kc, c
   dim3 grid(n_tiles, nkv, (max_tile_tokens * g + ATT_ROWS - 1) / ATT_ROWS);
   kern<<<grid, ATT_WARPS * 32, smem, stream>>>((const T*)q, ldq, (T*)out, ldo, (const T*)kc, (const T*)vc, page_table,
                                               table_stride, seq_slot, tile_seq, tile_tok0, tile_ntok, tile_pos0, nh, nkv,
-                                              hd, scale);
+                                              hd, scale, window);
   return 0;
 }
 
@@ -594,7 +605,7 @@ template <typename T, int NC>
 int launch_decode(const void* q, int ldq, void* out, int ldo, const void* kc, const void* vc, const int32_t* page_table,
                   int table_stride, const int32_t* seq_slot, const int32_t* seq_pos, int n_seqs, int nh, int nkv, int hd,
                   float scale, int n_splits, float* part_o, float* part_ml, int* err, cudaStream_t stream,
-                  const float* cos_t = nullptr, const float* sin_t = nullptr, int max_pos = 0) {
+                  const float* cos_t = nullptr, const float* sin_t = nullptr, int max_pos = 0, int window = 0) {
   constexpr int NP = NC <= 2 ? 1 : NC / 2;  // pairs of dims per lane: ceil(hd / 64)
   dim3 grid(n_seqs, nkv, n_splits);
   cudaError_t le = cudaSuccess;
@@ -605,7 +616,7 @@ int launch_decode(const void* q, int ldq, void* out, int ldo, const void* kc, co
     // query heads a kv head (with one, 15 of the 16 rows are zero, but the kernel is bound by the cache's bytes:
     // measured at 32/32 heads, 1,500 keys, batch 64: 136 us against the CUDA-core kernel's 210 us).
     const bool aligned = ldq % 8 == 0 && (uintptr_t)q % 16 == 0;   // it reads the query rows 16 bytes at a time
-    if ((hd == 32 || hd == 64 || hd == 96 || hd == 128) && !g_decode_cuda_cores && aligned) {
+    if ((hd == 32 || hd == 64 || hd == 96 || hd == 128) && !g_decode_cuda_cores && aligned && window <= 0) {   // (a window: the CUDA-core kernel)
       on_mma = true;
       const size_t smem = decode_mma_head_bytes(hd) + (size_t)DEC_WARPS * 2 * PAGE * (hd + 8) * 2;
       auto go = [&](auto kern) {
@@ -649,7 +660,7 @@ int launch_decode(const void* q, int ldq, void* out, int ldo, const void* kc, co
     // both kernels are programmatic dependent launches when that is switched on
     le = launch_pdl(2, kern, grid, dim3(DEC_WARPS * 32), smem, stream, (const T*)q, ldq, (T*)out, ldo,
                     (T*)const_cast<void*>(kc), (T*)const_cast<void*>(vc), page_table, table_stride, seq_slot, seq_pos,
-                    nh, nkv, hd, scale, n_splits, tk, part_o, part_ml, err, cos_t, sin_t, max_pos);
+                    nh, nkv, hd, scale, n_splits, tk, part_o, part_ml, err, cos_t, sin_t, max_pos, window);
   }
   g_decode_last_launches = n_splits > 1 ? 2 : 1;
   if (le == cudaSuccess && n_splits > 1) {
@@ -700,13 +711,13 @@ extern "C" int edgelm_attn_prefill(const void* q, int ldq, void* out, int ldo, c
                                    int dtype, const int32_t* page_table, int table_stride, const int32_t* seq_slot,
                                    const int32_t* tile_seq, const int32_t* tile_tok0, const int32_t* tile_ntok,
                                    const int32_t* tile_pos0, int n_tiles, int max_tile_tokens, int nh, int nkv, int hd,
-                                   float scale, cudaStream_t stream) {
+                                   float scale, int window, cudaStream_t stream) {
   if (n_tiles == 0) return 0;
   if (check_heads("attn_prefill", nh, nkv, hd)) return -1;
   EL_REFUSE(n_tiles > 0 && max_tile_tokens > 0, "attn_prefill: bad tile counts");
   EL_REFUSE(nkv <= 65535 && (max_tile_tokens * (nh / nkv) + ATT_ROWS - 1) / ATT_ROWS <= 65535, "attn_prefill: grid too large");
   EL_ATT_DISPATCH(launch_prefill, q, ldq, out, ldo, kcache, vcache, page_table, table_stride, seq_slot, tile_seq, tile_tok0,
-                  tile_ntok, tile_pos0, n_tiles, max_tile_tokens, nh, nkv, hd, scale, stream);
+                  tile_ntok, tile_pos0, n_tiles, max_tile_tokens, nh, nkv, hd, scale, window, stream);
   EL_LAUNCH_CHECK("attn_prefill");
   return 0;
 }
@@ -730,13 +741,13 @@ extern "C" int edgelm_attn_set_error_word(int* err) {
 extern "C" int edgelm_attn_decode(const void* q, int ldq, void* out, int ldo, const void* kcache, const void* vcache,
                                   int dtype, const int32_t* page_table, int table_stride, const int32_t* seq_slot,
                                   const int32_t* seq_pos, int n_seqs, int nh, int nkv, int hd, float scale, int n_splits,
-                                  float* part_o, float* part_ml, int* err, cudaStream_t stream) {
+                                  float* part_o, float* part_ml, int window, int* err, cudaStream_t stream) {
   if (n_seqs == 0) return 0;
   if (check_heads("attn_decode", nh, nkv, hd)) return -1;
   EL_REFUSE(n_splits >= 1 && n_splits <= 65535 && nkv <= 65535, "attn_decode: bad split count %d", n_splits);
   EL_REFUSE(n_splits == 1 || (part_o && part_ml), "attn_decode: %d splits need the scratch buffers", n_splits);
   EL_ATT_DISPATCH(launch_decode, q, ldq, out, ldo, kcache, vcache, page_table, table_stride, seq_slot, seq_pos, n_seqs, nh,
-                  nkv, hd, scale, n_splits, part_o, part_ml, err, stream);
+                  nkv, hd, scale, n_splits, part_o, part_ml, err, stream, (const float*)nullptr, (const float*)nullptr, 0, window);
   EL_LAUNCH_CHECK("attn_decode");
   return 0;
 }
@@ -749,14 +760,14 @@ extern "C" int edgelm_attn_decode_rope(const void* qkv, int ldq, void* out, int 
                                        const int32_t* page_table, int table_stride, const int32_t* seq_slot,
                                        const int32_t* seq_pos, const float* cos_t, const float* sin_t, int max_pos,
                                        int n_seqs, int nh, int nkv, int hd, float scale, int n_splits, float* part_o,
-                                       float* part_ml, int* err, cudaStream_t stream) {
+                                       float* part_ml, int window, int* err, cudaStream_t stream) {
   if (n_seqs == 0) return 0;
   if (check_heads("attn_decode_rope", nh, nkv, hd)) return -1;
   EL_REFUSE(n_splits >= 1 && n_splits <= 65535 && nkv <= 65535, "attn_decode_rope: bad split count %d", n_splits);
   EL_REFUSE(n_splits == 1 || (part_o && part_ml), "attn_decode_rope: %d splits need the scratch buffers", n_splits);
   EL_REFUSE(cos_t && sin_t && max_pos > 0, "attn_decode_rope: needs the position table");
   EL_ATT_DISPATCH(launch_decode, qkv, ldq, out, ldo, kcache, vcache, page_table, table_stride, seq_slot, seq_pos, n_seqs, nh,
-                  nkv, hd, scale, n_splits, part_o, part_ml, err, stream, cos_t, sin_t, max_pos);
+                  nkv, hd, scale, n_splits, part_o, part_ml, err, stream, cos_t, sin_t, max_pos, window);
   EL_LAUNCH_CHECK("attn_decode_rope");
   return 0;
 }

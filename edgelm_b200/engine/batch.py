@@ -180,7 +180,7 @@ class BatchBuffers:
         self._decode = None
         if T == B and R == B:
             self._decode = {"slots": list(seq_slots), "pos": [int(x) for x in pos0], "views": views, "words": o,
-                            "held": {g.id: g.n_held[slots].copy() for g in self.groups}, "slot_index": slots}
+                            "version": {g.id: g.version for g in self.groups}, "slot_index": slots}
         return ctx
 
     def refill_next_token(self, ctx, token_ids, seq_slots, seq_pos0):
@@ -200,12 +200,11 @@ class BatchBuffers:
         a = views["seq_pos"][0]
         h[a:a + B] += 1
         for g in self.groups:
-            held = g.n_held[d["slot_index"]]
-            if (held != d["held"][g.id]).any():
+            if g.version != d["version"][g.id]:    # a page was taken or given back since the rows were laid out
                 s = self.stride[g.id]
                 a = views[("table", g.id)][0]
                 h[a:a + B * s] = g.table[d["slot_index"]].reshape(-1)
-                d["held"][g.id] = held.copy()
+                d["version"][g.id] = g.version
         o = d["words"]
         self.dev[:o].copy_(self.host[:o], non_blocking=True)
         self._copied.record()

@@ -170,11 +170,11 @@ class Engine:
             n = len(e.tokens)
             while start < n:
                 room = self.max_step_tokens - cur_tokens
-                if room == 0 or len(cur) == self.max_step_seqs:
+                if room == 0 or len(cur) == self.max_step_seqs or (cur and cur[-1][0] is e):   # (a sequence takes part in a micro-step once)
                     micro.append(cur)
                     cur, cur_tokens = [], 0
                     room = self.max_step_tokens
-                take = min(room, n - start)
+                take = min(room, n - start, self.cache.piece_tokens or n)
                 cur.append((e, start, take))
                 cur_tokens += take
                 start += take
@@ -201,6 +201,9 @@ class Engine:
     def _run_pieces(self, pieces, logits, row0, row_of, order):
         token_ids, slots, ntok, pos0, want_rows = [], [], [], [], []
         t0 = 0
+        if self.cache.piece_tokens:     # windowed groups reserve piece by piece (what earlier pieces no longer need went back)
+            for e, start, take in pieces:
+                self.cache.reserve(e.slot, take)
         for e, start, take in pieces:
             token_ids.append(e.tokens[start:start + take])
             slots.append(e.slot)

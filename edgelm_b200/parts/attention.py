@@ -31,6 +31,12 @@ class Attention(Part):
         self.names = dict(spec["names"])
         self.dtype = env.dtype
         self.positions = env.build_shared("positions", spec["positions"])
+        # `window`: a token sees the last so many keys only, its own included (None: every key).  Nothing in the Llama
+        # decoder sets it; a model with windowed layers names it in the spec of those layers' mixers.
+        self.window = spec.get("window")
+        if self.window is not None and int(self.window) < 1:
+            raise ConfigError(f"attention: a window of {self.window} keys")
+        self.window = int(self.window) if self.window is not None else None
         self.scale = 1.0 / math.sqrt(self.hd)
         self.group = self.nh // self.nkv
         self.tile_tokens = max(1, 32 // self.group)  # tokens whose heads fill one block of the prefill kernel
@@ -39,10 +45,15 @@ class Attention(Part):
         self._tc = None   # whether the tcgen05 prefill kernel does
 
     def sizes(self):
-        return {"heads": self.nh, "kv_heads": self.nkv, "head_dim": self.hd, **self.positions.sizes()}
+        out = {"heads": self.nh, "kv_heads": self.nkv, "head_dim": self.hd, **self.positions.sizes()}
+        if self.window is not None:
+            out["window"] = self.window
+        return out
 
     def flops(self, n_tokens, attended):
         proj = 2.0 * n_tokens * self.hidden * (2 * self.nh + 2 * self.nkv) * self.hd    # q, k, v and the output projection
+        if self.window is not None:
+            attended = min(attended, n_tokens * self.window)
         return proj + 4.0 * attended * self.nh * self.hd                                # scores and weighted values
 
     def weight_shapes(self, prefix):
@@ -60,7 +71,7 @@ class Attention(Part):
     def _decode_resident(self):
         """Blocks of the tensor-core decode attention kernel that an SM holds (its shared memory: the staged
         queries and four warps' key and value tiles of 64 padded rows), or None where that kernel does not run."""
-        if self.dtype != torch.bfloat16 or self.hd not in (32, 64, 96, 128):
+        if self.dtype != torch.bfloat16 or self.hd not in (32, 64, 96, 128) or self.window is not None:
             return None
         head = (16 * (self.hd + 8) * 2 + 2 * self.hd * 2 + 4 * 8 + 127) // 128 * 128
         block = head + 4 * 2 * 64 * (self.hd + 8) * 2
@@ -70,14 +81,14 @@ class Attention(Part):
         return (self.w_qkv,)
 
     def decode_fusion(self):
-        if not hasattr(self.positions, "rotation_tables"):
+        if not hasattr(self.positions, "rotation_tables") or self.window is not None:
             return None
         cos, sin = self.positions.rotation_tables()
         return {"kind": "attention_rope", "w_qkv": self.w_qkv, "w_o": self.w_o, "num_heads": self.nh, "num_kv_heads": self.nkv,
                 "head_dim": self.hd, "scale": self.scale, "cos": cos, "sin": sin}
 
     def cache_need(self):
-        return KVNeed(self.nkv, self.hd)
+        return KVNeed(self.nkv, self.hd, self.window)
 
     # Steps whose longest sequence brings fewer new tokens than this stay on the mma.sync kernel (tiles of 64 rows):
     # measured at 9 heads of 64 (32 heads): 128 new tokens 4.6 (5.0) us against 5.7 (5.8) us on tcgen05, 256 tokens
@@ -91,13 +102,13 @@ class Attention(Part):
         return sizes + ((ops.MMA_PREFILL_TILE,) if self._mma_prefill() else (self.tile_tokens,))
 
     def _mma_prefill(self):
-        if self._mma is None:
-            self._mma = ops.attn_prefill_mma_takes(self.dtype, self.hd)
+        if self._mma is None:   # (the tensor-core kernels have no lower key bound: a windowed mixer stays on the CUDA cores)
+            self._mma = self.window is None and ops.attn_prefill_mma_takes(self.dtype, self.hd)
         return self._mma
 
     def _tc_prefill(self):
         if self._tc is None:
-            self._tc = ops.attn_prefill_tc_takes(self.dtype, self.hd)
+            self._tc = self.window is None and ops.attn_prefill_tc_takes(self.dtype, self.hd)
         return self._tc
 
     def workspace_bytes(self, n_tokens, n_seqs):
@@ -134,7 +145,8 @@ class Attention(Part):
                 part_ml = ws.alloc((ctx.n_seqs * self.nh * splits * 2,), torch.float32)
             with ctx.prof("attn_decode"):
                 ops.attn_decode_rope(qkv, a, cache.k, cache.v, table, ctx.seq_index, ctx.seq_pos, tables[0], tables[1],
-                                     ctx.n_seqs, self.nh, self.nkv, self.hd, self.scale, splits, part_o, part_ml, err=ctx.err)
+                                     ctx.n_seqs, self.nh, self.nkv, self.hd, self.scale, splits, part_o, part_ml, err=ctx.err,
+                                     window=self.window)
             with ctx.prof("o_proj_residual"):
                 linear.matmul(ctx, a, self.w_o, x, epilogue=linear.EPI_RESIDUAL, residual=x, prefetch=ctx.weights_after)
             return
@@ -149,7 +161,7 @@ class Attention(Part):
                 part_ml = ws.alloc((ctx.n_seqs * self.nh * splits * 2,), torch.float32)
             with ctx.prof("attn_decode"):
                 ops.attn_decode(qkv, a, cache.k, cache.v, table, ctx.seq_index, ctx.seq_pos, ctx.n_seqs, self.nh, self.nkv,
-                                self.hd, self.scale, splits, part_o, part_ml, err=ctx.err)
+                                self.hd, self.scale, splits, part_o, part_ml, err=ctx.err, window=self.window)
         elif self._tc_prefill() and max(ctx.seq_lengths) >= self.TC_PREFILL_MIN_TOKENS:
             tiles = ctx.tiles(ops.TC_PREFILL_TILE)
             with ctx.prof("attn_prefill"):
@@ -165,6 +177,6 @@ class Attention(Part):
             tiles = ctx.tiles(self.tile_tokens)
             with ctx.prof("attn_prefill"):
                 ops.attn_prefill(qkv, a, cache.k, cache.v, table, ctx.seq_index, tiles.seq, tiles.tok0, tiles.ntok,
-                                 tiles.pos0, tiles.count, self.tile_tokens, self.nh, self.nkv, self.hd, self.scale)
+                                 tiles.pos0, tiles.count, self.tile_tokens, self.nh, self.nkv, self.hd, self.scale, window=self.window)
         with ctx.prof("o_proj_residual"):
             linear.matmul(ctx, a, self.w_o, x, epilogue=linear.EPI_RESIDUAL, residual=x, prefetch=ctx.weights_after)

@@ -35,8 +35,8 @@ def test_groups_and_sizes():
     assert c.entries[3].group is not c.entries[0].group
     assert c.n_pages == 10 and c.max_pages_per_seq == 4 and c.n_slots == 10
     assert make_cache(100).n_pages == 2 and pages_for(65) == 2 and pages_for(64) == 1 and pages_for(0) == 0
-    with pytest.raises(CacheError, match="windowed"):
-        SequenceCache([KVNeed(2, 16, window=128)], 256, 256, device=None)
+    with pytest.raises(CacheError, match="window"):
+        SequenceCache([KVNeed(2, 16, window=0)], 256, 256, device=None)
 
 
 def test_sequences_grow_and_give_back():
@@ -260,3 +260,67 @@ def test_the_loop_asks_the_backend_for_its_account():
     out = loop.run([[0] * 500, [1] * 700, [2] * 900])
     assert [g.tokens for g in out] == [[5] * 3, [6] * 3, [7] * 3]
     assert be.max_live == 2      # the backend's slots, not the caller's max_batch, bound a batch
+
+
+def test_a_windowed_group_keeps_the_window_and_one_piece():
+    """Two groups with different needs, each with storage of its own: every key, and the last 100 keys.  The windowed
+    one gives pages back as a sequence grows, never holds more than the window and one piece of a step, and its
+    pool is sized for that."""
+    c = SequenceCache([KVNeed(2, 16), KVNeed(2, 16, window=100), KVNeed(2, 16, window=100), None], 64 * 64, 4096, device=None,
+                      max_seqs=4, piece_tokens=128)
+    full, win = c.kv_groups
+    assert full.window is None and win.window == 100 and win.n_entries == 2 and c.piece_tokens == 128
+    assert win.pages_per_seq == pages_for(99 + 128) + 1 == 5 and win.n_pages == 4 * 5 and full.n_pages == 64
+    s = c.open()
+    length = 0
+    for piece in [128, 128, 44, 1, 1, 1, 128, 7] + [1] * 150:
+        c.reserve(s, piece)
+        lo = win.first_page(length)             # the first page a token of this piece sees
+        assert all(win.table[s, i] >= 0 for i in range(lo, pages_for(length + piece)))
+        c.advance(s, piece)
+        length += piece
+        c.check()
+        assert int(win.n_held[s]) <= win.pages_per_seq
+        assert int(full.n_held[s]) == pages_for(length)
+        assert all(win.table[s, i] < 0 for i in range(0, win.first_page(length)))    # given back
+    assert win.pool.available() == win.n_pages - int(win.n_held[s])
+    c.close(s)
+    c.check()
+    assert win.pool.available() == win.n_pages and full.pool.available() == 64
+    # a long prompt is reserved piece by piece: the first call takes the first piece's pages only
+    s = c.open()
+    c.reserve(s, 1000)
+    assert int(win.n_held[s]) == 2 and int(full.n_held[s]) == pages_for(1000)
+    c.close(s)
+    # the footprint a planner counts is in units of the largest pool
+    assert c.footprint(64) == 64 * 4 and c.footprint(4000) == max(pages_for(4000), -(-5 * 64 // 20)) * 64
+    only = SequenceCache([KVNeed(2, 16, window=100)], 64 * 64, 4096, device=None, max_seqs=4, piece_tokens=128)
+    assert only.footprint(4000) == 16 * 64 and only.capacity_tokens == 64 * 64   # four sequences of any length fit
+
+
+def test_random_windowed_sequences_never_lose_a_page():
+    rng = random.Random(11)
+    c = SequenceCache([KVNeed(1, 16, window=70), KVNeed(1, 16)], 40 * 64, 2000, device=None, max_seqs=6, piece_tokens=64)
+    live = {}
+    for _ in range(1500):
+        try:
+            r = rng.random()
+            if r < 0.2 and c.slots.available():
+                live[c.open()] = 0
+            elif r < 0.85 and live:
+                s = rng.choice(list(live))
+                n = rng.choice([1, 1, 1, 5, 64, 33])
+                c.reserve(s, n)
+                c.advance(s, n)
+                live[s] += n
+            elif live:
+                s = rng.choice(list(live))
+                c.close(s)
+                del live[s]
+        except CacheError:
+            pass
+        c.check()
+    for s in list(live):
+        c.close(s)
+    c.check()
+    assert all(g.pool.available() == g.n_pages for g in c.kv_groups)

@@ -166,8 +166,9 @@ class PagedCase:
         self.seq_slot = torch.tensor(slots, dtype=torch.int32, device=dev())
 
 
-def attention_rows(q, k, v, pos0, nh, nkv, hd):
-    """Plain causal attention of new rows at positions pos0.. over keys 0..pos0+t (float64)."""
+def attention_rows(q, k, v, pos0, nh, nkv, hd, window=None):
+    """Plain causal attention of new rows at positions pos0.. over keys 0..pos0+t (float64); with `window` over the
+    last `window` of them only."""
     T = q.shape[0]
     q = q.double().reshape(T, nh, hd)
     k = k.double()
@@ -176,10 +177,11 @@ def attention_rows(q, k, v, pos0, nh, nkv, hd):
     out = torch.zeros(T, nh, hd, dtype=torch.float64)
     for t in range(T):
         n = pos0 + t + 1
+        lo = max(0, n - window) if window else 0
         for h in range(nh):
-            s = (k[:n, h // g] @ q[t, h]) / math.sqrt(hd)
+            s = (k[lo:n, h // g] @ q[t, h]) / math.sqrt(hd)
             p = torch.softmax(s, dim=0)
-            out[t, h] = p @ v[:n, h // g]
+            out[t, h] = p @ v[lo:n, h // g]
     return out.reshape(T, nh * hd)
 
 
@@ -234,6 +236,96 @@ def test_attn_decode(dtype, nh, nkv, hd, n_splits):
     for s, n in enumerate(lengths):
         want = attention_rows(qkv[s:s + 1, :nh * hd].float().cpu(), case.k[s], case.v[s], n - 1, nh, nkv, hd)
         assert rel_err(out[s:s + 1], want) < (1e-5 if dtype == torch.float32 else 1e-2), (s, n)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 16, 40), (9, 3, 64, 100), (2, 1, 128, 64), (3, 3, 48, 1), (6, 2, 32, 200)])
+def test_attention_with_a_window(dtype, nh, nkv, hd, window):
+    """The last `window` keys only, in prompt steps (whole, continued, single tokens) and in decode steps (1, 3 and 16
+    splits).  The pages before a sequence's window hold poison (1e4 keys, NaN values) as pages that were given back
+    may: a kernel that looked there would show."""
+    o = ops()
+    seqs = [(0, 5), (0, 150), (64, 1), (100, 129), (63, 2), (300, 70)]
+    lengths = [a + b for a, b in seqs]
+    case = PagedCase(o, dtype, lengths, nkv, hd, seed=nh * 10 + hd)
+    P = o.PAGE
+    for s_, (p0, n) in enumerate(seqs):      # poison the pages that no token of this step sees
+        slot = int(case.seq_slot[s_])
+        for pg in range(0, max(0, p0 - window + 1) // P):
+            page = int(case.table[slot, pg])
+            case.kcache[page] = 1e4
+            case.vcache[page] = float("nan")
+    g = nh // nkv
+    T = sum(b for _, b in seqs)
+    qkv = rnd((T, (nh + 2 * nkv) * hd), dtype, 22)
+    tq = max(1, 32 // g)
+    cols = [[], [], [], []]
+    t0 = 0
+    for s_, (p0, n) in enumerate(seqs):
+        for a in range(0, n, tq):
+            for c, v in zip(cols, (s_, t0 + a, min(tq, n - a), p0 + a)):
+                c.append(v)
+        t0 += n
+    mk = lambda x: torch.tensor(x, dtype=torch.int32, device=dev())
+    out = torch.zeros(T, nh * hd, dtype=dtype, device=dev())
+    o.attn_prefill(qkv, out, case.kcache, case.vcache, case.table, case.seq_slot, *[mk(c) for c in cols], len(cols[0]), tq, nh, nkv, hd,
+                   1.0 / math.sqrt(hd), window=window)
+    t0 = 0
+    for s_, (p0, n) in enumerate(seqs):
+        want = attention_rows(qkv[t0:t0 + n, :nh * hd].float().cpu(), case.k[s_], case.v[s_], p0, nh, nkv, hd, window)
+        assert rel_err(out[t0:t0 + n], want) < (1e-5 if dtype == torch.float32 else 1e-2), (s_, p0, n)
+        t0 += n
+    # decoding: the new token is the last of each sequence
+    B = len(lengths)
+    for s_, n in enumerate(lengths):
+        slot = int(case.seq_slot[s_])
+        for pg in range(0, max(0, n - window) // P):
+            page = int(case.table[slot, pg])
+            case.kcache[page] = 1e4
+            case.vcache[page] = float("nan")
+    q1 = rnd((B, (nh + 2 * nkv) * hd), dtype, 23)
+    seq_pos = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=dev())
+    for n_splits in (1, 3, 16):
+        out = torch.zeros(B, nh * hd, dtype=dtype, device=dev())
+        po = torch.full((B * nh * n_splits * hd,), float("nan"), device=dev())
+        pm = torch.full((B * nh * n_splits * 2,), float("nan"), device=dev())
+        o.attn_decode(q1, out, case.kcache, case.vcache, case.table, case.seq_slot, seq_pos, B, nh, nkv, hd, 1.0 / math.sqrt(hd),
+                      n_splits, po, pm, window=window)
+        for s_, n in enumerate(lengths):
+            want = attention_rows(q1[s_:s_ + 1, :nh * hd].float().cpu(), case.k[s_], case.v[s_], n - 1, nh, nkv, hd, window)
+            assert rel_err(out[s_:s_ + 1], want) < (1e-5 if dtype == torch.float32 else 1e-2), (n_splits, s_, n)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_windows_edge_stands_out(dtype):
+    """One key is made to dominate every query.  Placed on the window's first key the output is its value; placed one
+    key earlier it must leave no trace."""
+    o = ops()
+    nh, nkv, hd, n, window = 2, 1, 32, 700, 130
+    for where, inside in ((n - window, True), (n - window - 1, False)):
+        case = PagedCase(o, dtype, [n], nkv, hd, seed=9)
+        qkv = rnd((1, (nh + 2 * nkv) * hd), dtype, 24)
+        qkv[:, :nh * hd] = 0
+        qkv[:, 0] = 30.0
+        qkv[:, hd] = 30.0           # both heads look along dim 0
+        page = int(case.table[int(case.seq_slot[0]), where // o.PAGE])
+        case.kcache[page, 0, where % o.PAGE] = 0
+        case.kcache[page, 0, where % o.PAGE, 0] = 30.0
+        case.k[0][where] = 0
+        case.k[0][where, 0, 0] = 30.0
+        seq_pos = torch.tensor([n - 1], dtype=torch.int32, device=dev())
+        out = torch.zeros(1, nh * hd, dtype=dtype, device=dev())
+        po, pm = torch.empty(nh * 4 * hd, device=dev()), torch.empty(nh * 4 * 2, device=dev())
+        o.attn_decode(qkv, out, case.kcache, case.vcache, case.table, case.seq_slot, seq_pos, 1, nh, nkv, hd, 1.0 / math.sqrt(hd), 4, po, pm,
+                      window=window)
+        tiles = [torch.tensor([v], dtype=torch.int32, device=dev()) for v in (0, 0, 1, n - 1)]
+        out2 = torch.zeros(1, nh * hd, dtype=dtype, device=dev())
+        o.attn_prefill(qkv, out2, case.kcache, case.vcache, case.table, case.seq_slot, *tiles, 1, 16, nh, nkv, hd, 1.0 / math.sqrt(hd), window=window)
+        want = attention_rows(qkv[:, :nh * hd].float().cpu(), case.k[0], case.v[0], n - 1, nh, nkv, hd, window)
+        for got in (out, out2):
+            assert rel_err(got, want) < (1e-5 if dtype == torch.float32 else 1e-2)
+            close = rel_err(got[:, :hd], case.v[0][where, 0][None]) < 5e-2
+            assert close == inside, (where, inside)
 
 
 def test_attention_far_key_stands_out():

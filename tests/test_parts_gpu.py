@@ -331,6 +331,117 @@ def test_a_toy_architecture_through_every_program(tmp_path, capsys):
     assert H.rel_err(got, _toy_plain(W, d, toks)) < 5e-5
 
 
+# ----------------------------------------------------------------------------- layers with a window beside layers without
+def _register_windowed():
+    """A toy architecture whose layers use the package's own attention, some with a window: two cache groups with
+    different needs (every key; the last keys), each with storage of its own."""
+    from edgelm_b200.config import register_architecture
+    from edgelm_b200.config.base import LayerSpec, ModelPlan, PartSpec, ScheduleEntry
+    from edgelm_b200.config.registry import registered_architectures
+
+    if "ToyWindowedForCausalLM" in registered_architectures():
+        return
+
+    @register_architecture("ToyWindowedForCausalLM", model_type="toy_windowed")
+    class ToyWindowedConfig:
+        def __init__(self, d):
+            self.d = d
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d)
+
+        def plan(self):
+            d = self.d
+            D, V, hd = d["width"], d["vocab_size"], d["head_dim"]
+            norm = lambda name: PartSpec("rmsnorm", {"dim": D, "eps": 1e-5, "name": name})
+            rope = PartSpec("rope", {"head_dim": hd, "theta": 2000.0, "max_positions": d["positions"]})
+            names = {"q": "q.weight", "k": "k.weight", "v": "v.weight", "o": "o.weight"}
+            att = lambda w: PartSpec("attention", {"hidden_size": D, "num_heads": d["heads"], "num_kv_heads": d["kv_heads"], "head_dim": hd,
+                                                   "positions": rope, "names": names, **({"window": w} if w else {})})
+            ffn = PartSpec("swiglu", {"hidden_size": D, "intermediate_size": d["inner"],
+                                      "names": {"gate": "g.weight", "up": "u.weight", "down": "d.weight"}})
+            layers = tuple(LayerSpec(f"l{i}.", "prenorm", att(w), norm("n1.weight"), ffn, norm("n2.weight")) for i, w in enumerate(d["windows"]))
+            return ModelPlan(hidden_size=D, vocab_size=V, max_positions=d["positions"],
+                             embedding=PartSpec("embedding", {"vocab_size": V, "dim": D, "name": "emb.weight"}),
+                             layers=layers, schedule=tuple(ScheduleEntry(i) for i in range(len(layers))), final_norm=norm("final.weight"),
+                             head=PartSpec("lm_head", {"vocab_size": V, "dim": D, "tied_to": "emb.weight", "name": "head.weight"}))
+
+
+def _windowed_plain(W, d, tokens):
+    """The toy model in plain NumPy: whole sequence, no cache; a windowed layer masks the keys before its window."""
+    nh, nkv, hd = d["heads"], d["kv_heads"], d["head_dim"]
+    x = plain.embed(W["emb.weight"], tokens)
+    T = len(tokens)
+    pos = np.arange(T)
+    for i, w in enumerate(d["windows"]):
+        p = f"l{i}."
+        h = plain.rmsnorm(x, W[p + "n1.weight"], 1e-5)
+        q = plain.rope(h @ W[p + "q.weight"].T, pos, nh, hd, 2000.0).reshape(T, nh, hd)
+        k = plain.rope(h @ W[p + "k.weight"].T, pos, nkv, hd, 2000.0).reshape(T, nkv, hd)
+        v = (h @ W[p + "v.weight"].T).reshape(T, nkv, hd)
+        a = np.zeros((T, nh, hd), dtype=np.float32)
+        hidden = pos[None, :] > pos[:, None]
+        if w:
+            hidden = hidden | (pos[None, :] < pos[:, None] - w + 1)
+        for hh in range(nh):
+            sc = (q[:, hh] @ k[:, hh // (nh // nkv)].T).astype(np.float32) * np.float32(1.0 / math.sqrt(hd))
+            sc[hidden] = -np.inf
+            sc = sc - sc.max(axis=1, keepdims=True)
+            pr = np.exp(sc).astype(np.float32)
+            a[:, hh] = (pr / pr.sum(axis=1, keepdims=True)) @ v[:, hh // (nh // nkv)]
+        x = (x + a.reshape(T, nh * hd) @ W[p + "o.weight"].T).astype(np.float32)
+        h2 = plain.rmsnorm(x, W[p + "n2.weight"], 1e-5)
+        x = (x + plain.swiglu_mlp(h2, W[p + "g.weight"], W[p + "u.weight"], W[p + "d.weight"])).astype(np.float32)
+    return plain.rmsnorm(x, W["final.weight"], 1e-5) @ W["emb.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("shape", [dict(width=48, heads=4, kv_heads=2, head_dim=16, inner=72, windows=[40, 0, 100]),
+                                   dict(width=64, heads=2, kv_heads=1, head_dim=64, inner=96, windows=[0, 70])])
+def test_windowed_layers_beside_full_ones(tmp_path, dtype, shape):
+    """Whole prompts (cut into pieces by the engine so that a windowed group holds its window and one piece), the last
+    tokens one by one far beyond the window (pages are given back on the way), unequal batches on reused slots."""
+    _register_windowed()
+    from edgelm_b200.config import read_config
+    from edgelm_b200.engine.engine import Engine, load_model
+    from edgelm_b200.engine.model import expected_weights
+    from edgelm_b200.weights import random_tensors, read_dir, write_file
+    d = {"architectures": ["ToyWindowedForCausalLM"], "vocab_size": 97, "positions": 700, **shape}
+    folder = tmp_path / "win"
+    folder.mkdir()
+    (folder / "config.json").write_text(json.dumps(d))
+    exp = expected_weights(read_config(str(folder)).plan())
+    write_file(str(folder / "model.safetensors"), random_tensors(exp, seed=21, sigma=0.12, dtype=torch.bfloat16))
+    W = {k: v.float().numpy() for k, v in read_dir(str(folder)).items()}
+    eng = Engine(load_model(str(folder), dtype), max_tokens=64 * 30, max_seqs=4)
+    groups = {g.window: g for g in eng.cache.kv_groups}
+    assert len(groups) == len(set(shape["windows"])) and None in groups            # a group per need
+    for w, g in groups.items():
+        if w:
+            assert g.n_pages == 4 * g.pages_per_seq < groups[None].n_pages          # storage of its own, sized by the window
+    tol = H.TOL[dtype]
+    reqs = [[int(v) for v in np.random.default_rng(40 + i).integers(0, 97, size=n)] for i, n in enumerate([650, 30, 257, 129, 64, 300])]
+    want = [_windowed_plain(W, d, r) for r in reqs]
+    for r, wnt in list(zip(reqs, want))[:3]:
+        assert H.rel_err(H.run_whole(eng, r), wnt) < tol, len(r)
+        assert H.rel_err(H.run_tail_one_by_one(eng, r, min(len(r) - 1, 200)), wnt) < tol, len(r)
+        eng.cache.check()
+    got = H.run_batches(eng, reqs, batch_size=3, decode_tail=20)
+    for r, g_, wnt in zip(reqs, got, want):
+        assert H.rel_err(g_, wnt) < tol, len(r)
+    eng.cache.check()
+    assert all(g.pool.available() == g.n_pages for g in eng.cache.kv_groups)
+    eng.check_device_errors()
+    # generation (captured decode steps) equals the plain model's greedy choice
+    import edgelm_b200
+    if dtype == "float32":
+        out = edgelm_b200.generate(None, [reqs[1], reqs[4]], n=60, engine=eng, slots=2, stop=[], ignore_eos=True)
+        for p, o_ in zip([reqs[1], reqs[4]], out):
+            lg = _windowed_plain(W, d, p + o_[:-1])
+            assert [int(np.argmax(lg[len(p) - 1 + j])) for j in range(60)] == o_
+
+
 # ----------------------------------------------------------------------------- a toy feed-forward with routing, a toy position encoding
 def _register_toy_routed():
     """A feed-forward that sends every token to one of a few small experts (the router's first maximum) and scales
