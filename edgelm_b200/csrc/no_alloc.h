@@ -16,7 +16,10 @@
 //    n_seqs * n_heads * n_splits * (head_dim + 2) floats; a call that needs more is refused with
 //    a message and launches nothing.  With n_splits == 1 no scratch is used.
 //  * The first call on a device looks up the array's device address (cudaGetSymbolAddress) and
-//    remembers it for that device; make that first call before any stream capture.
+//    remembers it for that device; with lazy module loading that call may also be the one that
+//    loads the library's device code and so brings the array into being.  Make that first call
+//    during set-up: before the region in which nothing may be allocated, and before any stream
+//    capture.
 //  * All calls share the one array, which keeps whatever the last call left in it.  Nothing in it
 //    has to start at zero: every (sequence, head, split) cell that the second kernel reads has
 //    been written by the first kernel of the same call.  Two calls that may run at the same time

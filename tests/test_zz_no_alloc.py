@@ -30,18 +30,36 @@ def _case(o, dtype, lengths, nh, nkv, hd, seed):
     kc = torch.full((n_pages, nkv, P, hd), float("nan"))
     vc = torch.full((n_pages, nkv, P, hd), float("nan"))
     it = iter(perm)
+    keys, values = [], []   # per sequence [n, nkv, hd], as the cache's dtype holds them
     for s, n in enumerate(lengths):
+        ks, vs = [], []
         for pg in range(need[s]):
             page = next(it)
             table[s, pg] = page
             rows = min(n, (pg + 1) * P) - pg * P
             kc[page, :, :rows] = torch.randn(nkv, rows, hd, generator=g)
             vc[page, :, :rows] = torch.randn(nkv, rows, hd, generator=g)
+            ks.append(kc[page, :, :rows].transpose(0, 1))
+            vs.append(vc[page, :, :rows].transpose(0, 1))
+        keys.append(torch.cat(ks).to(dtype).double())
+        values.append(torch.cat(vs).to(dtype).double())
     d = torch.device("cuda:0")
     qkv = torch.randn(len(lengths), (nh + 2 * nkv) * hd, generator=g).to(dtype).to(d)
-    return dict(qkv=qkv, k=kc.to(dtype).to(d), v=vc.to(dtype).to(d), table=table.to(d),
+    return dict(qkv=qkv, k=kc.to(dtype).to(d), v=vc.to(dtype).to(d), table=table.to(d), keys=keys, values=values,
                 seq=torch.arange(len(lengths), dtype=torch.int32, device=d),
                 pos=torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=d))
+
+
+def _plain(c, nh, nkv, hd):
+    """softmax(q . K / sqrt(hd)) V of every sequence's one query row over all its keys, in float64: written here from
+    the formula, sharing nothing with the library."""
+    out = torch.zeros(len(c["keys"]), nh * hd, dtype=torch.float64)
+    q = c["qkv"][:, :nh * hd].double().cpu().reshape(-1, nh, hd)
+    for s, (k, v) in enumerate(zip(c["keys"], c["values"])):
+        for h in range(nh):
+            p = torch.softmax((k[:, h // (nh // nkv)] @ q[s, h]) / math.sqrt(hd), dim=0)
+            out[s, h * hd:(h + 1) * hd] = p @ v[:, h // (nh // nkv)]
+    return out
 
 
 def _noalloc(o, c, out, nh, nkv, hd, splits):
@@ -66,13 +84,20 @@ def test_no_alloc_matches_regular_entry_point_twice(dtype):
         pm = torch.zeros(B * nh * splits * 2, device="cuda:0")
         o.attn_decode(c["qkv"], want, c["k"], c["v"], c["table"], c["seq"], c["pos"], B, nh, nkv, hd, 1.0 / math.sqrt(hd), splits, po, pm)
         got = torch.full_like(want, float("nan"))
-        before = torch.cuda.memory_allocated()
+        if call == 0:   # set-up: the first call on a device may load the library's module and looks up the array's address
+            assert _noalloc(o, c, got, nh, nkv, hd, splits) == 0, o.lib().edgelm_last_error().decode()
+            got.fill_(float("nan"))
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]   # the device's own count: an allocation by anyone in the process would show
         rc = _noalloc(o, c, got, nh, nkv, hd, splits)
         assert rc == 0, o.lib().edgelm_last_error().decode()
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
+        assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the device's free memory"
         assert torch.isfinite(got.float()).all()
         err = float((got.double() - want.double()).abs().max() / max(1.0, float(want.double().abs().max())))
+        assert err < tol, (call, err)
+        plain = _plain(c, nh, nkv, hd)     # and against the formula itself, not only against the other entry point
+        err = float((got.double().cpu() - plain).abs().max() / max(1.0, float(plain.abs().max())))
         assert err < tol, (call, err)
 
 
