@@ -215,6 +215,33 @@ class SequenceCache:
         for g in self.kv_groups:
             g.trim(slot, int(self.length[slot]))
 
+    def reserve_next(self, slots):
+        """`reserve(slot, 1)` for every slot of a step of one token each (distinct slots), with the same outcome; the
+        pages are looked at for the sequences that cross into a new page only, which is one step in 64."""
+        held = self.slots._held
+        for s in slots:
+            if s not in held:
+                raise CacheError(f"slot {s} is not held by a live sequence")
+        idx = np.asarray(slots, dtype=np.int64)
+        new_len = self.length[idx] + 1
+        if int(new_len.max()) > self.max_positions:
+            raise CacheError(f"a sequence of {int(new_len.max())} tokens is longer than the {self.max_positions} positions the model has")
+        want = (new_len + (PAGE - 1)) // PAGE
+        for g in self.kv_groups:
+            short = want > g.low[idx] + g.n_held[idx]
+            if short.any():
+                for s in idx[short]:
+                    g.ensure(int(s), int(self.length[s]), int(self.length[s]) + 1)
+
+    def advance_next(self, slots):
+        """`advance(slot, 1)` for every slot that `reserve_next` was called with."""
+        idx = np.asarray(slots, dtype=np.int64)
+        self.length[idx] += 1
+        for g in self.kv_groups:
+            if g.window is not None:
+                for s in slots:
+                    g.trim(s, int(self.length[s]))
+
     def close(self, slot):
         """The sequence is over: its pages and its slot go back."""
         self._held(slot)

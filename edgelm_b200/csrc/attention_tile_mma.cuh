@@ -26,6 +26,11 @@ __device__ __forceinline__ uint32_t dm_pack(float a, float b) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<const uint32_t*>(&v);
 }
+__device__ __forceinline__ float dm_exp2(float x) {   // 2^x on the special-function unit; 2^-inf = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t dm_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 // Rotary encoding of eight dims d .. d + 7 of a head row's first half (`lo`) with their partners in the second
@@ -87,14 +92,19 @@ __device__ __forceinline__ void dm_tile_update(const __nv_bfloat16* Kt, const __
       dm_mma(s[nt], qa[ks2 + 1][0], qa[ks2 + 1][1], qa[ks2 + 1][2], qa[ks2 + 1][3], b2, b3);
     }
   }
+  // the exponentials are 2^x on the special-function unit: p = 2^((s - max) * scale * log2(e)), with the scale
+  // folded into one multiply-add per score; the running maximum stays in the units of the scaled scores
+  if (valid < DM_TILE_KEYS) {
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      const int key = nt * 8 + tig * 2;
+      if (key >= valid) s[nt][0] = s[nt][2] = -CUDART_INF_F;
+      if (key + 1 >= valid) s[nt][1] = s[nt][3] = -CUDART_INF_F;
+    }
+  }
   float mxA = -CUDART_INF_F, mxB = -CUDART_INF_F;
 #pragma unroll
   for (int nt = 0; nt < 8; ++nt) {
-    const int key = nt * 8 + tig * 2;
-    s[nt][0] = key < valid ? s[nt][0] * scale : -CUDART_INF_F;
-    s[nt][1] = key + 1 < valid ? s[nt][1] * scale : -CUDART_INF_F;
-    s[nt][2] = key < valid ? s[nt][2] * scale : -CUDART_INF_F;
-    s[nt][3] = key + 1 < valid ? s[nt][3] * scale : -CUDART_INF_F;
     mxA = fmaxf(mxA, fmaxf(s[nt][0], s[nt][1]));
     mxB = fmaxf(mxB, fmaxf(s[nt][2], s[nt][3]));
   }
@@ -102,15 +112,18 @@ __device__ __forceinline__ void dm_tile_update(const __nv_bfloat16* Kt, const __
   mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 2));
   mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 1));
   mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2));
-  const float nmA = fmaxf(mA, mxA), nmB = fmaxf(mB, mxB);   // finite: valid >= 1
-  const float corrA = expf(mA - nmA), corrB = expf(mB - nmB);
+  constexpr float LOG2E = 1.4426950408889634f;
+  const float c2 = scale * LOG2E;
+  const float nmA = fmaxf(mA, mxA * scale), nmB = fmaxf(mB, mxB * scale);   // finite: valid >= 1, scale > 0
+  const float corrA = dm_exp2((mA - nmA) * LOG2E), corrB = dm_exp2((mB - nmB) * LOG2E);
+  const float offA = nmA * LOG2E, offB = nmB * LOG2E;
   float sumA = 0.f, sumB = 0.f;
 #pragma unroll
   for (int nt = 0; nt < 8; ++nt) {
-    s[nt][0] = expf(s[nt][0] - nmA);
-    s[nt][1] = expf(s[nt][1] - nmA);
-    s[nt][2] = expf(s[nt][2] - nmB);
-    s[nt][3] = expf(s[nt][3] - nmB);
+    s[nt][0] = dm_exp2(fmaf(s[nt][0], c2, -offA));
+    s[nt][1] = dm_exp2(fmaf(s[nt][1], c2, -offA));
+    s[nt][2] = dm_exp2(fmaf(s[nt][2], c2, -offB));
+    s[nt][3] = dm_exp2(fmaf(s[nt][3], c2, -offB));
     sumA += s[nt][0] + s[nt][1];
     sumB += s[nt][2] + s[nt][3];
   }

@@ -343,11 +343,11 @@ class Engine:
         self._raise_pending()
         B = len(slots)
         vocab = self.plan.vocab_size
-        for s, t in zip(slots, last_tokens):
+        for t in last_tokens:
             if not 0 <= int(t) < vocab:
                 raise EngineError(f"token id {t} is outside the vocabulary of {vocab}")
-            self.cache.reserve(s, 1)
-        pos0 = [int(self.cache.length[s]) for s in slots]
+        self.cache.reserve_next(slots)
+        pos0 = self.cache.length[list(slots)].tolist()
         ctx = self.ctx
         if not self.buffers.refill_next_token(ctx, list(last_tokens), list(slots), pos0):
             ctx = self.buffers.fill(self.ctx, list(last_tokens), list(slots), [1] * B, pos0, list(range(B)), self.cache)
@@ -359,8 +359,7 @@ class Engine:
             self._graphs[key] = g
         g["graph"].replay()
         ops.count_launches(g["launches"])
-        for s in slots:
-            self.cache.advance(s, 1)
+        self.cache.advance_next(slots)
         self.steps_run += 1
         return g
 

@@ -121,6 +121,24 @@ class Attention(Part):
         part = nbytes((cells * self.hd,), torch.float32) + nbytes((cells * 2,), torch.float32)
         return qkv + out + h + part
 
+    def _attend_decode(self, ctx, qkv, a, cache, table, tables):
+        """One new token per sequence.  `tables`: the rotation tables if rotation and cache append are this kernel's
+        to do (then `qkv` holds the raw projections), else None."""
+        ws = ctx.ws
+        cos, sin = tables if tables is not None else (None, None)
+        splits = ctx.decode_splits(self.nkv, self._decode_resident())
+        part_o = part_ml = None
+        if splits > 1:
+            part_o = ws.alloc((ctx.n_seqs * self.nh * splits * self.hd,), torch.float32)
+            part_ml = ws.alloc((ctx.n_seqs * self.nh * splits * 2,), torch.float32)
+        with ctx.prof("attn_decode"):
+            if tables is not None:
+                ops.attn_decode_rope(qkv, a, cache.k, cache.v, table, ctx.seq_index, ctx.seq_pos, cos, sin, ctx.n_seqs, self.nh,
+                                     self.nkv, self.hd, self.scale, splits, part_o, part_ml, err=ctx.err, window=self.window)
+            else:
+                ops.attn_decode(qkv, a, cache.k, cache.v, table, ctx.seq_index, ctx.seq_pos, ctx.n_seqs, self.nh, self.nkv,
+                                self.hd, self.scale, splits, part_o, part_ml, err=ctx.err, window=self.window)
+
     def forward(self, ctx, h, x, cache):
         T = h.shape[0]
         ws = ctx.ws
@@ -138,15 +156,7 @@ class Attention(Part):
                 linear.matmul(ctx, h, self.w_qkv, qkv, prefetch=(self.w_o,))
         if ctx.all_single and tables is not None:
             # one token per sequence: rotation, append and attention in one kernel
-            splits = ctx.decode_splits(self.nkv, self._decode_resident())
-            part_o = part_ml = None
-            if splits > 1:
-                part_o = ws.alloc((ctx.n_seqs * self.nh * splits * self.hd,), torch.float32)
-                part_ml = ws.alloc((ctx.n_seqs * self.nh * splits * 2,), torch.float32)
-            with ctx.prof("attn_decode"):
-                ops.attn_decode_rope(qkv, a, cache.k, cache.v, table, ctx.seq_index, ctx.seq_pos, tables[0], tables[1],
-                                     ctx.n_seqs, self.nh, self.nkv, self.hd, self.scale, splits, part_o, part_ml, err=ctx.err,
-                                     window=self.window)
+            self._attend_decode(ctx, qkv, a, cache, table, tables)
             with ctx.prof("o_proj_residual"):
                 linear.matmul(ctx, a, self.w_o, x, epilogue=linear.EPI_RESIDUAL, residual=x, prefetch=ctx.weights_after)
             return
@@ -154,14 +164,7 @@ class Attention(Part):
             with ctx.prof("rope_kv_append"):
                 self.positions.encode_and_append(ctx, qkv, cache, self.nh, self.nkv)
         if ctx.all_single:
-            splits = ctx.decode_splits(self.nkv, self._decode_resident())
-            part_o = part_ml = None
-            if splits > 1:
-                part_o = ws.alloc((ctx.n_seqs * self.nh * splits * self.hd,), torch.float32)
-                part_ml = ws.alloc((ctx.n_seqs * self.nh * splits * 2,), torch.float32)
-            with ctx.prof("attn_decode"):
-                ops.attn_decode(qkv, a, cache.k, cache.v, table, ctx.seq_index, ctx.seq_pos, ctx.n_seqs, self.nh, self.nkv,
-                                self.hd, self.scale, splits, part_o, part_ml, err=ctx.err, window=self.window)
+            self._attend_decode(ctx, qkv, a, cache, table, None)
         elif self._tc_prefill() and max(ctx.seq_lengths) >= self.TC_PREFILL_MIN_TOKENS:
             tiles = ctx.tiles(ops.TC_PREFILL_TILE)
             with ctx.prof("attn_prefill"):

@@ -324,3 +324,46 @@ def test_random_windowed_sequences_never_lose_a_page():
         c.close(s)
     c.check()
     assert all(g.pool.available() == g.n_pages for g in c.kv_groups)
+
+
+def test_a_step_of_one_token_each_reserves_like_one_sequence_at_a_time():
+    """`reserve_next` / `advance_next` (a decode step's bookkeeping for all its sequences at once) leave the cache as
+    `reserve(slot, 1)` / `advance(slot, 1)` per sequence do: the same tables, lengths, pools and errors, with a full
+    group and a windowed one, across page edges, the window's edge and the end of the position table."""
+    needs = [KVNeed(2, 16), KVNeed(2, 16, window=70), None]
+    a = SequenceCache(needs, 30 * 64, 400, device=None, max_seqs=5, piece_tokens=64)
+    b = SequenceCache(needs, 30 * 64, 400, device=None, max_seqs=5, piece_tokens=64)
+    starts = [1, 63, 64, 130, 200]
+    slots = []
+    for c in (a, b):
+        slots = [c.open() for _ in starts]
+        for s, n in zip(slots, starts):
+            c.reserve(s, n)
+            c.advance(s, n)
+    for step in range(210):
+        failed = [None, None]
+        try:
+            a.reserve_next(slots)
+            a.advance_next(slots)
+        except CacheError as e:
+            failed[0] = str(e)
+        try:
+            for s in slots:
+                b.reserve(s, 1)
+            for s in slots:
+                b.advance(s, 1)
+        except CacheError as e:
+            failed[1] = str(e)
+        assert failed[0] == failed[1]
+        if failed[0]:
+            assert "longer than the 400 positions" in failed[0] and step == 200   # the sequence that began at 200
+            break
+        a.check()
+        assert (a.length == b.length).all()
+        for ga, gb in zip(a.kv_groups, b.kv_groups):
+            assert (ga.n_held == gb.n_held).all() and (ga.low == gb.low).all() and ga.pool.available() == gb.pool.available()
+            assert ((ga.table >= 0) == (gb.table >= 0)).all()
+    else:
+        raise AssertionError("the position table's end was never reached")
+    with pytest.raises(CacheError, match="not held"):
+        a.reserve_next([slots[0], 4 if 4 not in slots else 99])
