@@ -4,10 +4,11 @@
 //
 // Same decomposition as the CUDA-core kernel: grid (sequence, kv head, split), 4 warps, a warp per
 // 64-key tile, partials folded in shared memory and, across splits, by the combine kernel.  What
-// differs is inside a tile.  The g query heads that share the kv head are the rows of a 16-row A
-// operand (rows from g on are zero), so one tile costs 8 x hd/16 MMAs for the scores and as many
-// for the values instead of thousands of multiply-adds: at batch 64 the kernel was bound by
-// instruction issue, not by memory.  Key and value rows come by 16-byte cp.async into rows padded by
+// differs is inside a tile.  With up to 8 query heads on the kv head the keys are the 16-row operand
+// and the heads the 8 columns (S^T = K Q^T, O^T = V^T P^T: dm_tile_update_t), so no row of a product is
+// padding; with more, the heads are the rows of a 16-row A operand (rows from g on are zero).  Either
+// way one tile costs a few dozen MMAs instead of thousands of multiply-adds: at batch 64 the CUDA-core
+// kernel was bound by instruction issue, not by memory.  Key and value rows come by 16-byte cp.async into rows padded by
 // 16 bytes (each lane's share arriving on the warp's mbarrier), so that ldmatrix reads hit distinct
 // banks; a bulk copy per row, 128 small requests a tile, was bound by their issue.  Value rows of the
 // last tile that lie past the sequence's end are zeroed in shared memory before use.
@@ -24,8 +25,9 @@ __host__ __device__ inline size_t decode_mma_head_bytes(int hd) {
   return (b + 127) / 128 * 128;
 }
 
-template <int HDT>  // head size / 16 (2, 4, 6, 8: the MMAs pair up K steps and value columns)
-__global__ void __launch_bounds__(DEC_WARPS * 32)
+template <int HDT>  // head size / 16 (2, 4, 6, 8: the MMAs pair up K steps and value columns); up to head size 64
+                    // three blocks share an SM's shared memory, so they have to share its registers too
+__global__ void __launch_bounds__(DEC_WARPS * 32, HDT <= 4 ? 3 : 1)
 attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat16* __restrict__ out, int ldo,
                        __nv_bfloat16* kcache, __nv_bfloat16* vcache, const int32_t* __restrict__ page_table,
                        int table_stride, const int32_t* __restrict__ seq_slot, const int32_t* __restrict__ seq_pos, int nh,
@@ -121,54 +123,87 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat
       }
     }
     __syncthreads();
-    uint32_t qa[HDT][4];
-    dm_load_queries<HDT>(Qs, qa);
-    float o[HD / 8][4];
-#pragma unroll
-    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    float mA = -CUDART_INF_F, mB = -CUDART_INF_F, lA = 0.f, lB = 0.f;   // rows gid and gid + 8
-
-    for (int t = warp; t < n_tiles && !failed; t += DEC_WARPS) {
-      const int key0 = (p_begin + t) * PAGE;
-      const int valid = min(PAGE, nkeys - key0);
-      if (pre_issued) pre_issued = false;
-      else issue_tile(t);
-      {
-        const long long t0 = clock64();
-        bool done = dec_mbar_try(bar, phase);
-        while (!done) {
-          done = dec_mbar_try(bar, phase);
-          if (!done && clock64() - t0 > DEC_WAIT_CYCLES) break;
-        }
-        failed = !__all_sync(0xffffffffu, done);
-        if (failed) break;
-        phase ^= 1;
-      }
-      if (owner && pos >= key0 && pos < key0 + PAGE) {   // the copy may have read the row before the append landed
-        for (int d = lane; d < HD; d += 32) {
-          Kt[(pos - key0) * PITCH + d] = newkv[d];
-          Vt[(pos - key0) * PITCH + d] = newkv[HD + d];
-        }
-      }
-      if (valid < PAGE) {   // rows past the sequence's end are not this sequence's: their scores are masked whatever the
-        // keys hold and their weights are exactly zero; zero values keep a stale NaN from meeting them
-        for (int i = lane; i < (PAGE - valid) * (HD / 8); i += 32) {
-          const int r = valid + i / (HD / 8), c = i - (i / (HD / 8)) * (HD / 8);
-          *reinterpret_cast<uint4*>(Vt + r * PITCH + c * 8) = make_uint4(0, 0, 0, 0);
-        }
-      }
-      __syncwarp();
-      dm_tile_update<HDT>(Kt, Vt, qa, valid, scale, o, mA, mB, lA, lB);
-      __syncwarp();
-    }
-    if (failed) {
-      if (lane == 0 && err) atomicOr(err, ERR_WAIT_TIMEOUT);
-      mA = mB = lA = lB = CUDART_NAN_F;
-    }
-    // ---- warps -> shared memory (each into its own key tile, which it no longer reads): rows gid and gid + 8
     auto partial = [&](int w) { return reinterpret_cast<float*>(dm_raw + decode_mma_head_bytes(HD)) + (size_t)w * 2 * TILE / 2; };
-    __syncwarp();
-    {
+    // The warp's tiles one after the other: wait for the copy, mend the tile, `fold(valid)` it into the running state.
+    auto each_tile = [&](auto&& fold) {
+      for (int t = warp; t < n_tiles && !failed; t += DEC_WARPS) {
+        const int key0 = (p_begin + t) * PAGE;
+        const int valid = min(PAGE, nkeys - key0);
+        if (pre_issued) pre_issued = false;
+        else issue_tile(t);
+        {
+          const long long t0 = clock64();
+          bool done = dec_mbar_try(bar, phase);
+          while (!done) {
+            done = dec_mbar_try(bar, phase);
+            if (!done && clock64() - t0 > DEC_WAIT_CYCLES) break;
+          }
+          failed = !__all_sync(0xffffffffu, done);
+          if (failed) break;
+          phase ^= 1;
+        }
+        if (owner && pos >= key0 && pos < key0 + PAGE) {   // the copy may have read the row before the append landed
+          for (int d = lane; d < HD; d += 32) {
+            Kt[(pos - key0) * PITCH + d] = newkv[d];
+            Vt[(pos - key0) * PITCH + d] = newkv[HD + d];
+          }
+        }
+        if (valid < PAGE) {   // rows past the sequence's end are not this sequence's: their scores are masked whatever the
+          // keys hold and their weights are exactly zero; zero values keep a stale NaN from meeting them
+          for (int i = lane; i < (PAGE - valid) * (HD / 8); i += 32) {
+            const int r = valid + i / (HD / 8), c = i - (i / (HD / 8)) * (HD / 8);
+            *reinterpret_cast<uint4*>(Vt + r * PITCH + c * 8) = make_uint4(0, 0, 0, 0);
+          }
+        }
+        __syncwarp();
+        fold(valid);
+        __syncwarp();
+      }
+    };
+    float mA = -CUDART_INF_F, mB = -CUDART_INF_F, lA = 0.f, lB = 0.f;
+    if (g <= DM_HEADS_T) {
+      // up to 8 query heads on the kv head: the keys are the 16-row operand (dm_tile_update_t); a lane holds the
+      // heads 2 tig and 2 tig + 1, and of each the dims gid and gid + 8 of every block of 16
+      uint32_t qb[HDT][2];
+      dm_load_queries_t<HDT>(Qs, qb);
+      float o[HDT][4];
+#pragma unroll
+      for (int i = 0; i < HDT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+      each_tile([&](int valid) { dm_tile_update_t<HDT>(Kt, Vt, qb, valid, scale, o, mA, mB, lA, lB); });
+      dm_sum_over_keys(lA, lB);
+      if (failed) {
+        if (lane == 0 && err) atomicOr(err, ERR_WAIT_TIMEOUT);
+        mA = mB = lA = lB = CUDART_NAN_F;
+      }
+      __syncwarp();
+      float* wa = partial(warp) + (tig * 2) * WS;      // rows of the partial are heads
+      float* wb = wa + WS;
+#pragma unroll
+      for (int dt = 0; dt < HDT; ++dt) {
+        wa[dt * 16 + gid] = o[dt][0];
+        wb[dt * 16 + gid] = o[dt][1];
+        wa[dt * 16 + gid + 8] = o[dt][2];
+        wb[dt * 16 + gid + 8] = o[dt][3];
+      }
+      if (gid == 0) {
+        wa[HD] = mA;
+        wa[HD + 1] = lA;
+        wb[HD] = mB;
+        wb[HD + 1] = lB;
+      }
+    } else {
+      uint32_t qa[HDT][4];
+      dm_load_queries<HDT>(Qs, qa);
+      float o[HD / 8][4];
+#pragma unroll
+      for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+      each_tile([&](int valid) { dm_tile_update<HDT>(Kt, Vt, qa, valid, scale, o, mA, mB, lA, lB); });   // rows gid and gid + 8
+      if (failed) {
+        if (lane == 0 && err) atomicOr(err, ERR_WAIT_TIMEOUT);
+        mA = mB = lA = lB = CUDART_NAN_F;
+      }
+      // ---- warps -> shared memory (each into its own key tile, which it no longer reads): rows gid and gid + 8
+      __syncwarp();
       float* wa = partial(warp) + gid * WS;
       float* wb = partial(warp) + (gid + 8) * WS;
 #pragma unroll

@@ -70,17 +70,18 @@ __device__ __forceinline__ void dm_load_queries(const __nv_bfloat16* Qs, uint32_
     dm_ldmatrix_x4(dm_smem_u32(Qs + ((mi & 1) * 8 + (lane & 7)) * PITCH + ks * 16 + (mi >> 1) * 8), qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3]);
 }
 
-// Fold one tile into the warp's running state.  A lane holds rows gid = lane / 4 (state mA, lA and
-// o[.][0..1]) and gid + 8 (mB, lB, o[.][2..3]); `valid` >= 1 keys of the tile belong to the sequence,
-// the rows of the others hold zeros.
+// Fold one tile into the warp's running state, in two halves so that a caller can wait for the values while the
+// scores are computed: dm_tile_scores needs the key tile only and leaves the tile's weights in `s` (with the running
+// maximum, the sum and the rescaled accumulators up to date), dm_tile_values adds the weighted values.  A lane holds
+// rows gid = lane / 4 (state mA, lA and o[.][0..1]) and gid + 8 (mB, lB, o[.][2..3]); `valid` >= 1 keys of the tile
+// belong to the sequence, the value rows of the others hold zeros.
 template <int HDT>
-__device__ __forceinline__ void dm_tile_update(const __nv_bfloat16* Kt, const __nv_bfloat16* Vt, const uint32_t (&qa)[HDT][4],
-                                               int valid, float scale, float (&o)[HDT * 2][4], float& mA, float& mB,
-                                               float& lA, float& lB) {
+__device__ __forceinline__ void dm_tile_scores(const __nv_bfloat16* Kt, const uint32_t (&qa)[HDT][4], int valid, float scale,
+                                               float (&s)[8][4], float (&o)[HDT * 2][4], float& mA, float& mB, float& lA,
+                                               float& lB) {
   constexpr int HD = HDT * 16, PITCH = HD + 8;
   const int lane = threadIdx.x & 31, tig = lane & 3, mi = lane >> 3;
   // ---- scores: 8 tiles of 8 keys
-  float s[8][4];
 #pragma unroll
   for (int nt = 0; nt < 8; ++nt) {
     s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
@@ -142,6 +143,12 @@ __device__ __forceinline__ void dm_tile_update(const __nv_bfloat16* Kt, const __
     o[i][2] *= corrB;
     o[i][3] *= corrB;
   }
+}
+
+template <int HDT>
+__device__ __forceinline__ void dm_tile_values(const __nv_bfloat16* Vt, const float (&s)[8][4], float (&o)[HDT * 2][4]) {
+  constexpr int HD = HDT * 16, PITCH = HD + 8;
+  const int lane = threadIdx.x & 31, mi = lane >> 3;
   // ---- values: 4 steps of 16 keys
 #pragma unroll
   for (int kt = 0; kt < 4; ++kt) {
@@ -154,6 +161,149 @@ __device__ __forceinline__ void dm_tile_update(const __nv_bfloat16* Kt, const __
       dm_mma(o[dt], a0, a1, a2, a3, b0, b1);
       dm_mma(o[dt + 1], a0, a1, a2, a3, b2, b3);
     }
+  }
+}
+
+template <int HDT>
+__device__ __forceinline__ void dm_tile_update(const __nv_bfloat16* Kt, const __nv_bfloat16* Vt, const uint32_t (&qa)[HDT][4],
+                                               int valid, float scale, float (&o)[HDT * 2][4], float& mA, float& mB,
+                                               float& lA, float& lB) {
+  float s[8][4];
+  dm_tile_scores<HDT>(Kt, qa, valid, scale, s, o, mA, mB, lA, lB);
+  dm_tile_values<HDT>(Vt, s, o);
+}
+
+}  // namespace edgelm
+
+// ---------------------------------------------------------------------------------------------------------------
+// The same tile for up to 8 query heads, with the roles of the operands swapped: the keys are the 16-row operand and
+// the heads the 8 columns, S^T = K Q^T and O^T = V^T P^T.  No row of a product is padding then (with the heads as
+// rows, 8 of the 16 are zeros whenever a kv head serves 8 heads or fewer), a lane holds 16 scores instead of 32,
+// and the accumulators are half as many: the tile costs half the tensor-core work and half the exponentials.
+namespace edgelm {
+
+__device__ __forceinline__ void dm_mma_b(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  dm_mma(c, a0, a1, a2, a3, b0, b1);
+}
+__device__ __forceinline__ uint32_t dm_transpose8(uint32_t x) {   // an 8 x 8 matrix of 16-bit values spread over the warp, transposed
+  uint32_t y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
+
+constexpr int DM_HEADS_T = 8;   // query heads of a kv head that the swapped form serves in one pass
+
+// Query rows 0..7 of Qs [.][HD + 8] as the B fragments of the score products: qb[ks] = dims ks * 16 .. + 15.
+template <int HDT>
+__device__ __forceinline__ void dm_load_queries_t(const __nv_bfloat16* Qs, uint32_t (&qb)[HDT][2]) {
+  constexpr int PITCH = HDT * 16 + 8;
+  const int lane = threadIdx.x & 31, mi = lane >> 3;
+  // matrices: (heads, dims 0-7), (heads, dims 8-15) of step ks2, then of step ks2 + 1
+#pragma unroll
+  for (int ks2 = 0; ks2 < HDT; ks2 += 2)
+    dm_ldmatrix_x4(dm_smem_u32(Qs + (lane & 7) * PITCH + (ks2 + (mi >> 1)) * 16 + (mi & 1) * 8), qb[ks2][0], qb[ks2][1], qb[ks2 + 1][0], qb[ks2 + 1][1]);
+}
+
+// Fold one tile into the warp's running state.  A lane holds the heads 2 tig (state mA, lA, o[.][0] and o[.][2]) and
+// 2 tig + 1 (mB, lB, o[.][1], o[.][3]); o[dt][0..1] is dim dt * 16 + gid, o[dt][2..3] dim dt * 16 + gid + 8.  mA and
+// mB are the same in the eight lanes that share a head; lA and lB are the lane's own share of the sum (its keys
+// gid, gid + 8, gid + 16, ..): add the eight lanes' shares when the tiles are done (dm_sum_over_keys).
+template <int HDT>
+__device__ __forceinline__ void dm_tile_scores_t(const __nv_bfloat16* Kt, const uint32_t (&qb)[HDT][2], int valid, float scale,
+                                                 float (&s)[4][4], float (&o)[HDT][4], float& mA, float& mB, float& lA, float& lB) {
+  constexpr int HD = HDT * 16, PITCH = HD + 8;
+  const int lane = threadIdx.x & 31, gid = lane >> 2, mi = lane >> 3;
+  // ---- scores: 4 blocks of 16 keys; s[mt][0..1] is key mt * 16 + gid, s[mt][2..3] key mt * 16 + gid + 8
+#pragma unroll
+  for (int mt = 0; mt < 4; ++mt) {
+    s[mt][0] = s[mt][1] = s[mt][2] = s[mt][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < HDT; ++ks) {
+      uint32_t a0, a1, a2, a3;
+      dm_ldmatrix_x4(dm_smem_u32(Kt + (mt * 16 + (mi & 1) * 8 + (lane & 7)) * PITCH + ks * 16 + (mi >> 1) * 8), a0, a1, a2, a3);
+      dm_mma_b(s[mt], a0, a1, a2, a3, qb[ks][0], qb[ks][1]);
+    }
+  }
+  if (valid < DM_TILE_KEYS) {
+#pragma unroll
+    for (int mt = 0; mt < 4; ++mt) {
+      if (mt * 16 + gid >= valid) s[mt][0] = s[mt][1] = -CUDART_INF_F;
+      if (mt * 16 + gid + 8 >= valid) s[mt][2] = s[mt][3] = -CUDART_INF_F;
+    }
+  }
+  float mxA = -CUDART_INF_F, mxB = -CUDART_INF_F;
+#pragma unroll
+  for (int mt = 0; mt < 4; ++mt) {
+    mxA = fmaxf(mxA, fmaxf(s[mt][0], s[mt][2]));
+    mxB = fmaxf(mxB, fmaxf(s[mt][1], s[mt][3]));
+  }
+#pragma unroll
+  for (int off = 4; off < 32; off <<= 1) {   // over the lanes that hold the other keys of the same heads
+    mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, off));
+    mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, off));
+  }
+  constexpr float LOG2E = 1.4426950408889634f;
+  const float c2 = scale * LOG2E;
+  const float nmA = fmaxf(mA, mxA * scale), nmB = fmaxf(mB, mxB * scale);   // finite: valid >= 1, scale > 0
+  const float corrA = dm_exp2((mA - nmA) * LOG2E), corrB = dm_exp2((mB - nmB) * LOG2E);
+  const float offA = nmA * LOG2E, offB = nmB * LOG2E;
+  float sumA = 0.f, sumB = 0.f;
+#pragma unroll
+  for (int mt = 0; mt < 4; ++mt) {
+    s[mt][0] = dm_exp2(fmaf(s[mt][0], c2, -offA));
+    s[mt][1] = dm_exp2(fmaf(s[mt][1], c2, -offB));
+    s[mt][2] = dm_exp2(fmaf(s[mt][2], c2, -offA));
+    s[mt][3] = dm_exp2(fmaf(s[mt][3], c2, -offB));
+    sumA += s[mt][0] + s[mt][2];
+    sumB += s[mt][1] + s[mt][3];
+  }
+  lA = lA * corrA + sumA;
+  lB = lB * corrB + sumB;
+  mA = nmA;
+  mB = nmB;
+#pragma unroll
+  for (int dt = 0; dt < HDT; ++dt) {
+    o[dt][0] *= corrA;
+    o[dt][1] *= corrB;
+    o[dt][2] *= corrA;
+    o[dt][3] *= corrB;
+  }
+}
+
+template <int HDT>
+__device__ __forceinline__ void dm_tile_values_t(const __nv_bfloat16* Vt, const float (&s)[4][4], float (&o)[HDT][4]) {
+  constexpr int HD = HDT * 16, PITCH = HD + 8;
+  const int lane = threadIdx.x & 31, mi = lane >> 3;
+  // ---- values: O^T += V^T P^T, 4 steps of 16 keys; the weights of a step, held as (key, two heads) per lane, go
+  // through a transpose to (head, two keys), which is how the 8-column operand wants them
+#pragma unroll
+  for (int kt = 0; kt < 4; ++kt) {
+    const uint32_t b0 = dm_transpose8(dm_pack(s[kt][0], s[kt][1])), b1 = dm_transpose8(dm_pack(s[kt][2], s[kt][3]));
+#pragma unroll
+    for (int dt = 0; dt < HDT; ++dt) {
+      uint32_t a0, a1, a2, a3;
+      // matrices as stored (8 keys x 8 dims each): (keys 0-7, dims 0-7), (keys 0-7, dims 8-15), (keys 8-15, dims 0-7), (keys 8-15, dims 8-15)
+      dm_ldmatrix_x4_trans(dm_smem_u32(Vt + (kt * 16 + (mi >> 1) * 8 + (lane & 7)) * PITCH + dt * 16 + (mi & 1) * 8), a0, a1, a2, a3);
+      dm_mma_b(o[dt], a0, a1, a2, a3, b0, b1);
+    }
+  }
+}
+
+template <int HDT>
+__device__ __forceinline__ void dm_tile_update_t(const __nv_bfloat16* Kt, const __nv_bfloat16* Vt, const uint32_t (&qb)[HDT][2],
+                                                 int valid, float scale, float (&o)[HDT][4], float& mA, float& mB, float& lA,
+                                                 float& lB) {
+  float s[4][4];
+  dm_tile_scores_t<HDT>(Kt, qb, valid, scale, s, o, mA, mB, lA, lB);
+  dm_tile_values_t<HDT>(Vt, s, o);
+}
+
+// The eight lanes that share a head each hold a share of its sum of weights: all of them get the whole.
+__device__ __forceinline__ void dm_sum_over_keys(float& lA, float& lB) {
+#pragma unroll
+  for (int off = 4; off < 32; off <<= 1) {
+    lA += __shfl_xor_sync(0xffffffffu, lA, off);
+    lB += __shfl_xor_sync(0xffffffffu, lB, off);
   }
 }
 

@@ -636,54 +636,92 @@ __device__ __forceinline__ void ds_attention(uint8_t* head, uint8_t* tiles, uint
       }
     }
     __syncthreads();
-    float o[HD / 8][4];
-#pragma unroll
-    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    float mA = -CUDART_INF_F, mB = -CUDART_INF_F, lA = 0.f, lB = 0.f;   // rows gid and gid + 8
-    if (has_tile) {
-      uint32_t qa[HDT][4];
-      dm_load_queries<HDT>(Qs, qa);
-      const int key0 = (a.p_begin + warp) * PAGE;
-      const int valid = min(PAGE, nkeys - key0);
-      if (ds_mbar_wait(bar, phase)) {
-        phase ^= 1;
-        if (owner && pos >= key0 && pos < key0 + PAGE) {   // the copy read the row before the append, or while it landed
-          for (int d = lane; d < HD; d += 32) {
-            Kt[(pos - key0) * PITCH + d] = newkv[d];
-            Vt[(pos - key0) * PITCH + d] = newkv[HD + d];
-          }
-        }
-        if (valid < PAGE) {   // rows past the sequence's end are not this sequence's: their scores are masked whatever the
-          // keys hold, their weights are exactly zero, and zero values keep a stale NaN from meeting them
-          for (int i = lane; i < (PAGE - valid) * (HD / 8); i += 32) {
-            const int r = valid + i / (HD / 8), c = i - (i / (HD / 8)) * (HD / 8);
-            *reinterpret_cast<uint4*>(Vt + r * PITCH + c * 8) = make_uint4(0, 0, 0, 0);
-          }
-        }
-        __syncwarp();
-        dm_tile_update<HDT>(Kt, Vt, qa, valid, L.scale, o, mA, mB, lA, lB);
-      } else {
+    float mA = -CUDART_INF_F, mB = -CUDART_INF_F, lA = 0.f, lB = 0.f;
+    // Waits for the warp's tile and mends it (the new token's row, the rows past the sequence's end); false, with the
+    // error word set, if the tile never came.
+    auto tile_ready = [&](int key0, int valid) {
+      if (!ds_mbar_wait(bar, phase)) {
         if (lane == 0) atomicOr(err, ERR_WAIT_TIMEOUT);
         mA = mB = lA = lB = CUDART_NAN_F;
+        return false;
       }
-    }
-    // ---- warps -> shared memory, each into its own key tile, which it no longer reads
-    __syncwarp();
-    if (warp < att_warps) {
-      float* wa = partial(warp) + gid * WS;
-      float* wb = partial(warp) + (gid + 8) * WS;
+      phase ^= 1;
+      if (owner && pos >= key0 && pos < key0 + PAGE) {   // the copy read the row before the append, or while it landed
+        for (int d = lane; d < HD; d += 32) {
+          Kt[(pos - key0) * PITCH + d] = newkv[d];
+          Vt[(pos - key0) * PITCH + d] = newkv[HD + d];
+        }
+      }
+      if (valid < PAGE) {   // rows past the sequence's end are not this sequence's: their scores are masked whatever the
+        // keys hold, their weights are exactly zero, and zero values keep a stale NaN from meeting them
+        for (int i = lane; i < (PAGE - valid) * (HD / 8); i += 32) {
+          const int r = valid + i / (HD / 8), c = i - (i / (HD / 8)) * (HD / 8);
+          *reinterpret_cast<uint4*>(Vt + r * PITCH + c * 8) = make_uint4(0, 0, 0, 0);
+        }
+      }
+      __syncwarp();
+      return true;
+    };
+    const int key0 = (a.p_begin + warp) * PAGE;
+    const int valid = min(PAGE, nkeys - key0);
+    // ---- the warp's tile, then its partial into shared memory: into its own key tile, which it no longer reads
+    if (g <= DM_HEADS_T) {
+      // up to 8 query heads on the kv head: the keys are the 16-row operand; a lane holds the heads 2 tig and 2 tig + 1
+      float o[HDT][4];
 #pragma unroll
-      for (int dt = 0; dt < HD / 8; ++dt) {
-        wa[dt * 8 + tig * 2] = o[dt][0];
-        wa[dt * 8 + tig * 2 + 1] = o[dt][1];
-        wb[dt * 8 + tig * 2] = o[dt][2];
-        wb[dt * 8 + tig * 2 + 1] = o[dt][3];
+      for (int i = 0; i < HDT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+      if (has_tile) {
+        uint32_t qb[HDT][2];
+        dm_load_queries_t<HDT>(Qs, qb);
+        if (tile_ready(key0, valid)) {
+          dm_tile_update_t<HDT>(Kt, Vt, qb, valid, L.scale, o, mA, mB, lA, lB);
+          dm_sum_over_keys(lA, lB);
+        }
       }
-      if (tig == 0) {
-        wa[HD] = mA;
-        wa[HD + 1] = lA;
-        wb[HD] = mB;
-        wb[HD + 1] = lB;
+      __syncwarp();
+      if (warp < att_warps) {
+        float* wa = partial(warp) + (tig * 2) * WS;
+        float* wb = wa + WS;
+#pragma unroll
+        for (int dt = 0; dt < HDT; ++dt) {
+          wa[dt * 16 + gid] = o[dt][0];
+          wb[dt * 16 + gid] = o[dt][1];
+          wa[dt * 16 + gid + 8] = o[dt][2];
+          wb[dt * 16 + gid + 8] = o[dt][3];
+        }
+        if (gid == 0) {
+          wa[HD] = mA;
+          wa[HD + 1] = lA;
+          wb[HD] = mB;
+          wb[HD + 1] = lB;
+        }
+      }
+    } else {
+      float o[HD / 8][4];   // rows gid and gid + 8
+#pragma unroll
+      for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+      if (has_tile) {
+        uint32_t qa[HDT][4];
+        dm_load_queries<HDT>(Qs, qa);
+        if (tile_ready(key0, valid)) dm_tile_update<HDT>(Kt, Vt, qa, valid, L.scale, o, mA, mB, lA, lB);
+      }
+      __syncwarp();
+      if (warp < att_warps) {
+        float* wa = partial(warp) + gid * WS;
+        float* wb = partial(warp) + (gid + 8) * WS;
+#pragma unroll
+        for (int dt = 0; dt < HD / 8; ++dt) {
+          wa[dt * 8 + tig * 2] = o[dt][0];
+          wa[dt * 8 + tig * 2 + 1] = o[dt][1];
+          wb[dt * 8 + tig * 2] = o[dt][2];
+          wb[dt * 8 + tig * 2 + 1] = o[dt][3];
+        }
+        if (tig == 0) {
+          wa[HD] = mA;
+          wa[HD + 1] = lA;
+          wb[HD] = mB;
+          wb[HD + 1] = lB;
+        }
       }
     }
     __syncthreads();
