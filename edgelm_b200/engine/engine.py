@@ -74,7 +74,11 @@ class Engine:
         self.ws = Workspace(ws_bytes, self.device)
         # the device error word: kernels OR a bit into it for bad input (a token id, a position, a page) and for a
         # bounded wait that ran out; every call that hands results to the host reads it with them
-        self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # (the tokens that a graph-replayed decode step samples lie right behind it, so that one copy brings both)
+        self._result = torch.zeros(1 + self.max_step_seqs, dtype=torch.int32, device=self.device)
+        self._result_host = torch.zeros(1 + self.max_step_seqs, dtype=torch.int32).pin_memory()
+        self._result_np = self._result_host.numpy()
+        self.err = self._result[:1]
         self._err_host = torch.zeros(1, dtype=torch.int32).pin_memory()
         self._err_copied = torch.cuda.Event()
         self._err_pending = False
@@ -330,12 +334,12 @@ class Engine:
             out = tokens.tolist()
             self.check_device_errors()
             return out
-        g = self.decode_launch(slots, last_tokens, params)
-        g["host"].copy_(g["tokens"], non_blocking=True)
-        self._err_host.copy_(self.err, non_blocking=True)   # the error word comes with the tokens: one wait for both
+        self.decode_launch(slots, last_tokens, params)
+        self._result_host[:1 + B].copy_(self._result[:1 + B], non_blocking=True)   # the error word and the tokens: one copy, one wait
         torch.cuda.current_stream().synchronize()
-        self._flagged(int(self._err_host[0]))
-        return g["host"].tolist()
+        out = self._result_np[:1 + B].tolist()
+        self._flagged(out[0])
+        return out[1:]
 
     def decode_launch(self, slots, last_tokens, params):
         """Issue one decode step (metadata copy + graph replay) without waiting for it; the
@@ -343,9 +347,8 @@ class Engine:
         self._raise_pending()
         B = len(slots)
         vocab = self.plan.vocab_size
-        for t in last_tokens:
-            if not 0 <= int(t) < vocab:
-                raise EngineError(f"token id {t} is outside the vocabulary of {vocab}")
+        if min(last_tokens) < 0 or max(last_tokens) >= vocab:
+            raise EngineError(f"token id {min(last_tokens) if min(last_tokens) < 0 else max(last_tokens)} is outside the vocabulary of {vocab}")
         self.cache.reserve_next(slots)
         pos0 = self.cache.length[list(slots)].tolist()
         ctx = self.ctx
@@ -368,8 +371,7 @@ class Engine:
         the same addresses for every step of B sequences, so the graph reads each step's fresh
         metadata; the number of attention splits is frozen with the graph."""
         logits = torch.empty((B, self.plan.vocab_size), dtype=torch.float32, device=self.device)
-        tokens = torch.empty(B, dtype=torch.int32, device=self.device)
-        host = torch.empty(B, dtype=torch.int32).pin_memory()
+        tokens = self._result[1:1 + B]
         ops.lib()  # library loaded and kernels' attributes set before capture
         # one eager run first: it sets kernel attributes (shared-memory sizes) outside of the capture.  It writes
         # the same cache rows as the replay that follows; what it advances (the sampler's streams, the fixed-size
@@ -388,4 +390,4 @@ class Engine:
             self.sampler.sample(logits, params, ctx.seq_slots, tokens)
         launches = ops.LAUNCHES - before
         ops.count_launches(-launches)  # captured, not run
-        return {"graph": graph, "logits": logits, "tokens": tokens, "host": host, "launches": launches}
+        return {"graph": graph, "logits": logits, "tokens": tokens, "launches": launches}
