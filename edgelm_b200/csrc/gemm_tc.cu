@@ -45,7 +45,15 @@ constexpr int TC_BM = 128;   // rows of `a` per tile = lanes of tensor memory
 constexpr int TC_STAGES = 3;   // ring stages of the one-tile kernel when several blocks share an SM (48 KB stages: 144 KB)
 constexpr int TC_DEEP_BYTES = 192 * 1024;   // ring of the one-tile kernel when the grid is at most one block an SM
 constexpr int TC_THREADS = 192;
-__device__ __forceinline__ float silu_tc(float z) { return z / (1.0f + expf(-z)); }
+// z / (1 + e^-z) with the exponential and the reciprocal on the special-function unit (2^x and 1/x to about 2^-22):
+// the result is rounded to bfloat16 right after; an epilogue thread computes 64 to 128 of these while its tile's
+// tensor memory is held.  (z < -88: 2^x overflows to infinity, the reciprocal is 0 and the result -0, the limit.)
+__device__ __forceinline__ float silu_tc(float z) {
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(z * -1.4426950408889634f));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return z * r;
+}
 
 template <typename TOut> struct OutVec;
 template <> struct OutVec<float> {
