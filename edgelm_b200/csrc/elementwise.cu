@@ -76,6 +76,45 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
   }
 }
 
+// The same for rows of up to MAXV * 128 values that are read four at a time: a warp a row, the row in registers
+// between the sum of squares and the scaling (one pass over memory, no block-wide barrier).
+constexpr int NORM_ROW_WARPS = 4;
+template <typename TOut, int MAXV>
+__global__ void __launch_bounds__(NORM_ROW_WARPS * 32)
+rmsnorm_row_kernel(const float* __restrict__ x, const float* __restrict__ w, TOut* __restrict__ y,
+                   const int32_t* __restrict__ rows_idx, int rows, int dim, float eps) {
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * NORM_ROW_WARPS + (threadIdx.x >> 5);
+  float4 g[MAXV];   // the weights: nothing on the stream writes them, so they are read ahead of the wait
+#pragma unroll
+  for (int j = 0; j < MAXV; ++j) {
+    const int i = lane * 4 + j * 128;
+    g[j] = i < dim ? *reinterpret_cast<const float4*>(w + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  pdl_wait();   // (launched as a programmatic dependent: the rows are the kernel before this one's)
+  if (r >= rows) return;
+  const float* xr = x + (size_t)(rows_idx ? rows_idx[r] : r) * dim;
+  float4 v[MAXV];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < MAXV; ++j) {
+    const int i = lane * 4 + j * 128;
+    v[j] = i < dim ? *reinterpret_cast<const float4*>(xr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+#pragma unroll
+  for (int j = 0; j < MAXV; ++j) {
+    ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss); ss = fmaf(v[j].z, v[j].z, ss); ss = fmaf(v[j].w, v[j].w, ss);
+  }
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+#pragma unroll
+  for (int j = 0; j < MAXV; ++j) {
+    const int i = lane * 4 + j * 128;
+    if (i < dim) NormStore<TOut>::store4(y + (size_t)r * dim + i, v[j].x * inv * g[j].x, v[j].y * inv * g[j].y, v[j].z * inv * g[j].z, v[j].w * inv * g[j].w);
+  }
+}
+
 // ---------------------------------------------------------------- RoPE + cache append
 // qkv: [tokens, (nh + 2 nkv) * hd], the fused projection's output.  For every token: rotate
 // the nh query heads in place, rotate the nkv key heads and write them, with the raw value
@@ -200,6 +239,18 @@ extern "C" int edgelm_rmsnorm(const float* x, const float* w, void* y, int out_d
   EL_REFUSE(rows > 0 && dim > 0, "rmsnorm: bad sizes rows=%d dim=%d", rows, dim);
   const int threads = dim >= 1024 ? 256 : 128;
   const bool vec = dim % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)y % 16 == 0;
+  if (vec && dim <= 2048 && (out_dtype == DT_F32 || out_dtype == DT_BF16)) {   // a warp a row, the row in registers
+    const dim3 grid((rows + NORM_ROW_WARPS - 1) / NORM_ROW_WARPS), block(NORM_ROW_WARPS * 32);
+    if (out_dtype == DT_F32) {
+      if (dim <= 640) launch_pdl(32, rmsnorm_row_kernel<float, 5>, grid, block, (size_t)0, stream, x, w, (float*)y, rows_idx, rows, dim, eps);
+      else launch_pdl(32, rmsnorm_row_kernel<float, 16>, grid, block, (size_t)0, stream, x, w, (float*)y, rows_idx, rows, dim, eps);
+    } else {
+      if (dim <= 640) launch_pdl(32, rmsnorm_row_kernel<__nv_bfloat16, 5>, grid, block, (size_t)0, stream, x, w, (__nv_bfloat16*)y, rows_idx, rows, dim, eps);
+      else launch_pdl(32, rmsnorm_row_kernel<__nv_bfloat16, 16>, grid, block, (size_t)0, stream, x, w, (__nv_bfloat16*)y, rows_idx, rows, dim, eps);
+    }
+    EL_LAUNCH_CHECK("rmsnorm");
+    return 0;
+  }
   if (out_dtype == DT_F32) {
     if (vec) launch_pdl(32, rmsnorm_kernel<float, true>, dim3(rows), dim3(threads), (size_t)0, stream, x, w, (float*)y, rows_idx, dim, eps);
     else launch_pdl(32, rmsnorm_kernel<float, false>, dim3(rows), dim3(threads), (size_t)0, stream, x, w, (float*)y, rows_idx, dim, eps);
