@@ -120,6 +120,7 @@ class BatchBuffers:
         self.last_bytes = 0
         self._copied = torch.cuda.Event()
         self._decode = None   # layout of the last step if it was one token per sequence: lets the next one be patched in place
+        self._tile_cols = {}  # (tokens per sequence, first positions, tile size) -> the tiles' four columns: shapes come back
 
     def fill(self, ctx, token_ids, seq_slots, seq_ntok, seq_pos0, want_rows, cache):
         """Lay out the step and copy it; sets every tensor of `ctx` (views of the device buffer)."""
@@ -154,11 +155,17 @@ class BatchBuffers:
             put(("table", g.id), g.table[slots].reshape(-1), B * s)
         tile_counts = {}
         if T != B:  # steps of one token per sequence use no tiles
+            shape = (tuple(int(v) for v in ntok), tuple(int(v) for v in pos0))
             for ts in self.tile_sizes:
-                cols = make_tiles([int(v) for v in ntok], [int(v) for v in pos0], ts)
+                cols = self._tile_cols.get(shape + (ts,))
+                if cols is None:
+                    if len(self._tile_cols) >= 64:
+                        self._tile_cols.clear()
+                    cols = [np.asarray(col, dtype=np.int32) for col in make_tiles(list(shape[0]), list(shape[1]), ts)]
+                    self._tile_cols[shape + (ts,)] = cols
                 tile_counts[ts] = len(cols[0])
                 for j, col in enumerate(cols):
-                    put(("tiles", ts, j), np.asarray(col, dtype=np.int32), len(col))
+                    put(("tiles", ts, j), col, len(col))
         self.dev[:o].copy_(self.host[:o], non_blocking=True)
         self._copied.record()
         self.last_bytes = o * 4

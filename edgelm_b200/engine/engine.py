@@ -246,7 +246,7 @@ class Engine:
             return False
         if n_want * self.plan.vocab_size * 4 > self.STEP_GRAPH_MAX_LOGIT_BYTES:
             return False
-        if any(t not in ctx._tiles for t in self.model.tile_sizes()):
+        if any(t not in ctx._tiles for t in self.buffers.tile_sizes):   # (the model's own list, taken when the buffers were made)
             return False
         key = (shape, n_want)
         g = self._step_graphs.get(key)
