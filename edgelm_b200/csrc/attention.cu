@@ -546,25 +546,59 @@ attn_decode_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ld
 #include "attention_decode_mma.cuh"
 namespace edgelm {
 
+// One (sequence, head) a block; every warp of the block reads the splits' maxima and sums 32 at a time (a lane a
+// split), finds the overall maximum and each split's weight, and then walks the splits that hold anything, in
+// their order, handing a split's weight and sum round by shuffle: a split that got no page (most of them when a
+// short sequence is dealt to many) costs nothing, and the exponentials are one per split, not one per split and dim.
 template <typename T>
 __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                            T* __restrict__ out, int ldo, int nh, int hd, int n_splits) {
-  const int seq = blockIdx.x, head = blockIdx.y;
+  const int seq = blockIdx.x, head = blockIdx.y, lane = threadIdx.x & 31;
   const size_t base = ((size_t)seq * nh + head) * n_splits;
   pdl_launch_dependents();
   pdl_wait();  // the partials are the previous kernel's
   float M = -CUDART_INF_F;
-  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
-  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-    float L = 0.f, o = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-      const float ms = part_ml[(base + s) * 2];
-      if (ms == -CUDART_INF_F) continue;  // a split that held no page
-      const float f = expf(ms - M);
-      L = fmaf(part_ml[(base + s) * 2 + 1], f, L);
-      o = fmaf(part_o[(base + s) * hd + d], f, o);
+  for (int s = lane; s < n_splits; s += 32) M = fmaxf(M, part_ml[(base + s) * 2]);
+#pragma unroll
+  for (int o = 16; o; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+  float L = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};   // dims threadIdx.x, + blockDim.x, ..: head sizes up to 4 x the block
+  for (int s0 = 0; s0 < n_splits; s0 += 32) {
+    const int s = s0 + lane;
+    const float ms = s < n_splits ? part_ml[(base + s) * 2] : -CUDART_INF_F;
+    const float ls = s < n_splits ? part_ml[(base + s) * 2 + 1] : 0.f;
+    const float f = ms == -CUDART_INF_F ? 0.f : expf(ms - M);   // (a split that held no page: -inf)
+    unsigned live = __ballot_sync(0xffffffffu, ms != -CUDART_INF_F);
+    while (live) {   // eight splits at a time: their sums are requested together and added in the splits' order
+      int js[8];
+      float v[8][4];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        js[q] = live ? __ffs(live) - 1 : -1;
+        live &= live - 1;   // (0 stays 0)
+        if (js[q] >= 0) {
+          const float* po = part_o + (base + s0 + js[q]) * hd;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int d = threadIdx.x + i * blockDim.x;
+            v[q][i] = d < hd ? po[d] : 0.f;
+          }
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        if (js[q] >= 0) {
+          const float fj = __shfl_sync(0xffffffffu, f, js[q]), lj = __shfl_sync(0xffffffffu, ls, js[q]);
+          L = fmaf(lj, fj, L);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) acc[i] = fmaf(v[q][i], fj, acc[i]);
+        }
+      }
     }
-    out[(size_t)seq * ldo + head * hd + d] = from_f32<T>(o / L);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int d = threadIdx.x + i * blockDim.x;
+    if (d < hd) out[(size_t)seq * ldo + head * hd + d] = from_f32<T>(acc[i] / L);
   }
 }
 

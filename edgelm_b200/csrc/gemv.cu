@@ -74,6 +74,8 @@ gemv_kernel(const T* __restrict__ act, int lda, const float* __restrict__ x, con
     }
   }
 
+  pdl_launch_dependents();
+  pdl_wait();   // (launched as a programmatic dependent: from here on, what the kernel before this one wrote)
   if (NORM) {  // 1 / sqrt(mean(x^2) + eps) per row, a warp per row
     for (int r = warp; r < rows; r += nwarps) {
       const float* xr = x + (size_t)(m0 + r) * K;
@@ -113,35 +115,52 @@ gemv_kernel(const T* __restrict__ act, int lda, const float* __restrict__ x, con
     }
     __syncthreads();
     if (col0 < N) {
-      for (int k = lane * V; k < kn; k += 32 * V) {
-        uint4 wv[NW][CW];
+      // UNR steps of K at a time: their weight vectors are requested together and used in order (a lane's sum runs
+      // over its k in increasing order whatever UNR is), so a warp waits for memory once per UNR steps instead of
+      // once per step
+      constexpr int UNR = NW * CW <= 2 ? 4 : 2;
+      for (int kb = lane * V; kb < kn; kb += 32 * V * UNR) {
+        uint4 wv[UNR][NW][CW];
 #pragma unroll
-        for (int c = 0; c < CW; ++c) {
-          if (k0 == 0 && k == lane * V) {
-            wv[0][c] = wpre[0][c];
-            if (NW == 2) wv[1][c] = wpre[1][c];
-          } else {
-            const int n = min(col0 + c, N - 1);
-            wv[0][c] = *reinterpret_cast<const uint4*>(W + (size_t)n * K + k0 + k);
-            if (NW == 2) wv[1][c] = *reinterpret_cast<const uint4*>(W2 + (size_t)n * K + k0 + k);
+        for (int u = 0; u < UNR; ++u) {
+          const int k = kb + u * 32 * V;
+#pragma unroll
+          for (int c = 0; c < CW; ++c) {
+            if (k0 == 0 && u == 0 && kb == lane * V) {
+              wv[u][0][c] = wpre[0][c];
+              if (NW == 2) wv[u][1][c] = wpre[1][c];
+            } else if (k < kn) {
+              const int n = min(col0 + c, N - 1);
+              wv[u][0][c] = *reinterpret_cast<const uint4*>(W + (size_t)n * K + k0 + k);
+              if (NW == 2) wv[u][1][c] = *reinterpret_cast<const uint4*>(W2 + (size_t)n * K + k0 + k);
+            } else {
+              wv[u][0][c] = make_uint4(0, 0, 0, 0);
+              if (NW == 2) wv[u][1][c] = make_uint4(0, 0, 0, 0);
+            }
           }
         }
-        float wf[NW][CW][V];
 #pragma unroll
-        for (int w = 0; w < NW; ++w)
-#pragma unroll
-          for (int c = 0; c < CW; ++c) Vec16<T>::unpack(wv[w][c], wf[w][c]);
-#pragma unroll
-        for (int r = 0; r < GV_ROWS; ++r) {
-          if (r < rows) {
-            float af[V];
-            Vec16<T>::unpack(*reinterpret_cast<const uint4*>(As + r * kc + k), af);
+        for (int u = 0; u < UNR; ++u) {
+          const int k = kb + u * 32 * V;
+          if (k < kn) {
+            float wf[NW][CW][V];
 #pragma unroll
             for (int w = 0; w < NW; ++w)
 #pragma unroll
-              for (int c = 0; c < CW; ++c)
+              for (int c = 0; c < CW; ++c) Vec16<T>::unpack(wv[u][w][c], wf[w][c]);
 #pragma unroll
-                for (int v = 0; v < V; ++v) acc[w][c][r] = fmaf(af[v], wf[w][c][v], acc[w][c][r]);
+            for (int r = 0; r < GV_ROWS; ++r) {
+              if (r < rows) {
+                float af[V];
+                Vec16<T>::unpack(*reinterpret_cast<const uint4*>(As + r * kc + k), af);
+#pragma unroll
+                for (int w = 0; w < NW; ++w)
+#pragma unroll
+                  for (int c = 0; c < CW; ++c)
+#pragma unroll
+                    for (int v = 0; v < V; ++v) acc[w][c][r] = fmaf(af[v], wf[w][c][v], acc[w][c][r]);
+              }
+            }
           }
         }
       }
@@ -179,8 +198,13 @@ static int launch_gemv_cw(const void* act, int lda, const float* x, const float*
   const size_t smem = (size_t)GV_ROWS * kc * sizeof(T) + GV_ROWS * sizeof(float);
   const int nwarps = threads / 32;
   dim3 grid((N + nwarps * CW - 1) / (nwarps * CW), (M + GV_ROWS - 1) / GV_ROWS);
-  gemv_kernel<T, EPI, TOut, CW, NORM><<<grid, threads, smem, stream>>>((const T*)act, lda, x, norm_w, eps, (const T*)W, (const T*)W2,
-                                                                      (TOut*)out, ldo, residual, M, N, K, kc);
+  // a programmatic dependent launch, like the tensor-core few-rows kernel: the first weight loads run ahead of the wait
+  const cudaError_t le = launch_pdl(1, gemv_kernel<T, EPI, TOut, CW, NORM>, grid, dim3(threads), smem, stream, (const T*)act, lda, x, norm_w,
+                                    eps, (const T*)W, (const T*)W2, (TOut*)out, ldo, residual, M, N, K, kc);
+  if (le != cudaSuccess) {
+    set_error("gemv: launch failed: %s", cudaGetErrorString(le));
+    return -2;
+  }
   return 0;
 }
 
@@ -229,22 +253,24 @@ extern "C" int edgelm_gemv(const void* act, int lda, const float* norm_w, float 
 #define EL_GV(T, EPI, TOUT)                                                                                             \
   (normed ? launch_gemv<T, EPI, TOUT, true>(nullptr, 0, x, norm_w, eps, w, w2, out, ldo, residual, M, N, K, n_sms, stream) \
           : launch_gemv<T, EPI, TOUT, false>(act, lda, nullptr, nullptr, 0.f, w, w2, out, ldo, residual, M, N, K, n_sms, stream))
+  int rc = 0;
   if (dtype == DT_BF16) {
-    if (epilogue == GV_STORE && out_dtype == DT_BF16) EL_GV(__nv_bfloat16, GV_STORE, __nv_bfloat16);
-    else if (epilogue == GV_STORE && out_dtype == DT_F32) EL_GV(__nv_bfloat16, GV_STORE, float);
-    else if (epilogue == GV_RESIDUAL) EL_GV(__nv_bfloat16, GV_RESIDUAL, float);
-    else if (epilogue == GV_SWIGLU && out_dtype == DT_BF16) EL_GV(__nv_bfloat16, GV_SWIGLU, __nv_bfloat16);
+    if (epilogue == GV_STORE && out_dtype == DT_BF16) rc = EL_GV(__nv_bfloat16, GV_STORE, __nv_bfloat16);
+    else if (epilogue == GV_STORE && out_dtype == DT_F32) rc = EL_GV(__nv_bfloat16, GV_STORE, float);
+    else if (epilogue == GV_RESIDUAL) rc = EL_GV(__nv_bfloat16, GV_RESIDUAL, float);
+    else if (epilogue == GV_SWIGLU && out_dtype == DT_BF16) rc = EL_GV(__nv_bfloat16, GV_SWIGLU, __nv_bfloat16);
     else EL_REFUSE(false, "gemv: unsupported epilogue %d with output dtype %d", epilogue, out_dtype);
   } else if (dtype == DT_F32) {
     EL_REFUSE(out_dtype == DT_F32, "gemv: float32 activations give float32 outputs");
-    if (epilogue == GV_STORE) EL_GV(float, GV_STORE, float);
-    else if (epilogue == GV_RESIDUAL) EL_GV(float, GV_RESIDUAL, float);
-    else if (epilogue == GV_SWIGLU) EL_GV(float, GV_SWIGLU, float);
+    if (epilogue == GV_STORE) rc = EL_GV(float, GV_STORE, float);
+    else if (epilogue == GV_RESIDUAL) rc = EL_GV(float, GV_RESIDUAL, float);
+    else if (epilogue == GV_SWIGLU) rc = EL_GV(float, GV_SWIGLU, float);
     else EL_REFUSE(false, "gemv: unknown epilogue %d", epilogue);
   } else {
     EL_REFUSE(false, "gemv: unknown dtype code %d", dtype);
   }
 #undef EL_GV
+  if (rc) return rc;
   EL_LAUNCH_CHECK("gemv");
   return 0;
 }
