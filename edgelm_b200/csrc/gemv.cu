@@ -59,18 +59,26 @@ gemv_kernel(const T* __restrict__ act, int lda, const float* __restrict__ x, con
   const int rows = min(GV_ROWS, M - m0);
   const int col0 = (blockIdx.x * nwarps + warp) * CW;          // this warp's first column
 
-  // the first weight vectors of this warp's columns: on their way while the prologue runs
-  uint4 wpre[NW][CW];
+  // UNR steps of K at a time: their weight vectors are requested together and used in order (a lane's sum runs over
+  // its k in increasing order whatever UNR is), so a warp waits for memory once per UNR steps instead of once per
+  // step.  The first UNR steps of this warp's columns are requested here, ahead of the wait for the kernel before
+  // this one and of the prologue (weights: nothing on the stream writes them).
+  constexpr int UNR = NW * CW <= 2 ? 4 : 2;
+  const int kn0 = min(kc, K);   // the first chunk of K
+  uint4 wpre[UNR][NW][CW];
 #pragma unroll
-  for (int c = 0; c < CW; ++c) {
-    const int n = min(col0 + c, N - 1);
-    const int k = lane * V;
-    if (k < K) {
-      wpre[0][c] = *reinterpret_cast<const uint4*>(W + (size_t)n * K + k);
-      if (NW == 2) wpre[1][c] = *reinterpret_cast<const uint4*>(W2 + (size_t)n * K + k);
-    } else {
-      wpre[0][c] = make_uint4(0, 0, 0, 0);
-      if (NW == 2) wpre[1][c] = make_uint4(0, 0, 0, 0);
+  for (int u = 0; u < UNR; ++u) {
+    const int k = lane * V + u * 32 * V;
+#pragma unroll
+    for (int c = 0; c < CW; ++c) {
+      const int n = min(col0 + c, N - 1);
+      if (k < kn0) {
+        wpre[u][0][c] = *reinterpret_cast<const uint4*>(W + (size_t)n * K + k);
+        if (NW == 2) wpre[u][1][c] = *reinterpret_cast<const uint4*>(W2 + (size_t)n * K + k);
+      } else {
+        wpre[u][0][c] = make_uint4(0, 0, 0, 0);
+        if (NW == 2) wpre[u][1][c] = make_uint4(0, 0, 0, 0);
+      }
     }
   }
 
@@ -115,10 +123,6 @@ gemv_kernel(const T* __restrict__ act, int lda, const float* __restrict__ x, con
     }
     __syncthreads();
     if (col0 < N) {
-      // UNR steps of K at a time: their weight vectors are requested together and used in order (a lane's sum runs
-      // over its k in increasing order whatever UNR is), so a warp waits for memory once per UNR steps instead of
-      // once per step
-      constexpr int UNR = NW * CW <= 2 ? 4 : 2;
       for (int kb = lane * V; kb < kn; kb += 32 * V * UNR) {
         uint4 wv[UNR][NW][CW];
 #pragma unroll
@@ -126,9 +130,9 @@ gemv_kernel(const T* __restrict__ act, int lda, const float* __restrict__ x, con
           const int k = kb + u * 32 * V;
 #pragma unroll
           for (int c = 0; c < CW; ++c) {
-            if (k0 == 0 && u == 0 && kb == lane * V) {
-              wv[u][0][c] = wpre[0][c];
-              if (NW == 2) wv[u][1][c] = wpre[1][c];
+            if (k0 == 0 && kb == lane * V) {
+              wv[u][0][c] = wpre[u][0][c];
+              if (NW == 2) wv[u][1][c] = wpre[u][1][c];
             } else if (k < kn) {
               const int n = min(col0 + c, N - 1);
               wv[u][0][c] = *reinterpret_cast<const uint4*>(W + (size_t)n * K + k0 + k);
