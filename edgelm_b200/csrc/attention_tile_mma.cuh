@@ -1,8 +1,7 @@
 // One 64-key tile of decode attention on the tensor cores: scores, running softmax and weighted
 // values of up to 16 query rows against a key tile and a value tile in shared memory (bfloat16,
-// rows padded by 16 bytes so that ldmatrix reads hit distinct banks).  Shared by the stand-alone
-// decode attention kernel and by the fused decode kernel of a whole layer stack; pure register
-// arithmetic of one warp, no synchronisation beyond the warp's own.
+// rows padded by 16 bytes so that ldmatrix reads hit distinct banks).  Pure register arithmetic of
+// one warp, no synchronisation beyond the warp's own.
 #pragma once
 #include <cuda_bf16.h>
 #include <math_constants.h>

@@ -442,30 +442,3 @@ def read_error_word(err):
         err.zero_()
         raise KernelError("a kernel reported: " + "; ".join(what))
 
-
-def decode_stack_chunk_pages(hd, max_k, n_seqs):
-    """Cache pages one attention unit of the fused decode kernel covers in a step of `n_seqs` sequences, for layers
-    whose widest matrix-product input is `max_k`; 0 if it does not take these sizes."""
-    return int(lib().edgelm_decode_stack_chunk_pages(int(hd), int(max_k), int(n_seqs)))
-
-
-DECODE_STACK_MAX_SEQS = 16  # sequences the fused decode kernel takes in one step (two 8-column MMA tiles)
-
-
-def decode_stack(records, n_layers, x, hd, max_k, seq_index, seq_pos, qkv, mid, part_o, part_ml, max_chunks, sync, err,
-                 trace=None):
-    """A run of `n_layers` decoder layers on the residual stream x[B, D] (float32, in place) for one new token
-    per sequence, as one persistent kernel.  `records`: the layers' packed descriptions (uint8, device).
-    `trace` (int64 [n_layers, 10], optional) receives block 0's nanosecond stamps around each phase."""
-    _need(trace is None or (trace.dtype == torch.int64 and trace.is_contiguous() and trace.numel() >= 10 * n_layers), "decode_stack: trace")
-    _need(x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2, "decode_stack: x is float32 [sequences, width]")
-    _need(records.dtype == torch.uint8 and records.numel() >= n_layers * lib().edgelm_decode_stack_record_bytes(), "decode_stack: records too short")
-    for t, n in ((seq_index, "seq_index"), (seq_pos, "seq_pos"), (sync, "sync")):
-        _i32(t, n)
-    for t in (qkv, mid):
-        _need(t.dtype == torch.bfloat16 and t.is_contiguous(), "decode_stack: bfloat16 scratch")
-    _need(part_o.dtype == torch.float32 and part_ml.dtype == torch.float32, "decode_stack: float32 partials")
-    B, D = x.shape
-    _check(lib().edgelm_decode_stack(_p(records), int(n_layers), _p(x), int(B), int(D), int(hd), int(max_k), _p(seq_index),
-                                     _p(seq_pos), _p(qkv), _p(mid), _p(part_o), _p(part_ml), int(max_chunks),
-                                     _p(sync), _p(err), _p(trace), _stream()))

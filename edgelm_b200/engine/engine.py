@@ -295,12 +295,10 @@ class Engine:
         self._flagged(int(self.err.item()))
 
     def _flagged(self, word):
-        """`word`: the error word as the host read it.  Non-zero: the word and whatever a kernel that gave up left
-        behind (the fused decode kernel's barrier words) are put right again, the captured graphs stay valid, and
-        the call raises; the logits and tokens of the steps since the last reading are not to be used."""
+        """`word`: the error word as the host read it.  Non-zero: the word is put right again, the captured graphs
+        stay valid, and the call raises; the logits and tokens of the steps since the last reading are not to be used."""
         if word:
             self.err.zero_()
-            self.model.reset_after_device_error()
             what = [m for b, m in ops.ERR_BITS.items() if word & b]
             raise ops.KernelError("a kernel reported: " + "; ".join(what or [f"error word {word:#x}"]))
 

@@ -10,7 +10,6 @@ import torch
 from ..config.base import ConfigError, ModelPlan
 from ..parts import registry as part_registry
 from ..parts.base import nbytes
-from .profiler import NULL_PROFILER
 
 
 class DecoderModel:
@@ -29,8 +28,6 @@ class DecoderModel:
         self.head = env.build("head", plan.head)
         self.schedule = plan.schedule
         self.device = None
-        self.fuse_decode = True      # small decode steps run fused runs of layers as one kernel each
-        self._decode_runs = None
         for i, e in enumerate(self.schedule):
             need = self.layers[e.layer].cache_need()
             if e.reads_cache_of is not None and need is not None and not getattr(self.layers[e.layer].mixer, "reads_foreign_cache", False):
@@ -63,20 +60,7 @@ class DecoderModel:
             self.head.load(tensors, "", device, tied_table=self.embedding.table)
         else:
             self.head.load(tensors, "", device)
-        self._decode_runs = None
         return self
-
-    def decode_runs(self):
-        """The schedule cut into runs that the fused decode kernel takes and single entries (planned once)."""
-        if self._decode_runs is None:
-            from .fusion import plan_decode_runs
-            self._decode_runs = plan_decode_runs(self)
-        return self._decode_runs
-
-    def reset_after_device_error(self):
-        for stack, _ in (self._decode_runs or ()):
-            if stack is not None:
-                stack.reset()
 
     # ------------------------------------------------------------------ cache and workspace
     def cache_needs(self):
@@ -153,17 +137,11 @@ class DecoderModel:
         x = ws.alloc((T, self.plan.hidden_size), torch.float32)
         with ctx.prof("embedding"):
             self.embedding.forward(ctx, x)
-        fused = self.fuse_decode and ctx.all_single and self.dtype == torch.bfloat16 and ctx.prof is NULL_PROFILER
-        for stack, indices in (self.decode_runs() if fused else [(None, range(len(self.schedule)))]):
-            if stack is not None and stack.takes(ctx):
-                stack.run(ctx, cache, x)
-                continue
-            for i in indices:
-                e = self.schedule[i]
-                entry = cache.entries[e.reads_cache_of if e.reads_cache_of is not None else i]
-                nxt = self.schedule[i + 1].layer if i + 1 < len(self.schedule) else None
-                ctx.weights_after = self.layers[nxt].first_weights() if nxt is not None else ()
-                self.layers[e.layer].forward(ctx, x, entry)
+        for i, e in enumerate(self.schedule):
+            entry = cache.entries[e.reads_cache_of if e.reads_cache_of is not None else i]
+            nxt = self.schedule[i + 1].layer if i + 1 < len(self.schedule) else None
+            ctx.weights_after = self.layers[nxt].first_weights() if nxt is not None else ()
+            self.layers[e.layer].forward(ctx, x, entry)
         ctx.weights_after = ()
         if R:
             with ws.frame():

@@ -2,7 +2,6 @@
 
     python -m edgelm_b200.kernel_bench --case decode  [--preset smollm2-135m] [--batch 8] [--ctx 1500]
     python -m edgelm_b200.kernel_bench --case prefill [--preset smollm2-135m] [--tokens 2048]
-    python -m edgelm_b200.kernel_bench --case stack   [--preset smollm2-135m] [--batch 8] [--ctx 1500]
     ... [--only attn_prefill] [--layers 30] [--reps 5] [--plain]
 
 Every kernel is launched once per layer on that layer's own weights and cache (so that weights
@@ -11,10 +10,6 @@ graph is replayed `reps` times between two CUDA events: the figure is device tim
 without host overhead.  `--plain` launches eagerly instead (one pass, no graph, no timing): the
 form to run under a profiler, which sees one launch per layer.  Random weights; nothing here is
 model code: it calls the same kernel wrappers the parts call.
-
-`--case stack` runs the fused decode kernel (all layers of a small decode step in one persistent
-kernel) and prints, from the kernel's own nanosecond stamps in block 0, the mean time of each phase
-of a layer and of the grid barrier after it, next to the time of the whole launch.
 """
 import argparse
 import math
@@ -25,7 +20,7 @@ import torch
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--case", choices=["decode", "prefill", "stack"], required=True)
+    ap.add_argument("--case", choices=["decode", "prefill"], required=True)
     ap.add_argument("--preset", default="smollm2-135m")
     ap.add_argument("--batch", type=int, default=8, help="decode: sequences")
     ap.add_argument("--ctx", type=int, default=1500, help="decode: cached tokens per sequence")
@@ -49,7 +44,7 @@ def main(argv=None):
     L = args.layers or cfg.num_hidden_layers
     QKV = (nh + 2 * nkv) * hd
     bf = torch.bfloat16
-    decode = args.case in ("decode", "stack")
+    decode = args.case == "decode"
     T = args.batch if decode else args.tokens
     B = args.batch if decode else 1
     ctx_len = args.ctx if decode else args.tokens
@@ -80,8 +75,6 @@ def main(argv=None):
     scale = 1.0 / math.sqrt(hd)
     mk = lambda v: torch.tensor(v, dtype=torch.int32, device=d)
     flops = {}
-    if args.case == "stack":
-        return run_stack(args, o, cfg, L, wq, wo, wg, wu, wd, kc, vc, table, seq, cos, sin, err, x, nw)
     if decode:
         pos = torch.full((B,), ctx_len - 1, dtype=torch.int32, device=d)
         tokpos, tokseq = pos.clone(), seq.clone()
@@ -180,68 +173,6 @@ def main(argv=None):
         extra = f"  {flops[name] / us / 1e6:8.1f} TFLOP/s" if name in flops else ""
         print(f"{name:24s} {us:8.2f} us{extra}")
     o.read_error_word(err)
-    return 0
-
-
-def run_stack(args, o, cfg, L, wq, wo, wg, wu, wd, kc, vc, table, seq, cos, sin, err, x, nw):
-    """The fused decode kernel over L layers: launch time and the phases' times from its own stamps."""
-    from .engine.fusion import RECORD
-    d = x.device
-    B, D = x.shape
-    nh, nkv, hd, inter = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.intermediate_size
-    blob = bytearray()
-    for l in range(L):
-        blob += RECORD.pack(wq[l].data_ptr(), wo[l].data_ptr(), wg[l].data_ptr(), wu[l].data_ptr(), wd[l].data_ptr(), nw.data_ptr(),
-                            nw.data_ptr(), cos.data_ptr(), sin.data_ptr(), kc[l].data_ptr(), vc[l].data_ptr(), table.data_ptr(),
-                            nh, nkv, inter, table.stride(0), cos.shape[0], kc[l].shape[0], 1e-5, 1e-5, hd ** -0.5, 0)
-    rec = torch.frombuffer(blob, dtype=torch.uint8).to(d)
-    max_k = max(D, nh * hd, inter)
-    chunk = o.decode_stack_chunk_pages(hd, max_k, B)
-    if chunk < 1:
-        print("the fused decode kernel does not take these sizes")
-        return 1
-    max_chunks = -(-table.stride(0) // chunk)
-    bf = torch.bfloat16
-    qkv = torch.empty(16, (nh + 2 * nkv) * hd, dtype=bf, device=d)
-    mid = torch.empty(16, inter, dtype=bf, device=d)
-    po = torch.empty(16 * nh * max_chunks * hd, device=d)
-    pm = torch.empty(16 * nh * max_chunks * 2, device=d)
-    sync = torch.zeros(2, dtype=torch.int32, device=d)
-    pos = torch.full((B,), args.ctx - 1, dtype=torch.int32, device=d)
-    trace = torch.zeros(L, 10, dtype=torch.int64, device=d)
-    run = lambda tr: o.decode_stack(rec, L, x, hd, max_k, seq, pos, qkv, mid, po, pm, max_chunks, sync, err, tr)
-    print(f"stack: {args.preset}, batch {B}, context {args.ctx}, {L} layers, attention units of {chunk} pages")
-    if args.plain:
-        run(None)
-        torch.cuda.synchronize()
-        print("decode_stack launched once")
-        o.read_error_word(err)
-        return 0
-    for _ in range(3):
-        run(None)
-    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    s.record()
-    for _ in range(args.reps):
-        run(None)
-    e.record()
-    torch.cuda.synchronize()
-    us = s.elapsed_time(e) * 1000 / args.reps
-    run(trace)
-    torch.cuda.synchronize()
-    o.read_error_word(err)
-    t = trace.cpu().double()
-    names = ["qkv_normed", "barrier", "attention", "barrier", "o_proj_residual", "barrier", "gate_up_swiglu_normed", "barrier",
-             "down_proj_residual", "barrier"]
-    spans = torch.zeros(max(L - 1, 1), 10, dtype=torch.float64)
-    for l in range(L - 1):
-        spans[l, :9] = t[l, 1:] - t[l, :9]
-        spans[l, 9] = t[l + 1, 0] - t[l, 9]
-    mean = spans.mean(0) / 1e3
-    print(f"{'decode_stack (launch)':24s} {us:8.2f} us = {us / L:6.2f} us a layer")
-    for n, v in zip(names, mean.tolist()):
-        print(f"  {n:22s} {v:8.2f} us")
-    print(f"  {'sum of a layer':22s} {float(mean.sum()):8.2f} us  (block 0's view; a barrier's time includes waiting for the slowest block)")
     return 0
 
 

@@ -80,13 +80,6 @@ class Attention(Part):
     def first_weights(self):
         return (self.w_qkv,)
 
-    def decode_fusion(self):
-        if not hasattr(self.positions, "rotation_tables") or self.window is not None:
-            return None
-        cos, sin = self.positions.rotation_tables()
-        return {"kind": "attention_rope", "w_qkv": self.w_qkv, "w_o": self.w_o, "num_heads": self.nh, "num_kv_heads": self.nkv,
-                "head_dim": self.hd, "scale": self.scale, "cos": cos, "sin": sin}
-
     def cache_need(self):
         return KVNeed(self.nkv, self.hd, self.window)
 

@@ -79,12 +79,6 @@ class Part:
         inner = ", ".join(f"{k} {v}" for k, v in self.sizes().items())
         return f"{self.kind}({inner})"
 
-    def decode_fusion(self):
-        """What a fused decode kernel needs to know to do this part's work itself: a dict with a "kind" and the
-        part's tensors and constants, or None (the default) if the part only runs through its own `forward`.
-        The engine's fusion pass reads these once the weights are loaded; a part never sees the fused kernel."""
-        return None
-
     def first_weights(self):
         """The weight tensors that this part's `forward` reads first (at most two): whoever runs before it may
         start them on their way into the L2 cache.  Default: none."""

@@ -53,16 +53,6 @@ class PreNormBlock(Part):
         return nbytes((n_tokens, self.hidden), self.dtype) + max(self.mixer.workspace_bytes(n_tokens, n_seqs),
                                                                   self.ffn.workspace_bytes(n_tokens, n_seqs))
 
-    def decode_fusion(self):
-        """This layer as a record of the fused decode kernel, if its four parts are the kinds that kernel computes."""
-        n1, m, n2, f = (p.decode_fusion() for p in self.parts)
-        if None in (n1, m, n2, f) or (n1["kind"], m["kind"], n2["kind"], f["kind"]) != ("rmsnorm", "attention_rope", "rmsnorm", "swiglu"):
-            return None
-        out = {"kind": "prenorm_attention_swiglu", "norm1": n1["weight"], "eps1": n1["eps"], "norm2": n2["weight"], "eps2": n2["eps"]}
-        out.update({k: v for k, v in m.items() if k != "kind"})
-        out.update({k: v for k, v in f.items() if k != "kind"})
-        return out
-
     def _normed(self, ctx, x, norm, part):
         """The part's input: lazily normalised if both the norm and the part can work that way
         (the part's first matrix product then computes the norm itself when the step is small)."""

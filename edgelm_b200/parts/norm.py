@@ -23,8 +23,5 @@ class RMSNorm(Part):
     def load(self, tensors, prefix, device):
         self.weight = as_vector(tensors[prefix + self.name], device)
 
-    def decode_fusion(self):
-        return {"kind": "rmsnorm", "weight": self.weight, "eps": self.eps}
-
     def forward(self, ctx, x, out, rows=None):
         ops.rmsnorm(x, self.weight, self.eps, out, rows_idx=rows)

@@ -35,9 +35,6 @@ class SwiGLU(Part):
         self.w_up = as_matrix(tensors[prefix + n["up"]], self.dtype, device)
         self.w_down = as_matrix(tensors[prefix + n["down"]], self.dtype, device)
 
-    def decode_fusion(self):
-        return {"kind": "swiglu", "w_gate": self.w_gate, "w_up": self.w_up, "w_down": self.w_down, "inter": self.inter}
-
     def workspace_bytes(self, n_tokens, n_seqs):
         return nbytes((n_tokens, self.inter), self.dtype) + nbytes((n_tokens, self.hidden), self.dtype)
 

@@ -22,7 +22,7 @@ TINY_C = dict(model_type="llama", architectures=["LlamaForCausalLM"], vocab_size
               intermediate_size=70, num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=3, head_dim=48,
               max_position_embeddings=160, rope_theta=777.0, rms_norm_eps=3e-4, tie_word_embeddings=True,
               bos_token_id=0, eos_token_id=1)
-# sizes the fused decode kernel takes (head size 64), and room for contexts of several attention chunks
+# a head size that the tensor-core kernels take (64), and room for contexts of many pages
 TINY_D = dict(model_type="llama", architectures=["LlamaForCausalLM"], vocab_size=300, hidden_size=72,
               intermediate_size=88, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
               max_position_embeddings=1200, rope_theta=50000.0, rms_norm_eps=2e-5, tie_word_embeddings=False,

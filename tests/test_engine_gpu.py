@@ -112,40 +112,18 @@ def test_long_decoding(model_dirs, oracles, dtype):
     assert H.rel_err(got, oracles[name].logits(toks)) < H.TOL[dtype]
 
 
-def test_fused_decode_steps(model_dirs, oracles):
-    """bfloat16 decode steps of few sequences run each run of layers as one kernel.  Against the plain
-    implementation and against the same engine with the fusion off: contexts of one, two and three attention
-    chunks in one batch, sequences that end earlier, a slot used again."""
-    from edgelm_b200.csrc import ops
-    from edgelm_b200.engine.engine import StepEntry
+def test_decode_steps_of_few_sequences_over_many_pages(model_dirs, oracles):
+    """bfloat16 decode steps of a few sequences whose contexts span one, nine and eighteen pages in one batch (the
+    decode attention deals a sequence's pages to many blocks and folds them), sequences that end earlier, a slot
+    used again."""
     name = "tiny_d"
     eng = engine_for(model_dirs, name, "bfloat16", max_tokens=4096)
-    runs = eng.model.decode_runs()
-    assert len(runs) == 1 and runs[0][0] is not None and runs[0][1] == [0, 1, 2]
     lens = [1100, 40, 530, 7, 449]
     reqs = [H.tokens_for(name, n, 300 + i) for i, n in enumerate(lens)]
     want = [oracles[name].logits(r) for r in reqs]
-    got = {}
-    for fuse in (True, False):
-        eng.model.fuse_decode = fuse
-        got[fuse] = H.run_batches(eng, reqs, batch_size=3, decode_tail=24)
-        for g, w in zip(got[fuse], want):
-            assert H.rel_err(g, w) < H.TOL["bfloat16"]
-    for a, b in zip(got[True], got[False]):
-        assert H.rel_err(a, b) < 2e-2
-    # the fused step is a handful of launches: embedding, the layers' kernel, final norm + head
-    eng.model.fuse_decode = True
-    slots = eng.open(2)
-    eng.step([StepEntry(slots[0], reqs[1], []), StepEntry(slots[1], reqs[3], [])])
-    n0 = ops.LAUNCHES
-    eng.step([StepEntry(slots[0], [5], [0]), StepEntry(slots[1], [6], [0])])
-    fused_launches = ops.LAUNCHES - n0
-    eng.model.fuse_decode = False
-    n0 = ops.LAUNCHES
-    eng.step([StepEntry(slots[0], [7], [0]), StepEntry(slots[1], [8], [0])])
-    assert fused_launches <= 5 < ops.LAUNCHES - n0
-    eng.model.fuse_decode = True
-    eng.close(slots)
+    got = H.run_batches(eng, reqs, batch_size=3, decode_tail=24)
+    for g, w in zip(got, want):
+        assert H.rel_err(g, w) < H.TOL["bfloat16"]
     eng.cache.check()
     eng.check_device_errors()
 

@@ -1012,95 +1012,3 @@ def test_attn_decode_rope_equals_separate_kernels(dtype, nh, nkv, hd, n_splits):
             assert rel_err(cache_b[page, :, (n - 1) % o.PAGE], cache_a[page, :, (n - 1) % o.PAGE]) < (1e-6 if dtype == torch.float32 else 8e-3)
     same = torch.isclose(a.kcache.float(), b.kcache.float(), rtol=1e-2, atol=1e-2, equal_nan=True)
     assert bool(same.all())
-
-
-# ----------------------------------------------------------------------------- a run of layers in one kernel
-@pytest.mark.parametrize("hd,layers,lengths", [
-    (64, [(9, 3, 136), (6, 2, 200), (9, 3, 136)], [1, 64, 65, 700, 128, 37, 513, 1100]),       # chunks of 8 pages: 1, 2 and 3 of them
-    (32, [(3, 1, 200), (4, 4, 72)], [5]),                                                       # one sequence
-    (128, [(4, 2, 96)], [30, 1, 64, 200, 400, 500, 65, 3, 129, 256, 2, 90, 450, 17, 64, 100]),  # 16 sequences, 6-page chunks
-    (96, [(16, 1, 64), (2, 1, 64)], [100, 520, 3]),                                             # 16 query heads on one kv head
-])
-def test_decode_stack_equals_separate_kernels(hd, layers, lengths):
-    """The persistent kernel of a run of layers against the same layers as separate kernels, each on
-    its own copy of the cache: the residual stream afterwards, the appended rows, nothing else touched."""
-    from edgelm_b200.engine.fusion import RECORD
-    o = ops()
-    bf = torch.bfloat16
-    B, D = len(lengths), 88
-    max_pos = max(lengths) + 8
-    cos, sin = plain.rope_angles(np.arange(max_pos), hd, 5000.0)
-    cos_t, sin_t = torch.from_numpy(cos).to(dev()), torch.from_numpy(sin).to(dev())
-    seq_pos = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=dev())
-    err = torch.zeros(1, dtype=torch.int32, device=dev())
-    x0 = rnd((B, D), torch.float32, 7)
-    W, sep, fus = [], [], []
-    for l, (nh, nkv, inter) in enumerate(layers):
-        s = 100 * l
-        W.append(dict(qkv=rnd(((nh + 2 * nkv) * hd, D), bf, s + 1, D ** -0.5), o=rnd((D, nh * hd), bf, s + 2, (nh * hd) ** -0.5),
-                      gate=rnd((inter, D), bf, s + 3, D ** -0.5), up=rnd((inter, D), bf, s + 4, D ** -0.5),
-                      down=rnd((D, inter), bf, s + 5, inter ** -0.5), n1=1 + rnd((D,), torch.float32, s + 6, 0.1),
-                      n2=1 + rnd((D,), torch.float32, s + 7, 0.1), eps1=1e-5 * (l + 1), eps2=1e-6))
-        sep.append(PagedCase(o, bf, lengths, nkv, hd, seed=11))
-        fus.append(PagedCase(o, bf, lengths, nkv, hd, seed=11))
-    # ---- separate kernels
-    x = x0.clone()
-    for (nh, nkv, inter), w, c in zip(layers, W, sep):
-        qkv = torch.empty(B, (nh + 2 * nkv) * hd, dtype=bf, device=dev())
-        o.gemv_mma(x, w["qkv"], qkv, norm_weight=w["n1"], eps=w["eps1"])
-        att = torch.empty(B, nh * hd, dtype=bf, device=dev())
-        po, pm = torch.empty(B * nh * 3 * hd, device=dev()), torch.empty(B * nh * 3 * 2, device=dev())
-        o.attn_decode_rope(qkv, att, c.kcache, c.vcache, c.table, c.seq_slot, seq_pos, cos_t, sin_t, B, nh, nkv, hd, hd ** -0.5, 3, po, pm)
-        o.gemv_mma(att, w["o"], x, epilogue=o.EPI_RESIDUAL, residual=x)
-        mid = torch.empty(B, inter, dtype=bf, device=dev())
-        o.gemv_mma(x, w["gate"], mid, epilogue=o.EPI_SWIGLU, w2=w["up"], norm_weight=w["n2"], eps=w["eps2"])
-        o.gemv_mma(mid, w["down"], x, epilogue=o.EPI_RESIDUAL, residual=x)
-    want = x
-    # ---- one kernel
-    blob = bytearray()
-    for (nh, nkv, inter), w, c in zip(layers, W, fus):
-        blob += RECORD.pack(w["qkv"].data_ptr(), w["o"].data_ptr(), w["gate"].data_ptr(), w["up"].data_ptr(), w["down"].data_ptr(),
-                            w["n1"].data_ptr(), w["n2"].data_ptr(), cos_t.data_ptr(), sin_t.data_ptr(), c.kcache.data_ptr(),
-                            c.vcache.data_ptr(), c.table.data_ptr(), nh, nkv, inter, c.table.stride(0), max_pos, c.kcache.shape[0],
-                            w["eps1"], w["eps2"], hd ** -0.5, 0)
-    rec = torch.frombuffer(blob, dtype=torch.uint8).to(dev())
-    max_nh = max(l[0] for l in layers)
-    max_k = max([D] + [l[0] * hd for l in layers] + [l[2] for l in layers])
-    chunk = o.decode_stack_chunk_pages(hd, max_k, B)
-    assert chunk >= 1
-    max_chunks = -(-fus[0].table.stride(0) // chunk)
-    qkv = torch.empty(16, max((nh + 2 * nkv) * hd for nh, nkv, _ in layers), dtype=bf, device=dev())
-    mid = torch.empty(16, max(l[2] for l in layers), dtype=bf, device=dev())
-    po = torch.full((16 * max_nh * max_chunks * hd,), float("nan"), device=dev())
-    pm = torch.full((16 * max_nh * max_chunks * 2,), float("nan"), device=dev())
-    sync = torch.zeros(2, dtype=torch.int32, device=dev())
-    got = x0.clone()
-    o.decode_stack(rec, len(layers), got, hd, max_k, fus[0].seq_slot, seq_pos, qkv, mid, po, pm, max_chunks, sync, err)
-    torch.cuda.synchronize()
-    assert int(err.item()) == 0
-    assert int(sync.abs().sum()) == 0          # barrier words and counters are zero again
-    assert rel_err(got, want) < 1e-2
-    for a, b in zip(sep, fus):
-        same = torch.isclose(a.kcache.float(), b.kcache.float(), rtol=2e-2, atol=2e-2, equal_nan=True)
-        assert bool(same.all())
-        same = torch.isclose(a.vcache.float(), b.vcache.float(), rtol=2e-2, atol=2e-2, equal_nan=True)
-        assert bool(same.all())
-    # a second launch on the words the first one left
-    got2 = x0.clone()
-    o.decode_stack(rec, len(layers), got2, hd, max_k, fus[0].seq_slot, seq_pos, qkv, mid, po, pm, max_chunks, sync, err)
-    torch.cuda.synchronize()
-    assert int(err.item()) == 0 and int(sync.abs().sum()) == 0
-    assert rel_err(got2, want) < 1e-2
-
-
-def test_decode_stack_refuses():
-    o = ops()
-    assert o.decode_stack_chunk_pages(48, 64, 4) == 0 and o.decode_stack_chunk_pages(256, 64, 4) == 0 and o.decode_stack_chunk_pages(64, 64, 17) == 0
-    x = torch.zeros(17, 64, device=dev())
-    z = torch.zeros(64, dtype=torch.int32, device=dev())
-    b = torch.zeros(16, 64, dtype=torch.bfloat16, device=dev())
-    rec = torch.zeros(136, dtype=torch.uint8, device=dev())
-    with pytest.raises(o.KernelError):   # 17 sequences
-        o.decode_stack(rec, 1, x, 64, 64, z, z, b, b, x, x, 1, z, z)
-    with pytest.raises(o.KernelError):   # head size
-        o.decode_stack(rec, 1, x[:4], 48, 64, z, z, b, b, x, x, 1, z, z)

@@ -690,6 +690,28 @@ def _register_reader():
                              head=PartSpec("lm_head", {"vocab_size": V, "dim": D, "tied_to": None, "name": "head.weight"}))
 
 
+def _reader_plain(W, tokens, hd, third_layer):
+    """The toy reader architecture, whole sequences, in plain NumPy."""
+    x = plain.embed(W["emb.weight"], tokens)
+    h = plain.rmsnorm(x, W["a.n1.weight"], 1e-5)
+    pos = np.arange(len(x))
+    q = plain.rope(h @ W["a.q.weight"].T, pos, 2, hd, 1000.0)
+    k = plain.rope(h @ W["a.k.weight"].T, pos, 2, hd, 1000.0)
+    v = h @ W["a.v.weight"].T
+    x = x + plain.attention(q, k, v, 2, 2, hd) @ W["a.o.weight"].T
+    x = x + plain.swiglu_mlp(plain.rmsnorm(x, W["a.n2.weight"], 1e-5), W["a.g.weight"], W["a.u.weight"], W["a.d.weight"])
+    means = np.cumsum(v[:, :hd], axis=0) / (pos + 1)[:, None]          # kv head 0 of the attention layer's values
+    x = x + means.astype(np.float32) @ W["r.read.weight"].T
+    x = x + plain.swiglu_mlp(plain.rmsnorm(x, W["r.n2.weight"], 1e-5), W["r.g.weight"], W["r.u.weight"], W["r.d.weight"])
+    if third_layer:
+        h = plain.rmsnorm(x, W["c.n1.weight"], 1e-5)
+        q = plain.rope(h @ W["c.q.weight"].T, pos, 3, hd, 1000.0)
+        k = plain.rope(h @ W["c.k.weight"].T, pos, 1, hd, 1000.0)
+        x = x + plain.attention(q, k, h @ W["c.v.weight"].T, 3, 1, hd) @ W["c.o.weight"].T
+        x = x + plain.swiglu_mlp(plain.rmsnorm(x, W["c.n2.weight"], 1e-5), W["c.g.weight"], W["c.u.weight"], W["c.d.weight"])
+    return plain.rmsnorm(x, W["final.weight"], 1e-5) @ W["head.weight"].T
+
+
 def test_a_layer_reads_another_layers_cache(tmp_path):
     _register_reader()
     from edgelm_b200.config import read_config
@@ -706,20 +728,7 @@ def test_a_layer_reads_another_layers_cache(tmp_path):
     assert len(eng.cache.kv_groups) == 1 and eng.cache.kv_groups[0].n_entries == 1 and eng.cache.entries[1] is None
     W = {k: v.float().numpy() for k, v in read_dir(str(folder)).items()}
 
-    def plain_model(tokens):
-        x = plain.embed(W["emb.weight"], tokens)
-        h = plain.rmsnorm(x, W["a.n1.weight"], 1e-5)
-        pos = np.arange(len(x))
-        q = plain.rope(h @ W["a.q.weight"].T, pos, 2, 16, 1000.0)
-        k = plain.rope(h @ W["a.k.weight"].T, pos, 2, 16, 1000.0)
-        v = h @ W["a.v.weight"].T
-        x = x + plain.attention(q, k, v, 2, 2, 16) @ W["a.o.weight"].T
-        x = x + plain.swiglu_mlp(plain.rmsnorm(x, W["a.n2.weight"], 1e-5), W["a.g.weight"], W["a.u.weight"], W["a.d.weight"])
-        means = np.cumsum(v[:, :16], axis=0) / (pos + 1)[:, None]          # kv head 0 of the attention layer's values
-        x = x + means.astype(np.float32) @ W["r.read.weight"].T
-        x = x + plain.swiglu_mlp(plain.rmsnorm(x, W["r.n2.weight"], 1e-5), W["r.g.weight"], W["r.u.weight"], W["r.d.weight"])
-        return plain.rmsnorm(x, W["final.weight"], 1e-5) @ W["head.weight"].T
-
+    plain_model = lambda tokens: _reader_plain(W, tokens, 16, third_layer=False)
     reqs = [[int(v) for v in np.random.default_rng(10 + i).integers(0, 41, size=n)] for i, n in enumerate([70, 9, 130])]
     for r in reqs:
         want = plain_model(r)
@@ -729,33 +738,27 @@ def test_a_layer_reads_another_layers_cache(tmp_path):
         assert H.rel_err(g, plain_model(r)) < 5e-5
 
 
-def test_fusion_pass_cuts_the_schedule_around_a_layer_it_cannot_take(tmp_path):
-    """Attention layer, a toy layer that reads the first one's cache, attention layer with other head counts: in
-    bfloat16 the decode steps run the first and the third as fused kernels and the toy layer through its own
-    forward; the logits are those of the same engine with the fusion off."""
+def test_layers_of_other_kinds_between_attention_layers_in_bfloat16(tmp_path):
+    """Attention layer, a toy layer that reads the first one's cache, attention layer with other head counts: the
+    float32 engine and the bfloat16 engine (tensor-core kernels for the attention layers, the toy layer's own
+    forward between them) against plain NumPy, token by token and in unequal batches."""
     _register_reader()
     from edgelm_b200.config import read_config
     from edgelm_b200.engine.engine import Engine, load_model
     from edgelm_b200.engine.model import expected_weights
-    from edgelm_b200.weights import random_tensors, write_file
+    from edgelm_b200.weights import random_tensors, read_dir, write_file
     d = {"architectures": ["ToyReaderForCausalLM"], "vocab_size": 41, "width": 32, "head_dim": 32, "third_layer": True}
     folder = tmp_path / "sandwich"
     folder.mkdir()
     (folder / "config.json").write_text(json.dumps(d))
     exp = expected_weights(read_config(str(folder)).plan())
     write_file(str(folder / "model.safetensors"), random_tensors(exp, seed=4, sigma=0.2, dtype=torch.float32))
-    model = load_model(str(folder), "bfloat16")
-    eng = Engine(model, max_tokens=1024)
-    runs = model.decode_runs()
-    assert [(s is not None, list(i)) for s, i in runs] == [(True, [0]), (False, [1]), (True, [2])]
-    assert runs[0][0].fusions[0]["num_heads"] == 2 and runs[2][0].fusions[0]["num_heads"] == 3 and runs[2][0].max_inter == 40
     reqs = [[int(v) for v in np.random.default_rng(20 + i).integers(0, 41, size=n)] for i, n in enumerate([70, 9, 130, 64])]
-    got = {}
-    for fuse in (True, False):
-        model.fuse_decode = fuse
-        got[fuse] = [H.run_tail_one_by_one(eng, r, 12) for r in reqs] + H.run_batches(eng, reqs, batch_size=3, decode_tail=6)
-    for a, b in zip(got[True], got[False]):
-        assert np.isfinite(a).all() and H.rel_err(a, b) < 2e-2
-    # float32 keeps to the parts' own kernels
-    assert all(s is None for s, _ in load_model(str(folder), "float32").decode_runs())
-    eng.check_device_errors()
+    W = {k: v.float().numpy() for k, v in read_dir(str(folder)).items()}
+    want = [_reader_plain(W, r, 32, third_layer=True) for r in reqs]
+    for dtype, tol in (("float32", 5e-5), ("bfloat16", H.TOL["bfloat16"])):
+        eng = Engine(load_model(str(folder), dtype), max_tokens=1024)
+        got = [H.run_tail_one_by_one(eng, r, 12) for r in reqs] + H.run_batches(eng, reqs, batch_size=3, decode_tail=6)
+        eng.check_device_errors()
+        for a, b in zip(got, want + want):
+            assert np.isfinite(a).all() and H.rel_err(a, b) < tol, dtype
