@@ -546,28 +546,32 @@ attn_decode_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ld
 #include "attention_decode_mma.cuh"
 namespace edgelm {
 
-// One (sequence, head) a block; every warp of the block reads the splits' maxima and sums 32 at a time (a lane a
-// split), finds the overall maximum and each split's weight, and then walks the splits that hold anything, in
-// their order, handing a split's weight and sum round by shuffle: a split that got no page (most of them when a
-// short sequence is dealt to many) costs nothing, and the exponentials are one per split, not one per split and dim.
-template <typename T>
+// One (sequence, head) a block; every warp of the block holds the splits' maxima and sums (a lane a split, up to
+// CHUNKS x 32 of them, read once), finds the overall maximum and each split's weight, and walks the splits that hold
+// anything, in their order, handing a split's weight and sum round by shuffle: a split that got no page (most of
+// them when a short sequence is dealt to many) costs nothing, the exponentials are one per split, not one per split
+// and dim, and the splits' weighted values are requested eight at a time, before the maximum is known (which
+// splits hold anything shows in the first read): two round trips to memory in all.
+template <typename T, int CHUNKS>
 __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                            T* __restrict__ out, int ldo, int nh, int hd, int n_splits) {
   const int seq = blockIdx.x, head = blockIdx.y, lane = threadIdx.x & 31;
   const size_t base = ((size_t)seq * nh + head) * n_splits;
   pdl_launch_dependents();
   pdl_wait();  // the partials are the previous kernel's
-  float M = -CUDART_INF_F;
-  for (int s = lane; s < n_splits; s += 32) M = fmaxf(M, part_ml[(base + s) * 2]);
+  float2 ml[CHUNKS];
 #pragma unroll
-  for (int o = 16; o; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int s = c * 32 + lane;
+    ml[c] = s < n_splits ? *reinterpret_cast<const float2*>(part_ml + (base + s) * 2) : make_float2(-CUDART_INF_F, 0.f);
+  }
   float L = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};   // dims threadIdx.x, + blockDim.x, ..: head sizes up to 4 x the block
-  for (int s0 = 0; s0 < n_splits; s0 += 32) {
-    const int s = s0 + lane;
-    const float ms = s < n_splits ? part_ml[(base + s) * 2] : -CUDART_INF_F;
-    const float ls = s < n_splits ? part_ml[(base + s) * 2 + 1] : 0.f;
-    const float f = ms == -CUDART_INF_F ? 0.f : expf(ms - M);   // (a split that held no page: -inf)
-    unsigned live = __ballot_sync(0xffffffffu, ms != -CUDART_INF_F);
+  float M = -CUDART_INF_F;
+  bool have_m = false;
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    unsigned live = __ballot_sync(0xffffffffu, ml[c].x != -CUDART_INF_F);
+    float f = 0.f;
     while (live) {   // eight splits at a time: their sums are requested together and added in the splits' order
       int js[8];
       float v[8][4];
@@ -576,7 +580,7 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, con
         js[q] = live ? __ffs(live) - 1 : -1;
         live &= live - 1;   // (0 stays 0)
         if (js[q] >= 0) {
-          const float* po = part_o + (base + s0 + js[q]) * hd;
+          const float* po = part_o + (base + c * 32 + js[q]) * hd;
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const int d = threadIdx.x + i * blockDim.x;
@@ -584,10 +588,18 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, con
           }
         }
       }
+      if (!have_m) {   // (once, while the first requests are on their way)
+#pragma unroll
+        for (int cc = 0; cc < CHUNKS; ++cc) M = fmaxf(M, ml[cc].x);
+#pragma unroll
+        for (int o = 16; o; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        have_m = true;
+      }
+      if (f == 0.f) f = ml[c].x == -CUDART_INF_F ? 0.f : expf(ml[c].x - M);   // (a split that held no page: -inf)
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
         if (js[q] >= 0) {
-          const float fj = __shfl_sync(0xffffffffu, f, js[q]), lj = __shfl_sync(0xffffffffu, ls, js[q]);
+          const float fj = __shfl_sync(0xffffffffu, f, js[q]), lj = __shfl_sync(0xffffffffu, ml[c].y, js[q]);
           L = fmaf(lj, fj, L);
 #pragma unroll
           for (int i = 0; i < 4; ++i) acc[i] = fmaf(v[q][i], fj, acc[i]);
@@ -699,8 +711,12 @@ int launch_decode(const void* q, int ldq, void* out, int ldo, const void* kc, co
   g_decode_last_launches = n_splits > 1 ? 2 : 1;
   if (le == cudaSuccess && n_splits > 1) {
     dim3 cgrid(n_seqs, nh);
-    le = launch_pdl(2, attn_decode_combine_kernel<T>, cgrid, dim3(64), 0, stream, (const float*)part_o, (const float*)part_ml,
-                    (T*)out, ldo, nh, hd, n_splits);
+    auto fold = [&](auto kern) {
+      return launch_pdl(2, kern, cgrid, dim3(64), 0, stream, (const float*)part_o, (const float*)part_ml, (T*)out, ldo, nh, hd, n_splits);
+    };
+    // (a lane holds one split of every 32: 1, 2, 8 or 64 of them in registers)
+    le = n_splits <= 32 ? fold(attn_decode_combine_kernel<T, 1>) : n_splits <= 64 ? fold(attn_decode_combine_kernel<T, 2>)
+         : n_splits <= 256 ? fold(attn_decode_combine_kernel<T, 8>) : fold(attn_decode_combine_kernel<T, 64>);
   }
   if (le != cudaSuccess) {
     set_error("attn_decode: launch failed: %s", cudaGetErrorString(le));
@@ -778,7 +794,7 @@ extern "C" int edgelm_attn_decode(const void* q, int ldq, void* out, int ldo, co
                                   float* part_o, float* part_ml, int window, int* err, cudaStream_t stream) {
   if (n_seqs == 0) return 0;
   if (check_heads("attn_decode", nh, nkv, hd)) return -1;
-  EL_REFUSE(n_splits >= 1 && n_splits <= 65535 && nkv <= 65535, "attn_decode: bad split count %d", n_splits);
+  EL_REFUSE(n_splits >= 1 && n_splits <= 2048 && nkv <= 65535, "attn_decode: bad split count %d (takes 1 to 2,048)", n_splits);
   EL_REFUSE(n_splits == 1 || (part_o && part_ml), "attn_decode: %d splits need the scratch buffers", n_splits);
   EL_ATT_DISPATCH(launch_decode, q, ldq, out, ldo, kcache, vcache, page_table, table_stride, seq_slot, seq_pos, n_seqs, nh,
                   nkv, hd, scale, n_splits, part_o, part_ml, err, stream, (const float*)nullptr, (const float*)nullptr, 0, window);
@@ -797,7 +813,7 @@ extern "C" int edgelm_attn_decode_rope(const void* qkv, int ldq, void* out, int 
                                        float* part_ml, int window, int* err, cudaStream_t stream) {
   if (n_seqs == 0) return 0;
   if (check_heads("attn_decode_rope", nh, nkv, hd)) return -1;
-  EL_REFUSE(n_splits >= 1 && n_splits <= 65535 && nkv <= 65535, "attn_decode_rope: bad split count %d", n_splits);
+  EL_REFUSE(n_splits >= 1 && n_splits <= 2048 && nkv <= 65535, "attn_decode_rope: bad split count %d (takes 1 to 2,048)", n_splits);
   EL_REFUSE(n_splits == 1 || (part_o && part_ml), "attn_decode_rope: %d splits need the scratch buffers", n_splits);
   EL_REFUSE(cos_t && sin_t && max_pos > 0, "attn_decode_rope: needs the position table");
   EL_ATT_DISPATCH(launch_decode, qkv, ldq, out, ldo, kcache, vcache, page_table, table_stride, seq_slot, seq_pos, n_seqs, nh,
@@ -849,7 +865,7 @@ extern "C" int edgelm_attn_decode_noalloc(const void* q, int ldq, void* out, int
                                           int hd, float scale, int n_splits, cudaStream_t stream) {
   if (n_seqs == 0) return 0;
   if (check_heads("attn_decode_noalloc", nh, nkv, hd)) return -1;
-  EL_REFUSE(n_seqs > 0 && n_splits >= 1 && n_splits <= 65535 && nkv <= 65535, "attn_decode_noalloc: bad counts (%d sequences, %d splits)", n_seqs, n_splits);
+  EL_REFUSE(n_seqs > 0 && n_splits >= 1 && n_splits <= 2048 && nkv <= 65535, "attn_decode_noalloc: bad counts (%d sequences, %d splits)", n_seqs, n_splits);
   float* part_o = nullptr;
   float* part_ml = nullptr;
   if (n_splits > 1) {
