@@ -651,7 +651,7 @@ template <typename T, int NC>
 int launch_decode(const void* q, int ldq, void* out, int ldo, const void* kc, const void* vc, const int32_t* page_table,
                   int table_stride, const int32_t* seq_slot, const int32_t* seq_pos, int n_seqs, int nh, int nkv, int hd,
                   float scale, int n_splits, float* part_o, float* part_ml, int* err, cudaStream_t stream,
-                  const float* cos_t = nullptr, const float* sin_t = nullptr, int max_pos = 0, int window = 0) {
+                  const float* cos_t = nullptr, const float* sin_t = nullptr, int max_pos = 0, int window = 0, int meta_ready = 0) {
   constexpr int NP = NC <= 2 ? 1 : NC / 2;  // pairs of dims per lane: ceil(hd / 64)
   dim3 grid(n_seqs, nkv, n_splits);
   cudaError_t le = cudaSuccess;
@@ -684,7 +684,7 @@ int launch_decode(const void* q, int ldq, void* out, int ldo, const void* kc, co
         cfg.numAttrs = n_attr;
         return cudaLaunchKernelEx(&cfg, kern, (const __nv_bfloat16*)q, ldq, (__nv_bfloat16*)out, ldo,
                                   (__nv_bfloat16*)const_cast<void*>(kc), (__nv_bfloat16*)const_cast<void*>(vc), page_table, table_stride,
-                                  seq_slot, seq_pos, nh, nkv, scale, n_splits, part_o, part_ml, err, cos_t, sin_t, max_pos);
+                                  seq_slot, seq_pos, nh, nkv, scale, n_splits, part_o, part_ml, err, cos_t, sin_t, max_pos, meta_ready);
       };
       switch (hd / 16) {
         case 2: le = go(attn_decode_mma_kernel<2>); break;
@@ -788,16 +788,18 @@ extern "C" int edgelm_attn_set_error_word(int* err) {
 }
 
 // Scratch: part_o holds n_seqs*nh*n_splits*hd floats, part_ml n_seqs*nh*n_splits*2 (unused when n_splits == 1).
+// meta_ready != 0: the caller vouches that seq_pos, seq_slot and page_table were complete before the kernel that
+// precedes this call on the stream started; the tensor-core kernel then reads them ahead of its wait for that kernel.
 extern "C" int edgelm_attn_decode(const void* q, int ldq, void* out, int ldo, const void* kcache, const void* vcache,
                                   int dtype, const int32_t* page_table, int table_stride, const int32_t* seq_slot,
                                   const int32_t* seq_pos, int n_seqs, int nh, int nkv, int hd, float scale, int n_splits,
-                                  float* part_o, float* part_ml, int window, int* err, cudaStream_t stream) {
+                                  float* part_o, float* part_ml, int window, int meta_ready, int* err, cudaStream_t stream) {
   if (n_seqs == 0) return 0;
   if (check_heads("attn_decode", nh, nkv, hd)) return -1;
   EL_REFUSE(n_splits >= 1 && n_splits <= 2048 && nkv <= 65535, "attn_decode: bad split count %d (takes 1 to 2,048)", n_splits);
   EL_REFUSE(n_splits == 1 || (part_o && part_ml), "attn_decode: %d splits need the scratch buffers", n_splits);
   EL_ATT_DISPATCH(launch_decode, q, ldq, out, ldo, kcache, vcache, page_table, table_stride, seq_slot, seq_pos, n_seqs, nh,
-                  nkv, hd, scale, n_splits, part_o, part_ml, err, stream, (const float*)nullptr, (const float*)nullptr, 0, window);
+                  nkv, hd, scale, n_splits, part_o, part_ml, err, stream, (const float*)nullptr, (const float*)nullptr, 0, window, meta_ready);
   EL_LAUNCH_CHECK("attn_decode");
   return 0;
 }
@@ -810,14 +812,14 @@ extern "C" int edgelm_attn_decode_rope(const void* qkv, int ldq, void* out, int 
                                        const int32_t* page_table, int table_stride, const int32_t* seq_slot,
                                        const int32_t* seq_pos, const float* cos_t, const float* sin_t, int max_pos,
                                        int n_seqs, int nh, int nkv, int hd, float scale, int n_splits, float* part_o,
-                                       float* part_ml, int window, int* err, cudaStream_t stream) {
+                                       float* part_ml, int window, int meta_ready, int* err, cudaStream_t stream) {
   if (n_seqs == 0) return 0;
   if (check_heads("attn_decode_rope", nh, nkv, hd)) return -1;
   EL_REFUSE(n_splits >= 1 && n_splits <= 2048 && nkv <= 65535, "attn_decode_rope: bad split count %d (takes 1 to 2,048)", n_splits);
   EL_REFUSE(n_splits == 1 || (part_o && part_ml), "attn_decode_rope: %d splits need the scratch buffers", n_splits);
   EL_REFUSE(cos_t && sin_t && max_pos > 0, "attn_decode_rope: needs the position table");
   EL_ATT_DISPATCH(launch_decode, qkv, ldq, out, ldo, kcache, vcache, page_table, table_stride, seq_slot, seq_pos, n_seqs, nh,
-                  nkv, hd, scale, n_splits, part_o, part_ml, err, stream, cos_t, sin_t, max_pos, window);
+                  nkv, hd, scale, n_splits, part_o, part_ml, err, stream, cos_t, sin_t, max_pos, window, meta_ready);
   EL_LAUNCH_CHECK("attn_decode_rope");
   return 0;
 }

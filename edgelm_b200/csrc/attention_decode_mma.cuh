@@ -32,7 +32,10 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat
                        __nv_bfloat16* kcache, __nv_bfloat16* vcache, const int32_t* __restrict__ page_table,
                        int table_stride, const int32_t* __restrict__ seq_slot, const int32_t* __restrict__ seq_pos, int nh,
                        int nkv, float scale, int n_splits, float* __restrict__ part_o, float* __restrict__ part_ml, int* err,
-                       const float* __restrict__ cos_t, const float* __restrict__ sin_t, int max_pos) {
+                       const float* __restrict__ cos_t, const float* __restrict__ sin_t, int max_pos, int meta_ready) {
+  // meta_ready != 0: the lengths, slots and page tables were complete before the kernel that precedes this one on the
+  // stream started (a step's metadata, copied at its start).  The block then reads them, down to the page of its first
+  // tile, before it waits for that kernel: two round trips to memory that would otherwise follow the wait.
   using T = __nv_bfloat16;
   constexpr int HD = HDT * 16;
   constexpr int PITCH = HD + 8;          // elements per padded row
@@ -56,7 +59,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat
   }
   __syncwarp();
   pdl_launch_dependents();
-  pdl_wait();
+  if (!meta_ready) pdl_wait();
   const int nkeys = seq_pos[seq] + 1;
   const int32_t* pages = page_table + (size_t)seq_slot[seq] * table_stride;
   const int n_pages = (nkeys + PAGE - 1) / PAGE;
@@ -76,8 +79,10 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat
     new_page = pages[pos / PAGE];
     if (new_page < 0 && threadIdx.x == 0 && err) atomicOr(err, ERR_PAGE_RANGE);
   }
-  auto issue_tile = [&](int t) {   // whole warp: 16-byte asynchronous copies into padded rows, a lane's share arriving on the warp's mbarrier
-    const size_t src = ((size_t)pages[p_begin + t] * nkv + kvh) * PAGE * HD;
+  const int first_page = warp < n_tiles ? pages[p_begin + warp] : 0;
+  if (meta_ready) pdl_wait();   // the queries, the new key and value and the cache rows of the step before are the earlier kernels'
+  auto issue_tile = [&](int t, int page) {   // whole warp: 16-byte asynchronous copies into padded rows, a lane's share arriving on the warp's mbarrier
+    const size_t src = ((size_t)page * nkv + kvh) * PAGE * HD;
 #pragma unroll
     for (int i = lane; i < PAGE * (HD / 8); i += 32) {
       const int r = i / (HD / 8), c = (i - r * (HD / 8)) * 8;
@@ -88,7 +93,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat
   };
   bool pre_issued = false;
   if (warp < n_tiles) {   // the first tile is on its way while the queries are staged
-    issue_tile(warp);
+    issue_tile(warp, first_page);
     pre_issued = true;
   }
 
@@ -130,7 +135,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat
         const int key0 = (p_begin + t) * PAGE;
         const int valid = min(PAGE, nkeys - key0);
         if (pre_issued) pre_issued = false;
-        else issue_tile(t);
+        else issue_tile(t, pages[p_begin + t]);
         {
           const long long t0 = clock64();
           bool done = dec_mbar_try(bar, phase);

@@ -114,6 +114,18 @@ gemv_mma_kernel(const __nv_bfloat16* __restrict__ act, int lda, const float* __r
   }
   pdl_launch_dependents();
   pdl_wait();  // from here on: activations that the kernel before this one wrote
+  // the residual values that the epilogue adds to, requested now by the warp that will run it: a round trip to
+  // memory less at the end of the block's life (out may be the residual itself: nobody else writes these elements)
+  float res_ahead[NT][4];
+  if (EPI == GM_RESIDUAL && warp == 0) {
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int n = n0 + gid + (j >> 1) * 8, m = t * 8 + tig * 2 + (j & 1);
+        res_ahead[t][j] = n < N && m < M ? residual[(size_t)m * ldo + n] : 0.f;
+      }
+  }
   // ---- activations into shared memory (rows >= M are zero)
   if (NORM) {
     for (int r = warp; r < ROWS; r += GM_WARPS) {
@@ -276,7 +288,7 @@ gemv_mma_kernel(const __nv_bfloat16* __restrict__ act, int lda, const float* __r
       if (n < N && m < M) {
         const size_t idx = (size_t)m * ldo + n;
         if (EPI == GM_STORE) out[idx] = from_f32<TOut>(s[0][j]);
-        if (EPI == GM_RESIDUAL) out[idx] = from_f32<TOut>(residual[idx] + s[0][j]);
+        if (EPI == GM_RESIDUAL) out[idx] = from_f32<TOut>(res_ahead[t][j] + s[0][j]);
         if (EPI == GM_SWIGLU) out[idx] = from_f32<TOut>(gm_silu(s[0][j]) * s[NW - 1][j]);
       }
     }

@@ -364,10 +364,11 @@ def attn_prefill_tc_trace(buffer):
 
 
 def attn_decode(qkv, out, kcache, vcache, page_table, seq_slot, seq_pos, n_seqs, nh, nkv, hd, scale, n_splits=1,
-                part_o=None, part_ml=None, err=None, window=0):
+                part_o=None, part_ml=None, err=None, window=0, meta_ready=False):
     """Attention of one new token per sequence over the paged cache, pages dealt to `n_splits` blocks.
     `err`: the device error word that a copy which never arrives is reported to.  `window` > 0: the token sees the
-    last `window` keys only (the CUDA-core kernel then, whatever the dtype)."""
+    last `window` keys only (the CUDA-core kernel then, whatever the dtype).  `meta_ready`: the caller vouches that
+    positions, slots and page table were complete before the kernel that precedes this call on the stream started."""
     _need(qkv.dtype == out.dtype == kcache.dtype and qkv.stride(1) == 1 and out.stride(1) == 1, "attn_decode: layout")
     for t, n in ((page_table, "page_table"), (seq_slot, "seq_slot"), (seq_pos, "seq_pos")):
         _i32(t, n)
@@ -376,13 +377,14 @@ def attn_decode(qkv, out, kcache, vcache, page_table, seq_slot, seq_pos, n_seqs,
         _need(part_ml is not None and part_ml.dtype == torch.float32 and part_ml.numel() >= n_seqs * nh * n_splits * 2, "attn_decode: part_ml too small")
     _check(lib().edgelm_attn_decode(_p(qkv), qkv.stride(0), _p(out), out.stride(0), _p(kcache), _p(vcache), _dt(qkv),
                                     _p(page_table), page_table.stride(0), _p(seq_slot), _p(seq_pos), n_seqs, nh, nkv, hd,
-                                    ctypes.c_float(scale), n_splits, _p(part_o), _p(part_ml), int(window or 0), _p(err), _stream()),
+                                    ctypes.c_float(scale), n_splits, _p(part_o), _p(part_ml), int(window or 0), 1 if meta_ready else 0,
+                                    _p(err), _stream()),
            launches=0)
     count_launches(lib().edgelm_attn_decode_last_launches())
 
 
 def attn_decode_rope(qkv, out, kcache, vcache, page_table, seq_slot, seq_pos, cos, sin, n_seqs, nh, nkv, hd, scale,
-                     n_splits=1, part_o=None, part_ml=None, err=None, window=0):
+                     n_splits=1, part_o=None, part_ml=None, err=None, window=0, meta_ready=False):
     """Decode attention with RoPE and the cache append fused in: `qkv` holds the raw projections of one
     new token per sequence; the rotated keys and the values are written into the cache pages."""
     _need(qkv.dtype == out.dtype == kcache.dtype and qkv.stride(1) == 1 and out.stride(1) == 1, "attn_decode_rope: layout")
@@ -396,7 +398,7 @@ def attn_decode_rope(qkv, out, kcache, vcache, page_table, seq_slot, seq_pos, co
     _check(lib().edgelm_attn_decode_rope(_p(qkv), qkv.stride(0), _p(out), out.stride(0), _p(kcache), _p(vcache), _dt(qkv),
                                          _p(page_table), page_table.stride(0), _p(seq_slot), _p(seq_pos), _p(cos), _p(sin),
                                          cos.shape[0], n_seqs, nh, nkv, hd, ctypes.c_float(scale), n_splits, _p(part_o),
-                                         _p(part_ml), int(window or 0), _p(err), _stream()),
+                                         _p(part_ml), int(window or 0), 1 if meta_ready else 0, _p(err), _stream()),
            launches=0)
     count_launches(lib().edgelm_attn_decode_last_launches())
 

@@ -55,6 +55,10 @@ class StepContext:
         self._tiles = {}
         self._seq_ntok = self._seq_pos0 = None
         self._fixed_splits = None
+        # positions, slots and page tables reach the device in one copy at the step's start, before its first kernel,
+        # and the step's first kernels are the embedding's and a product's: a later kernel launched as a programmatic
+        # dependent may read them before it waits for the kernel ahead of it
+        self.metadata_precedes_kernels = True
 
     def page_table(self, group):
         """Device page-table rows [n_seqs, pages] of a key/value cache group, one row per sequence of the batch."""

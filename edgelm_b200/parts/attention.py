@@ -124,13 +124,15 @@ class Attention(Part):
         if splits > 1:
             part_o = ws.alloc((ctx.n_seqs * self.nh * splits * self.hd,), torch.float32)
             part_ml = ws.alloc((ctx.n_seqs * self.nh * splits * 2,), torch.float32)
+        ready = getattr(ctx, "metadata_precedes_kernels", False)
         with ctx.prof("attn_decode"):
             if tables is not None:
                 ops.attn_decode_rope(qkv, a, cache.k, cache.v, table, ctx.seq_index, ctx.seq_pos, cos, sin, ctx.n_seqs, self.nh,
-                                     self.nkv, self.hd, self.scale, splits, part_o, part_ml, err=ctx.err, window=self.window)
+                                     self.nkv, self.hd, self.scale, splits, part_o, part_ml, err=ctx.err, window=self.window,
+                                     meta_ready=ready)
             else:
                 ops.attn_decode(qkv, a, cache.k, cache.v, table, ctx.seq_index, ctx.seq_pos, ctx.n_seqs, self.nh, self.nkv,
-                                self.hd, self.scale, splits, part_o, part_ml, err=ctx.err, window=self.window)
+                                self.hd, self.scale, splits, part_o, part_ml, err=ctx.err, window=self.window, meta_ready=ready)
 
     def forward(self, ctx, h, x, cache):
         T = h.shape[0]
