@@ -127,7 +127,44 @@ gemv_mma_kernel(const __nv_bfloat16* __restrict__ act, int lda, const float* __r
       }
   }
   // ---- activations into shared memory (rows >= M are zero)
-  if (NORM) {
+  // A normalised row of up to 1,024 values in one chunk: a warp takes a row, keeps it in registers between the sum of
+  // squares and the scaling and writes it out rounded: one pass over x, with the norm's weights requested beside it.
+  const bool one_pass = NORM && K <= 1024 && K <= kc;
+  if (NORM && one_pass) {
+    float4 g[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int k = lane * 4 + j * 128;
+      g[j] = k < K ? *reinterpret_cast<const float4*>(norm_w + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int r = warp; r < ROWS; r += GM_WARPS) {
+      float4 v[8];
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int k = lane * 4 + j * 128;
+        v[j] = r < M && k < K ? *reinterpret_cast<const float4*>(x + (size_t)r * K + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss); ss = fmaf(v[j].z, v[j].z, ss); ss = fmaf(v[j].w, v[j].w, ss);
+      }
+      ss = warp_sum(ss);
+      const float sc = r < M ? 1.0f / sqrtf(ss / (float)K + eps) : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int k = lane * 4 + j * 128;
+        if (k < K) {
+          __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j].x * sc * g[j].x, v[j].y * sc * g[j].y);
+          __nv_bfloat162 h1 = __floats2bfloat162_rn(v[j].z * sc * g[j].z, v[j].w * sc * g[j].w);
+          uint2 u;
+          u.x = *reinterpret_cast<uint32_t*>(&h0);
+          u.y = *reinterpret_cast<uint32_t*>(&h1);
+          *reinterpret_cast<uint2*>(As + (size_t)r * pitch + k) = u;
+        }
+      }
+    }
+  } else if (NORM) {
     for (int r = warp; r < ROWS; r += GM_WARPS) {
       float ss = 0.f;
       if (r < M) {
@@ -171,7 +208,7 @@ gemv_mma_kernel(const __nv_bfloat16* __restrict__ act, int lda, const float* __r
           *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
       }
       asm volatile("cp.async.wait_all;" ::: "memory");
-    } else {
+    } else if (!one_pass) {
       for (int i0 = threadIdx.x; i0 < ROWS * kvec; i0 += blockDim.x * 2) {   // two pieces' loads in flight together
         float4 x0[2], x1[2], w0[2], w1[2];
 #pragma unroll
