@@ -84,7 +84,43 @@ gemv_kernel(const T* __restrict__ act, int lda, const float* __restrict__ x, con
 
   pdl_launch_dependents();
   pdl_wait();   // (launched as a programmatic dependent: from here on, what the kernel before this one wrote)
-  if (NORM) {  // 1 / sqrt(mean(x^2) + eps) per row, a warp per row
+  // A normalised row of up to 1,024 values in one chunk: a warp takes a row, keeps it in registers between the sum of
+  // squares and the scaling and writes it out in the compute dtype: one pass over x, the norm's weights beside it.
+  const bool one_pass = NORM && K <= 1024 && K <= kc && K % 4 == 0;
+  if (NORM && one_pass) {
+    float4 g[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int k = lane * 4 + j * 128;
+      g[j] = k < K ? *reinterpret_cast<const float4*>(norm_w + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int r = warp; r < rows; r += nwarps) {
+      float4 v[8];
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int k = lane * 4 + j * 128;
+        v[j] = k < K ? *reinterpret_cast<const float4*>(x + (size_t)(m0 + r) * K + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss); ss = fmaf(v[j].z, v[j].z, ss); ss = fmaf(v[j].w, v[j].w, ss);
+      }
+      ss = warp_sum(ss);
+      const float sc = 1.0f / sqrtf(ss / (float)K + eps);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int k = lane * 4 + j * 128;
+        if (k < K) {
+          T* dst = As + r * kc + k;
+          dst[0] = from_f32<T>(v[j].x * sc * g[j].x);
+          dst[1] = from_f32<T>(v[j].y * sc * g[j].y);
+          dst[2] = from_f32<T>(v[j].z * sc * g[j].z);
+          dst[3] = from_f32<T>(v[j].w * sc * g[j].w);
+        }
+      }
+    }
+  } else if (NORM) {  // 1 / sqrt(mean(x^2) + eps) per row, a warp per row
     for (int r = warp; r < rows; r += nwarps) {
       const float* xr = x + (size_t)(m0 + r) * K;
       float ss = 0.f;
@@ -109,7 +145,7 @@ gemv_kernel(const T* __restrict__ act, int lda, const float* __restrict__ x, con
   for (int k0 = 0; k0 < K; k0 += kc) {          // K in chunks that fit shared memory (one chunk for the usual sizes)
     const int kn = min(kc, K - k0);
     if (k0) __syncthreads();
-    for (int i = threadIdx.x * V; i < rows * kn; i += blockDim.x * V) {
+    for (int i = threadIdx.x * V; i < (one_pass ? 0 : rows * kn); i += blockDim.x * V) {
       const int r = i / kn, k = i - r * kn;     // kn is a multiple of V: a vector never crosses rows
       if (NORM) {
         const float s = inv[r];
