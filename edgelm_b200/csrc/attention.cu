@@ -19,6 +19,7 @@
 #include <math_constants.h>
 
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -546,13 +547,56 @@ attn_decode_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ld
 #include "attention_decode_mma.cuh"
 namespace edgelm {
 
+// The fold of up to Q splits whose values a thread holds all at once (see the kernel below): `ml` are the lane's
+// maxima and sums (split c * 32 + lane), `dst` the head's row of the output.
+template <typename T, int CHUNKS, int DPT, int Q>
+__device__ __forceinline__ void fold_eager(const float* __restrict__ part_o, const float2 (&ml)[CHUNKS], size_t base, int n_splits,
+                                           int hd, T* __restrict__ dst) {
+  float v[Q][DPT];
+#pragma unroll
+  for (int q = 0; q < Q; ++q)
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+      const int d = threadIdx.x + i * blockDim.x;
+      v[q][i] = q < n_splits && d < hd ? part_o[(base + q) * hd + d] : 0.f;
+    }
+  float M = -CUDART_INF_F;
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) M = fmaxf(M, ml[c].x);
+#pragma unroll
+  for (int o = 16; o; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+  float f[CHUNKS];
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) f[c] = ml[c].x == -CUDART_INF_F ? 0.f : expf(ml[c].x - M);
+  float L = 0.f, acc[DPT];
+#pragma unroll
+  for (int i = 0; i < DPT; ++i) acc[i] = 0.f;
+#pragma unroll
+  for (int q = 0; q < Q; ++q) {
+    constexpr int LAST = CHUNKS - 1;
+    const int c = (q >> 5) < LAST ? (q >> 5) : LAST;
+    const float mq = __shfl_sync(0xffffffffu, ml[c].x, q & 31), fq = __shfl_sync(0xffffffffu, f[c], q & 31);
+    const float lq = __shfl_sync(0xffffffffu, ml[c].y, q & 31);
+    if (q < n_splits && mq != -CUDART_INF_F) {
+      L = fmaf(lq, fq, L);
+#pragma unroll
+      for (int i = 0; i < DPT; ++i) acc[i] = fmaf(v[q][i], fq, acc[i]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < DPT; ++i) {
+    const int d = threadIdx.x + i * blockDim.x;
+    if (d < hd) dst[d] = from_f32<T>(acc[i] / L);
+  }
+}
+
 // One (sequence, head) a block; every warp of the block holds the splits' maxima and sums (a lane a split, up to
 // CHUNKS x 32 of them, read once), finds the overall maximum and each split's weight, and walks the splits that hold
 // anything, in their order, handing a split's weight and sum round by shuffle: a split that got no page (most of
 // them when a short sequence is dealt to many) costs nothing, the exponentials are one per split, not one per split
 // and dim, and the splits' weighted values are requested eight at a time, before the maximum is known (which
 // splits hold anything shows in the first read): two round trips to memory in all.
-template <typename T, int CHUNKS>
+template <typename T, int CHUNKS, int DPT>   // DPT: dims a thread of the 64 holds (head size / 64, rounded up)
 __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                            T* __restrict__ out, int ldo, int nh, int hd, int n_splits) {
   const int seq = blockIdx.x, head = blockIdx.y, lane = threadIdx.x & 31;
@@ -565,8 +609,17 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, con
     const int s = c * 32 + lane;
     ml[c] = s < n_splits ? *reinterpret_cast<const float2*>(part_ml + (base + s) * 2) : make_float2(-CUDART_INF_F, 0.f);
   }
-  float L = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};   // dims threadIdx.x, + blockDim.x, ..: head sizes up to 4 x the block
+  float L = 0.f, acc[DPT];   // dims threadIdx.x, + blockDim.x, ..
+#pragma unroll
+  for (int i = 0; i < DPT; ++i) acc[i] = 0.f;
   float M = -CUDART_INF_F;
+  if (CHUNKS == 1 && n_splits <= 16) {
+    // few splits: every split's values are requested at once, beside the maxima and sums, whether the split holds
+    // anything or not (one round trip to memory in all); what an empty split's scratch holds is never used.  (With
+    // more splits than that most are empty when it matters, and walking the live ones is cheaper.)
+    fold_eager<T, CHUNKS, DPT, 16>(part_o, ml, base, n_splits, hd, out + (size_t)seq * ldo + head * hd);
+    return;
+  }
   bool have_m = false;
 #pragma unroll
   for (int c = 0; c < CHUNKS; ++c) {
@@ -574,7 +627,7 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, con
     float f = 0.f;
     while (live) {   // eight splits at a time: their sums are requested together and added in the splits' order
       int js[8];
-      float v[8][4];
+      float v[8][DPT];
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
         js[q] = live ? __ffs(live) - 1 : -1;
@@ -582,7 +635,7 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, con
         if (js[q] >= 0) {
           const float* po = part_o + (base + c * 32 + js[q]) * hd;
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
+          for (int i = 0; i < DPT; ++i) {
             const int d = threadIdx.x + i * blockDim.x;
             v[q][i] = d < hd ? po[d] : 0.f;
           }
@@ -602,13 +655,13 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, con
           const float fj = __shfl_sync(0xffffffffu, f, js[q]), lj = __shfl_sync(0xffffffffu, ml[c].y, js[q]);
           L = fmaf(lj, fj, L);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) acc[i] = fmaf(v[q][i], fj, acc[i]);
+          for (int i = 0; i < DPT; ++i) acc[i] = fmaf(v[q][i], fj, acc[i]);
         }
       }
     }
   }
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < DPT; ++i) {
     const int d = threadIdx.x + i * blockDim.x;
     if (d < hd) out[(size_t)seq * ldo + head * hd + d] = from_f32<T>(acc[i] / L);
   }
@@ -715,8 +768,13 @@ int launch_decode(const void* q, int ldq, void* out, int ldo, const void* kc, co
       return launch_pdl(2, kern, cgrid, dim3(64), 0, stream, (const float*)part_o, (const float*)part_ml, (T*)out, ldo, nh, hd, n_splits);
     };
     // (a lane holds one split of every 32: 1, 2, 8 or 64 of them in registers)
-    le = n_splits <= 32 ? fold(attn_decode_combine_kernel<T, 1>) : n_splits <= 64 ? fold(attn_decode_combine_kernel<T, 2>)
-         : n_splits <= 256 ? fold(attn_decode_combine_kernel<T, 8>) : fold(attn_decode_combine_kernel<T, 64>);
+    auto chunks = [&](auto dpt) {
+      constexpr int D = decltype(dpt)::value;
+      return n_splits <= 32 ? fold(attn_decode_combine_kernel<T, 1, D>) : n_splits <= 64 ? fold(attn_decode_combine_kernel<T, 2, D>)
+             : n_splits <= 256 ? fold(attn_decode_combine_kernel<T, 8, D>) : fold(attn_decode_combine_kernel<T, 64, D>);
+    };
+    le = hd <= 64 ? chunks(std::integral_constant<int, 1>{}) : hd <= 128 ? chunks(std::integral_constant<int, 2>{})
+         : chunks(std::integral_constant<int, 4>{});
   }
   if (le != cudaSuccess) {
     set_error("attn_decode: launch failed: %s", cudaGetErrorString(le));
