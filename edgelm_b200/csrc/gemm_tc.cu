@@ -559,7 +559,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 // 128 x 256 tiles and two accumulator stages (1.10 to 1.16 PFLOP/s at 2048 x 8192 x 2048 against 0.88 to 0.91
 // of the other), everything else to the one-tile-per-CTA kernel with 128 x 128 tiles, two CTAs per SM (the
 // persistent kernel with narrow tiles starves on shared-memory bandwidth: 0.68 to 0.78).  Forced for comparisons.
-static int g_tc_auto = 1, g_tc_persistent = 1, g_tc_wide = 1, g_tc_narrow = 1, g_tc_deep = 1;
+static int g_tc_auto = 1, g_tc_persistent = 1, g_tc_wide = 1, g_tc_narrow = 1, g_tc_deep = 1, g_tc_tiny = 1;
 
 // Scratch for split-K launches (set by the caller once; nothing is allocated here): without it no product is split.
 static float* g_splitk_ws = nullptr;
@@ -687,6 +687,12 @@ extern "C" int edgelm_gemm_tc_splitk(float* scratch, size_t bytes, int on) {
 }
 
 // bit 0: 64-column tiles where they apply; bit 1: the deep ring for grids of at most one block an SM (comparisons)
+// 1 (default): products whose rows are one tile and whose output is narrow run on tiles of 32 columns; 0: never.
+extern "C" int edgelm_gemm_tc_tiny(int on) {
+  g_tc_tiny = on & 1;
+  return 0;
+}
+
 extern "C" int edgelm_gemm_tc_narrow(int on) {
   g_tc_narrow = on & 1;
   g_tc_deep = (on >> 1) & 1;
@@ -725,7 +731,13 @@ static int gemm_tc_run(const void* a, int lda, const void* w, const void* w2, vo
   const long long tiles128 = (long long)((M + TC_BM - 1) / TC_BM) * ((N + 127) / 128);
   const bool narrow = !wide && epilogue != TC_EPI_SWIGLU && g_tc_narrow && tiles128 < 148 && M > TC_BM &&
                       (epilogue != TC_EPI_ROPE || rope.hd == 64);   // (a tile holds whole heads)
-  const int bn = epilogue == TC_EPI_SWIGLU ? (wide ? 128 : 64) : (wide ? 256 : (narrow ? 64 : 128));
+  // tiles of 32 columns when all rows are one tile (decode steps of 17 to 128 sequences) and the weights are small
+  // (under 4 Mi elements): they then stream through four times as many SMs, and an epilogue thread has one piece of
+  // 32 columns, whose residual it fetched ahead, instead of four one after the other (64 rows: N 576, K 576 7.3 ->
+  // 4.5 us; N 576, K 1536 8.6 -> 6.5; N 960, K 2560 8.1 -> 6.9).  Every block reads all rows of `a`, so with large
+  // weights the narrow tiles lose (N 2048, K 2048 7.5 -> 8.5 us; K 8192 14.5 -> 17.8).
+  const bool tiny = !wide && M <= TC_BM && (long long)N * K < (4LL << 20) && epilogue != TC_EPI_ROPE && g_tc_tiny;
+  const int bn = tiny ? 32 : epilogue == TC_EPI_SWIGLU ? (wide ? 128 : 64) : (wide ? 256 : (narrow ? 64 : 128));
   CUtensorMap ma, mb, mb2;
   if (tensor_map(a, M, K, lda, TC_BM, &ma)) return -1;
   if (tensor_map(w, N, K, K, bn, &mb)) return -1;
@@ -748,7 +760,15 @@ static int gemm_tc_run(const void* a, int lda, const void* w, const void* w2, vo
       rc = launch_tc<256, TC_EPI_ROPE, __nv_bfloat16>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent, rope);
     else
       EL_REFUSE(false, "gemm_tc: unsupported epilogue %d with output dtype %d", epilogue, out_dtype);
-  } else if (narrow && epilogue == TC_EPI_ROPE && out_dtype == DT_BF16)
+  } else if (tiny && epilogue == TC_EPI_STORE && out_dtype == DT_BF16)
+    rc = launch_tc<32, TC_EPI_STORE, __nv_bfloat16>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent, rope);
+  else if (tiny && epilogue == TC_EPI_STORE && out_dtype == DT_F32)
+    rc = launch_tc<32, TC_EPI_STORE, float>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent, rope);
+  else if (tiny && epilogue == TC_EPI_RESIDUAL)
+    rc = launch_tc<32, TC_EPI_RESIDUAL, float>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent, rope);
+  else if (tiny && epilogue == TC_EPI_SWIGLU && out_dtype == DT_BF16)
+    rc = launch_tc<32, TC_EPI_SWIGLU, __nv_bfloat16>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent, rope);
+  else if (narrow && epilogue == TC_EPI_ROPE && out_dtype == DT_BF16)
     rc = launch_tc<64, TC_EPI_ROPE, __nv_bfloat16>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent, rope);
   else if (epilogue == TC_EPI_ROPE && out_dtype == DT_BF16)
     rc = launch_tc<128, TC_EPI_ROPE, __nv_bfloat16>(ma, mb, mb2, out, ldo, residual, M, N, K, vec_ok, err, stream, persistent, rope);

@@ -570,6 +570,8 @@ def test_gemm_tc_dispatch_names_its_kernel():
     for (M, N, K), want in (((2048, 576, 576), dict(tile_columns=64, persistent=False, k_splits=1)),
                             ((2048, 2048, 256), dict(tile_columns=128, persistent=False, k_splits=1)),
                             ((256, 960, 576), dict(tile_columns=64, persistent=False)),
+                            ((64, 576, 576), dict(tile_columns=32, persistent=False, k_splits=1)),
+                            ((64, 2048, 2048), dict(tile_columns=128, persistent=False)),     # 4 Mi weights: not small enough for tiles of 32
                             ((64, 2048, 8192), dict(tile_columns=128, persistent=False))):
         a = rnd((M, K), torch.bfloat16, 158)
         w = rnd((N, K), torch.bfloat16, 159, 0.2)
@@ -580,6 +582,47 @@ def test_gemm_tc_dispatch_names_its_kernel():
         assert rel_err(out, _products(a, w)) < 1.6e-2
     k = o.gemm_tc_last_kernel()
     assert k["k_splits"] > 1, k   # 64 rows, N 2048, K 8192: sixteen tiles, split over K
+
+
+@pytest.mark.parametrize("M,N,K", [(17, 576, 576), (64, 960, 576), (128, 1536, 576), (64, 576, 1536), (33, 100, 200), (64, 4704, 96),
+                                     (100, 2040, 2048)])
+def test_gemm_tc_tiles_of_32_columns_when_all_rows_are_one_tile(M, N, K):
+    """Decode steps of 17 to 128 sequences: one tile of rows, and weights so small that wider tiles would come to a
+    handful of blocks: tiles of 32 columns, every epilogue, with and without K split over the grid, a ragged last
+    tile; against float64 and against the same product on wider tiles."""
+    o = ops()
+    a = rnd((M, K), torch.bfloat16, 160, 0.5)
+    w = rnd((N, K), torch.bfloat16, 161, 0.2)
+    w2 = rnd((N, K), torch.bfloat16, 162, 0.2)
+    res0 = rnd((M, N), torch.float32, 163)
+    err = torch.zeros(1, dtype=torch.int32, device=dev())
+    want = _products(a, w)
+    u = _products(a, w2)
+
+    def run():
+        out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev())
+        o.gemm_tc(a, w, out, err)
+        cols = o.gemm_tc_last_kernel()["tile_columns"]
+        out32 = torch.full((M, N), float("nan"), dtype=torch.float32, device=dev())
+        o.gemm_tc(a, w, out32, err)
+        res = res0.clone()
+        o.gemm_tc(a, w, res, err, epilogue=o.EPI_RESIDUAL, residual=res)
+        sw = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev())
+        o.gemm_tc(a, w, sw, err, epilogue=o.EPI_SWIGLU, w2=w2)
+        torch.cuda.synchronize()
+        return cols, out, out32, res, sw
+
+    cols, out, out32, res, sw = run()
+    assert cols == 32 and int(err.item()) == 0
+    assert rel_err(out, want) < 1.6e-2 and rel_err(out32, want) < 2e-5 and rel_err(res, res0.double().cpu() + want) < 2e-5
+    assert rel_err(sw, want / (1 + torch.exp(-want)) * u) < 1.6e-2
+    o.lib().edgelm_gemm_tc_tiny(0)
+    try:
+        wider = run()
+    finally:
+        o.lib().edgelm_gemm_tc_tiny(1)
+    assert wider[0] > 32
+    assert rel_err(out32, wider[2].double().cpu()) < 1e-5 and rel_err(res, wider[3].double().cpu()) < 1e-5
 
 
 def test_gemm_tc_strided_rows_and_refusals():
