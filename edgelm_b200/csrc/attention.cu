@@ -667,6 +667,29 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, con
   }
 }
 
+// The fold for any number of splits, one thread a dim, the splits one after the other.
+template <typename T>
+__global__ void attn_decode_combine_many_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                                T* __restrict__ out, int ldo, int nh, int hd, int n_splits) {
+  const int seq = blockIdx.x, head = blockIdx.y;
+  const size_t base = ((size_t)seq * nh + head) * n_splits;
+  pdl_launch_dependents();
+  pdl_wait();  // the partials are the previous kernel's
+  float M = -CUDART_INF_F;
+  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float L = 0.f, o = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float ms = part_ml[(base + s) * 2];
+      if (ms == -CUDART_INF_F) continue;  // a split that held no page
+      const float f = expf(ms - M);
+      L = fmaf(part_ml[(base + s) * 2 + 1], f, L);
+      o = fmaf(part_o[(base + s) * hd + d], f, o);
+    }
+    out[(size_t)seq * ldo + head * hd + d] = from_f32<T>(o / L);
+  }
+}
+
 template <typename T, int NC>
 int launch_prefill(const void* q, int ldq, void* out, int ldo, const void* kc, const void* vc, const int32_t* page_table,
                    int table_stride, const int32_t* seq_slot, const int32_t* tile_seq, const int32_t* tile_tok0,
@@ -767,13 +790,14 @@ int launch_decode(const void* q, int ldq, void* out, int ldo, const void* kc, co
     auto fold = [&](auto kern) {
       return launch_pdl(2, kern, cgrid, dim3(64), 0, stream, (const float*)part_o, (const float*)part_ml, (T*)out, ldo, nh, hd, n_splits);
     };
-    // (a lane holds one split of every 32: 1, 2, 8 or 64 of them in registers)
+    // (a lane holds one split of every 32: 1 or 2 of them in registers)
     auto chunks = [&](auto dpt) {
       constexpr int D = decltype(dpt)::value;
-      return n_splits <= 32 ? fold(attn_decode_combine_kernel<T, 1, D>) : n_splits <= 64 ? fold(attn_decode_combine_kernel<T, 2, D>)
-             : n_splits <= 256 ? fold(attn_decode_combine_kernel<T, 8, D>) : fold(attn_decode_combine_kernel<T, 64, D>);
+      return n_splits <= 32 ? fold(attn_decode_combine_kernel<T, 1, D>) : fold(attn_decode_combine_kernel<T, 2, D>);
     };
-    le = hd <= 64 ? chunks(std::integral_constant<int, 1>{}) : hd <= 128 ? chunks(std::integral_constant<int, 2>{})
+    // (more than 64 splits: no step of the engine asks for them; a plain kernel folds those)
+    le = n_splits > 64 ? fold(attn_decode_combine_many_kernel<T>)
+         : hd <= 64 ? chunks(std::integral_constant<int, 1>{}) : hd <= 128 ? chunks(std::integral_constant<int, 2>{})
          : chunks(std::integral_constant<int, 4>{});
   }
   if (le != cudaSuccess) {
