@@ -154,6 +154,7 @@ class SequenceCache:
         self.n_slots = min(n_pages, int(max_seqs)) if max_seqs else n_pages
         self.max_pages_per_seq = min(n_pages, pages_for(max_positions))
         self.slots = FreeList(self.n_slots, "slot")
+        self._quiet = None   # [slots, their indices, steps]: so many further one-token steps of exactly these sequences need no look at the pages
         self.length = np.zeros(self.n_slots, dtype=np.int64)
         self.dtype, self.device = dtype, device
         self.groups, self.entries = [], []
@@ -186,6 +187,7 @@ class SequenceCache:
     # ------------------------------------------------------------------ sequences
     def open(self):
         """A slot for a new sequence of length 0."""
+        self._quiet = None
         slot = self.slots.take()
         self.length[slot] = 0
         for g in self.state_groups:
@@ -201,6 +203,7 @@ class SequenceCache:
         first piece only (at most `piece_tokens` tokens): the engine asks again before each later piece, after
         `advance` gave back what the earlier ones no longer need."""
         self._held(slot)
+        self._quiet = None
         old_len = int(self.length[slot])
         new_len = old_len + int(n_new)
         if new_len > self.max_positions:
@@ -211,6 +214,7 @@ class SequenceCache:
     def advance(self, slot, n_new):
         """The step that wrote `n_new` tokens is issued: they count from now on."""
         self._held(slot)
+        self._quiet = None
         self.length[slot] += int(n_new)
         for g in self.kv_groups:
             g.trim(slot, int(self.length[slot]))
@@ -218,6 +222,11 @@ class SequenceCache:
     def reserve_next(self, slots):
         """`reserve(slot, 1)` for every slot of a step of one token each (distinct slots), with the same outcome; the
         pages are looked at for the sequences that cross into a new page only, which is one step in 64."""
+        q = self._quiet
+        if q is not None and q[2] > 0 and q[0] == tuple(slots):
+            q[2] -= 1     # (nothing else touched the cache since these sequences' last step, and no page edge is near)
+            return
+        self._quiet = None
         held = self.slots._held
         for s in slots:
             if s not in held:
@@ -232,10 +241,17 @@ class SequenceCache:
             if short.any():
                 for s in idx[short]:
                     g.ensure(int(s), int(self.length[s]), int(self.length[s]) + 1)
+        if self.kv_groups and all(g.window is None for g in self.kv_groups):
+            # how many further steps of these sequences need nothing: none reaches a page edge or the last position
+            room = self.max_positions - new_len
+            for g in self.kv_groups:
+                room = np.minimum(room, (g.low[idx] + g.n_held[idx]) * PAGE - new_len)
+            self._quiet = [tuple(slots), idx, int(room.min())]
 
     def advance_next(self, slots):
         """`advance(slot, 1)` for every slot that `reserve_next` was called with."""
-        idx = np.asarray(slots, dtype=np.int64)
+        q = self._quiet
+        idx = q[1] if q is not None and q[0] == tuple(slots) else np.asarray(slots, dtype=np.int64)
         self.length[idx] += 1
         for g in self.kv_groups:
             if g.window is not None:
@@ -245,6 +261,7 @@ class SequenceCache:
     def close(self, slot):
         """The sequence is over: its pages and its slot go back."""
         self._held(slot)
+        self._quiet = None
         for g in self.kv_groups:
             g.release(slot)
         self.length[slot] = 0

@@ -217,7 +217,9 @@ class BatchBuffers:
                 h[a:a + B * s] = g.table[d["slot_index"]].reshape(-1)
                 d["version"][g.id] = g.version
         o = d["words"]
-        self.dev[:o].copy_(self.host[:o], non_blocking=True)
+        if "copy" not in d:
+            d["copy"] = (self.dev[:o], self.host[:o])   # (the two views, made once for the steps of this layout)
+        d["copy"][0].copy_(d["copy"][1], non_blocking=True)
         self._copied.record()
         self.last_bytes = o * 4
         d["pos"] = list(seq_pos0)
