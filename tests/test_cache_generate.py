@@ -367,3 +367,47 @@ def test_a_step_of_one_token_each_reserves_like_one_sequence_at_a_time():
         raise AssertionError("the position table's end was never reached")
     with pytest.raises(CacheError, match="not held"):
         a.reserve_next([slots[0], 4 if 4 not in slots else 99])
+
+
+def test_the_quiet_steps_of_a_decode_batch_end_when_anything_else_touches_the_cache():
+    """Between page edges `reserve_next` answers from a count of steps that need nothing; whatever else touches the
+    cache (a sequence opened, closed, or stepped on its own) ends that count, so the next call looks again."""
+    rng = random.Random(5)
+    needs = [KVNeed(2, 16)]
+    a = SequenceCache(needs, 40 * 64, 1000, device=None, max_seqs=6)
+    b = SequenceCache(needs, 40 * 64, 1000, device=None, max_seqs=6)
+    live = []
+    for c in (a, b):
+        live = [c.open() for _ in range(3)]
+        for s, n in zip(live, (5, 70, 129)):
+            c.reserve(s, n)
+            c.advance(s, n)
+    extra = None
+    for step in range(400):
+        r = rng.random()
+        if r < 0.05 and extra is None:                       # another sequence comes and goes beside the batch
+            extra = a.open()
+            assert b.open() == extra
+            for c in (a, b):
+                c.reserve(extra, 64)
+                c.advance(extra, 64)
+        elif r < 0.1 and extra is not None:
+            a.close(extra)
+            b.close(extra)
+            extra = None
+        elif r < 0.13 and len(live) > 1:                     # a sequence of the batch ends
+            s = live.pop(rng.randrange(len(live)))
+            a.close(s)
+            b.close(s)
+            with pytest.raises(CacheError, match="not held"):
+                a.reserve_next(live + [s])
+        a.reserve_next(live)
+        a.advance_next(live)
+        for s in live:
+            b.reserve(s, 1)
+        for s in live:
+            b.advance(s, 1)
+        a.check()
+        assert (a.length == b.length).all()
+        ga, gb = a.kv_groups[0], b.kv_groups[0]
+        assert (ga.n_held == gb.n_held).all() and ga.pool.available() == gb.pool.available() and ((ga.table >= 0) == (gb.table >= 0)).all()
