@@ -277,6 +277,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  // The weights' tiles of the first ring of stages are requested ahead of the wait for the kernel before this one
+  // (nothing on the stream writes weights): when that kernel is done, only the rows of `a` are still to come.
+  const int n_ahead = n_k < STAGES ? n_k : STAGES;
+  if (warp == 0 && elect_one()) {
+    for (int i = 0; i < n_ahead; ++i) {
+      const uint32_t bar = smem_u32(&full_bar[i]);
+      const uint32_t sa = smem_u32(smem + i * STAGE_BYTES);
+      const int x = (k_first + i) * TC_BK;
+      mbar_expect_tx(bar, STAGE_BYTES);
+      tma_load_2d(sa + A_BYTES, &map_b, bar, x, n0);
+      if (NB == 2) tma_load_2d(sa + A_BYTES + B_BYTES, &map_b2, bar, x, n0);
+    }
+  }
+  __syncwarp();
   pdl_launch_dependents();
   pdl_wait();   // (launched as a programmatic dependent: up to here nothing of the kernel before this one was read)
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -295,10 +309,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
       const int x = (k_first + i) * TC_BK;
       if (leader) {
-        mbar_expect_tx(bar, STAGE_BYTES);
-        tma_load_2d(sa, &map_a, bar, x, m0);
-        tma_load_2d(sa + A_BYTES, &map_b, bar, x, n0);
-        if (NB == 2) tma_load_2d(sa + A_BYTES + B_BYTES, &map_b2, bar, x, n0);
+        if (i < n_ahead) {   // (the stage's barrier is armed and its weights are on their way)
+          tma_load_2d(sa, &map_a, bar, x, m0);
+        } else {
+          mbar_expect_tx(bar, STAGE_BYTES);
+          tma_load_2d(sa, &map_a, bar, x, m0);
+          tma_load_2d(sa + A_BYTES, &map_b, bar, x, n0);
+          if (NB == 2) tma_load_2d(sa + A_BYTES + B_BYTES, &map_b2, bar, x, n0);
+        }
       }
       __syncwarp();
     }
