@@ -78,7 +78,7 @@ def main(argv=None):
     if decode:
         pos = torch.full((B,), ctx_len - 1, dtype=torch.int32, device=d)
         tokpos, tokseq = pos.clone(), seq.clone()
-        splits = args.splits or min(64, max(1, (2 * 148 + B * nkv - 1) // (B * nkv)))
+        splits = args.splits or min(16, max(1, (2 * 148 + B * nkv - 1) // (B * nkv)))
         po = torch.empty(B * nh * splits * hd, device=d)
         pm = torch.empty(B * nh * splits * 2, device=d)
         few = B <= 16

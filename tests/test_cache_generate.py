@@ -216,14 +216,14 @@ def test_sampling_params_and_stream():
 
 def test_decode_splits_rule():
     """Blocks per (sequence, kv head) of the decode attention: about two blocks an SM for few pairs; whole waves of
-    resident blocks once there are as many pairs as SMs; never less than one, never more than 64."""
+    resident blocks once there are as many pairs as SMs; never less than one, never more than 16."""
     from edgelm_b200.engine.batch import StepContext
     ctx = StepContext(None, None, "cpu", 148)
 
     def splits(n_seqs, n_kv, resident=None):
         ctx.n_seqs = n_seqs
         return ctx.decode_splits(n_kv, resident)
-    assert splits(1, 1) == 64 and splits(8, 3) == 13 and splits(8, 3, 3) == 13      # few pairs: the caller's knowledge changes nothing
+    assert splits(1, 1) == 16 and splits(2, 3) == 16 and splits(8, 3) == 13 and splits(8, 3, 3) == 13      # few pairs: the caller's knowledge changes nothing
     assert splits(4, 32, 3) == 3                                                    # 128 pairs, under the SMs: ceil(296 / 128)
     assert splits(8, 32) == 2 and splits(8, 32, 3) == 3                             # 256 pairs: two waves of 444 blocks hold 3 splits
     assert splits(16, 32) == 1 and splits(16, 32, 3) == 2                           # 512 pairs: three waves hold 2
