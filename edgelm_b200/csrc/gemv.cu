@@ -84,6 +84,13 @@ gemv_kernel(const T* __restrict__ act, int lda, const float* __restrict__ x, con
 
   pdl_launch_dependents();
   pdl_wait();   // (launched as a programmatic dependent: from here on, what the kernel before this one wrote)
+  // the residual values that the epilogue adds to, one a lane (column c, row r in lane c * 8 + r), requested now: a
+  // trip to memory less at the end of the warp's life (out may be the residual itself: nobody else writes these)
+  float res_mine = 0.f;
+  if (EPI == GV_RESIDUAL) {
+    const int c = lane / GV_ROWS, r = lane - c * GV_ROWS;
+    if (c < CW && r < rows && col0 + c < N) res_mine = residual[(size_t)(m0 + r) * ldo + col0 + c];
+  }
   // A normalised row of up to 1,024 values in one chunk: a warp takes a row, keeps it in registers between the sum of
   // squares and the scaling and writes it out in the compute dtype: one pass over x, the norm's weights beside it.
   const bool one_pass = NORM && K <= 1024 && K <= kc && K % 4 == 0;
@@ -215,10 +222,11 @@ gemv_kernel(const T* __restrict__ act, int lda, const float* __restrict__ x, con
       if (r < rows) {  // uniform over the warp
         const float s = warp_sum(acc[0][c][r]);
         const float s2 = NW == 2 ? warp_sum(acc[NW - 1][c][r]) : 0.f;
+        const float res = EPI == GV_RESIDUAL ? __shfl_sync(0xffffffffu, res_mine, c * GV_ROWS + r) : 0.f;
         if (lane == 0 && n < N) {
           const size_t idx = (size_t)(m0 + r) * ldo + n;
           if (EPI == GV_STORE) out[idx] = from_f32<TOut>(s);
-          if (EPI == GV_RESIDUAL) out[idx] = from_f32<TOut>(residual[idx] + s);
+          if (EPI == GV_RESIDUAL) out[idx] = from_f32<TOut>(res + s);
           if (EPI == GV_SWIGLU) out[idx] = from_f32<TOut>(gv_silu(s) * s2);
         }
       }
